@@ -1,0 +1,99 @@
+"""One engine step: schedule, execute, read samples, update (reference: src/control/core.py:25-156)."""
+
+from __future__ import annotations
+
+import gc
+import time
+
+from ..config import EngineConfig
+from ..data import EngineCoreOutput, KVManager, Sequence
+from ..utils.metrics import EngineMetrics
+from .scheduler import Scheduler
+
+__all__ = ["EngineCore"]
+
+
+class EngineCore:
+    # Consecutive empty schedules tolerated while requests remain; beyond this the KV pool
+    # is assumed exhausted and the step raises instead of spinning forever.
+    _MAX_IDLE_STEPS = 1024
+
+    def __init__(self, config: EngineConfig, *, eos_token_id: int, device=None, dtype=None,
+                 executor=None) -> None:
+        self.config = config
+        self.eos_token_id = eos_token_id
+        if executor is None:
+            from .executor import create_executor
+
+            executor = create_executor(config, device, dtype)
+        self.executor = executor
+        self.metrics = EngineMetrics()
+        self._idle_steps = 0
+        self._init_kv()
+
+    def _build_scheduler(self) -> Scheduler:
+        return Scheduler(
+            self.kv,
+            max_num_seqs=self.config.max_num_seqs,
+            max_num_batched_tokens=self.config.max_num_batched_tokens,
+            eos_token_id=self.eos_token_id,
+            mix_prefill_decode=self.config.mix_prefill_decode,
+        )
+
+    def _init_kv(self) -> None:
+        self.kv: KVManager = self.executor.init_kv()
+        self.scheduler = self._build_scheduler()
+        self.last_num_cached_tokens = 0
+
+    def reset_kv(self, prefix_backend: str | None = None) -> None:
+        self.kv = self.executor.reset_kv(prefix_backend)
+        self.scheduler = self._build_scheduler()
+        self.last_num_cached_tokens = 0
+
+    def add_request(self, seq: Sequence) -> None:
+        if not seq.t_arrival:
+            seq.t_arrival = time.perf_counter()
+        self.metrics.requests_added += 1
+        self.scheduler.add(seq)
+
+    def has_unfinished(self) -> bool:
+        return not self.scheduler.is_finished()
+
+    def step(self) -> tuple[list[EngineCoreOutput], int]:
+        """Returns (per-sequence increments, tokens processed this step)."""
+        t0 = time.perf_counter()
+        sched = self.scheduler.schedule()
+        if sched.is_empty():
+            if sched.released:
+                # nothing to run, but workers should still learn about dropped rows
+                self.scheduler._released[:0] = sched.released
+            if not self.scheduler.is_finished():
+                self._idle_steps += 1
+                if self._idle_steps >= self._MAX_IDLE_STEPS:
+                    raise RuntimeError(
+                        "scheduler returned empty for too long while requests remain "
+                        f"(idle_steps={self._idle_steps}). Likely KV pool exhaustion "
+                        f"(free_blocks={self.kv.num_free})."
+                    )
+            return [], 0
+        self._idle_steps = 0
+        t1 = time.perf_counter()
+        n_p, n_d = self.executor.run(sched)
+        self.last_num_cached_tokens = self.kv.last_num_cached_tokens
+        prefill_tokens = sum(s.num_scheduled_tokens for s in sched.prefills)
+        metric = prefill_tokens + len(sched.decodes)
+        p_ids, d_ids = self.executor.read_samples(n_p, n_d)
+        t2 = time.perf_counter()
+        outputs = self.scheduler.update(sched, p_ids, d_ids)
+        t3 = time.perf_counter()
+        self.metrics.on_step(
+            sched, outputs, prefill_tokens, schedule_s=t1 - t0, execute_s=t2 - t1, update_s=t3 - t2,
+            kv_usage=self.kv.usage(), preemptions=self.scheduler.num_preemptions, kv=self.kv, now=t3,
+        )
+        return outputs, metric
+
+    def destroy(self) -> None:
+        self.executor.destroy()
+        self.kv = None
+        self.scheduler = None
+        gc.collect()

@@ -1,0 +1,172 @@
+"""Continuous-batching scheduler (reference: src/control/scheduler.py:8-218).
+
+Parallelism-agnostic: it owns the waiting/running queues and the KV page budget and emits a
+``ScheduledBatch``. Tensor/pipeline fan-out happens in the executor, data-parallel fan-out
+in the client.
+
+Policy kept from the reference:
+* mixed mode (default): running sequences decode first, then waiting prompts fill what is
+  left of the token budget; prefill-first mode runs prompts alone when any can start;
+* a prompt that does not fit the remaining budget is chunked, at most one partial chunk
+  per step;
+* when a decode cannot get a page, sequences are preempted from the tail of ``running``
+  and recomputed later;
+* a sequence ends on EOS (unless ``ignore_eos``) or at ``max_tokens``; ``max_tokens <= 0``
+  ends right after prefill.
+"""
+
+from __future__ import annotations
+
+from collections import deque
+
+from ..data import EngineCoreOutput, KVManager, ScheduledBatch, Sequence, SequenceStatus
+
+__all__ = ["Scheduler"]
+
+
+class Scheduler:
+    def __init__(self, kv: KVManager, *, max_num_seqs: int, max_num_batched_tokens: int,
+                 eos_token_id: int, mix_prefill_decode: bool = True) -> None:
+        self.kv = kv
+        self.max_num_seqs = max_num_seqs
+        self.max_num_batched_tokens = max_num_batched_tokens
+        self.eos = eos_token_id
+        self.mix_prefill_decode = mix_prefill_decode
+        self.waiting: deque[Sequence] = deque()
+        self.running: deque[Sequence] = deque()
+        self._released: list[int] = []   # seq ids whose worker-side rows can be dropped
+        self._step = 0
+        self.num_preemptions = 0
+
+    def is_finished(self) -> bool:
+        return not self.waiting and not self.running
+
+    def add(self, seq: Sequence) -> None:
+        seq.status = SequenceStatus.WAITING
+        self.waiting.append(seq)
+
+    # ------------------------------------------------------------------ scheduling
+    def schedule(self) -> ScheduledBatch:
+        prefills: list[Sequence] = []
+        decodes: list[Sequence] = []
+        if self.mix_prefill_decode:
+            used = self._take_decodes(prefills, decodes, 0)
+            if decodes:
+                self._take_prefills(prefills, decodes, used, allow_trailing_partial=True)
+            else:
+                self._prefill_first(prefills, decodes)
+        else:
+            self._prefill_first(prefills, decodes)
+        self._step += 1
+        released, self._released = self._released, []
+        return ScheduledBatch(prefills=prefills, decodes=decodes, released=released, step_id=self._step)
+
+    def _prefill_first(self, prefills: list[Sequence], decodes: list[Sequence]) -> None:
+        self._take_prefills(prefills, decodes, 0, allow_trailing_partial=False)
+        if not prefills:
+            self._take_decodes(prefills, decodes, 0)
+
+    def _has_room(self, prefills, decodes) -> bool:
+        return len(prefills) + len(decodes) < self.max_num_seqs
+
+    def _take_decodes(self, prefills, decodes, used: int) -> int:
+        run = self.running
+        while run and self._has_room(prefills, decodes) and used < self.max_num_batched_tokens:
+            seq = run.popleft()
+            while not self.kv.can_append(seq) and run:
+                self.preempt(run.pop())
+            if not self.kv.can_append(seq):
+                self.preempt(seq)
+                break
+            seq.num_scheduled_tokens = 1
+            self.kv.may_append(seq)
+            decodes.append(seq)
+            used += 1
+        if decodes:   # scheduled sequences keep their place at the head of the queue
+            run.extendleft(reversed(decodes))
+        return used
+
+    def _take_prefills(self, prefills, decodes, used: int, *, allow_trailing_partial: bool) -> int:
+        for seq in list(self.waiting):
+            if not self._has_room(prefills, decodes):
+                break
+            budget = self.max_num_batched_tokens - used
+            if budget <= 0:
+                break
+            if not seq.block_table:
+                if not self.kv.can_allocate(seq):
+                    break
+                self.kv.allocate(seq)
+            need = seq.num_tokens - seq.num_cached_tokens
+            if need <= 0:   # nothing to compute (cannot happen with the last-page rule, kept as a guard)
+                self._promote(seq)
+                continue
+            if budget < need and prefills and not allow_trailing_partial:
+                break
+            chunk = min(need, budget)
+            seq.num_scheduled_tokens = chunk
+            prefills.append(seq)
+            used += chunk
+            if chunk == need:
+                seq.need_sample = True
+                self._promote(seq)
+            else:
+                seq.need_sample = False
+                break   # one partial chunk per step
+        return used
+
+    def _promote(self, seq: Sequence) -> None:
+        seq.status = SequenceStatus.RUNNING
+        self.waiting.remove(seq)
+        self.running.append(seq)
+
+    def preempt(self, seq: Sequence) -> None:
+        """Give the sequence's pages back and recompute it later from the front of the queue."""
+        if seq.status is SequenceStatus.FINISHED:
+            return
+        seq.status = SequenceStatus.WAITING
+        self.kv.deallocate(seq, publish=False)
+        self._released.append(seq.seq_id)
+        self.waiting.appendleft(seq)
+        self.num_preemptions += 1
+
+    # ------------------------------------------------------------------ post-step
+    def update(self, sched: ScheduledBatch, p_ids: list[int], d_ids: list[int]) -> list[EngineCoreOutput]:
+        out: list[EngineCoreOutput] = []
+        done: set[int] = set()
+        if sched.decodes:
+            self._apply(sched.decodes, d_ids, False, out, done)
+        if sched.prefills:
+            self._apply(sched.prefills, p_ids, True, out, done)
+        if done:
+            self.running = deque(s for s in self.running if s.seq_id not in done)
+            self._released.extend(done)
+        return out
+
+    def _finish(self, seq: Sequence, done: set[int]) -> None:
+        seq.status = SequenceStatus.FINISHED
+        self.kv.deallocate(seq, publish=True)
+        done.add(seq.seq_id)
+
+    def _apply(self, seqs, token_ids, is_prefill: bool, out, done: set[int]) -> None:
+        for seq, tok in zip(seqs, token_ids):
+            seq.num_cached_tokens += seq.num_scheduled_tokens
+            self.kv.sync_prefix(seq)
+            seq.num_scheduled_tokens = 0
+            if is_prefill and seq.num_cached_tokens < seq.num_prompt_tokens:
+                out.append(EngineCoreOutput(seq_id=seq.seq_id))      # mid-prompt chunk
+                continue
+            if is_prefill and seq.num_cached_tokens < seq.num_tokens:
+                # recomputation of a preempted sequence, chunk not at the end yet
+                out.append(EngineCoreOutput(seq_id=seq.seq_id))
+                continue
+            if seq.max_tokens <= 0:
+                self._finish(seq, done)
+                out.append(EngineCoreOutput(seq_id=seq.seq_id, is_finished=True))
+                continue
+            tok = int(tok)
+            seq.append_token(tok)
+            if ((not seq.ignore_eos) and tok == self.eos) or seq.num_completion_tokens >= seq.max_tokens:
+                self._finish(seq, done)
+            out.append(EngineCoreOutput(seq_id=seq.seq_id, new_token_ids=[tok],
+                                        is_finished=seq.seq_id in done))

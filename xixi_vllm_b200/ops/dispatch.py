@@ -1,0 +1,76 @@
+"""Entry points used by model code. A CUDA tensor goes to the sm_100a kernels, a CPU tensor
+to the PyTorch oracle. There is exactly one GPU implementation per op; if the CUDA library
+is missing on a machine with a GPU the call raises instead of falling back.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import cpu_ref
+
+__all__ = [
+    "rmsnorm", "add_rmsnorm", "linear", "silu_mul", "embedding", "qk_norm_rope_cache",
+    "paged_attention", "sample", "argmax", "build_cos_sin_cache", "gather_rows",
+]
+
+build_cos_sin_cache = cpu_ref.build_cos_sin_cache
+
+
+def _cuda():
+    from . import cuda
+
+    return cuda
+
+
+def rmsnorm(x, w, eps):
+    return _cuda().rmsnorm(x, w, eps) if x.is_cuda else cpu_ref.rmsnorm(x, w, eps)
+
+
+def add_rmsnorm(x, residual, w, eps):
+    return _cuda().add_rmsnorm(x, residual, w, eps) if x.is_cuda else cpu_ref.add_rmsnorm(x, residual, w, eps)
+
+
+def linear(x, w, bias=None):
+    return _cuda().linear(x, w, bias) if x.is_cuda else cpu_ref.linear(x, w, bias)
+
+
+def silu_mul(x):
+    return _cuda().silu_mul(x) if x.is_cuda else cpu_ref.silu_mul(x)
+
+
+def embedding(ids, w, vocab_start=0):
+    return _cuda().embedding(ids, w, vocab_start) if w.is_cuda else cpu_ref.embedding(ids, w, vocab_start)
+
+
+def qk_norm_rope_cache(qkv, q_w, k_w, eps, cos_sin, positions, slots, k_cache, v_cache,
+                       num_q_heads, num_kv_heads, head_dim):
+    f = _cuda().qk_norm_rope_cache if qkv.is_cuda else cpu_ref.qk_norm_rope_cache
+    return f(qkv, q_w, k_w, eps, cos_sin, positions, slots, k_cache, v_cache,
+             num_q_heads, num_kv_heads, head_dim)
+
+
+def paged_attention(q, k_cache, v_cache, attn, scale, num_q_heads, num_kv_heads, head_dim):
+    """``attn`` is a ``runtime.staging.AttnBatch`` (cu_q, kv_lens, block_tables, decode split)."""
+    if q.is_cuda:
+        return _cuda().paged_attention(q, k_cache, v_cache, attn, scale, num_q_heads, num_kv_heads, head_dim)
+    return cpu_ref.paged_attention(q, k_cache, v_cache, attn.cu_q, attn.kv_lens, attn.block_tables,
+                                   scale, num_q_heads, num_kv_heads, head_dim)
+
+
+def argmax(logits):
+    return _cuda().argmax(logits) if logits.is_cuda else cpu_ref.argmax(logits)
+
+
+def sample(logits, temperature, top_k, top_p, min_p, *, rng=None, generator=None):
+    """``rng``: device int32 ``[seed, step]`` (GPU path); ``generator``: torch generator (CPU path)."""
+    if logits.is_cuda:
+        return _cuda().sample(logits, temperature, top_k, top_p, min_p, rng)
+    return cpu_ref.sample(logits, temperature, top_k, top_p, min_p, generator)
+
+
+def gather_rows(x, rows):
+    """``x[rows]`` for int32 row indices."""
+    if x.is_cuda:
+        return _cuda().gather_rows(x, rows)
+    return x.index_select(0, rows.long())

@@ -1,0 +1,152 @@
+"""Runs one scheduled step on this rank (reference: src/compute/model_runner.py:22-361).
+
+A step is ONE forward over the packed batch (decode rows then prefill chunks). Pure-decode
+steps replay a CUDA graph when graphs are enabled. Pipeline hand-off tensors move with NCCL
+p2p outside the graphs. Sampled ids leave the device on a side stream into pinned memory;
+``read_samples`` is the only point that waits.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..ops import dispatch as ops
+from ..parallel.collectives import recv_tensors, send_tensors
+from ..parallel.groups import get_pp_group, get_tp_group
+from ..parallel.pp import IntermediateTensors
+from .graphs import CUDAGraphRunner, make_bs_list
+from .kv_pool import KVPool
+from .sampler import Sampler
+from .staging import BatchStager
+
+__all__ = ["ModelRunner"]
+
+
+class ModelRunner:
+    def __init__(self, model, kv: KVPool, sampler: Sampler, *, config, device) -> None:
+        self.model, self.kv, self.sampler, self.config = model, kv, sampler, config
+        self.device = torch.device(device)
+        self.is_cuda = self.device.type == "cuda"
+        self.block_size = kv.block_size
+        self.hidden_size = config.hf_config.hidden_size
+        pp, tp = get_pp_group(), get_tp_group()
+        self._pp = pp
+        self.is_first_pp, self.is_last_pp = pp.is_first_rank, pp.is_last_rank
+        self.is_driver = self.is_last_pp and tp.group_rank == 0
+        self.max_bs = config.max_num_seqs
+        self.max_tokens = max(config.max_num_batched_tokens, self.max_bs)
+        self.max_blocks = -(-config.context_len // self.block_size)
+        self.stager = BatchStager(max_seqs=self.max_bs, max_tokens=self.max_tokens,
+                                  max_blocks=self.max_blocks, block_size=self.block_size, device=self.device)
+        self._pp_buf = None
+        if not self.is_first_pp:
+            shape = (self.max_tokens, self.hidden_size)
+            self._pp_buf = (torch.empty(shape, dtype=kv.dtype, device=self.device),
+                            torch.empty(shape, dtype=kv.dtype, device=self.device))
+        self._copy_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
+        self._sample_event = torch.cuda.Event() if self.is_cuda else None
+        self._host_samples = torch.zeros(self.max_bs, dtype=torch.int64, pin_memory=self.is_cuda)
+        self._dev_samples: torch.Tensor | None = None
+        self._n_samples = 0
+        self._last: tuple[int, int, list[bool]] = (0, 0, [])
+        self.graphs: CUDAGraphRunner | None = None
+        if self.is_cuda and not config.enforce_eager:
+            self._capture_graphs()
+
+    # --- forward --------------------------------------------------------------------------
+    def _forward(self, batch, intermediate=None):
+        out = self.model.forward(batch.input_ids, batch, self.kv, intermediate)
+        if not self.is_last_pp:
+            return out
+        hidden = ops.gather_rows(out, batch.sample_rows)
+        if batch.all_greedy:
+            return self.model.greedy_tokens(hidden)
+        logits = self.model.compute_logits(hidden)
+        return self.sampler(logits, batch.temperature, batch.top_k, batch.top_p, batch.min_p, rng=batch.rng)
+
+    def _recv(self, n_tokens: int) -> IntermediateTensors:
+        h, r = self._pp_buf[0][:n_tokens], self._pp_buf[1][:n_tokens]
+        recv_tensors([h, r], group=self._pp)
+        return IntermediateTensors(hidden_states=h, residual=r)
+
+    def _send(self, inter: IntermediateTensors) -> None:
+        for w in send_tensors([inter["hidden_states"], inter["residual"]], group=self._pp):
+            w.wait()
+
+    def run_forward(self, sched) -> tuple[int, int]:
+        """Launches the step (no host wait). Returns (#prefill sequences, #decode sequences)."""
+        n_p, n_d = len(sched.prefills), len(sched.decodes)
+        use_graph = (self.graphs is not None and n_p == 0 and 0 < n_d <= self.graphs.max_bs
+                     and self.is_first_pp and self.is_last_pp)
+        with torch.no_grad():
+            if use_graph:
+                bucket = self.graphs.pad_bs(n_d)
+                batch = self.stager.build(sched, pad_to=bucket, fixed_blocks=True)
+                greedy = batch.all_greedy
+                tokens = self.graphs.replay(bucket, greedy)
+            else:
+                batch = self.stager.build(sched)
+                inter = None if self.is_first_pp else self._recv(batch.num_tokens)
+                tokens = self._forward(batch, inter)
+                if not self.is_last_pp:
+                    self._send(tokens)
+                    tokens = None
+        self._last = (n_p, n_d, batch.prefill_sampled)
+        if tokens is not None:
+            self._stage_samples(tokens, batch.num_samples)
+        return n_p, n_d
+
+    def _stage_samples(self, tokens: torch.Tensor, n: int) -> None:
+        self._n_samples = n
+        if not self.is_cuda:
+            self._host_samples[:n].copy_(tokens[:n])
+            return
+        self._dev_samples = tokens
+        cur = torch.cuda.current_stream(self.device)
+        self._copy_stream.wait_stream(cur)
+        with torch.cuda.stream(self._copy_stream):
+            self._host_samples[:n].copy_(tokens[:n], non_blocking=True)
+            self._sample_event.record(self._copy_stream)
+
+    def read_samples(self, n_p: int, n_d: int) -> tuple[list[int], list[int]]:
+        """Blocks until this step's ids are on the host. Prefill entries that did not sample are -1."""
+        if self.is_cuda:
+            self._sample_event.synchronize()
+        flat = self._host_samples[: self._n_samples].tolist()
+        _, _, sampled = self._last
+        d_ids = flat[:n_d]
+        p_ids, k = [], n_d
+        for s in sampled:
+            if s:
+                p_ids.append(flat[k])
+                k += 1
+            else:
+                p_ids.append(-1)
+        return p_ids, d_ids
+
+    # --- CUDA graphs ---------------------------------------------------------------------------
+    def _capture_graphs(self) -> None:
+        from ..data.wire import SchedulerOutput, SeqSchedule
+
+        if not (self.is_first_pp and self.is_last_pp):
+            return   # with pipeline stages the p2p hand-off brackets the forward; run eagerly
+        runner = CUDAGraphRunner(make_bs_list(min(self.max_bs, 512)))
+
+        def make_inputs(bs: int, greedy: bool):
+            self.stager.reset()
+            entry = SeqSchedule(seq_id=-1, num_cached_tokens=0, token_ids=[0], bt_from=0, bt_tail=[0],
+                                temperature=0.0 if greedy else 1.0)
+            batch = self.stager.build(SchedulerOutput(decodes=[entry]), pad_to=bs, fixed_blocks=True)
+            batch.slots.fill_(-1)      # capture must not write real KV slots
+            batch.all_greedy = greedy
+            return batch
+
+        runner.capture((True, False), make_inputs, self._forward)
+        self.stager.reset()
+        self.graphs = runner
+
+    def destroy(self) -> None:
+        if self.graphs is not None:
+            self.graphs.destroy()
+        self.graphs = None
+        self._dev_samples = None

@@ -1,0 +1,78 @@
+"""Paged attention kernels (decode and prefill) against the PyTorch oracle."""
+import pytest
+import torch
+
+from xixi_vllm_b200.ops import cpu_ref
+from xixi_vllm_b200.runtime.staging import AttnBatch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+D = 128
+
+
+def _make_cache(num_blocks, hkv, bs, seed):
+    g = torch.Generator().manual_seed(seed)
+    k = torch.randn(num_blocks, hkv, bs, D, generator=g).bfloat16()
+    v = torch.randn(num_blocks, hkv, bs, D, generator=g).bfloat16()
+    return k, v
+
+
+def _run(q_lens, kv_lens, hq, hkv, bs=16, n_decode=0, seed=0):
+    B = len(kv_lens)
+    maxb = max(-(-l // bs) for l in kv_lens) + 1
+    num_blocks = B * maxb + 3
+    g = torch.Generator().manual_seed(seed + 100)
+    perm = torch.randperm(num_blocks, generator=g)
+    bt = torch.zeros(B, maxb, dtype=torch.int32)
+    for b in range(B):
+        bt[b] = perm[b * maxb:(b + 1) * maxb].to(torch.int32)
+    k, v = _make_cache(num_blocks, hkv, bs, seed)
+    T = sum(q_lens)
+    q = torch.randn(T, hq * D, generator=g).bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    kvl = torch.tensor(kv_lens, dtype=torch.int32)
+    scale = D ** -0.5
+    ref = cpu_ref.paged_attention(q.float(), k.float(), v.float(), cu, kvl, bt, scale, hq, hkv, D)
+    from xixi_vllm_b200.ops import cuda
+    attn = AttnBatch(cu_q=cu.to(DEV), kv_lens=kvl.to(DEV), block_tables=bt.to(DEV), num_seqs=B,
+                     num_decode=n_decode, max_q_len=max(q_lens), max_kv_len=max(kv_lens), num_tokens=T)
+    out = cuda.paged_attention(q.to(DEV), k.to(DEV), v.to(DEV), attn, scale, hq, hkv, D)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("hq,hkv", [(16, 8), (32, 8), (8, 1), (4, 1), (16, 1)])
+def test_decode_gqa_groups(hq, hkv):
+    _run([1] * 5, [1, 15, 16, 17, 300], hq, hkv, n_decode=5)
+
+
+def test_decode_page_boundaries_every_batch_size():
+    for bsz in (1, 2, 3, 9, 17):
+        lens = [((i * 37) % 95) + 1 for i in range(bsz)]
+        _run([1] * bsz, lens, 16, 8, n_decode=bsz, seed=bsz)
+
+
+def test_decode_long_context_uses_splits():
+    _run([1, 1], [4000, 2049], 32, 8, n_decode=2)
+
+
+def test_decode_empty_rows_give_zeros():
+    _run([1, 1, 1], [0, 33, 0], 16, 8, n_decode=3)
+
+
+def test_decode_block_size_32():
+    _run([1] * 3, [31, 32, 70], 16, 8, bs=32, n_decode=3)
+
+
+@pytest.mark.parametrize("hq,hkv", [(16, 8), (8, 1)])
+def test_prefill_no_prefix(hq, hkv):
+    lens = [1, 15, 16, 17, 63, 64, 65, 200]
+    _run(lens, lens, hq, hkv)
+
+
+def test_prefill_with_cached_prefix():
+    _run([5, 64, 100, 17], [16 + 5, 32 + 64, 48 + 100, 512 + 17], 16, 8)
+
+
+def test_mixed_decode_then_prefill():
+    _run([1, 1, 1, 40, 130], [77, 16, 1, 40, 16 + 130], 32, 8, n_decode=3)

@@ -1,0 +1,327 @@
+// Memory-bound glue kernels in bf16 with 16-byte vector accesses: RMSNorm, fused
+// residual-add + RMSNorm, SiLU-mul, vocab-shard embedding lookup, row gather, and the fused
+// per-head QK-RMSNorm + NeoX RoPE + paged KV-cache append.
+//
+// The reference runs these as separate library kernels (FlashInfer RMSNorm / fused add+norm /
+// RoPE / SiLU-mul, a Triton KV-append kernel, ATen embedding) with extra slice copies in
+// between (reference: src/compute/layers/ops.py:20-85, src/compute/kv_ops.py:8-62,
+// src/compute/models/qwen3.py:117-128). Here the q-norm, k-norm, RoPE and cache append are one
+// pass over the QKV activations.
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../common/ptx.cuh"
+#include "xv_cuda.h"
+
+namespace xv {
+
+struct alignas(16) Bf16x8 {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const Bf16x8 r = *reinterpret_cast<const Bf16x8*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(r.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  Bf16x8 r;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) r.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<Bf16x8*>(p) = r;
+}
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = lane < nw ? scratch[lane] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+constexpr int kNormThreads = 256;
+constexpr int kNormMaxVec = 4;   // up to 256 * 4 * 8 = 8192 columns held in registers
+
+// One CTA per row. ADD: residual += x first, and the sum is what gets normalised.
+template <bool ADD>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,
+               const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int hidden, float eps) {
+  __shared__ float scratch[32];
+  const size_t row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * hidden;
+  __nv_bfloat16* rr = ADD ? residual + row * hidden : nullptr;
+  __nv_bfloat16* yr = y + row * hidden;
+  const int nvec = hidden >> 3;
+  float vals[kNormMaxVec][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kNormMaxVec; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    if (v < nvec) {
+      load8(xr + v * 8, vals[i]);
+      if (ADD) {
+        float r[8];
+        load8(rr + v * 8, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vals[i][j] += r[j];
+        store8(rr + v * 8, vals[i]);
+        // normalise what was stored (the rounded sum), as a separate add kernel would
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vals[i][j] = __bfloat162float(__float2bfloat16(vals[i][j]));
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+    }
+  }
+  const float inv = rsqrtf(block_sum(ss, scratch) / static_cast<float>(hidden) + eps);
+#pragma unroll
+  for (int i = 0; i < kNormMaxVec; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    if (v < nvec) {
+      float g[8], o[8];
+      load8(w + v * 8, g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * inv * g[j];
+      store8(yr + v * 8, o);
+    }
+  }
+}
+
+__global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long long rows,
+                                int inter) {
+  const int vec_per_row = inter >> 3;
+  const long long total = rows * vec_per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int c = static_cast<int>(i - r * vec_per_row) * 8;
+    float g[8], u[8], o[8];
+    load8(x + r * 2 * inter + c, g);
+    load8(x + r * 2 * inter + inter + c, u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    store8(y + r * inter + c, o);
+  }
+}
+
+// out[t] = w[ids[t] - vocab_start] when the id is inside this rank's shard, zeros otherwise.
+__global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ w,
+                                 __nv_bfloat16* __restrict__ y, int hidden, int vocab_start, int vocab_rows) {
+  const size_t t = blockIdx.x;
+  const int local = ids[t] - vocab_start;
+  const bool mine = local >= 0 && local < vocab_rows;
+  const int nvec = hidden >> 3;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    uint4 val = zero;
+    if (mine) val = *reinterpret_cast<const uint4*>(w + static_cast<size_t>(local) * hidden + v * 8);
+    *reinterpret_cast<uint4*>(y + t * hidden + v * 8) = val;
+  }
+}
+
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ rows,
+                                   __nv_bfloat16* __restrict__ y, int hidden) {
+  const size_t i = blockIdx.x;
+  const size_t src = static_cast<size_t>(rows[i]);
+  const int nvec = hidden >> 3;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x)
+    *reinterpret_cast<uint4*>(y + i * hidden + v * 8) = *reinterpret_cast<const uint4*>(x + src * hidden + v * 8);
+}
+
+// One warp per (token, head). Lane l holds elements [2l, 2l+1] of the first half and the same
+// of the second half (D = 128: 2 + 2 values; D = 64: lanes 0..15 active per half... handled by
+// the generic loop). The NeoX rotation pairs element i with i + D/2, both held by one lane.
+template <int D>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ q_w,
+                          const __nv_bfloat16* __restrict__ k_w, float eps, const float* __restrict__ cos_sin,
+                          const int* __restrict__ positions, const int* __restrict__ slots,
+                          __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
+                          __nv_bfloat16* __restrict__ v_cache, int tokens, int hq, int hkv, int block_size) {
+  constexpr int HALF = D / 2;
+  constexpr int PER = HALF / 32;           // elements per lane per half (2 for D=128, 1 for D=64)
+  static_assert(PER == 1 || PER == 2, "head_dim must be 64 or 128");
+  const int heads = hq + 2 * hkv;
+  const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= static_cast<long long>(tokens) * heads) return;
+  const int t = static_cast<int>(gw / heads);
+  const int h = static_cast<int>(gw - static_cast<long long>(t) * heads);
+  const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * heads * D + static_cast<size_t>(h) * D;
+  const int slot = slots[t];
+
+  float lo[PER], hi[PER];
+  if (PER == 2) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + lane * 2));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + HALF + lane * 2));
+    lo[0] = a.x; lo[PER - 1] = a.y; hi[0] = b.x; hi[PER - 1] = b.y;
+  } else {
+    lo[0] = __bfloat162float(src[lane]);
+    hi[0] = __bfloat162float(src[HALF + lane]);
+  }
+
+  if (h >= hq + hkv) {
+    // V head: straight copy into the cache
+    if (slot >= 0) {
+      const int hv = h - hq - hkv;
+      __nv_bfloat16* dst = v_cache + ((static_cast<size_t>(slot / block_size) * hkv + hv) * block_size +
+                                      slot % block_size) * D;
+      if (PER == 2) {
+        *reinterpret_cast<__nv_bfloat162*>(dst + lane * 2) = __floats2bfloat162_rn(lo[0], lo[PER - 1]);
+        *reinterpret_cast<__nv_bfloat162*>(dst + HALF + lane * 2) = __floats2bfloat162_rn(hi[0], hi[PER - 1]);
+      } else {
+        dst[lane] = __float2bfloat16(lo[0]);
+        dst[HALF + lane] = __float2bfloat16(hi[0]);
+      }
+    }
+    return;
+  }
+
+  const bool is_q = h < hq;
+  const __nv_bfloat16* nw = is_q ? q_w : k_w;
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) ss += lo[i] * lo[i] + hi[i] * hi[i];
+  const float inv = rsqrtf(warp_sum(ss) / static_cast<float>(D) + eps);
+  const float* cs = cos_sin + static_cast<size_t>(positions[t]) * D;
+  float olo[PER], ohi[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = lane * PER + i;
+    const float x1 = lo[i] * inv * __bfloat162float(nw[e]);
+    const float x2 = hi[i] * inv * __bfloat162float(nw[HALF + e]);
+    const float c = cs[e], s = cs[HALF + e];
+    olo[i] = x1 * c - x2 * s;
+    ohi[i] = x2 * c + x1 * s;
+  }
+  __nv_bfloat16* dst;
+  if (is_q) {
+    dst = q_out + static_cast<size_t>(t) * hq * D + static_cast<size_t>(h) * D;
+  } else {
+    if (slot < 0) return;
+    dst = k_cache + ((static_cast<size_t>(slot / block_size) * hkv + (h - hq)) * block_size + slot % block_size) * D;
+  }
+  if (PER == 2) {
+    *reinterpret_cast<__nv_bfloat162*>(dst + lane * 2) = __floats2bfloat162_rn(olo[0], olo[PER - 1]);
+    *reinterpret_cast<__nv_bfloat162*>(dst + HALF + lane * 2) = __floats2bfloat162_rn(ohi[0], ohi[PER - 1]);
+  } else {
+    dst[lane] = __float2bfloat16(olo[0]);
+    dst[HALF + lane] = __float2bfloat16(ohi[0]);
+  }
+}
+
+__global__ void bounded_wait_kernel(volatile int* flag, int* status, unsigned limit) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    bool seen = false;
+    for (unsigned i = 0; i < limit; ++i) {
+      if (*flag != 0) {
+        seen = true;
+        break;
+      }
+      __nanosleep(100);
+    }
+    if (!seen) report_status(status, 99, kHostFlagTimeout);
+  }
+}
+
+}  // namespace xv
+
+using namespace xv;
+
+static inline int launch_ok() { return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH; }
+
+extern "C" {
+
+int xv_rmsnorm(const void* x, const void* w, void* y, int rows, int hidden, float eps, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (hidden % 8 || hidden > kNormThreads * kNormMaxVec * 8) return XV_ERR_SHAPE;
+  rmsnorm_kernel<false><<<rows, kNormThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), nullptr,
+                                                          static_cast<const __nv_bfloat16*>(w),
+                                                          static_cast<__nv_bfloat16*>(y), hidden, eps);
+  return launch_ok();
+}
+
+int xv_add_rmsnorm(const void* x, void* residual, const void* w, void* y, int rows, int hidden, float eps,
+                   cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (hidden % 8 || hidden > kNormThreads * kNormMaxVec * 8) return XV_ERR_SHAPE;
+  rmsnorm_kernel<true><<<rows, kNormThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
+                                                         static_cast<__nv_bfloat16*>(residual),
+                                                         static_cast<const __nv_bfloat16*>(w),
+                                                         static_cast<__nv_bfloat16*>(y), hidden, eps);
+  return launch_ok();
+}
+
+int xv_silu_mul(const void* x, void* y, int rows, int inter, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (inter % 8) return XV_ERR_SHAPE;
+  const long long total = static_cast<long long>(rows) * (inter / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  silu_mul_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
+                                                                     static_cast<__nv_bfloat16*>(y), rows, inter);
+  return launch_ok();
+}
+
+int xv_embedding(const int* ids, const void* w, void* y, int tokens, int hidden, int vocab_start, int vocab_rows,
+                 cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (hidden % 8) return XV_ERR_SHAPE;
+  embedding_kernel<<<tokens, 128, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(w),
+                                               static_cast<__nv_bfloat16*>(y), hidden, vocab_start, vocab_rows);
+  return launch_ok();
+}
+
+int xv_gather_rows(const void* x, const int* rows, void* y, int n, int hidden, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (hidden % 8) return XV_ERR_SHAPE;
+  gather_rows_kernel<<<n, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows,
+                                            static_cast<__nv_bfloat16*>(y), hidden);
+  return launch_ok();
+}
+
+int xv_qk_norm_rope_cache(const void* qkv, const void* q_w, const void* k_w, float eps, const float* cos_sin,
+                          const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
+                          int tokens, int hq, int hkv, int d, int block_size, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const long long warps = static_cast<long long>(tokens) * (hq + 2 * hkv);
+  const unsigned blocks = static_cast<unsigned>((warps + 7) / 8);
+#define XV_QKR(D)                                                                                         \
+  qk_norm_rope_cache_kernel<D><<<blocks, 256, 0, stream>>>(                                                \
+      static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(q_w),                      \
+      static_cast<const __nv_bfloat16*>(k_w), eps, cos_sin, positions, slots,                              \
+      static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),                            \
+      static_cast<__nv_bfloat16*>(v_cache), tokens, hq, hkv, block_size)
+  if (d == 128) {
+    XV_QKR(128);
+  } else if (d == 64) {
+    XV_QKR(64);
+  } else {
+    return XV_ERR_UNSUPPORTED;
+  }
+#undef XV_QKR
+  return launch_ok();
+}
+
+int xv_selftest_bounded_wait(int* flag, int* status, unsigned limit, cudaStream_t stream) {
+  bounded_wait_kernel<<<1, 32, 0, stream>>>(flag, status, limit);
+  return launch_ok();
+}
+
+int xv_num_sms(void) {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  return n;
+}
+
+}  // extern "C"

@@ -1,0 +1,460 @@
+// bf16 GEMM for sm_100a on the 5th-generation tensor cores: Y[M,N] = X[M,K] * W[N,K]^T.
+//
+// Structure of one CTA (192 threads):
+//   warp 0      - TMA producer: cp.async.bulk.tensor 2-D tile loads of both operands into a
+//                 ring of shared-memory stages (128-byte swizzle), completion on mbarriers.
+//   warp 1      - allocates TMEM and issues tcgen05.mma (one elected thread); accumulator
+//                 D[128 x BN] stays in tensor memory for the whole K loop.
+//   warps 2..5  - epilogue: tcgen05.ld the accumulator (each warp owns 32 TMEM lanes),
+//                 convert and store.
+//
+// Two orientations share the kernel. "Normal" puts tokens on the MMA M axis (A = X) and
+// output features on N (B = W); it is used when M is large (prefill). "Swapped" puts output
+// features on M (A = W) and tokens on N (B = X, BN = tokens rounded up to 16), so a decode
+// step with a handful of tokens still issues full 128-row MMAs and streams each weight byte
+// exactly once; the epilogue writes the transposed tile. Split-K (grid.z) spreads the K loop
+// over more CTAs when there are too few output tiles to fill 148 SMs; partial sums go to an
+// fp32 workspace that a second small kernel reduces.
+//
+// The reference calls cuBLAS through torch.nn.functional.linear for all of these
+// (reference: src/compute/layers/linear.py:87,148,268,307).
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
+#include "../common/ptx.cuh"
+#include "xv_cuda.h"
+
+namespace xv {
+
+constexpr int kBM = 128;          // MMA M (rows of operand A per CTA)
+constexpr int kBK = 64;           // K elements per stage = one 128-byte swizzle row
+constexpr int kUmmaK = 16;        // K per tcgen05.mma for 16-bit inputs
+constexpr int kGemmThreads = 192;
+constexpr int kMaxStages = 8;
+constexpr int kGemmKernelId = 1;
+
+struct GemmParams {
+  int rows_a;        // valid rows of operand A (M axis of the MMA)
+  int rows_b;        // valid rows of operand B (N axis of the MMA)
+  int k;             // reduction length
+  int bn;            // MMA N = rows of B per CTA (multiple of 16, <= 256)
+  int stages;
+  int k_blocks_per_split;
+  int transposed;    // 1: out[(b_row) * ldc + a_row], 0: out[a_row * ldc + b_row]
+  int out_fp32;      // 1: fp32 partials at out + split * split_stride, 0: bf16
+  long long ldc;
+  long long split_stride;   // elements between split-K partial planes
+  void* out;
+  int* status;
+  uint32_t idesc;
+  uint32_t tmem_cols;
+};
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // Dynamic shared memory is only guaranteed 16-byte alignment; the swizzled tiles need 1024.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const uint32_t a_bytes = kBM * kBK * 2;
+  const uint32_t b_bytes = static_cast<uint32_t>(p.bn) * kBK * 2;
+  const uint32_t stage_bytes = a_bytes + b_bytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(p.stages) * stage_bytes);
+  uint64_t* empty_bar = full_bar + kMaxStages;
+  uint64_t* accum_bar = empty_bar + kMaxStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tile_a = blockIdx.x;   // along rows of A
+  const int tile_b = blockIdx.y;   // along rows of B
+  const int split = blockIdx.z;
+
+  const int total_kb = (p.k + kBK - 1) / kBK;
+  const int kb_begin = split * p.k_blocks_per_split;
+  int kb_end = kb_begin + p.k_blocks_per_split;
+  if (kb_end > total_kb) kb_end = total_kb;
+  const int num_kb = kb_end > kb_begin ? kb_end - kb_begin : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_b);
+      // Operand A is the streamed weight matrix in the swapped orientation and the re-read
+      // activation matrix otherwise; hints follow that.
+      const uint64_t hint_a = p.transposed ? l2_policy_evict_first() : l2_policy_evict_normal();
+      const uint64_t hint_b = p.transposed ? l2_policy_evict_last() : l2_policy_evict_normal();
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % p.stages;
+        const uint32_t round = static_cast<uint32_t>(i / p.stages);
+        if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
+          report_status(p.status, kGemmKernelId, kWaitEmptyTimeout);
+          *abort_flag = 1;
+          break;
+        }
+        if (*abort_flag) break;
+        uint8_t* sa = smem + static_cast<size_t>(s) * stage_bytes;
+        uint8_t* sb = sa + a_bytes;
+        mbar_expect_tx(&full_bar[s], stage_bytes);
+        const int kx = (kb_begin + i) * kBK;
+        tma_load_2d(sa, &map_a, &full_bar[s], kx, tile_a * kBM, hint_a);
+        tma_load_2d(sb, &map_b, &full_bar[s], kx, tile_b * p.bn, hint_b);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % p.stages;
+        const uint32_t round = static_cast<uint32_t>(i / p.stages);
+        if (!mbar_wait(&full_bar[s], round & 1)) {
+          report_status(p.status, kGemmKernelId, kWaitFullTimeout);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t sa = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
+        const uint32_t sb = sa + a_bytes;
+#pragma unroll
+        for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+          const uint64_t da = umma_desc_sw128(sa + kk * kUmmaK * 2);
+          const uint64_t db = umma_desc_sw128(sb + kk * kUmmaK * 2);
+          umma_bf16(tmem_base, da, db, p.idesc, (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);   // stage is free once these MMAs have read it
+      }
+      umma_commit(accum_bar);          // accumulator complete (or nothing was issued)
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int quarter = warp & 3;                       // TMEM lane quarter this warp may read
+    const int a_row = tile_a * kBM + quarter * 32 + lane;
+    bool ok = mbar_wait(accum_bar, 0);
+    if (!ok) {
+      report_status(p.status, kGemmKernelId, kWaitAccumTimeout);
+    }
+    tc_fence_after_sync();
+    // warp-uniform: the aligned TMEM loads below must be executed by all 32 lanes or none
+    ok = __all_sync(0xffffffffu, ok && (*abort_flag == 0) && num_kb > 0);
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const int b0 = tile_b * p.bn;
+    for (int c = 0; c < p.bn; c += 16) {
+      uint32_t r[16];
+      if (ok) {
+        tmem_ld16(lane_addr + static_cast<uint32_t>(c), r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) r[j] = 0u;
+      }
+      if (p.transposed) {
+        // lanes hold consecutive output columns (a_row); tokens run along the registers
+        if (a_row < p.rows_a) {
+          if (p.out_fp32) {
+            float* o = static_cast<float*>(p.out) + static_cast<size_t>(split) * p.split_stride;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int b_row = b0 + c + j;
+              if (b_row < p.rows_b) o[static_cast<size_t>(b_row) * p.ldc + a_row] = __uint_as_float(r[j]);
+            }
+          } else {
+            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int b_row = b0 + c + j;
+              if (b_row < p.rows_b)
+                o[static_cast<size_t>(b_row) * p.ldc + a_row] = __float2bfloat16(__uint_as_float(r[j]));
+            }
+          }
+        }
+      } else if (a_row < p.rows_a) {
+        const int col = b0 + c;
+        if (p.out_fp32) {
+          float* o = static_cast<float*>(p.out) + static_cast<size_t>(split) * p.split_stride +
+                     static_cast<size_t>(a_row) * p.ldc + col;
+          if (col + 16 <= p.rows_b && (p.ldc & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4)
+              *reinterpret_cast<float4*>(o + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                              __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+          } else {
+            for (int j = 0; j < 16; ++j)
+              if (col + j < p.rows_b) o[j] = __uint_as_float(r[j]);
+          }
+        } else {
+          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(a_row) * p.ldc + col;
+          if (col + 16 <= p.rows_b && (p.ldc & 7) == 0) {
+            uint4 v0, v1;
+            v0.x = pack_bf16(__uint_as_float(r[0]), __uint_as_float(r[1]));
+            v0.y = pack_bf16(__uint_as_float(r[2]), __uint_as_float(r[3]));
+            v0.z = pack_bf16(__uint_as_float(r[4]), __uint_as_float(r[5]));
+            v0.w = pack_bf16(__uint_as_float(r[6]), __uint_as_float(r[7]));
+            v1.x = pack_bf16(__uint_as_float(r[8]), __uint_as_float(r[9]));
+            v1.y = pack_bf16(__uint_as_float(r[10]), __uint_as_float(r[11]));
+            v1.z = pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13]));
+            v1.w = pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15]));
+            *reinterpret_cast<uint4*>(o) = v0;
+            *reinterpret_cast<uint4*>(o + 8) = v1;
+          } else {
+            for (int j = 0; j < 16; ++j)
+              if (col + j < p.rows_b) o[j] = __float2bfloat16(__uint_as_float(r[j]));
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, p.tmem_cols);
+  }
+}
+
+// out[m, n] = sum_s partial[s, m, n], rounded to bf16.
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
+                                     long long elems, int splits, long long split_stride) {
+  const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  if (i >= elems) return;
+  if (i + 4 <= elems) {
+    float4 acc = *reinterpret_cast<const float4*>(partial + i);
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(partial + s * split_stride + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    uint2 o;
+    o.x = pack_bf16(acc.x, acc.y);
+    o.y = pack_bf16(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(out + i) = o;
+  } else {
+    for (long long j = i; j < elems; ++j) {
+      float acc = 0.f;
+      for (int s = 0; s < splits; ++s) acc += partial[s * split_stride + j];
+      out[j] = __float2bfloat16(acc);
+    }
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn get_encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(p);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  long long rows, k, ld;
+  int box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && k == o.k && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h ^= static_cast<size_t>(k.rows) * 0x9E3779B97F4A7C15ULL + (h << 6) + (h >> 2);
+    h ^= static_cast<size_t>(k.k) * 0xC2B2AE3D27D4EB4FULL + (h << 6) + (h >> 2);
+    h ^= static_cast<size_t>(k.ld * 31 + k.box_rows) + (h << 6) + (h >> 2);
+    return h;
+  }
+};
+
+// Tensor maps depend only on (address, shape, box); weights never move and the caching
+// allocator hands activations the same addresses step after step, so encodes are cached.
+static int get_tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long k, long long ld,
+                          int box_rows) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  MapKey key{ptr, rows, k, ld, box_rows};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return 0;
+    }
+  }
+  EncodeFn enc = get_encode_fn();
+  if (!enc) return XV_ERR_DRIVER;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return XV_ERR_TENSORMAP;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 65536) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
+
+static int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+static uint32_t pow2_cols(int n) {
+  uint32_t c = 32;
+  while (c < static_cast<uint32_t>(n)) c <<= 1;
+  return c;
+}
+
+}  // namespace xv
+
+using namespace xv;
+
+extern "C" {
+
+// Chooses orientation, tile and split-K for a problem; fills *plan. Pure host arithmetic so
+// callers (and CPU tests) can size the workspace before launching.
+int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan) {
+  if (m <= 0 || n <= 0 || k <= 0 || (k % 8) != 0) return XV_ERR_SHAPE;
+  if (num_sms <= 0) num_sms = 148;
+  XvGemmPlan pl;
+  std::memset(&pl, 0, sizeof(pl));
+  const int total_kb = (k + kBK - 1) / kBK;
+  if (m <= 256) {
+    pl.swapped = 1;
+    pl.bn = round_up(m, 16);
+    pl.tiles_a = (n + kBM - 1) / kBM;
+    pl.tiles_b = 1;
+  } else {
+    pl.swapped = 0;
+    pl.bn = n >= 256 ? 256 : round_up(n, 16);
+    pl.tiles_a = (m + kBM - 1) / kBM;
+    pl.tiles_b = (n + pl.bn - 1) / pl.bn;
+  }
+  const int tiles = pl.tiles_a * pl.tiles_b;
+  int splits = 1;
+  if (tiles < num_sms) {
+    splits = num_sms / tiles;
+    // keep at least 4 K blocks (256 elements) per split so the pipeline has work
+    while (splits > 1 && total_kb / splits < 4) --splits;
+    if (splits > 16) splits = 16;
+  }
+  pl.k_blocks_per_split = (total_kb + splits - 1) / splits;
+  pl.splits = (total_kb + pl.k_blocks_per_split - 1) / pl.k_blocks_per_split;
+  const int stage_bytes = kBM * kBK * 2 + pl.bn * kBK * 2;
+  // small-token tiles leave room for two resident CTAs per SM (more loads in flight while
+  // another CTA drains its epilogue); big tiles take the whole SM
+  const int smem_budget = (pl.swapped && pl.bn <= 64) ? 100 * 1024 : 200 * 1024;
+  int stages = smem_budget / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages > pl.k_blocks_per_split) stages = pl.k_blocks_per_split < 2 ? 2 : pl.k_blocks_per_split;
+  pl.stages = stages;
+  pl.smem_bytes = stages * stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  pl.workspace_bytes = pl.splits > 1 ? static_cast<long long>(pl.splits) * m * n * 4 : 0;
+  *plan = pl;
+  return 0;
+}
+
+// Y[m,n] (bf16, row stride ldy) = X[m,k] (row stride ldx) * W[n,k]^T (row stride ldw).
+// `workspace` must hold plan.workspace_bytes when the plan splits K. `status` may be null.
+int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
+                 long long ldy, void* workspace, long long workspace_bytes, int num_sms, int* status,
+                 cudaStream_t stream) {
+  XvGemmPlan pl;
+  int rc = xv_gemm_plan(m, n, k, num_sms, &pl);
+  if (rc) return rc;
+  if ((ldx % 8) || (ldw % 8) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
+    return XV_ERR_ALIGN;
+  if (pl.workspace_bytes > workspace_bytes || (pl.workspace_bytes && !workspace)) return XV_ERR_WORKSPACE;
+
+  CUtensorMap map_a, map_b;
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  if (pl.swapped) {
+    if ((rc = get_tensor_map(&map_a, w, n, k, ldw, kBM))) return rc;
+    if ((rc = get_tensor_map(&map_b, x, m, k, ldx, pl.bn))) return rc;
+    p.rows_a = n;
+    p.rows_b = m;
+    p.transposed = 1;
+  } else {
+    if ((rc = get_tensor_map(&map_a, x, m, k, ldx, kBM))) return rc;
+    if ((rc = get_tensor_map(&map_b, w, n, k, ldw, pl.bn))) return rc;
+    p.rows_a = m;
+    p.rows_b = n;
+    p.transposed = 0;
+  }
+  p.k = k;
+  p.bn = pl.bn;
+  p.stages = pl.stages;
+  p.k_blocks_per_split = pl.k_blocks_per_split;
+  p.status = status;
+  p.idesc = umma_idesc_bf16(kBM, pl.bn);
+  p.tmem_cols = pow2_cols(pl.bn);
+  if (pl.splits > 1) {
+    p.out = workspace;
+    p.out_fp32 = 1;
+    p.ldc = n;
+    p.split_stride = static_cast<long long>(m) * n;
+  } else {
+    p.out = y;
+    p.out_fp32 = 0;
+    p.ldc = ldy;
+    p.split_stride = 0;
+  }
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return XV_ERR_LAUNCH;
+    attr_set = true;
+  }
+  dim3 grid(pl.tiles_a, pl.tiles_b, pl.splits);
+  gemm_tcgen05_kernel<<<grid, kGemmThreads, pl.smem_bytes, stream>>>(map_a, map_b, p);
+  if (cudaGetLastError() != cudaSuccess) return XV_ERR_LAUNCH;
+  if (pl.splits > 1) {
+    const long long elems = static_cast<long long>(m) * n;
+    if (ldy != n) return XV_ERR_SHAPE;   // split-K output must be dense
+    const int threads = 256;
+    const long long blocks = (elems / 4 + threads) / threads;
+    splitk_reduce_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+        static_cast<const float*>(workspace), static_cast<__nv_bfloat16*>(y), elems, pl.splits, p.split_stride);
+    if (cudaGetLastError() != cudaSuccess) return XV_ERR_LAUNCH;
+  }
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,79 @@
+// C ABI of the sm_100a kernel library (loaded from Python through ctypes). Every function
+// enqueues work on the given stream and returns 0, or a negative XV_ERR_* code without
+// launching. Pointers are device pointers unless stated otherwise; bf16 activations/weights.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define XV_ERR_SHAPE (-1)
+#define XV_ERR_ALIGN (-2)
+#define XV_ERR_WORKSPACE (-3)
+#define XV_ERR_DRIVER (-4)
+#define XV_ERR_TENSORMAP (-5)
+#define XV_ERR_LAUNCH (-6)
+#define XV_ERR_UNSUPPORTED (-7)
+
+typedef struct XvGemmPlan {
+  int swapped;             // 1: weights on the MMA M axis (few tokens)
+  int bn;                  // MMA N
+  int tiles_a, tiles_b;
+  int splits;              // split-K factor (grid.z)
+  int k_blocks_per_split;
+  int stages;
+  int smem_bytes;
+  long long workspace_bytes;
+} XvGemmPlan;
+
+int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan);
+int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
+                 long long ldy, void* workspace, long long workspace_bytes, int num_sms, int* status,
+                 cudaStream_t stream);
+
+// ---- elementwise / normalisation ----
+int xv_rmsnorm(const void* x, const void* w, void* y, int rows, int hidden, float eps, cudaStream_t stream);
+// residual += x (in place), y = rmsnorm(residual) * w
+int xv_add_rmsnorm(const void* x, void* residual, const void* w, void* y, int rows, int hidden, float eps,
+                   cudaStream_t stream);
+int xv_silu_mul(const void* x, void* y, int rows, int inter, cudaStream_t stream);
+int xv_embedding(const int* ids, const void* w, void* y, int tokens, int hidden, int vocab_start, int vocab_rows,
+                 cudaStream_t stream);
+int xv_gather_rows(const void* x, const int* rows, void* y, int n, int hidden, cudaStream_t stream);
+// Per-head RMSNorm of q and k, NeoX RoPE, q written to q_out [T, hq*d], k/v appended to the
+// paged cache [blocks, hkv, block_size, d] at `slots` (negative slot = skip).
+int xv_qk_norm_rope_cache(const void* qkv, const void* q_w, const void* k_w, float eps, const float* cos_sin,
+                          const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
+                          int tokens, int hq, int hkv, int d, int block_size, cudaStream_t stream);
+
+// ---- attention ----
+// Decode: one query row per sequence (rows 0..num_seqs-1 of q) against the paged cache.
+// `workspace` holds split partials: xv_attn_decode_workspace_bytes(...) bytes.
+long long xv_attn_decode_workspace_bytes(int num_seqs, int hq, int d, int splits);
+int xv_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                   const int* kv_lens, void* out, int num_seqs, int hq, int hkv, int d, int block_size,
+                   int max_blocks, float scale, int splits, void* workspace, cudaStream_t stream);
+// Prefill: packed varlen causal attention; sequence b owns query rows cu_q[b]..cu_q[b+1] which
+// are the last rows of its kv_lens[b] cached tokens. `q_row0` offsets the first query row.
+int xv_attn_prefill(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                    const int* cu_q, const int* kv_lens, void* out, int seq_begin, int num_seqs, int max_q_len,
+                    int hq, int hkv, int d, int block_size, int max_blocks, float scale, cudaStream_t stream);
+
+// ---- sampling ----
+int xv_argmax(const void* logits, long long* out, int rows, int vocab, long long ld, cudaStream_t stream);
+// rng: device int32[2] = {seed, step}. Rows with temperature <= 1e-5 are greedy.
+int xv_sample(const void* logits, long long* out, int rows, int vocab, long long ld, const float* temperature,
+              const int* top_k, const float* top_p, const float* min_p, const int* rng, cudaStream_t stream);
+
+// ---- diagnostics ----
+// Waits (bounded) on a flag nobody sets and reports kHostFlagTimeout through `status`;
+// proves the timeout path returns instead of hanging. `limit` polls.
+int xv_selftest_bounded_wait(int* flag, int* status, unsigned limit, cudaStream_t stream);
+int xv_num_sms(void);
+
+#ifdef __cplusplus
+}
+#endif

@@ -256,6 +256,8 @@ class ParallelLMHead(_VocabShard):
     __call__ = forward
 
     def argmax(self, x: torch.Tensor) -> torch.Tensor:
+        if self.tp.size == 1:
+            return ops.argmax(self.local_logits(x)[..., : self.num_embeddings])
         logits = self.local_logits(x).float()
         n_valid = max(0, min(self.per_rank, self.num_embeddings - self.vocab_start))
         if n_valid < self.per_rank:

@@ -1,0 +1,290 @@
+"""ctypes bindings of the sm_100a kernel library (``_xv_cuda.so``, built by ``ops.build``).
+
+Tensors are passed as raw device pointers together with the current CUDA stream; outputs
+are allocated with torch so they live in its caching allocator (and in CUDA-graph pools
+during capture). Only bf16 activations and weights are supported on the GPU. A missing
+library raises: there is no silent fallback to library kernels.
+
+``XV_GEMM=cublas`` in the environment swaps the GEMM for ``torch.matmul`` (cuBLAS); it
+exists to A/B the hand-written kernel and to bisect numerical differences.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from . import build as _build
+
+__all__ = [
+    "lib", "rmsnorm", "add_rmsnorm", "linear", "silu_mul", "embedding", "gather_rows",
+    "qk_norm_rope_cache", "paged_attention", "argmax", "sample", "check_status", "gemm_plan",
+    "decode_splits", "launch_count",
+]
+
+_lib = None
+_vp, _i32, _i64, _f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+ERRORS = {-1: "bad shape", -2: "misaligned pointer or stride", -3: "workspace too small",
+          -4: "driver entry point missing", -5: "tensor map encode failed", -6: "launch failed",
+          -7: "unsupported configuration"}
+
+# number of kernel launches issued through this module (bench.py reports it)
+launch_count = 0
+
+
+class GemmPlan(ctypes.Structure):
+    _fields_ = [("swapped", _i32), ("bn", _i32), ("tiles_a", _i32), ("tiles_b", _i32), ("splits", _i32),
+                ("k_blocks_per_split", _i32), ("stages", _i32), ("smem_bytes", _i32),
+                ("workspace_bytes", _i64)]
+
+
+def lib():
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB
+    if not os.path.isfile(path) or _build.needs_build():
+        path = _build.build()
+    L = ctypes.CDLL(path)
+    L.xv_gemm_plan.argtypes = [_i32, _i32, _i32, _i32, ctypes.POINTER(GemmPlan)]
+    L.xv_gemm_bf16.argtypes = [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _vp, _i64, _i32, _vp, _vp]
+    L.xv_rmsnorm.argtypes = [_vp, _vp, _vp, _i32, _i32, _f32, _vp]
+    L.xv_add_rmsnorm.argtypes = [_vp, _vp, _vp, _vp, _i32, _i32, _f32, _vp]
+    L.xv_silu_mul.argtypes = [_vp, _vp, _i32, _i32, _vp]
+    L.xv_embedding.argtypes = [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]
+    L.xv_gather_rows.argtypes = [_vp, _vp, _vp, _i32, _i32, _vp]
+    L.xv_qk_norm_rope_cache.argtypes = [_vp, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
+                                        _i32, _i32, _vp]
+    L.xv_attn_decode_workspace_bytes.argtypes = [_i32, _i32, _i32, _i32]
+    L.xv_attn_decode_workspace_bytes.restype = _i64
+    L.xv_attn_decode.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _i32,
+                                 _vp, _vp]
+    L.xv_attn_prefill.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
+                                  _i32, _f32, _vp]
+    L.xv_argmax.argtypes = [_vp, _vp, _i32, _i32, _i64, _vp]
+    L.xv_sample.argtypes = [_vp, _vp, _i32, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp]
+    L.xv_selftest_bounded_wait.argtypes = [_vp, _vp, ctypes.c_uint, _vp]
+    L.xv_num_sms.restype = _i32
+    _lib = L
+    return L
+
+
+def _check(rc: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
+    if rc != 0:
+        raise RuntimeError(f"{what}: {ERRORS.get(rc, rc)}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _bf16(*tensors) -> None:
+    for t in tensors:
+        if t.dtype != torch.bfloat16:
+            raise TypeError(f"GPU kernels take bfloat16 tensors, got {t.dtype}")
+
+
+class _DeviceState:
+    """Per-device scratch: split-K / split-KV workspaces, the status word, SM count."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.device = device
+        self.num_sms = torch.cuda.get_device_properties(device).multi_processor_count
+        self.gemm_ws = torch.empty(32 << 20, dtype=torch.uint8, device=device)
+        self.attn_ws = torch.empty(16 << 20, dtype=torch.uint8, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+
+_states: dict[int, _DeviceState] = {}
+
+
+def _state(t: torch.Tensor) -> _DeviceState:
+    idx = t.device.index if t.device.index is not None else torch.cuda.current_device()
+    st = _states.get(idx)
+    if st is None:
+        st = _states[idx] = _DeviceState(torch.device("cuda", idx))
+    return st
+
+
+def check_status(device=None) -> int:
+    """Reads (and clears) the device status word; raises if a kernel reported a problem."""
+    idx = torch.device(device).index if device is not None else torch.cuda.current_device()
+    st = _states.get(idx)
+    if st is None:
+        return 0
+    code = int(st.status.item())
+    if code:
+        st.status.zero_()
+        raise RuntimeError(f"kernel {code >> 16} reported status {code & 0xFFFF} "
+                           "(1/2/3 = pipeline wait ran out, 4 = peer flag wait ran out, 5 = bad index)")
+    return 0
+
+
+def gemm_plan(m: int, n: int, k: int, num_sms: int = 148) -> GemmPlan:
+    pl = GemmPlan()
+    rc = lib().xv_gemm_plan(m, n, k, num_sms, ctypes.byref(pl))
+    if rc:
+        raise RuntimeError(f"gemm_plan({m},{n},{k}): {ERRORS.get(rc, rc)}")
+    return pl
+
+
+_USE_CUBLAS = os.environ.get("XV_GEMM", "") == "cublas"
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``x[M,K] @ w[N,K]^T`` on the tcgen05 GEMM."""
+    _bf16(x, w)
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
+        raise ValueError(f"linear: bad shapes {tuple(x.shape)} x {tuple(w.shape)}")
+    M, K = x.shape
+    N = w.shape[0]
+    if M == 0:
+        return x.new_empty((0, N))
+    if _USE_CUBLAS:
+        y = torch.matmul(x, w.t())
+    else:
+        if x.stride(1) != 1 or w.stride(1) != 1:
+            x, w = x.contiguous(), w.contiguous()
+        st = _state(x)
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        rc = lib().xv_gemm_bf16(x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K, x.stride(0), w.stride(0), N,
+                                st.gemm_ws.data_ptr(), st.gemm_ws.numel(), st.num_sms, st.status.data_ptr(),
+                                _stream())
+        _check(rc, f"gemm {M}x{N}x{K}")
+    if bias is not None:
+        y += bias
+    return y
+
+
+def rmsnorm(x, w, eps):
+    _bf16(x, w)
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    rows = x.numel() // x.shape[-1]
+    _check(lib().xv_rmsnorm(x.data_ptr(), w.data_ptr(), y.data_ptr(), rows, x.shape[-1], eps, _stream()), "rmsnorm")
+    return y
+
+
+def add_rmsnorm(x, residual, w, eps):
+    _bf16(x, residual, w)
+    if not (x.is_contiguous() and residual.is_contiguous()):
+        raise ValueError("add_rmsnorm needs contiguous inputs (the residual is updated in place)")
+    y = torch.empty_like(x)
+    rows = x.numel() // x.shape[-1]
+    _check(lib().xv_add_rmsnorm(x.data_ptr(), residual.data_ptr(), w.data_ptr(), y.data_ptr(), rows,
+                                x.shape[-1], eps, _stream()), "add_rmsnorm")
+    return y
+
+
+def silu_mul(x):
+    _bf16(x)
+    x = x.contiguous()
+    inter = x.shape[-1] // 2
+    rows = x.numel() // x.shape[-1]
+    y = torch.empty(x.shape[:-1] + (inter,), dtype=x.dtype, device=x.device)
+    _check(lib().xv_silu_mul(x.data_ptr(), y.data_ptr(), rows, inter, _stream()), "silu_mul")
+    return y
+
+
+def embedding(ids, w, vocab_start=0):
+    _bf16(w)
+    if ids.dtype != torch.int32:
+        ids = ids.to(torch.int32)
+    y = torch.empty((ids.numel(), w.shape[1]), dtype=w.dtype, device=w.device)
+    _check(lib().xv_embedding(ids.data_ptr(), w.data_ptr(), y.data_ptr(), ids.numel(), w.shape[1], vocab_start,
+                              w.shape[0], _stream()), "embedding")
+    return y
+
+
+def gather_rows(x, rows):
+    _bf16(x)
+    if rows.dtype != torch.int32:
+        rows = rows.to(torch.int32)
+    x = x.contiguous()
+    y = torch.empty((rows.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    _check(lib().xv_gather_rows(x.data_ptr(), rows.data_ptr(), y.data_ptr(), rows.numel(), x.shape[1], _stream()),
+           "gather_rows")
+    return y
+
+
+def qk_norm_rope_cache(qkv, q_w, k_w, eps, cos_sin, positions, slots, k_cache, v_cache, num_q_heads,
+                       num_kv_heads, head_dim):
+    _bf16(qkv, q_w, k_w, k_cache, v_cache)
+    if not (qkv.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError("qk_norm_rope_cache needs contiguous qkv and cache tensors")
+    T = qkv.shape[0]
+    q = torch.empty((T, num_q_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    _check(lib().xv_qk_norm_rope_cache(qkv.data_ptr(), q_w.data_ptr(), k_w.data_ptr(), eps, cos_sin.data_ptr(),
+                                       positions.data_ptr(), slots.data_ptr(), q.data_ptr(), k_cache.data_ptr(),
+                                       v_cache.data_ptr(), T, num_q_heads, num_kv_heads, head_dim,
+                                       k_cache.shape[2], _stream()), "qk_norm_rope_cache")
+    return q
+
+
+def decode_splits(num_seqs: int, num_kv_heads: int, num_sms: int, max_blocks_tokens: int) -> int:
+    """KV splits so that a small batch still fills the GPU; depends only on launch-shape
+    constants (never on sequence lengths) so it is stable under CUDA-graph replay."""
+    ctas = max(1, num_seqs * num_kv_heads)
+    want = -(-2 * num_sms // ctas)
+    by_len = max(1, max_blocks_tokens // 256)      # at least ~256 tokens per split
+    return int(max(1, min(want, by_len, 16)))
+
+
+def paged_attention(q, k_cache, v_cache, attn, scale, num_q_heads, num_kv_heads, head_dim):
+    """Decode rows (the first ``attn.num_decode`` sequences) and prefill chunks of one packed batch."""
+    _bf16(q, k_cache, v_cache)
+    st = _state(q)
+    L = lib()
+    out = torch.empty_like(q)
+    bs = k_cache.shape[2]
+    maxb = attn.block_tables.shape[1]
+    n_d = attn.num_decode
+    if n_d > 0:
+        splits = decode_splits(n_d, num_kv_heads, st.num_sms, maxb * bs)
+        need = L.xv_attn_decode_workspace_bytes(n_d, num_q_heads, head_dim, splits)
+        if need > st.attn_ws.numel():
+            st.attn_ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+        _check(L.xv_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), attn.block_tables.data_ptr(),
+                                attn.kv_lens.data_ptr(), out.data_ptr(), n_d, num_q_heads, num_kv_heads, head_dim,
+                                bs, maxb, scale, splits, st.attn_ws.data_ptr(), _stream()), "attn_decode")
+    n_p = attn.num_seqs - n_d
+    if n_p > 0:
+        _check(L.xv_attn_prefill(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), attn.block_tables.data_ptr(),
+                                 attn.cu_q.data_ptr(), attn.kv_lens.data_ptr(), out.data_ptr(), n_d, n_p,
+                                 attn.max_q_len, num_q_heads, num_kv_heads, head_dim, bs, maxb, scale, _stream()),
+               "attn_prefill")
+    return out
+
+
+def argmax(logits):
+    _bf16(logits)
+    rows, vocab = logits.shape
+    out = torch.empty(rows, dtype=torch.int64, device=logits.device)
+    _check(lib().xv_argmax(logits.data_ptr(), out.data_ptr(), rows, vocab, logits.stride(0), _stream()), "argmax")
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, min_p, rng):
+    _bf16(logits)
+    rows, vocab = logits.shape
+    if rng is None:
+        rng = torch.zeros(2, dtype=torch.int32, device=logits.device)
+    out = torch.empty(rows, dtype=torch.int64, device=logits.device)
+    _check(lib().xv_sample(logits.data_ptr(), out.data_ptr(), rows, vocab, logits.stride(0),
+                           temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(), min_p.data_ptr(),
+                           rng.data_ptr(), _stream()), "sample")
+    return out
+
+
+def selftest_bounded_wait(limit: int = 1000) -> int:
+    """Runs a kernel that waits on a flag nobody sets; returns the status code it reports."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    _check(lib().xv_selftest_bounded_wait(flag.data_ptr(), status.data_ptr(), limit, _stream()), "selftest")
+    return int(status.item())

@@ -1,0 +1,300 @@
+"""Serving benchmark: output tokens per second of continuous batching on Qwen3-8B.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--model Qwen3-8B]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Workload (synthetic: random-init bf16 weights of the named architecture, uniform random
+token prompts): requests with prompt length U[256, 2048] and 512 output tokens each,
+greedy, EOS ignored, continuous batching with at most 256 running sequences and 16384
+batched tokens per step, tensor parallel over N GPUs.
+
+A bench *step* is one engine step (schedule -> forward -> sample -> update). The engine is
+first brought to the workload's steady state without timing: the running batch is filled and
+the initial requests get staggered remaining lengths, so finished requests are replaced at
+the steady rate (a replacement's whole prompt is prefilled in the same step as the other
+sequences' decodes). Then W untimed warm-up steps run, then exactly K timed steps.
+
+Two numbers come out of the timed region:
+* ``value``   - output tokens / device time, where device time is the sum over the K steps of
+                the CUDA-event time of each step's forward+sampling on the GPU (max over ranks);
+* ``e2e``     - output tokens / wall time of the K ``Engine.step()`` calls, bracketed by a
+                barrier and a device synchronise on both sides. Every step copies its inputs
+                host->device from pinned memory and reads its sampled ids back device->host.
+
+``--impl reference`` runs the unmodified reference engine installed under ``baseline/_ref``
+through its own ``Engine`` API on the same workload and prints the same line with
+``"impl": "reference"`` (its paged attention needs 256-token pages; ours uses 16).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "output_tokens_per_s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--model", default="Qwen3-8B")
+    ap.add_argument("--max-num-seqs", type=int, default=256)
+    ap.add_argument("--max-batched-tokens", type=int, default=16384)
+    ap.add_argument("--prompt-min", type=int, default=256)
+    ap.add_argument("--prompt-max", type=int, default=2048)
+    ap.add_argument("--out-tokens", type=int, default=512)
+    ap.add_argument("--eager", action="store_true", help="disable decode CUDA graphs")
+    ap.add_argument("--seed", type=int, default=0)
+    return ap.parse_args()
+
+
+class Workload:
+    """Endless stream of requests drawn from the benchmark's distribution."""
+
+    def __init__(self, args, vocab: int) -> None:
+        import numpy as np
+
+        self.rng = np.random.default_rng(args.seed)
+        self.args, self.vocab = args, vocab
+
+    def next(self, staggered: bool):
+        a = self.args
+        n = int(self.rng.integers(a.prompt_min, a.prompt_max + 1))
+        ids = self.rng.integers(0, self.vocab, size=n).tolist()
+        out = int(self.rng.integers(1, a.out_tokens + 1)) if staggered else a.out_tokens
+        return ids, out
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int = 0) -> None:
+        self.gpu_index = gpu_index
+        self.lines: list[str] = []
+        self.proc = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()           # the exact child we started
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def flush_l2(device) -> None:
+    """Writes a buffer larger than the 126 MB L2 so the next step starts cold."""
+    import torch
+
+    if not hasattr(flush_l2, "buf"):
+        flush_l2.buf = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    flush_l2.buf.zero_()
+
+
+def emit(record: dict) -> None:
+    print(json.dumps(record), flush=True)
+
+
+def baseline_number():
+    """BASELINE.md publishes no number for this metric, so vs_baseline is null."""
+    return None
+
+
+# ----------------------------------------------------------------------------------------------
+# ours
+# ----------------------------------------------------------------------------------------------
+def run_ours(args) -> None:
+    import torch
+
+    os.environ["XV_TIME_STEPS"] = "1"
+    from xixi_vllm_b200 import EngineConfig, SamplingParams
+    from xixi_vllm_b200.control.torchrun import env_rank_info, launch_from_env, shutdown_from_env
+    from xixi_vllm_b200.models.synth import make_model_dir
+    from xixi_vllm_b200.ops import cuda
+
+    rank, local_rank, world = env_rank_info()
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit(f"--gpus {args.gpus} needs torchrun with --nproc-per-node {args.gpus}")
+        raise SystemExit(f"WORLD_SIZE={world} does not match --gpus {args.gpus}")
+    model_dir = os.path.join(tempfile.gettempdir(), f"xv_bench_{args.model}_{os.getuid()}")
+    if rank == 0:
+        make_model_dir(model_dir, args.model, weights=False)
+    if world > 1:
+        time.sleep(0.0)
+    context = args.prompt_max + args.out_tokens
+    cfg_kwargs = dict(model=model_dir, load_format="dummy", dtype="bfloat16", context_len=context,
+                      max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_batched_tokens,
+                      kvcache_block_size=16, prefix_backend="none", enforce_eager=args.eager,
+                      tp_size=args.gpus, seed=args.seed, gpu_memory_utilization=0.9)
+    # rank 0 writes config.json before the others read it
+    if world > 1:
+        import torch.distributed as dist  # noqa: F401
+        deadline = time.time() + 60
+        while not os.path.isfile(os.path.join(model_dir, "config.json")) and time.time() < deadline:
+            time.sleep(0.05)
+    cfg = EngineConfig(**cfg_kwargs)
+    engine = launch_from_env(cfg)
+    if engine is None:      # ranks >= 1 served the driver until shutdown
+        return
+
+    device = torch.device("cuda", local_rank)
+    wl = Workload(args, cfg.hf_config.vocab_size)
+    core = engine._client.engine_core
+    sched = core.scheduler
+
+    def top_up(staggered: bool) -> None:
+        while len(sched.waiting) < 4:
+            ids, out = wl.next(staggered)
+            engine.add_request(ids, SamplingParams(temperature=0.0, max_tokens=out, ignore_eos=True))
+
+    # fill phase (untimed): admit until the running batch is full
+    top_up(True)
+    while len(sched.running) < args.max_num_seqs:
+        engine.step()
+        top_up(True)
+    for _ in range(args.warmup):
+        top_up(False)
+        engine.step()
+
+    runner = core.executor.worker.model_runner
+    clocks = ClockSampler(local_rank)
+    torch.cuda.synchronize(device)
+    first_step = sched._step + 1
+    launches0 = cuda.launch_count + (runner.graphs.replayed_kernels if runner.graphs else 0)
+    clocks.start()
+    out_tokens = 0
+    h2d = d2h = 0
+    step_ms = []
+    torch.cuda.synchronize(device)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        top_up(False)
+        flush_l2(device)
+        ts = time.perf_counter()
+        before = core.metrics.sampled_tokens
+        engine.step()
+        out_tokens += core.metrics.sampled_tokens - before
+        h2d += runner.h2d_bytes
+        d2h += runner.d2h_bytes
+        step_ms.append((time.perf_counter() - ts) * 1e3)
+    torch.cuda.synchronize(device)
+    wall = time.perf_counter() - t0
+    clk = clocks.stop()
+    launches = cuda.launch_count + (runner.graphs.replayed_kernels if runner.graphs else 0) - launches0
+    dev_ms = core.executor.device_time_ms(first_step, sched._step + 1)
+    e2e_wall = sum(step_ms) / 1e3            # Engine.step() wall time only (excludes the L2 flush)
+    cuda.check_status(device)
+
+    rec = {
+        "metric": METRIC, "value": out_tokens / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": baseline_number(), "dtype": "bf16",
+        "data": "synthetic (random-init weights, uniform random token prompts)", "impl": "ours",
+        "config": {"model": args.model, "global_batch": args.max_num_seqs, "seq_len": context,
+                   "parallelism": f"tp{args.gpus}", "prompt_len": f"U[{args.prompt_min},{args.prompt_max}]",
+                   "output_len": args.out_tokens, "max_num_batched_tokens": args.max_batched_tokens,
+                   "kv_block_size": 16, "decode_cuda_graph": not args.eager,
+                   "l2": "flushed between timed steps (256 MiB write)",
+                   "step": "one engine step in steady-state continuous batching"},
+        "clocks": clk,
+        "e2e": {"value": out_tokens / e2e_wall, "unit": "tokens/s", "h2d_bytes_per_step": h2d / args.steps,
+                "d2h_bytes_per_step": d2h / args.steps, "ms_per_step": 1e3 * e2e_wall / args.steps,
+                "wall_s_incl_flush": wall},
+        "gpu_launches": launches,
+        "output_tokens": out_tokens,
+        "engine": core.metrics.summary(),
+    }
+    emit(rec)
+    if world > 1:
+        shutdown_from_env(engine)
+    else:
+        engine.destroy()
+
+
+# ----------------------------------------------------------------------------------------------
+# reference
+# ----------------------------------------------------------------------------------------------
+def run_reference(args) -> None:
+    ref_root = os.path.join(ROOT, "baseline")
+    if not os.path.isfile(os.path.join(ref_root, "_ref", "control", "engine.py")):
+        emit({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --target install of /root/reference)"})
+        return
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        # the reference's single-node path spawns its own tensor-parallel workers from rank 0
+        return
+    try:
+        from baseline.ref_harness import run as run_ref
+
+        rec = run_ref(args, Workload, ClockSampler, flush_l2)
+    except Exception as e:  # the line must still be printed and the exit code stay 0
+        emit({"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:300]}"})
+        return
+    rec.update({"metric": METRIC, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+                "warmup": args.warmup, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": baseline_number(), "dtype": "bf16", "impl": "reference",
+                "data": "synthetic (random-init weights, uniform random token prompts)"})
+    emit(rec)
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

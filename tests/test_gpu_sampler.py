@@ -39,7 +39,11 @@ def _empirical(logits, temp, k, p, mp, draws=8000):
 def test_sample_distribution(temp, k, p, mp):
     g = torch.Generator().manual_seed(5)
     V = 1000
-    logits = (torch.randn(1, V, generator=g) * 2).bfloat16()
+    # distinct bf16 values: the kernel keeps every element tied with a threshold value, the
+    # oracle keeps exactly k, so ties at a boundary would make the two kept sets differ
+    pool = torch.unique((torch.randn(20000, generator=g) * 2).bfloat16().float())
+    logits = pool[torch.randperm(pool.numel(), generator=g)[:V]].reshape(1, V).bfloat16()
+    assert torch.unique(logits.float()).numel() == V
     want = cpu_ref.filtered_probs(logits.float(), torch.tensor([temp]), torch.tensor([k]),
                                   torch.tensor([p]), torch.tensor([mp]))[0]
     got = _empirical(logits, temp, k, p, mp)

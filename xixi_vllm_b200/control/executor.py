@@ -45,9 +45,10 @@ def _terminate_procs(procs: list) -> None:
 
 
 class ControlCommand(msgspec.Struct):
-    op: str                                  # "execute" | "reset_kv" | "shutdown"
+    op: str                                  # "execute" | "reset_kv" | "device_time" | "shutdown"
     sched: SchedulerOutput | None = None
     prefix_backend: str | None = None
+    args: list[int] = []
 
 
 class Executor(ABC):
@@ -111,6 +112,9 @@ def worker_loop(worker) -> None:
         if cmd.op == "reset_kv":
             worker.reset_kv(cmd.prefix_backend)
             continue
+        if cmd.op == "device_time":
+            worker.device_time_ms(cmd.args[0], cmd.args[1])
+            continue
         if cmd.op != "execute":
             raise ValueError(f"unknown control op: {cmd.op}")
         counts = worker.execute_model(cmd.sched)
@@ -155,6 +159,9 @@ class UniprocExecutor(Executor):
             self.worker.reset_kv(payload.get("prefix_backend"))
             return None
         return super().collective_rpc(op, **payload)
+
+    def device_time_ms(self, lo: int, hi: int) -> float:
+        return self.worker.device_time_ms(lo, hi)
 
     def destroy(self) -> None:
         self.kv = None
@@ -222,7 +229,8 @@ class MultiprocExecutor(Executor):
         return self.kv
 
     def collective_rpc(self, op: str, **payload) -> object:
-        cmd = ControlCommand(op=op, sched=payload.get("sched"), prefix_backend=payload.get("prefix_backend"))
+        cmd = ControlCommand(op=op, sched=payload.get("sched"), prefix_backend=payload.get("prefix_backend"),
+                             args=list(payload.get("args", [])))
         self._channel.broadcast(self._enc.encode(cmd), src=0)
         return None
 
@@ -247,6 +255,10 @@ class MultiprocExecutor(Executor):
             return self.worker.read_samples(n_p, n_d)
         reply, self._pending_reply = self._pending_reply, None
         return reply[1], reply[2]
+
+    def device_time_ms(self, lo: int, hi: int) -> float:
+        self.collective_rpc("device_time", args=[lo, hi])
+        return self.worker.device_time_ms(lo, hi)
 
     def shutdown(self) -> None:
         self.collective_rpc("shutdown")

@@ -15,6 +15,12 @@ from ..parallel.groups import graph_capture
 __all__ = ["CUDAGraphRunner", "make_bs_list"]
 
 
+def _launches() -> int:
+    from ..ops import cuda
+
+    return cuda.launch_count
+
+
 def make_bs_list(max_bs: int) -> list[int]:
     """1, 2, 4, 8, then multiples of 16 up to 128, multiples of 32 beyond."""
     out = [b for b in (1, 2, 4, 8) if b <= max_bs]
@@ -32,6 +38,8 @@ class CUDAGraphRunner:
         self.bs_list = sorted(bs_list)
         self.graphs: dict[tuple, torch.cuda.CUDAGraph] = {}
         self.outputs: dict[tuple, object] = {}
+        self.kernels: dict[tuple, int] = {}      # kernel launches recorded in each graph
+        self.replayed_kernels = 0                # kernels executed through replays so far
         self.pool = None
 
     @property
@@ -56,8 +64,10 @@ class CUDAGraphRunner:
                         body(batch)
                     torch.cuda.synchronize()
                     g = torch.cuda.CUDAGraph()
+                    n0 = _launches()
                     with torch.cuda.graph(g, pool=self.pool):
                         out = body(batch)
+                    self.kernels[(bs, variant)] = _launches() - n0
                     if self.pool is None:
                         self.pool = g.pool()
                     self.graphs[(bs, variant)] = g
@@ -67,6 +77,7 @@ class CUDAGraphRunner:
     def replay(self, bs: int, variant):
         key = (bs, variant)
         self.graphs[key].replay()
+        self.replayed_kernels += self.kernels[key]
         return self.outputs[key]
 
     def destroy(self) -> None:

@@ -8,6 +8,8 @@ p2p outside the graphs. Sampled ids leave the device on a side stream into pinne
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..ops import dispatch as ops
@@ -49,6 +51,11 @@ class ModelRunner:
         self._dev_samples: torch.Tensor | None = None
         self._n_samples = 0
         self._last: tuple[int, int, list[bool]] = (0, 0, [])
+        # per-step device time (CUDA events around the forward), kept for the last few thousand steps
+        self.time_steps = self.is_cuda and os.environ.get("XV_TIME_STEPS", "0") == "1"
+        self._step_events: dict[int, tuple] = {}
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
         self.graphs: CUDAGraphRunner | None = None
         if self.is_cuda and not config.enforce_eager:
             self._capture_graphs()
@@ -78,6 +85,10 @@ class ModelRunner:
         n_p, n_d = len(sched.prefills), len(sched.decodes)
         use_graph = (self.graphs is not None and n_p == 0 and 0 < n_d <= self.graphs.max_bs
                      and self.is_first_pp and self.is_last_pp)
+        ev = None
+        if self.time_steps:
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
         with torch.no_grad():
             if use_graph:
                 bucket = self.graphs.pad_bs(n_d)
@@ -92,9 +103,22 @@ class ModelRunner:
                     self._send(tokens)
                     tokens = None
         self._last = (n_p, n_d, batch.prefill_sampled)
+        self.h2d_bytes = self.stager.last_h2d_bytes
+        if ev is not None:
+            ev[1].record()
+            self._step_events[sched.step_id] = ev
+            if len(self._step_events) > 8192:
+                for k in sorted(self._step_events)[:4096]:
+                    del self._step_events[k]
         if tokens is not None:
             self._stage_samples(tokens, batch.num_samples)
+            self.d2h_bytes = batch.num_samples * 8
         return n_p, n_d
+
+    def device_time_ms(self, lo: int, hi: int) -> float:
+        """Sum of forward device time of the steps with ``lo <= step_id < hi``."""
+        torch.cuda.synchronize(self.device)
+        return float(sum(e0.elapsed_time(e1) for sid, (e0, e1) in self._step_events.items() if lo <= sid < hi))
 
     def _stage_samples(self, tokens: torch.Tensor, n: int) -> None:
         self._n_samples = n

@@ -78,6 +78,7 @@ class BatchStager:
         self.host = torch.zeros(cap, dtype=torch.int32, pin_memory=cuda)
         self.host_np = self.host.numpy()
         self.dev = torch.zeros(cap, dtype=torch.int32, device=self.device) if cuda else self.host
+        self.last_h2d_bytes = 0
         self._rows_tmp = np.zeros(max_seqs, dtype=np.int32)
         self._cached_tmp = np.zeros(max_seqs, dtype=np.int32)
 
@@ -232,6 +233,7 @@ class BatchStager:
             minp[n_s:B] = 0.0
         S = B if pad_to else n_s
 
+        self.last_h2d_bytes = used * 4
         if self.dev is not self.host:
             self.dev[:used].copy_(self.host[:used], non_blocking=True)
         d = self.dev

@@ -133,6 +133,18 @@ class Worker:
     def read_samples(self, n_p: int, n_d: int):
         return self.model_runner.read_samples(n_p, n_d)
 
+    def device_time_ms(self, lo: int, hi: int) -> float:
+        """Forward device time of steps [lo, hi) on this rank, maximised over the replica's ranks."""
+        t = self.model_runner.device_time_ms(lo, hi) if self.on_cuda else 0.0
+        world = groups.get_world_group()
+        if world.size > 1:
+            import torch.distributed as dist
+
+            buf = torch.tensor([t], dtype=torch.float64)
+            dist.all_reduce(buf, op=dist.ReduceOp.MAX, group=world.cpu_group)
+            t = float(buf.item())
+        return t
+
     def destroy_environment(self) -> None:
         if self.on_cuda and torch.cuda.is_available():
             try:

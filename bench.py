@@ -60,6 +60,8 @@ def parse_args():
     ap.add_argument("--out-tokens", type=int, default=512)
     ap.add_argument("--eager", action="store_true", help="disable decode CUDA graphs")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--profile", action="store_true",
+                    help="bracket the timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     return ap.parse_args()
 
 
@@ -213,6 +215,8 @@ def run_ours(args) -> None:
     first_step = sched._step + 1
     launches0 = cuda.launch_count + (runner.graphs.replayed_kernels if runner.graphs else 0)
     clocks.start()
+    if args.profile:
+        torch.cuda.profiler.start()
     out_tokens = 0
     h2d = d2h = 0
     step_ms = []
@@ -230,6 +234,8 @@ def run_ours(args) -> None:
         step_ms.append((time.perf_counter() - ts) * 1e3)
     torch.cuda.synchronize(device)
     wall = time.perf_counter() - t0
+    if args.profile:
+        torch.cuda.profiler.stop()
     clk = clocks.stop()
     launches = cuda.launch_count + (runner.graphs.replayed_kernels if runner.graphs else 0) - launches0
     dev_ms = core.executor.device_time_ms(first_step, sched._step + 1)

@@ -1,0 +1,177 @@
+"""Per-kernel microbenchmarks against the measured roofline.
+
+    python -m bench.kernels [--what gemm,decode,prefill,elementwise] [--json out.json]
+
+Each case is timed with CUDA events on the launching stream after 3 warm-up launches, with a
+256 MiB write between timed launches to flush the 126 MB L2, and reported as achieved
+bytes/s or FLOP/s and as a fraction of the measured peaks in ``MEASURED_PEAKS.json`` (a
+STREAM-style copy and a cuBLAS bf16 GEMM on this machine). cuBLAS (``torch.matmul``) is timed
+next to the GEMM for reference.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from xixi_vllm_b200.ops import cuda  # noqa: E402
+from xixi_vllm_b200.runtime.staging import AttnBatch  # noqa: E402
+
+DEV = "cuda"
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops"], "src": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "src": "fallback"}
+
+
+_flush = None
+
+
+def timeit(fn, iters: int = 10, warmup: int = 3) -> float:
+    """Median milliseconds per call."""
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(iters):
+        _flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def bench_gemm(out: list) -> None:
+    pk = peaks()
+    shapes = [
+        # decode (weight streaming): Qwen3-8B TP1 and TP8, 32B TP8
+        (1, 6144, 4096), (32, 6144, 4096), (256, 6144, 4096), (256, 4096, 4096), (256, 24576, 4096),
+        (256, 4096, 12288), (64, 151936, 4096), (32, 768, 4096), (32, 4096, 512), (32, 3072, 4096),
+        (32, 4096, 1536), (256, 6400, 5120), (256, 5120, 3200),
+        # prefill (compute bound)
+        (4096, 6144, 4096), (4096, 4096, 4096), (4096, 24576, 4096), (4096, 4096, 12288),
+        (16384, 24576, 4096), (8192, 8192, 8192),
+    ]
+    for m, n, k in shapes:
+        x = torch.randn(m, k, device=DEV).bfloat16()
+        w = torch.randn(n, k, device=DEV).bfloat16()
+        ms = timeit(lambda: cuda.linear(x, w))
+        ms_cublas = timeit(lambda: torch.matmul(x, w.t()))
+        flops = 2.0 * m * n * k
+        byts = 2.0 * (m * k + n * k + m * n)
+        tf, gbs = flops / ms / 1e9, byts / ms / 1e6
+        frac = max(tf / pk["tflops"], gbs / pk["hbm_gbs"])
+        pl = cuda.gemm_plan(m, n, k, 148)
+        out.append(dict(kernel="gemm_tcgen05", m=m, n=n, k=k, ms=ms, tflops=tf, gbs=gbs, frac_of_peak=frac,
+                        cublas_ms=ms_cublas, vs_cublas=ms_cublas / ms, swapped=pl.swapped, splits=pl.splits,
+                        bn=pl.bn, stages=pl.stages))
+        print(f"gemm {m:6d}x{n:6d}x{k:6d}: {ms:8.3f} ms {tf:8.1f} TF {gbs:8.1f} GB/s frac {frac:5.2f} of {pk['src']}"
+              f" | cublas {ms_cublas:8.3f} ms (x{ms_cublas / ms:4.2f})", flush=True)
+        del x, w
+
+
+def _attn_setup(q_lens, kv_lens, hq, hkv, bs=16):
+    B = len(kv_lens)
+    maxb = max(-(-l // bs) for l in kv_lens)
+    nblocks = sum(-(-l // bs) for l in kv_lens) + 1
+    bt = torch.zeros(B, maxb, dtype=torch.int32)
+    nxt = 0
+    perm = torch.randperm(nblocks)
+    for b, l in enumerate(kv_lens):
+        nb = -(-l // bs)
+        bt[b, :nb] = perm[nxt:nxt + nb].to(torch.int32)
+        nxt += nb
+    k = torch.randn(nblocks, hkv, bs, 128, device=DEV).bfloat16()
+    v = torch.randn(nblocks, hkv, bs, 128, device=DEV).bfloat16()
+    T = sum(q_lens)
+    q = torch.randn(T, hq * 128, device=DEV).bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    return q, k, v, cu, torch.tensor(kv_lens, dtype=torch.int32), bt
+
+
+def bench_decode(out: list) -> None:
+    pk = peaks()
+    for B, L, hq, hkv in [(256, 1408, 32, 8), (32, 1408, 32, 8), (1, 2048, 32, 8), (256, 1408, 4, 1),
+                          (256, 2048, 8, 1), (8, 4096, 32, 8)]:
+        q, k, v, cu, kvl, bt = _attn_setup([1] * B, [L] * B, hq, hkv)
+        attn = AttnBatch(cu_q=cu.to(DEV), kv_lens=kvl.to(DEV), block_tables=bt.to(DEV), num_seqs=B, num_decode=B,
+                         max_q_len=1, max_kv_len=L, num_tokens=B)
+        ms = timeit(lambda: cuda.paged_attention(q, k, v, attn, 128 ** -0.5, hq, hkv, 128))
+        byts = 2.0 * B * L * hkv * 128 * 2
+        gbs = byts / ms / 1e6
+        out.append(dict(kernel="attn_decode", batch=B, kv_len=L, hq=hq, hkv=hkv, ms=ms, gbs=gbs,
+                        frac_of_peak=gbs / pk["hbm_gbs"]))
+        print(f"decode B={B:4d} L={L:5d} hq={hq} hkv={hkv}: {ms:8.3f} ms {gbs:8.1f} GB/s frac "
+              f"{gbs / pk['hbm_gbs']:5.2f} of {pk['src']}", flush=True)
+        del q, k, v
+
+
+def bench_prefill(out: list) -> None:
+    pk = peaks()
+    for B, L, hq, hkv in [(8, 2048, 32, 8), (16, 1024, 32, 8), (4, 4096, 32, 8), (8, 2048, 4, 1)]:
+        q, k, v, cu, kvl, bt = _attn_setup([L] * B, [L] * B, hq, hkv)
+        attn = AttnBatch(cu_q=cu.to(DEV), kv_lens=kvl.to(DEV), block_tables=bt.to(DEV), num_seqs=B, num_decode=0,
+                         max_q_len=L, max_kv_len=L, num_tokens=B * L)
+        ms = timeit(lambda: cuda.paged_attention(q, k, v, attn, 128 ** -0.5, hq, hkv, 128))
+        flops = 4.0 * B * hq * 128 * L * L / 2       # causal: half the square
+        tf = flops / ms / 1e9
+        out.append(dict(kernel="attn_prefill", batch=B, seq=L, hq=hq, hkv=hkv, ms=ms, tflops=tf,
+                        frac_of_peak=tf / pk["tflops"]))
+        print(f"prefill B={B:3d} L={L:5d} hq={hq} hkv={hkv}: {ms:8.3f} ms {tf:8.1f} TF frac "
+              f"{tf / pk['tflops']:5.2f} of {pk['src']}", flush=True)
+        del q, k, v
+
+
+def bench_elementwise(out: list) -> None:
+    pk = peaks()
+    T, H, I = 16384, 4096, 12288
+    x = torch.randn(T, H, device=DEV).bfloat16()
+    r = torch.randn(T, H, device=DEV).bfloat16()
+    w = torch.ones(H, device=DEV).bfloat16()
+    cases = [("rmsnorm", lambda: cuda.rmsnorm(x, w, 1e-6), 2.0 * T * H * 2),
+             ("add_rmsnorm", lambda: cuda.add_rmsnorm(x, r, w, 1e-6), 4.0 * T * H * 2)]
+    gu = torch.randn(T, 2 * I, device=DEV).bfloat16()
+    cases.append(("silu_mul", lambda: cuda.silu_mul(gu), 3.0 * T * I * 2))
+    for name, fn, byts in cases:
+        ms = timeit(fn)
+        gbs = byts / ms / 1e6
+        out.append(dict(kernel=name, tokens=T, ms=ms, gbs=gbs, frac_of_peak=gbs / pk["hbm_gbs"]))
+        print(f"{name:12s} T={T}: {ms:8.3f} ms {gbs:8.1f} GB/s frac {gbs / pk['hbm_gbs']:5.2f} of {pk['src']}", flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--what", default="gemm,decode,prefill,elementwise")
+    ap.add_argument("--json", default=None)
+    a = ap.parse_args()
+    out: list = []
+    table = {"gemm": bench_gemm, "decode": bench_decode, "prefill": bench_prefill, "elementwise": bench_elementwise}
+    for name in a.what.split(","):
+        table[name](out)
+    cuda.check_status()
+    if a.json:
+        with open(a.json, "w") as f:
+            json.dump({"peaks": peaks(), "results": out}, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

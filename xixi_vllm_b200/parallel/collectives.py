@@ -33,8 +33,9 @@ def all_gather(x: torch.Tensor, group: Group, dim: int = -1) -> torch.Tensor:
         return x
     dim = dim % x.dim()
     x = x.contiguous()
-    out = torch.empty((n,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-    dist.all_gather_into_tensor(out, x, group=group.device_group)
+    flat = torch.empty((n * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(flat, x, group=group.device_group)
+    out = flat.view((n,) + tuple(x.shape))
     if dim == 0:
         return out.reshape((n * x.shape[0],) + tuple(x.shape[1:]))
     out = out.movedim(0, dim)

@@ -1,0 +1,375 @@
+// Tensor-parallel reductions over NVLink peer memory, fused with what follows them.
+//
+// Every rank keeps its partial results in a *symmetric* buffer: the same allocation exists on
+// each GPU and every rank has all peers' copies mapped into its address space (and, when the
+// fabric supports it, one multicast address that reaches all copies through NVSwitch).
+//
+//   tp_reduce_norm_kernel   - sum of the ranks' partial [T,H] tiles + residual add + RMSNorm in
+//                             one pass. Peers are read with plain system-scope loads from their
+//                             mapped buffers, or the sum is fetched already reduced inside the
+//                             switch with multimem.ld_reduce. The producing GEMM (or embedding
+//                             lookup) writes straight into the symmetric buffer, so there is no
+//                             NCCL call, no staging copy and no separate add+norm kernel.
+//   tp_argmax_kernel        - vocab-parallel greedy sampling: local argmax of this rank's logit
+//                             shard, (value, id) pushed into every peer's slot, global pick.
+//
+// Synchronisation: a monotonically increasing epoch per communicator, kept in device memory
+// (so a captured CUDA graph advances it on every replay). A rank announces "my partial for
+// epoch e is complete" by storing e into its slot of every peer's flag array with a
+// system-scope release; consumers poll their own flag array with acquire loads. Polls are
+// bounded: after `spin_limit` tries the kernel records a status code and returns.
+//
+// Buffer reuse rule (enforced by the caller): the buffer written for call k may be rewritten
+// only after the caller has passed the barrier of call k+1, i.e. never in two consecutive calls.
+//
+// The reference does these steps as NCCL all-reduce / all-gather calls followed by separate
+// kernels (reference: src/compute/layers/linear.py:141-154, src/compute/layers/vocab_parallel.py:171-216).
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+
+#include "../common/ptx.cuh"
+#include "xv_cuda.h"
+
+namespace xv {
+
+constexpr int kMaxRanks = 8;
+constexpr int kTpKernelId = 3;
+constexpr int kTpThreads = 256;
+
+struct TpComm {
+  const void* peer_buf[kMaxRanks];   // every rank's symmetric buffer base, as mapped here
+  uint32_t* peer_flags[kMaxRanks];   // every rank's flag array (kMaxRanks words per channel)
+  const void* mc_buf;                // multicast address of the buffer (nullptr = no NVLS)
+  uint32_t* epoch;                   // [0] current epoch, [1] finished-CTA ticket (local memory)
+  int rank, world;
+  unsigned spin_limit;
+  int* status;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+// Sum over all ranks of eight bf16 values, reduced inside NVSwitch with fp32 accumulation.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+
+// Announce this rank's data for `epoch` (one thread of the grid) and wait until every rank has
+// announced. Returns false if a peer never arrived within the spin limit.
+__device__ bool tp_barrier(const TpComm& c, uint32_t epoch, int channel) {
+  __shared__ int ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x < c.world) {
+    __threadfence_system();   // the producer kernel's writes are ordered before the flag
+    st_release_sys(c.peer_flags[threadIdx.x] + channel * kMaxRanks + c.rank, epoch);
+  }
+  if (threadIdx.x < c.world) {
+    const uint32_t* f = c.peer_flags[c.rank] + channel * kMaxRanks + threadIdx.x;
+    bool seen = false;
+    for (unsigned i = 0; i < c.spin_limit; ++i) {
+      // epochs only grow; signed distance tolerates wrap-around
+      if (static_cast<int32_t>(ld_acquire_sys(f) - epoch) >= 0) {
+        seen = true;
+        break;
+      }
+      __nanosleep(20);
+    }
+    if (!seen) {
+      report_status(c.status, kTpKernelId, kPeerFlagTimeout);
+      ok_flag = 0;
+    }
+  }
+  __syncthreads();
+  return ok_flag != 0;
+}
+
+// Last CTA to finish advances the epoch for the next call and resets the ticket.
+__device__ void tp_finish(const TpComm& c) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned t = atomicAdd(c.epoch + 1, 1u);
+    if (t == gridDim.x - 1) {
+      c.epoch[1] = 0;
+      __threadfence();
+      atomicAdd(c.epoch, 1u);
+    }
+  }
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  v.x = pack_bf16(f[0], f[1]);
+  v.y = pack_bf16(f[2], f[3]);
+  v.z = pack_bf16(f[4], f[5]);
+  v.w = pack_bf16(f[6], f[7]);
+  return v;
+}
+
+constexpr int kTpMaxVec = 4;   // hidden <= 256 * 4 * 8 = 8192
+
+// mode 0: y = rmsnorm(sum + residual) * w, residual (in/out) updated; residual_in may be null,
+//         in which case residual_out receives the plain sum.
+// mode 1: y = sum (all-reduce only).
+__global__ void __launch_bounds__(kTpThreads)
+tp_reduce_norm_kernel(const TpComm c, long long buf_offset, const __nv_bfloat16* __restrict__ residual_in,
+                      __nv_bfloat16* __restrict__ residual_out, const __nv_bfloat16* __restrict__ w,
+                      __nv_bfloat16* __restrict__ y, int rows, int hidden, float eps, int mode) {
+  __shared__ float scratch[32];
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(c.epoch);
+  const bool ok = tp_barrier(c, epoch, 0);
+  const int nvec = hidden >> 3;
+  if (ok) {
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+      const long long off = buf_offset + static_cast<long long>(row) * hidden * 2;
+      float vals[kTpMaxVec][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < kTpMaxVec; ++i) {
+        const int v = threadIdx.x + i * kTpThreads;
+        if (v < nvec) {
+          float acc[8];
+          if (c.mc_buf != nullptr) {
+            unpack8(multimem_ld_reduce_bf16x8(static_cast<const char*>(c.mc_buf) + off + v * 16), acc);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            // fixed rank order, fp32 accumulation: every rank computes bit-identical sums
+            for (int r = 0; r < c.world; ++r) {
+              float t[8];
+              unpack8(ld_relaxed_sys_v4(static_cast<const char*>(c.peer_buf[r]) + off + v * 16), t);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[j] += t[j];
+            }
+          }
+          if (mode == 0) {
+            if (residual_in != nullptr) {
+              float rr[8];
+              unpack8(*reinterpret_cast<const uint4*>(residual_in + static_cast<size_t>(row) * hidden + v * 8), rr);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[j] += rr[j];
+            }
+            *reinterpret_cast<uint4*>(residual_out + static_cast<size_t>(row) * hidden + v * 8) = pack8(acc);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              acc[j] = __bfloat162float(__float2bfloat16(acc[j]));
+              ss += acc[j] * acc[j];
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) vals[i][j] = acc[j];
+        }
+      }
+      float inv = 1.f;
+      if (mode == 0) {
+        ss = warp_sum(ss);
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        if (lane == 0) scratch[warp] = ss;
+        __syncthreads();
+        float t = lane < (kTpThreads >> 5) ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        __syncthreads();
+        inv = rsqrtf(t / static_cast<float>(hidden) + eps);
+      }
+#pragma unroll
+      for (int i = 0; i < kTpMaxVec; ++i) {
+        const int v = threadIdx.x + i * kTpThreads;
+        if (v < nvec) {
+          float o[8];
+          if (mode == 0) {
+            float g[8];
+            unpack8(*reinterpret_cast<const uint4*>(w + v * 8), g);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * inv * g[j];
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = vals[i][j];
+          }
+          *reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * hidden + v * 8) = pack8(o);
+        }
+      }
+    }
+  }
+  tp_finish(c);
+}
+
+struct ArgSlot {
+  float v;
+  int i;
+};
+
+// One CTA per row. slots: symmetric [world][rows] ArgSlot array; each rank writes its local
+// best into slot [rank][row] of every peer, then all ranks pick the same winner.
+__global__ void __launch_bounds__(1024)
+tp_argmax_kernel(const TpComm c, long long slots_offset, const __nv_bfloat16* __restrict__ logits, long long ld,
+                 int local_vocab, int valid_vocab, int vocab_start, long long* __restrict__ out, int rows) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int row = blockIdx.x;
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(c.epoch);
+  const __nv_bfloat16* lr = logits + static_cast<size_t>(row) * ld;
+  float bv = -CUDART_INF_F;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < valid_vocab && i < local_vocab; i += blockDim.x) {
+    const float x = __bfloat162float(lr[i]);
+    if (x > bv || (x == bv && i < bi)) { bv = x; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    bv = lane < (blockDim.x >> 5) ? sv[lane] : -CUDART_INF_F;
+    bi = lane < (blockDim.x >> 5) ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane < c.world) {
+      // push (value, global id) into slot [my rank][row] on peer `lane`
+      ArgSlot* dst = reinterpret_cast<ArgSlot*>(const_cast<char*>(static_cast<const char*>(c.peer_buf[lane])) +
+                                                slots_offset) + static_cast<size_t>(c.rank) * rows + row;
+      ArgSlot s;
+      s.v = bv;
+      s.i = bi == 0x7fffffff ? -1 : bi + vocab_start;
+      asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(s.v)), "r"(s.i)
+                   : "memory");
+      __threadfence_system();
+    }
+  }
+  __syncthreads();
+  // per-row flags would need rows x world words; one barrier per kernel is enough because the
+  // flag is raised by block 0 only after a grid-wide ticket says every row has been pushed
+  __shared__ int last;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    last = atomicAdd(c.epoch + 2, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (last && threadIdx.x < c.world) {
+    c.epoch[2] = 0;
+    st_release_sys(c.peer_flags[threadIdx.x] + 1 * kMaxRanks + c.rank, epoch);
+  }
+  // wait for every rank's pushes
+  __shared__ int ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    const uint32_t* f = c.peer_flags[c.rank] + 1 * kMaxRanks + threadIdx.x;
+    bool seen = false;
+    for (unsigned i = 0; i < c.spin_limit; ++i) {
+      if (static_cast<int32_t>(ld_acquire_sys(f) - epoch) >= 0) { seen = true; break; }
+      __nanosleep(20);
+    }
+    if (!seen) { report_status(c.status, kTpKernelId, kPeerFlagTimeout); ok_flag = 0; }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    long long pick = 0;
+    if (ok_flag) {
+      const ArgSlot* mine = reinterpret_cast<const ArgSlot*>(static_cast<const char*>(c.peer_buf[c.rank]) + slots_offset);
+      float best = -CUDART_INF_F;
+      int id = 0x7fffffff;
+      for (int r = 0; r < c.world; ++r) {
+        const volatile uint32_t* raw = reinterpret_cast<const volatile uint32_t*>(mine + static_cast<size_t>(r) * rows + row);
+        const float v = __uint_as_float(raw[0]);
+        const int i = static_cast<int>(raw[1]);
+        if (i >= 0 && (v > best || (v == best && i < id))) { best = v; id = i; }
+      }
+      pick = id == 0x7fffffff ? 0 : id;
+    }
+    out[row] = pick;
+  }
+  tp_finish(c);
+}
+
+}  // namespace xv
+
+using namespace xv;
+
+static int fill_comm(TpComm* c, const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf,
+                     void* epoch, int rank, int world, unsigned spin_limit, int* status) {
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return XV_ERR_SHAPE;
+  for (int r = 0; r < kMaxRanks; ++r) {
+    c->peer_buf[r] = r < world ? peer_bufs[r] : nullptr;
+    c->peer_flags[r] = r < world ? static_cast<uint32_t*>(peer_flags[r]) : nullptr;
+  }
+  c->mc_buf = mc_buf;
+  c->epoch = static_cast<uint32_t*>(epoch);
+  c->rank = rank;
+  c->world = world;
+  c->spin_limit = spin_limit;
+  c->status = status;
+  return 0;
+}
+
+extern "C" {
+
+// peer_bufs / peer_flags: HOST arrays of `world` device pointers (as mapped on this rank).
+// epoch: 4 uint32 words of local device memory, zero-initialised except epoch[0] = 1.
+int xv_tp_reduce_norm(const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf, void* epoch,
+                      int rank, int world, long long buf_offset, const void* residual_in, void* residual_out,
+                      const void* w, void* y, int rows, int hidden, float eps, int mode, unsigned spin_limit,
+                      int* status, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (hidden % 8 || hidden > kTpThreads * kTpMaxVec * 8 || (buf_offset & 15)) return XV_ERR_SHAPE;
+  TpComm c;
+  int rc = fill_comm(&c, peer_bufs, peer_flags, mc_buf, epoch, rank, world, spin_limit, status);
+  if (rc) return rc;
+  int grid = rows < 148 * 4 ? rows : 148 * 4;
+  tp_reduce_norm_kernel<<<grid, kTpThreads, 0, stream>>>(
+      c, buf_offset, static_cast<const __nv_bfloat16*>(residual_in), static_cast<__nv_bfloat16*>(residual_out),
+      static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), rows, hidden, eps, mode);
+  return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
+}
+
+int xv_tp_argmax(const void* const* peer_bufs, void* const* peer_flags, void* epoch, int rank, int world,
+                 long long slots_offset, const void* logits, long long ld, int local_vocab, int valid_vocab,
+                 int vocab_start, long long* out, int rows, unsigned spin_limit, int* status, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  TpComm c;
+  int rc = fill_comm(&c, peer_bufs, peer_flags, nullptr, epoch, rank, world, spin_limit, status);
+  if (rc) return rc;
+  tp_argmax_kernel<<<rows, 1024, 0, stream>>>(c, slots_offset, static_cast<const __nv_bfloat16*>(logits), ld,
+                                              local_vocab, valid_vocab, vocab_start, out, rows);
+  return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
+}
+
+}  // extern "C"

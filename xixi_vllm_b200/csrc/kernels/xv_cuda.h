@@ -68,6 +68,15 @@ int xv_argmax(const void* logits, long long* out, int rows, int vocab, long long
 int xv_sample(const void* logits, long long* out, int rows, int vocab, long long ld, const float* temperature,
               const int* top_k, const float* top_p, const float* min_p, const int* rng, cudaStream_t stream);
 
+// ---- tensor-parallel fused reductions over peer memory (see tp_fused.cu) ----
+int xv_tp_reduce_norm(const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf, void* epoch,
+                      int rank, int world, long long buf_offset, const void* residual_in, void* residual_out,
+                      const void* w, void* y, int rows, int hidden, float eps, int mode, unsigned spin_limit,
+                      int* status, cudaStream_t stream);
+int xv_tp_argmax(const void* const* peer_bufs, void* const* peer_flags, void* epoch, int rank, int world,
+                 long long slots_offset, const void* logits, long long ld, int local_vocab, int valid_vocab,
+                 int vocab_start, long long* out, int rows, unsigned spin_limit, int* status, cudaStream_t stream);
+
 // ---- diagnostics ----
 // Waits (bounded) on a flag nobody sets and reports kHostFlagTimeout through `status`;
 // proves the timeout path returns instead of hanging. `limit` polls.

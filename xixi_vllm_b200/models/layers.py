@@ -181,8 +181,8 @@ class RowParallelLinear(_Linear):
     def load_bias(self, src, name: str, shard_id=None) -> None:
         self.bias.copy_(src.read(name))
 
-    def forward(self, x: torch.Tensor, reduce: bool = True) -> torch.Tensor:
-        y = ops.linear(x, self.weight, None)
+    def forward(self, x: torch.Tensor, reduce: bool = True, out: torch.Tensor | None = None) -> torch.Tensor:
+        y = ops.linear(x, self.weight, None, out if not reduce else None)
         if not reduce:
             return y
         y = coll.all_reduce(y, self.tp)
@@ -224,8 +224,8 @@ class VocabParallelEmbedding(_VocabShard):
     def __init__(self, num_embeddings: int, embedding_dim: int, *, dtype=torch.bfloat16, device="cpu"):
         super().__init__(num_embeddings, embedding_dim, dtype, device)
 
-    def forward(self, ids: torch.Tensor, reduce: bool = True) -> torch.Tensor:
-        y = ops.embedding(ids, self.weight, self.vocab_start)
+    def forward(self, ids: torch.Tensor, reduce: bool = True, out: torch.Tensor | None = None) -> torch.Tensor:
+        y = ops.embedding(ids, self.weight, self.vocab_start, out if not reduce else None)
         if reduce and self.tp.size > 1:
             y = coll.all_reduce(y, self.tp)
         return y

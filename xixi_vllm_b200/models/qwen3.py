@@ -27,9 +27,9 @@ class Qwen3MLP:
                                                        dtype=dtype, device=device)
         self.down_proj = RowParallelLinear(cfg.intermediate_size, cfg.hidden_size, dtype=dtype, device=device)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """Returns this rank's partial sum of the MLP output."""
-        return self.down_proj(ops.silu_mul(self.gate_up_proj(x)), reduce=False)
+        return self.down_proj(ops.silu_mul(self.gate_up_proj(x)), reduce=False, out=out)
 
 
 class Qwen3Attention:
@@ -48,14 +48,15 @@ class Qwen3Attention:
         self.num_kv_heads = self.qkv_proj.num_kv_heads
         self.scale = cfg.head_dim ** -0.5
 
-    def forward(self, x: torch.Tensor, batch, k_cache: torch.Tensor, v_cache: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, batch, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                out: torch.Tensor | None = None) -> torch.Tensor:
         qkv = self.qkv_proj(x)
         q = ops.qk_norm_rope_cache(qkv, self.q_norm.weight, self.k_norm.weight, self.q_norm.eps,
                                    self.rotary.cos_sin, batch.positions, batch.slots, k_cache, v_cache,
                                    self.num_heads, self.num_kv_heads, self.head_dim)
         o = ops.paged_attention(q, k_cache, v_cache, batch.attn, self.scale, self.num_heads,
                                 self.num_kv_heads, self.head_dim)
-        return self.o_proj(o, reduce=False)
+        return self.o_proj(o, reduce=False, out=out)
 
 
 class Qwen3DecoderLayer:
@@ -66,14 +67,16 @@ class Qwen3DecoderLayer:
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
 
-    def forward(self, partial, residual, batch, k_cache, v_cache, comm: TPComm):
-        """``partial`` is the previous block's unreduced output (or the embedding partial)."""
+    def forward(self, partial, residual, batch, k_cache, v_cache, comm: TPComm, last: bool = False):
+        """``partial`` is the previous block's unreduced output (or the embedding partial).
+        ``last`` marks the layer whose MLP output feeds the forward's final reduction."""
+        T = partial.shape[0]
         ln = self.input_layernorm
         h, residual = comm.reduce_add_rmsnorm(partial, residual, ln.weight, ln.eps)
-        attn_partial = self.self_attn.forward(h, batch, k_cache, v_cache)
+        attn_partial = self.self_attn.forward(h, batch, k_cache, v_cache, out=comm.alloc_partial(T))
         ln = self.post_attention_layernorm
         h, residual = comm.reduce_add_rmsnorm(attn_partial, residual, ln.weight, ln.eps)
-        return self.mlp.forward(h), residual
+        return self.mlp.forward(h, out=comm.alloc_partial(T, final=last)), residual
 
 
 class Qwen3Model:
@@ -89,14 +92,18 @@ class Qwen3Model:
 
     def forward(self, input_ids, batch, kv, comm: TPComm, intermediate: IntermediateTensors | None = None):
         """Returns final-normed hidden states on the last stage, else ``IntermediateTensors``."""
+        comm.begin_forward()
         if self.is_first:
-            partial, residual = self.embed_tokens(input_ids, reduce=False), None
+            out = comm.alloc_partial(input_ids.shape[0], final=not self.layers)
+            partial, residual = self.embed_tokens(input_ids, reduce=False, out=out), None
         else:
             # the previous stage sends its last partial already reduced
             partial, residual = intermediate["hidden_states"], intermediate["residual"]
             comm = _NoReduceOnce(comm)
+        n = len(self.layers)
         for i, layer in enumerate(self.layers):
-            partial, residual = layer.forward(partial, residual, batch, kv.k_cache(i), kv.v_cache(i), comm)
+            partial, residual = layer.forward(partial, residual, batch, kv.k_cache(i), kv.v_cache(i), comm,
+                                              last=i == n - 1)
         if not self.is_last:
             return IntermediateTensors(hidden_states=comm.all_reduce(partial), residual=residual)
         h, _ = comm.reduce_add_rmsnorm(partial, residual, self.norm.weight, self.norm.eps)
@@ -111,6 +118,12 @@ class _NoReduceOnce(TPComm):
 
     def all_reduce(self, x):
         return self.inner.all_reduce(x)
+
+    def begin_forward(self):
+        self.inner.begin_forward()
+
+    def alloc_partial(self, tokens, final=False):
+        return self.inner.alloc_partial(tokens, final)
 
     def reduce_add_rmsnorm(self, partial, residual, w, eps):
         if self._first:
@@ -148,6 +161,11 @@ class Qwen3ForCausalLM:
         return self.lm_head(hidden)
 
     def greedy_tokens(self, hidden: torch.Tensor) -> torch.Tensor:
+        fused = getattr(self.comm, "argmax", None)
+        if fused is not None:
+            head = self.lm_head
+            valid = max(0, min(head.per_rank, head.num_embeddings - head.vocab_start))
+            return fused(head.local_logits(hidden), valid, head.vocab_start)
         return self.lm_head.argmax(hidden)
 
     # --- weights ---------------------------------------------------------------------------

@@ -66,6 +66,10 @@ def lib():
                                   _i32, _f32, _vp]
     L.xv_argmax.argtypes = [_vp, _vp, _i32, _i32, _i64, _vp]
     L.xv_sample.argtypes = [_vp, _vp, _i32, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp]
+    L.xv_tp_reduce_norm.argtypes = [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _vp, _vp, _vp, _vp, _i32, _i32, _f32,
+                                    _i32, ctypes.c_uint, _vp, _vp]
+    L.xv_tp_argmax.argtypes = [_vp, _vp, _vp, _i32, _i32, _i64, _vp, _i64, _i32, _i32, _i32, _vp, _i32,
+                               ctypes.c_uint, _vp, _vp]
     L.xv_selftest_bounded_wait.argtypes = [_vp, _vp, ctypes.c_uint, _vp]
     L.xv_num_sms.restype = _i32
     _lib = L
@@ -136,22 +140,25 @@ def gemm_plan(m: int, n: int, k: int, num_sms: int = 148) -> GemmPlan:
 _USE_CUBLAS = os.environ.get("XV_GEMM", "") == "cublas"
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
-    """``x[M,K] @ w[N,K]^T`` on the tcgen05 GEMM."""
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+           out: torch.Tensor | None = None) -> torch.Tensor:
+    """``x[M,K] @ w[N,K]^T`` on the tcgen05 GEMM; ``out`` (dense [M,N]) receives the result if given."""
     _bf16(x, w)
     if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
         raise ValueError(f"linear: bad shapes {tuple(x.shape)} x {tuple(w.shape)}")
     M, K = x.shape
     N = w.shape[0]
     if M == 0:
-        return x.new_empty((0, N))
+        return x.new_empty((0, N)) if out is None else out
+    if out is not None and (out.shape != (M, N) or not out.is_contiguous() or out.dtype != torch.bfloat16):
+        raise ValueError("linear: out must be a contiguous bf16 [M, N] tensor")
     if _USE_CUBLAS:
-        y = torch.matmul(x, w.t())
+        y = torch.matmul(x, w.t(), out=out) if out is not None else torch.matmul(x, w.t())
     else:
         if x.stride(1) != 1 or w.stride(1) != 1:
             x, w = x.contiguous(), w.contiguous()
         st = _state(x)
-        y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        y = out if out is not None else torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
         rc = lib().xv_gemm_bf16(x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K, x.stride(0), w.stride(0), N,
                                 st.gemm_ws.data_ptr(), st.gemm_ws.numel(), st.num_sms, st.status.data_ptr(),
                                 _stream())
@@ -191,11 +198,11 @@ def silu_mul(x):
     return y
 
 
-def embedding(ids, w, vocab_start=0):
+def embedding(ids, w, vocab_start=0, out=None):
     _bf16(w)
     if ids.dtype != torch.int32:
         ids = ids.to(torch.int32)
-    y = torch.empty((ids.numel(), w.shape[1]), dtype=w.dtype, device=w.device)
+    y = out if out is not None else torch.empty((ids.numel(), w.shape[1]), dtype=w.dtype, device=w.device)
     _check(lib().xv_embedding(ids.data_ptr(), w.data_ptr(), y.data_ptr(), ids.numel(), w.shape[1], vocab_start,
                               w.shape[0], _stream()), "embedding")
     return y
@@ -279,6 +286,30 @@ def sample(logits, temperature, top_k, top_p, min_p, rng):
                            temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(), min_p.data_ptr(),
                            rng.data_ptr(), _stream()), "sample")
     return out
+
+
+def tp_reduce_norm(peer_bufs, peer_flags, mc_ptr: int, epoch, rank: int, world: int, buf_offset: int,
+                   residual_in, residual_out, w, y, rows: int, hidden: int, eps: float, mode: int,
+                   spin_limit: int, status) -> None:
+    """Sum the ranks' partial tiles (+ residual, RMSNorm when ``mode == 0``); see tp_fused.cu."""
+    _check(lib().xv_tp_reduce_norm(peer_bufs, peer_flags, mc_ptr or None, epoch.data_ptr(), rank, world, buf_offset,
+                                   residual_in.data_ptr() if residual_in is not None else None,
+                                   residual_out.data_ptr() if residual_out is not None else None,
+                                   w.data_ptr() if w is not None else None, y.data_ptr(), rows, hidden, eps, mode,
+                                   spin_limit, status.data_ptr(), _stream()), "tp_reduce_norm")
+
+
+def tp_argmax(peer_bufs, peer_flags, epoch, rank: int, world: int, slots_offset: int, logits, local_vocab: int,
+              valid_vocab: int, vocab_start: int, out, spin_limit: int, status) -> None:
+    _bf16(logits)
+    _check(lib().xv_tp_argmax(peer_bufs, peer_flags, epoch.data_ptr(), rank, world, slots_offset, logits.data_ptr(),
+                              logits.stride(0), local_vocab, valid_vocab, vocab_start, out.data_ptr(),
+                              logits.shape[0], spin_limit, status.data_ptr(), _stream()), "tp_argmax")
+
+
+def device_status(t: torch.Tensor) -> torch.Tensor:
+    """The per-device status word kernels report problems through."""
+    return _state(t).status
 
 
 def selftest_bounded_wait(limit: int = 1000) -> int:

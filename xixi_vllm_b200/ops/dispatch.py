@@ -31,16 +31,28 @@ def add_rmsnorm(x, residual, w, eps):
     return _cuda().add_rmsnorm(x, residual, w, eps) if x.is_cuda else cpu_ref.add_rmsnorm(x, residual, w, eps)
 
 
-def linear(x, w, bias=None):
-    return _cuda().linear(x, w, bias) if x.is_cuda else cpu_ref.linear(x, w, bias)
+def linear(x, w, bias=None, out=None):
+    if x.is_cuda:
+        return _cuda().linear(x, w, bias, out)
+    y = cpu_ref.linear(x, w, bias)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
 
 
 def silu_mul(x):
     return _cuda().silu_mul(x) if x.is_cuda else cpu_ref.silu_mul(x)
 
 
-def embedding(ids, w, vocab_start=0):
-    return _cuda().embedding(ids, w, vocab_start) if w.is_cuda else cpu_ref.embedding(ids, w, vocab_start)
+def embedding(ids, w, vocab_start=0, out=None):
+    if w.is_cuda:
+        return _cuda().embedding(ids, w, vocab_start, out)
+    y = cpu_ref.embedding(ids, w, vocab_start)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
 
 
 def qk_norm_rope_cache(qkv, q_w, k_w, eps, cos_sin, positions, slots, k_cache, v_cache,

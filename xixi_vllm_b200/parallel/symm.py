@@ -1,0 +1,133 @@
+"""Symmetric peer-memory buffers and the fused tensor-parallel reduction path.
+
+Each rank allocates the same buffer through PyTorch's symmetric-memory allocator (CUDA VMM
+allocations whose handles are exchanged over the process group), which yields every peer's
+mapping of the buffer and, on NVSwitch systems, a multicast address. The hand-written
+kernels in ``csrc/kernels/tp_fused.cu`` read peers' partial results straight from those
+mappings (or let the switch add them with ``multimem.ld_reduce``) and finish with the
+residual add and RMSNorm, so the decoder issues no NCCL call and no separate add+norm kernel.
+The reference does an NCCL all-reduce followed by a FlashInfer fused add+norm kernel at
+each of these points (reference: src/compute/layers/linear.py:141-154).
+
+Buffer rotation: a forward's reductions use buffers A, B, A, B, ... and the last one uses C,
+so no buffer is written for two consecutive reductions, also across forwards and across
+CUDA-graph replays (see the reuse rule in tp_fused.cu).
+
+Environment: ``XV_TP_NVLS=0`` disables the multicast path (plain peer loads are used).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..ops import cuda
+from .groups import Group
+from .tp_comm import TPComm
+
+__all__ = ["SymmetricBuffer", "FusedTPComm"]
+
+FLAG_BYTES = 4096          # two channels x 8 ranks x 4 bytes used; one page reserved
+SPIN_LIMIT = 1 << 23       # polls of ~100 ns each: gives up after roughly a second
+
+
+class SymmetricBuffer:
+    """A byte buffer that exists on every rank of ``group`` and is mapped on all of them."""
+
+    def __init__(self, nbytes: int, group: Group, device: torch.device) -> None:
+        import torch.distributed._symmetric_memory as symm
+
+        self.group, self.device, self.nbytes = group, device, nbytes
+        self.local = symm.empty(nbytes, dtype=torch.uint8, device=device)
+        self.local.zero_()
+        torch.cuda.synchronize(device)
+        self.handle = symm.rendezvous(self.local, group.device_group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.rank, self.world = int(self.handle.rank), int(self.handle.world_size)
+        use_mc = os.environ.get("XV_TP_NVLS", "1") != "0"
+        self.multicast_ptr = int(self.handle.multicast_ptr) if (use_mc and self.handle.has_multicast_support) else 0
+        dist.barrier(group=group.cpu_group)      # every rank has zeroed and mapped before first use
+
+    def ptr_array(self, offset: int = 0):
+        return (ctypes.c_void_p * self.world)(*[p + offset for p in self.ptrs])
+
+
+class FusedTPComm(TPComm):
+    def __init__(self, group: Group, device, hidden_size: int, max_tokens: int, dtype) -> None:
+        if dtype != torch.bfloat16:
+            raise TypeError("the fused tensor-parallel path runs bfloat16")
+        self.group = group
+        self.device = torch.device(device)
+        self.hidden = hidden_size
+        self.max_tokens = max_tokens
+        self.buf_bytes = -(-max_tokens * hidden_size * 2 // 4096) * 4096
+        self.slot_bytes = -(-group.size * max_tokens * 8 // 4096) * 4096
+        total = 3 * self.buf_bytes + self.slot_bytes + FLAG_BYTES
+        self.symm = SymmetricBuffer(total, group, self.device)
+        self.rank, self.world = self.symm.rank, self.symm.world
+        self.flags_off = 3 * self.buf_bytes + self.slot_bytes
+        self.slots_off = 3 * self.buf_bytes
+        self._bufs = self.symm.ptr_array(0)
+        self._flags = self.symm.ptr_array(self.flags_off)
+        self.mc_ptr = self.symm.multicast_ptr
+        self.epoch = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.epoch[0] = 1
+        self.status = cuda.device_status(self.epoch)
+        self._idx = 0
+        self._base = self.symm.local.data_ptr()
+        self._views = [self.symm.local[i * self.buf_bytes:(i + 1) * self.buf_bytes].view(torch.bfloat16)
+                       for i in range(3)]
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group.cpu_group)
+
+    # --- buffer rotation ------------------------------------------------------------------
+    def begin_forward(self) -> None:
+        self._idx = 0
+
+    def alloc_partial(self, tokens: int, final: bool = False) -> torch.Tensor:
+        if tokens > self.max_tokens:
+            raise RuntimeError(f"{tokens} tokens exceed the symmetric buffer ({self.max_tokens})")
+        which = 2 if final else self._idx % 2
+        self._idx += 1
+        return self._views[which][: tokens * self.hidden].view(tokens, self.hidden)
+
+    def _offset_of(self, partial: torch.Tensor) -> int:
+        off = partial.data_ptr() - self._base
+        if 0 <= off < 3 * self.buf_bytes and partial.is_contiguous():
+            return off
+        # produced elsewhere: stage it through the next buffer
+        buf = self.alloc_partial(partial.shape[0])
+        buf.copy_(partial)
+        return buf.data_ptr() - self._base
+
+    # --- reductions -----------------------------------------------------------------------------
+    def reduce_add_rmsnorm(self, partial, residual, w, eps):
+        T = partial.shape[0]
+        off = self._offset_of(partial)
+        y = torch.empty((T, self.hidden), dtype=torch.bfloat16, device=self.device)
+        res_out = residual if residual is not None else torch.empty_like(y)
+        cuda.tp_reduce_norm(self._bufs, self._flags, self.mc_ptr, self.epoch, self.rank, self.world, off,
+                            residual, res_out, w, y, T, self.hidden, eps, 0, SPIN_LIMIT, self.status)
+        return y, res_out
+
+    def all_reduce(self, x):
+        T = x.shape[0]
+        off = self._offset_of(x)
+        y = torch.empty((T, self.hidden), dtype=torch.bfloat16, device=self.device)
+        cuda.tp_reduce_norm(self._bufs, self._flags, self.mc_ptr, self.epoch, self.rank, self.world, off,
+                            None, None, None, y, T, self.hidden, 0.0, 1, SPIN_LIMIT, self.status)
+        return y
+
+    def argmax(self, local_logits: torch.Tensor, valid_vocab: int, vocab_start: int) -> torch.Tensor:
+        rows = local_logits.shape[0]
+        out = torch.empty(rows, dtype=torch.int64, device=self.device)
+        cuda.tp_argmax(self._bufs, self._flags, self.epoch, self.rank, self.world, self.slots_off, local_logits,
+                       local_logits.shape[1], valid_vocab, vocab_start, out, SPIN_LIMIT, self.status)
+        return out
+
+    def destroy(self) -> None:
+        self._views = []
+        self.symm = None

@@ -25,6 +25,14 @@ class TPComm:
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
+    def begin_forward(self) -> None:
+        """Called once at the start of every model forward."""
+
+    def alloc_partial(self, tokens: int, final: bool = False) -> torch.Tensor | None:
+        """Where the producer of the next partial should write (None = allocate normally).
+        ``final`` marks the last reduction of a forward."""
+        return None
+
     def reduce_add_rmsnorm(self, partial: torch.Tensor, residual: torch.Tensor | None,
                            w: torch.Tensor, eps: float):
         """Sum ``partial`` over the TP group, add it to ``residual`` (or start the residual

@@ -60,6 +60,8 @@ def parse_args():
     ap.add_argument("--out-tokens", type=int, default=512)
     ap.add_argument("--eager", action="store_true", help="disable decode CUDA graphs")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--tp-comm", default="auto", choices=("auto", "fused", "nccl"),
+                    help="tensor-parallel reduction path (fused peer-memory kernels or NCCL)")
     ap.add_argument("--profile", action="store_true",
                     help="bracket the timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     return ap.parse_args()
@@ -178,7 +180,7 @@ def run_ours(args) -> None:
     cfg_kwargs = dict(model=model_dir, load_format="dummy", dtype="bfloat16", context_len=context,
                       max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_batched_tokens,
                       kvcache_block_size=16, prefix_backend="none", enforce_eager=args.eager,
-                      tp_size=args.gpus, seed=args.seed, gpu_memory_utilization=0.9)
+                      tp_size=args.gpus, seed=args.seed, gpu_memory_utilization=0.9, tp_comm=args.tp_comm)
     # rank 0 writes config.json before the others read it
     if world > 1:
         import torch.distributed as dist  # noqa: F401
@@ -250,7 +252,7 @@ def run_ours(args) -> None:
         "config": {"model": args.model, "global_batch": args.max_num_seqs, "seq_len": context,
                    "parallelism": f"tp{args.gpus}", "prompt_len": f"U[{args.prompt_min},{args.prompt_max}]",
                    "output_len": args.out_tokens, "max_num_batched_tokens": args.max_batched_tokens,
-                   "kv_block_size": 16, "decode_cuda_graph": not args.eager,
+                   "kv_block_size": 16, "decode_cuda_graph": not args.eager, "tp_comm": args.tp_comm,
                    "l2": "flushed between timed steps (256 MiB write)",
                    "step": "one engine step in steady-state continuous batching"},
         "clocks": clk,

@@ -48,6 +48,12 @@ class ModelRunner:
         self._copy_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
         self._sample_event = torch.cuda.Event() if self.is_cuda else None
         self._host_samples = torch.zeros(self.max_bs, dtype=torch.int64, pin_memory=self.is_cuda)
+        self._host_status = torch.zeros(1, dtype=torch.int32, pin_memory=self.is_cuda)
+        self._dev_status = None
+        if self.is_cuda:
+            from ..ops import cuda as _cuda
+
+            self._dev_status = _cuda.device_status(self._host_samples.to(self.device))
         self._dev_samples: torch.Tensor | None = None
         self._n_samples = 0
         self._last: tuple[int, int, list[bool]] = (0, 0, [])
@@ -130,12 +136,19 @@ class ModelRunner:
         self._copy_stream.wait_stream(cur)
         with torch.cuda.stream(self._copy_stream):
             self._host_samples[:n].copy_(tokens[:n], non_blocking=True)
+            self._host_status.copy_(self._dev_status, non_blocking=True)
             self._sample_event.record(self._copy_stream)
 
     def read_samples(self, n_p: int, n_d: int) -> tuple[list[int], list[int]]:
         """Blocks until this step's ids are on the host. Prefill entries that did not sample are -1."""
         if self.is_cuda:
             self._sample_event.synchronize()
+            code = int(self._host_status[0])
+            if code:
+                self._dev_status.zero_()
+                raise RuntimeError(
+                    f"GPU kernel {code >> 16} reported status {code & 0xFFFF} (1-3: pipeline wait ran out, "
+                    "4: a tensor-parallel peer did not arrive in time, 5: index out of range)")
         flat = self._host_samples[: self._n_samples].tolist()
         _, _, sampled = self._last
         d_ids = flat[:n_d]

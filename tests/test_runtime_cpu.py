@@ -1,0 +1,124 @@
+"""Batch staging, sampler oracle, graph buckets, CLI plumbing (CPU)."""
+import sys
+from unittest import mock
+
+import numpy as np
+import pytest
+import torch
+
+from xixi_vllm_b200.data.wire import SchedulerOutput, SeqSchedule
+from xixi_vllm_b200.ops import cpu_ref
+from xixi_vllm_b200.runtime.graphs import make_bs_list
+from xixi_vllm_b200.runtime.staging import BatchStager
+
+
+def test_stager_packs_decodes_then_prefills_and_tracks_table_tails():
+    st = BatchStager(max_seqs=8, max_tokens=128, max_blocks=8, block_size=16, device="cpu")
+    pre = SeqSchedule(seq_id=1, num_cached_tokens=0, token_ids=list(range(100, 120)), bt_from=0, bt_tail=[3, 5],
+                      need_sample=True, temperature=0.7, top_k=5)
+    b = st.build(SchedulerOutput(prefills=[pre]))
+    assert b.num_tokens == 20 and b.n_prefill == 1 and not b.all_greedy
+    assert b.positions.tolist() == list(range(20))
+    assert b.slots.tolist() == [3 * 16 + i for i in range(16)] + [5 * 16 + i for i in range(4)]
+    assert b.attn.cu_q.tolist() == [0, 20] and b.attn.kv_lens.tolist() == [20]
+    assert b.sample_rows.tolist() == [19] and b.top_k.tolist() == [5]
+    # next step: decode of seq 1 (no new pages on the wire) + chunk of a new seq 2 with a cached prefix
+    dec = SeqSchedule(seq_id=1, num_cached_tokens=20, token_ids=[7], bt_from=2, bt_tail=[])
+    pre2 = SeqSchedule(seq_id=2, num_cached_tokens=16, token_ids=[1, 2, 3], bt_from=0, bt_tail=[6, 2],
+                       need_sample=False)
+    b = st.build(SchedulerOutput(decodes=[dec], prefills=[pre2]))
+    assert b.input_ids.tolist() == [7, 1, 2, 3] and b.positions.tolist() == [20, 16, 17, 18]
+    assert b.slots.tolist() == [5 * 16 + 4, 2 * 16, 2 * 16 + 1, 2 * 16 + 2]
+    assert b.attn.num_decode == 1 and b.attn.kv_lens.tolist() == [21, 19] and b.attn.cu_q.tolist() == [0, 1, 4]
+    assert b.attn.block_tables[0, :2].tolist() == [3, 5] and b.attn.block_tables[1, :2].tolist() == [6, 2]
+    assert b.sample_rows.tolist() == [0] and b.prefill_sampled == [False] and b.all_greedy
+    # page growth arrives as a tail; release drops the row
+    dec = SeqSchedule(seq_id=1, num_cached_tokens=32, token_ids=[9], bt_from=2, bt_tail=[4])
+    b = st.build(SchedulerOutput(decodes=[dec], released=[2]))
+    assert b.slots.tolist() == [4 * 16] and 2 not in st.row_of
+    # padding to a graph bucket adds inert rows
+    b = st.build(SchedulerOutput(decodes=[SeqSchedule(seq_id=1, num_cached_tokens=33, token_ids=[9], bt_from=3)]),
+                 pad_to=4, fixed_blocks=True)
+    assert b.num_tokens == 4 and b.slots.tolist()[1:] == [-1, -1, -1] and b.attn.kv_lens.tolist() == [34, 0, 0, 0]
+    assert b.attn.block_tables.shape == (4, 8) and b.num_samples == 4
+
+
+def test_stager_python_and_native_fill_agree():
+    rng = np.random.default_rng(0)
+    outs = []
+    for use_native in (True, False):
+        st = BatchStager(max_seqs=16, max_tokens=64, max_blocks=16, block_size=16, device="cpu")
+        if not use_native:
+            st._lib = None
+        rng = np.random.default_rng(0)
+        entries = []
+        for i in range(10):
+            cached = int(rng.integers(0, 200))
+            nb = cached // 16 + 1
+            entries.append(SeqSchedule(seq_id=i + 1, num_cached_tokens=cached, token_ids=[int(rng.integers(1000))],
+                                       bt_from=0, bt_tail=rng.integers(0, 99, size=nb).tolist()))
+        b = st.build(SchedulerOutput(decodes=entries))
+        outs.append((b.positions.tolist(), b.slots.tolist(), b.attn.kv_lens.tolist(), b.attn.block_tables.tolist()))
+    assert outs[0] == outs[1]
+
+
+def test_filtered_probs_rules():
+    logits = torch.tensor([[4.0, 3.0, 2.0, 1.0, 0.0]])
+    one = torch.tensor([1.0])
+    p = cpu_ref.filtered_probs(logits, one, torch.tensor([2]), one, torch.tensor([0.0]))[0]
+    assert (p > 0).tolist() == [True, True, False, False, False] and abs(float(p.sum()) - 1) < 1e-6
+    full = torch.softmax(logits[0], -1)
+    p = cpu_ref.filtered_probs(logits, one, torch.tensor([0]), torch.tensor([0.7]), torch.tensor([0.0]))[0]
+    # 0.64 of the mass precedes token 1 (<= 0.7, kept), 0.87 precedes token 2 (dropped)
+    assert (p > 0).tolist() == [True, True, False, False, False]
+    p = cpu_ref.filtered_probs(logits, one, torch.tensor([0]), one, torch.tensor([0.2]))[0]
+    assert (p > 0).tolist() == (full >= 0.2 * full[0]).tolist()
+    g = torch.Generator().manual_seed(0)
+    ids = cpu_ref.sample(logits.expand(2000, 5), torch.ones(2000), torch.full((2000,), 2), torch.ones(2000),
+                         torch.zeros(2000), g)
+    assert set(ids.tolist()) == {0, 1}
+    assert cpu_ref.sample(logits, torch.tensor([0.0]), torch.tensor([0]), one, torch.tensor([0.0])).tolist() == [0]
+
+
+def test_graph_buckets():
+    assert make_bs_list(1) == [1]
+    assert make_bs_list(8) == [1, 2, 4, 8]
+    bl = make_bs_list(256)
+    assert bl[:5] == [1, 2, 4, 8, 16] and bl[-1] == 256 and 128 in bl and 160 in bl and 144 not in bl
+    assert make_bs_list(100)[-1] == 100
+
+
+def test_cli_precedence_and_cleanup(tmp_path):
+    """YAML overrides defaults, flags override YAML; destroy() runs exactly once on every exit path
+    (mirrors the reference's test/test_entrypoint_cleanup.py with a mocked engine)."""
+    root = __import__("os").path.dirname(__import__("os").path.dirname(__import__("os").path.abspath(__file__)))
+    sys.path.insert(0, root)
+    import run
+    y = tmp_path / "c.yaml"
+    y.write_text("max_new_tokens: 7\ntp_size: 2\nprefix_backend: radix\nunknown_key: 1\n")
+    args = run.build_parser().parse_args(["--config", str(y), "--tp", "4", "--cg", "--prefix-backend", "none",
+                                          "--device-ids", "3,2,1,0", "--pp-layer-counts", "12,28"])
+    cfg = run.config_from_args(args)
+    assert cfg["max_new_tokens"] == 7 and cfg["tp_size"] == 4 and cfg["prefix_backend"] == "none"
+    assert cfg["enforce_eager"] is False and cfg["device_ids"] == [3, 2, 1, 0] and cfg["pp_layer_counts"] == [12, 28]
+    assert "unknown_key" not in cfg and cfg["kvcache_block_size"] == 16
+
+    for fail_at in (None, "warmup", "generate"):
+        engine = mock.Mock()
+        engine.tokenizer.encode.return_value = [1, 2, 3]
+        engine.tokenizer.decode.return_value = "x"
+        seq = mock.Mock(is_finished=True, num_completion_tokens=1, token_ids=[1, 2, 3, 4], num_prompt_tokens=3)
+        engine.add_request.return_value = seq
+        if fail_at == "generate":
+            engine.add_request.side_effect = RuntimeError("boom")
+        warm = mock.Mock(return_value=0.0, side_effect=RuntimeError("warm") if fail_at == "warmup" else None)
+        with mock.patch.object(run, "_make_engine", return_value=engine), mock.patch.object(run, "_warmup", warm), \
+                mock.patch.object(run, "cuda_sync"):
+            for fn in (run.run_single, run.run_batch):
+                engine.destroy.reset_mock()
+                if fail_at:
+                    with pytest.raises(RuntimeError):
+                        fn(dict(cfg, prompt="hi", temperature=0.0, top_p=None, top_k=None))
+                else:
+                    fn(dict(cfg, prompt="hi", temperature=0.0, top_p=None, top_k=None))
+                assert engine.destroy.call_count == 1

@@ -458,3 +458,61 @@ int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, lon
 }
 
 }  // extern "C"
+
+// ---- allocation-free entry point ------------------------------------------------------------------
+// Split-K scratch for xv_gemm_bf16_noalloc lives in the library image itself. Every GPU that
+// loads this library carries these bytes until the process exits.
+#define XV_NOALLOC_SCRATCH_BYTES (16ll << 20)
+static __device__ __align__(256) unsigned char g_noalloc_scratch[XV_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_scratch_ptr[kMaxDevices] = {nullptr};
+int g_scratch_sms[kMaxDevices] = {0};
+std::mutex g_scratch_mu;
+
+// Resolves the device address of g_noalloc_scratch for the current device (once per device).
+// In host code the symbol's name is only a handle; the address kernels may use comes from
+// cudaGetSymbolAddress.
+int noalloc_setup(int* dev_out, void** ptr_out, int* sms_out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return XV_ERR_DRIVER;
+  std::lock_guard<std::mutex> g(g_scratch_mu);
+  if (g_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return XV_ERR_DRIVER;
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return XV_ERR_DRIVER;
+    g_scratch_ptr[dev] = p;
+    g_scratch_sms[dev] = sms;
+  }
+  *dev_out = dev;
+  *ptr_out = g_scratch_ptr[dev];
+  *sms_out = g_scratch_sms[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" {
+
+long long xv_gemm_noalloc_max_scratch_bytes(void) { return XV_NOALLOC_SCRATCH_BYTES; }
+
+int xv_gemm_bf16_noalloc(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
+                         long long ldy, int* status, cudaStream_t stream) {
+  int dev = 0, sms = 0;
+  void* scratch = nullptr;
+  int rc = noalloc_setup(&dev, &scratch, &sms);
+  if (rc) return rc;
+  XvGemmPlan pl;
+  if ((rc = xv_gemm_plan(m, n, k, sms, &pl))) return rc;
+  if (pl.workspace_bytes > XV_NOALLOC_SCRATCH_BYTES) {
+    std::fprintf(stderr,
+                 "xv_gemm_bf16_noalloc: %d x %d x %d needs %lld bytes of split-K scratch, the built-in buffer "
+                 "holds %lld; use xv_gemm_bf16 with a caller-provided workspace\n",
+                 m, n, k, pl.workspace_bytes, static_cast<long long>(XV_NOALLOC_SCRATCH_BYTES));
+    return XV_ERR_WORKSPACE;
+  }
+  return xv_gemm_bf16(x, w, y, m, n, k, ldx, ldw, ldy, scratch, XV_NOALLOC_SCRATCH_BYTES, sms, status, stream);
+}
+
+}  // extern "C"

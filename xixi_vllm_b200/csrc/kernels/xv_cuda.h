@@ -34,6 +34,27 @@ int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, lon
                  long long ldy, void* workspace, long long workspace_bytes, int num_sms, int* status,
                  cudaStream_t stream);
 
+// Same GEMM for callers that must not allocate GPU memory. This entry point has no counterpart
+// in the reference project. Who needs it: code that runs where a device allocation is not
+// allowed or would stall the GPU, for example a plug-in invoked from another runtime's execution
+// callback, a latency-critical serving loop whose memory pool is frozen after start-up, or a
+// host that only hands this library pre-existing buffers. xv_gemm_bf16 needs a caller-allocated
+// split-K workspace for small-M problems; this variant keeps that scratch in a fixed buffer
+// inside the library image instead (xv_gemm_noalloc_max_scratch_bytes() bytes, 16 MiB, resident
+// on every GPU that loads the library until the process exits). It calls no cudaMalloc,
+// cudaFree or allocating library routine; inputs and the output are still the caller's.
+//   * Problems whose split-K partials exceed the built-in buffer are rejected with
+//     XV_ERR_WORKSPACE and a message on stderr; nothing is launched.
+//   * The first call on each device looks up the buffer's device address; make that first
+//     call on a device before starting any stream capture on it.
+//   * All calls on a device share the one buffer, which keeps the previous call's bytes.
+//     Nothing in it has to start at zero: every element the reduction reads is rewritten by
+//     the same call first. Two calls that overlap on the GPU (different streams, or graphs
+//     replayed concurrently) race on it; serialise them.
+long long xv_gemm_noalloc_max_scratch_bytes(void);
+int xv_gemm_bf16_noalloc(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
+                         long long ldy, int* status, cudaStream_t stream);
+
 // ---- elementwise / normalisation ----
 int xv_rmsnorm(const void* x, const void* w, void* y, int rows, int hidden, float eps, cudaStream_t stream);
 // residual += x (in place), y = rmsnorm(residual) * w

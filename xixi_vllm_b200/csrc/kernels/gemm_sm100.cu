@@ -47,6 +47,8 @@ struct GemmParams {
   int bn;            // MMA N = rows of B per CTA (multiple of 16, <= 256)
   int stages;
   int k_blocks_per_split;
+  int tiles_a, tiles_b, splits;
+  int a_fastest;     // work order: 1 = consecutive work items walk the A tiles, 0 = the B tiles
   int transposed;    // 1: out[(b_row) * ldc + a_row], 0: out[a_row * ldc + b_row]
   int out_fp32;      // 1: fp32 partials at out + split * split_stride, 0: bf16
   long long ldc;
@@ -54,9 +56,32 @@ struct GemmParams {
   void* out;
   int* status;
   uint32_t idesc;
-  uint32_t tmem_cols;
+  uint32_t tmem_cols;       // total allocation (two accumulators)
+  uint32_t acc_stride;      // column offset of the second accumulator
 };
 
+struct WorkItem {
+  int tile_a, tile_b, split;
+};
+
+__device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int w) {
+  WorkItem it;
+  const int tiles = p.tiles_a * p.tiles_b;
+  it.split = w / tiles;
+  const int r = w - it.split * tiles;
+  if (p.a_fastest) {
+    it.tile_b = r / p.tiles_a;
+    it.tile_a = r - it.tile_b * p.tiles_a;
+  } else {
+    it.tile_a = r / p.tiles_b;
+    it.tile_b = r - it.tile_a * p.tiles_b;
+  }
+  return it;
+}
+
+// Persistent kernel: every CTA walks work items (output tile x K split) with stride gridDim.x.
+// The shared-memory stage ring and its phases run on across work items, and the accumulator
+// is double buffered in TMEM, so the epilogue of one tile overlaps the main loop of the next.
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p) {
@@ -69,28 +94,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t stage_bytes = a_bytes + b_bytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(p.stages) * stage_bytes);
   uint64_t* empty_bar = full_bar + kMaxStages;
-  uint64_t* accum_bar = empty_bar + kMaxStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  uint64_t* acc_full = empty_bar + kMaxStages;     // [2] accumulator ready for the epilogue
+  uint64_t* acc_empty = acc_full + 2;              // [2] accumulator drained, MMA may overwrite
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int tile_a = blockIdx.x;   // along rows of A
-  const int tile_b = blockIdx.y;   // along rows of B
-  const int split = blockIdx.z;
-
+  const int total_work = p.tiles_a * p.tiles_b * p.splits;
   const int total_kb = (p.k + kBK - 1) / kBK;
-  const int kb_begin = split * p.k_blocks_per_split;
-  int kb_end = kb_begin + p.k_blocks_per_split;
-  if (kb_end > total_kb) kb_end = total_kb;
-  const int num_kb = kb_end > kb_begin ? kb_end - kb_begin : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(accum_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);      // one arrival per epilogue warp
+    }
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -108,127 +130,150 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0) {
       prefetch_tensormap(&map_a);
       prefetch_tensormap(&map_b);
-      // Operand A is the streamed weight matrix in the swapped orientation and the re-read
-      // activation matrix otherwise; hints follow that.
+      // In the swapped orientation operand A is the weight matrix, streamed once; B (the
+      // activations) is re-read by every CTA. Hints follow that.
       const uint64_t hint_a = p.transposed ? l2_policy_evict_first() : l2_policy_evict_normal();
       const uint64_t hint_b = p.transposed ? l2_policy_evict_last() : l2_policy_evict_normal();
-      for (int i = 0; i < num_kb; ++i) {
-        const int s = i % p.stages;
-        const uint32_t round = static_cast<uint32_t>(i / p.stages);
-        if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
-          report_status(p.status, kGemmKernelId, kWaitEmptyTimeout);
-          *abort_flag = 1;
-          break;
+      uint32_t it = 0;                   // K blocks issued so far by this CTA, across work items
+      for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
+        const WorkItem wi = decode_work(p, w);
+        const int kb_begin = wi.split * p.k_blocks_per_split;
+        const int kb_end = min(kb_begin + p.k_blocks_per_split, total_kb);
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+          const uint32_t s = it % p.stages;
+          const uint32_t round = it / p.stages;
+          if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
+            report_status(p.status, kGemmKernelId, kWaitEmptyTimeout);
+            *abort_flag = 1;
+            break;
+          }
+          uint8_t* sa = smem + static_cast<size_t>(s) * stage_bytes;
+          mbar_expect_tx(&full_bar[s], stage_bytes);
+          tma_load_2d(sa, &map_a, &full_bar[s], kb * kBK, wi.tile_a * kBM, hint_a);
+          tma_load_2d(sa + a_bytes, &map_b, &full_bar[s], kb * kBK, wi.tile_b * p.bn, hint_b);
         }
-        if (*abort_flag) break;
-        uint8_t* sa = smem + static_cast<size_t>(s) * stage_bytes;
-        uint8_t* sb = sa + a_bytes;
-        mbar_expect_tx(&full_bar[s], stage_bytes);
-        const int kx = (kb_begin + i) * kBK;
-        tma_load_2d(sa, &map_a, &full_bar[s], kx, tile_a * kBM, hint_a);
-        tma_load_2d(sb, &map_b, &full_bar[s], kx, tile_b * p.bn, hint_b);
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      for (int i = 0; i < num_kb; ++i) {
-        const int s = i % p.stages;
-        const uint32_t round = static_cast<uint32_t>(i / p.stages);
-        if (!mbar_wait(&full_bar[s], round & 1)) {
-          report_status(p.status, kGemmKernelId, kWaitFullTimeout);
+      uint32_t it = 0, t = 0;
+      for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x, ++t) {
+        const WorkItem wi = decode_work(p, w);
+        const int kb_begin = wi.split * p.k_blocks_per_split;
+        const int kb_end = min(kb_begin + p.k_blocks_per_split, total_kb);
+        const uint32_t buf = t & 1, use = t >> 1;
+        if (use > 0 && !mbar_wait(&acc_empty[buf], (use - 1) & 1)) {
+          report_status(p.status, kGemmKernelId, kWaitAccumTimeout);
           *abort_flag = 1;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t sa = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
-        const uint32_t sb = sa + a_bytes;
+        const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+          const uint32_t s = it % p.stages;
+          const uint32_t round = it / p.stages;
+          if (!mbar_wait(&full_bar[s], round & 1)) {
+            report_status(p.status, kGemmKernelId, kWaitFullTimeout);
+            *abort_flag = 1;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
+          const uint32_t sb = sa + a_bytes;
 #pragma unroll
-        for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
-          const uint64_t da = umma_desc_sw128(sa + kk * kUmmaK * 2);
-          const uint64_t db = umma_desc_sw128(sb + kk * kUmmaK * 2);
-          umma_bf16(tmem_base, da, db, p.idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+            const uint64_t da = umma_desc_sw128(sa + kk * kUmmaK * 2);
+            const uint64_t db = umma_desc_sw128(sb + kk * kUmmaK * 2);
+            umma_bf16(d_tmem, da, db, p.idesc, (kb > kb_begin || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);   // stage is free once these MMAs have read it
         }
-        umma_commit(&empty_bar[s]);   // stage is free once these MMAs have read it
+        umma_commit(&acc_full[buf]);     // accumulator complete
       }
-      umma_commit(accum_bar);          // accumulator complete (or nothing was issued)
     }
   } else {
     // ---------------- epilogue ----------------
     const int quarter = warp & 3;                       // TMEM lane quarter this warp may read
-    const int a_row = tile_a * kBM + quarter * 32 + lane;
-    bool ok = mbar_wait(accum_bar, 0);
-    if (!ok) {
-      report_status(p.status, kGemmKernelId, kWaitAccumTimeout);
-    }
-    tc_fence_after_sync();
-    // warp-uniform: the aligned TMEM loads below must be executed by all 32 lanes or none
-    ok = __all_sync(0xffffffffu, ok && (*abort_flag == 0) && num_kb > 0);
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const int b0 = tile_b * p.bn;
-    for (int c = 0; c < p.bn; c += 16) {
-      uint32_t r[16];
-      if (ok) {
+    uint32_t t = 0;
+    for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++t) {
+      const WorkItem wi = decode_work(p, w);
+      const uint32_t buf = t & 1, use = t >> 1;
+      bool ok = mbar_wait(&acc_full[buf], use & 1);
+      if (!ok) {
+        report_status(p.status, kGemmKernelId, kWaitAccumTimeout);
+        *abort_flag = 1;
+      }
+      tc_fence_after_sync();
+      // warp-uniform: the aligned TMEM loads below must be executed by all 32 lanes or none
+      ok = __all_sync(0xffffffffu, ok && (*abort_flag == 0));
+      if (!ok) break;
+      const int a_row = wi.tile_a * kBM + quarter * 32 + lane;
+      const uint32_t lane_addr = tmem_base + buf * p.acc_stride + (static_cast<uint32_t>(quarter * 32) << 16);
+      const int b0 = wi.tile_b * p.bn;
+      for (int c = 0; c < p.bn; c += 16) {
+        uint32_t r[16];
         tmem_ld16(lane_addr + static_cast<uint32_t>(c), r);
         tmem_ld_wait();
-      } else {
+        if (p.transposed) {
+          // lanes hold consecutive output columns (a_row); tokens run along the registers
+          if (a_row < p.rows_a) {
+            if (p.out_fp32) {
+              float* o = static_cast<float*>(p.out) + static_cast<size_t>(wi.split) * p.split_stride;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) r[j] = 0u;
-      }
-      if (p.transposed) {
-        // lanes hold consecutive output columns (a_row); tokens run along the registers
-        if (a_row < p.rows_a) {
+              for (int j = 0; j < 16; ++j) {
+                const int b_row = b0 + c + j;
+                if (b_row < p.rows_b) o[static_cast<size_t>(b_row) * p.ldc + a_row] = __uint_as_float(r[j]);
+              }
+            } else {
+              __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int b_row = b0 + c + j;
+                if (b_row < p.rows_b)
+                  o[static_cast<size_t>(b_row) * p.ldc + a_row] = __float2bfloat16(__uint_as_float(r[j]));
+              }
+            }
+          }
+        } else if (a_row < p.rows_a) {
+          const int col = b0 + c;
           if (p.out_fp32) {
-            float* o = static_cast<float*>(p.out) + static_cast<size_t>(split) * p.split_stride;
+            float* o = static_cast<float*>(p.out) + static_cast<size_t>(wi.split) * p.split_stride +
+                       static_cast<size_t>(a_row) * p.ldc + col;
+            if (col + 16 <= p.rows_b && (p.ldc & 3) == 0) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int b_row = b0 + c + j;
-              if (b_row < p.rows_b) o[static_cast<size_t>(b_row) * p.ldc + a_row] = __uint_as_float(r[j]);
+              for (int j = 0; j < 16; j += 4)
+                *reinterpret_cast<float4*>(o + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            } else {
+              for (int j = 0; j < 16; ++j)
+                if (col + j < p.rows_b) o[j] = __uint_as_float(r[j]);
             }
           } else {
-            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int b_row = b0 + c + j;
-              if (b_row < p.rows_b)
-                o[static_cast<size_t>(b_row) * p.ldc + a_row] = __float2bfloat16(__uint_as_float(r[j]));
+            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(a_row) * p.ldc + col;
+            if (col + 16 <= p.rows_b && (p.ldc & 7) == 0) {
+              uint4 v0, v1;
+              v0.x = pack_bf16(__uint_as_float(r[0]), __uint_as_float(r[1]));
+              v0.y = pack_bf16(__uint_as_float(r[2]), __uint_as_float(r[3]));
+              v0.z = pack_bf16(__uint_as_float(r[4]), __uint_as_float(r[5]));
+              v0.w = pack_bf16(__uint_as_float(r[6]), __uint_as_float(r[7]));
+              v1.x = pack_bf16(__uint_as_float(r[8]), __uint_as_float(r[9]));
+              v1.y = pack_bf16(__uint_as_float(r[10]), __uint_as_float(r[11]));
+              v1.z = pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13]));
+              v1.w = pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15]));
+              *reinterpret_cast<uint4*>(o) = v0;
+              *reinterpret_cast<uint4*>(o + 8) = v1;
+            } else {
+              for (int j = 0; j < 16; ++j)
+                if (col + j < p.rows_b) o[j] = __float2bfloat16(__uint_as_float(r[j]));
             }
-          }
-        }
-      } else if (a_row < p.rows_a) {
-        const int col = b0 + c;
-        if (p.out_fp32) {
-          float* o = static_cast<float*>(p.out) + static_cast<size_t>(split) * p.split_stride +
-                     static_cast<size_t>(a_row) * p.ldc + col;
-          if (col + 16 <= p.rows_b && (p.ldc & 3) == 0) {
-#pragma unroll
-            for (int j = 0; j < 16; j += 4)
-              *reinterpret_cast<float4*>(o + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                              __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-          } else {
-            for (int j = 0; j < 16; ++j)
-              if (col + j < p.rows_b) o[j] = __uint_as_float(r[j]);
-          }
-        } else {
-          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(a_row) * p.ldc + col;
-          if (col + 16 <= p.rows_b && (p.ldc & 7) == 0) {
-            uint4 v0, v1;
-            v0.x = pack_bf16(__uint_as_float(r[0]), __uint_as_float(r[1]));
-            v0.y = pack_bf16(__uint_as_float(r[2]), __uint_as_float(r[3]));
-            v0.z = pack_bf16(__uint_as_float(r[4]), __uint_as_float(r[5]));
-            v0.w = pack_bf16(__uint_as_float(r[6]), __uint_as_float(r[7]));
-            v1.x = pack_bf16(__uint_as_float(r[8]), __uint_as_float(r[9]));
-            v1.y = pack_bf16(__uint_as_float(r[10]), __uint_as_float(r[11]));
-            v1.z = pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13]));
-            v1.w = pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15]));
-            *reinterpret_cast<uint4*>(o) = v0;
-            *reinterpret_cast<uint4*>(o + 8) = v1;
-          } else {
-            for (int j = 0; j < 16; ++j)
-              if (col + j < p.rows_b) o[j] = __float2bfloat16(__uint_as_float(r[j]));
           }
         }
       }
+      // this warp has drained its quarter of the accumulator
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
   }
 
@@ -356,9 +401,11 @@ int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan) {
   const int total_kb = (k + kBK - 1) / kBK;
   if (m <= 256) {
     pl.swapped = 1;
-    pl.bn = round_up(m, 16);
+    // above 128 tokens the batch is cut into two token tiles: twice as many (half-size) work
+    // items balance better over 148 SMs and halve the per-stage activation bytes
+    pl.tiles_b = m > 128 ? 2 : 1;
+    pl.bn = round_up((m + pl.tiles_b - 1) / pl.tiles_b, 16);
     pl.tiles_a = (n + kBM - 1) / kBM;
-    pl.tiles_b = 1;
   } else {
     pl.swapped = 0;
     pl.bn = n >= 256 ? 256 : round_up(n, 16);
@@ -366,24 +413,34 @@ int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan) {
     pl.tiles_b = (n + pl.bn - 1) / pl.bn;
   }
   const int tiles = pl.tiles_a * pl.tiles_b;
-  int splits = 1;
-  if (tiles < num_sms) {
-    splits = num_sms / tiles;
-    // keep at least 4 K blocks (256 elements) per split so the pipeline has work
-    while (splits > 1 && total_kb / splits < 4) --splits;
-    if (splits > 16) splits = 16;
-  }
-  pl.k_blocks_per_split = (total_kb + splits - 1) / splits;
-  pl.splits = (total_kb + pl.k_blocks_per_split - 1) / pl.k_blocks_per_split;
   const int stage_bytes = kBM * kBK * 2 + pl.bn * kBK * 2;
   // small-token tiles leave room for two resident CTAs per SM (more loads in flight while
   // another CTA drains its epilogue); big tiles take the whole SM
-  const int smem_budget = (pl.swapped && pl.bn <= 64) ? 100 * 1024 : 200 * 1024;
+  const int smem_budget = (pl.swapped && pl.bn <= 128) ? 100 * 1024 : 200 * 1024;
   int stages = smem_budget / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
-  if (stages > pl.k_blocks_per_split) stages = pl.k_blocks_per_split < 2 ? 2 : pl.k_blocks_per_split;
+  if (stages < 2) stages = 2;
+  const int smem_bytes = stages * stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  pl.ctas_per_sm = (smem_bytes <= 110 * 1024 && 2 * pow2_cols(pl.bn) <= 256) ? 2 : 1;
+  // Split K when the output tiles alone cannot occupy the machine. Bounds: at least 4 K blocks
+  // per split, at most 16 splits, and fp32 partials (written and read back once) no larger
+  // than about a quarter of the weight bytes.
+  const int slots = num_sms * pl.ctas_per_sm;
+  int splits = 1;
+  if (tiles < num_sms) {
+    splits = slots / tiles;
+    const int by_traffic = k / (8 * m) > 1 ? k / (8 * m) : 1;
+    if (splits > by_traffic) splits = by_traffic;
+    if (splits < num_sms / tiles) splits = num_sms / tiles < by_traffic ? num_sms / tiles : splits;
+    while (splits > 1 && total_kb / splits < 4) --splits;
+    if (splits > 16) splits = 16;
+    if (splits < 1) splits = 1;
+  }
+  pl.k_blocks_per_split = (total_kb + splits - 1) / splits;
+  pl.splits = (total_kb + pl.k_blocks_per_split - 1) / pl.k_blocks_per_split;
+  if (stages > pl.k_blocks_per_split && pl.k_blocks_per_split >= 2) stages = pl.k_blocks_per_split;
   pl.stages = stages;
-  pl.smem_bytes = stages * stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  pl.smem_bytes = stages * stage_bytes + 1024 + 256;
   pl.workspace_bytes = pl.splits > 1 ? static_cast<long long>(pl.splits) * m * n * 4 : 0;
   *plan = pl;
   return 0;
@@ -423,7 +480,12 @@ int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, lon
   p.k_blocks_per_split = pl.k_blocks_per_split;
   p.status = status;
   p.idesc = umma_idesc_bf16(kBM, pl.bn);
-  p.tmem_cols = pow2_cols(pl.bn);
+  p.acc_stride = pow2_cols(pl.bn);
+  p.tmem_cols = 2 * p.acc_stride;
+  p.tiles_a = pl.tiles_a;
+  p.tiles_b = pl.tiles_b;
+  p.splits = pl.splits;
+  p.a_fastest = pl.swapped ? 0 : 1;
   if (pl.splits > 1) {
     p.out = workspace;
     p.out_fp32 = 1;
@@ -442,7 +504,9 @@ int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, lon
     if (e != cudaSuccess) return XV_ERR_LAUNCH;
     attr_set = true;
   }
-  dim3 grid(pl.tiles_a, pl.tiles_b, pl.splits);
+  const int total_work = pl.tiles_a * pl.tiles_b * pl.splits;
+  const int slots = (num_sms > 0 ? num_sms : 148) * pl.ctas_per_sm;
+  const int grid = total_work < slots ? total_work : slots;
   gemm_tcgen05_kernel<<<grid, kGemmThreads, pl.smem_bytes, stream>>>(map_a, map_b, p);
   if (cudaGetLastError() != cudaSuccess) return XV_ERR_LAUNCH;
   if (pl.splits > 1) {

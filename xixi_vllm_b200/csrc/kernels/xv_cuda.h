@@ -26,6 +26,7 @@ typedef struct XvGemmPlan {
   int k_blocks_per_split;
   int stages;
   int smem_bytes;
+  int ctas_per_sm;         // resident CTAs per SM the persistent grid is sized for
   long long workspace_bytes;
 } XvGemmPlan;
 

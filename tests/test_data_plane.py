@@ -48,12 +48,12 @@ def test_wire_sends_block_table_tail_only():
     assert (w.prefills[0].bt_from, w.prefills[0].bt_tail) == (0, [5, 6, 7])
     s.num_cached_tokens = 40
     s.append_token(1)
-    w = ScheduledBatch(decodes=[s]).to_wire()
-    assert (w.decodes[0].bt_from, w.decodes[0].bt_tail, w.decodes[0].token_ids) == (3, [], [1])
+    d = ScheduledBatch(decodes=[s]).to_wire().decodes          # nothing new: no table traffic at all
+    assert (d.seq_ids, d.tokens, d.cached, d.bt_index, d.bt_vals) == ([s.seq_id], [1], [40], [], [])
     s.bt_append(9)
     s.bt_replace(1, 11)           # an edit below the synced mark resends from there
-    w = ScheduledBatch(decodes=[s]).to_wire()
-    assert (w.decodes[0].bt_from, w.decodes[0].bt_tail) == (1, [11, 7, 9])
+    d = ScheduledBatch(decodes=[s]).to_wire().decodes
+    assert (d.bt_index, d.bt_from, d.bt_count, d.bt_vals) == ([0], [1], [3], [11, 7, 9])
 
 
 def test_block_manager_invariants_random_walk():

@@ -87,3 +87,36 @@ def test_bounded_wait_reports_instead_of_hanging():
     assert code >> 16 == 99 and code & 0xFFFF == 6
     # the context is still usable afterwards
     assert float(torch.ones(4, device=DEV).sum().item()) == 4.0
+
+
+def test_split_k_partials_feed_consumers_directly():
+    """A deferred split-K GEMM hands fp32 partial planes to add+RMSNorm and to QK-norm/RoPE."""
+    from xixi_vllm_b200.ops import cuda
+    g = torch.Generator().manual_seed(9)
+    x = (torch.randn(24, 2048, generator=g) * 0.3).bfloat16().to(DEV)
+    w = (torch.randn(1024, 2048, generator=g) * 0.05).bfloat16().to(DEV)
+    part = cuda.linear(x, w, defer=True)
+    assert isinstance(part, cuda.SplitKPartial) and part.splits > 1
+    dense = cuda.linear(x, w)
+    _close(part.materialize(), dense, atol=2e-2, rtol=2e-2)
+    res = torch.randn(24, 1024, generator=g).bfloat16().to(DEV)
+    nw = (1 + 0.1 * torch.randn(1024, generator=g)).bfloat16().to(DEV)
+    r1, r2 = res.clone(), res.clone()
+    part = cuda.linear(x, w, defer=True)
+    y1 = cuda.add_rmsnorm(part, r1, nw, 1e-6)
+    y2 = cuda.add_rmsnorm(dense, r2, nw, 1e-6)
+    _close(r1, r2, atol=3e-2, rtol=3e-2)
+    _close(y1, y2, atol=3e-2, rtol=3e-2)
+    # QKV: 4 q heads + 2 x 2 kv heads of 128 = 1024 columns
+    hq, hkv, d, T = 4, 2, 128, 24
+    cs = cpu_ref.build_cos_sin_cache(d, 256, 1e6).to(DEV)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    slots = torch.arange(T, dtype=torch.int32, device=DEV)
+    qw = torch.ones(d, dtype=torch.bfloat16, device=DEV)
+    caches = [torch.zeros(4, hkv, 16, d, dtype=torch.bfloat16, device=DEV) for _ in range(4)]
+    part = cuda.linear(x, w, defer=True)
+    qa = cuda.qk_norm_rope_cache(part, qw, qw, 1e-6, cs, pos, slots, caches[0], caches[1], hq, hkv, d)
+    qb = cuda.qk_norm_rope_cache(dense, qw, qw, 1e-6, cs, pos, slots, caches[2], caches[3], hq, hkv, d)
+    _close(qa, qb, atol=3e-2, rtol=3e-2)
+    _close(caches[0], caches[2], atol=3e-2, rtol=3e-2)
+    _close(caches[1], caches[3], atol=3e-2, rtol=3e-2)

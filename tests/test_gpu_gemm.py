@@ -52,3 +52,26 @@ def test_gemm_strided_input_rows():
     y = cuda.linear(x, w)
     ref = x.float() @ w.float().t()
     assert (y.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
+
+
+def _interleave(gate, up, g=8):
+    n, k = gate.shape
+    return torch.stack([gate.view(n // g, g, k), up.view(n // g, g, k)], 1).reshape(2 * n, k)
+
+
+@pytest.mark.parametrize("m,inter,k", [(5, 1536, 1024), (64, 3072, 4096), (256, 12288, 1024), (200, 512, 2048),
+                                       (1000, 1536, 1024), (4096, 3072, 512)])
+def test_gemm_with_fused_silu_mul(m, inter, k):
+    """Swapped, normal and split-K plans of the gate/up projection with the activation fused."""
+    from xixi_vllm_b200.ops import cuda
+    g = torch.Generator().manual_seed(m + inter)
+    x = (torch.randn(m, k, generator=g) * 0.5).bfloat16().to(DEV)
+    gate = (torch.randn(inter, k, generator=g) * 0.05).bfloat16().to(DEV)
+    up = (torch.randn(inter, k, generator=g) * 0.05).bfloat16().to(DEV)
+    y = cuda.linear_silu_mul(x, _interleave(gate, up).contiguous())
+    torch.cuda.synchronize()
+    cuda.check_status()
+    gf, uf = x.float() @ gate.float().t(), x.float() @ up.float().t()
+    ref = torch.nn.functional.silu(gf) * uf
+    assert y.shape == (m, inter)
+    assert (y.float() - ref).abs().max().item() <= 3e-2 * ref.abs().max().item() + 1e-2

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from xixi_vllm_b200.data.wire import SchedulerOutput, SeqSchedule
+from xixi_vllm_b200.data.wire import DecodeBatch, SchedulerOutput, SeqSchedule
 from xixi_vllm_b200.ops import cpu_ref
 from xixi_vllm_b200.runtime.graphs import make_bs_list
 from xixi_vllm_b200.runtime.staging import BatchStager
@@ -23,22 +23,21 @@ def test_stager_packs_decodes_then_prefills_and_tracks_table_tails():
     assert b.attn.cu_q.tolist() == [0, 20] and b.attn.kv_lens.tolist() == [20]
     assert b.sample_rows.tolist() == [19] and b.top_k.tolist() == [5]
     # next step: decode of seq 1 (no new pages on the wire) + chunk of a new seq 2 with a cached prefix
-    dec = SeqSchedule(seq_id=1, num_cached_tokens=20, token_ids=[7], bt_from=2, bt_tail=[])
+    dec = DecodeBatch.of([(1, 7, 20, 2, [])])
     pre2 = SeqSchedule(seq_id=2, num_cached_tokens=16, token_ids=[1, 2, 3], bt_from=0, bt_tail=[6, 2],
                        need_sample=False)
-    b = st.build(SchedulerOutput(decodes=[dec], prefills=[pre2]))
+    b = st.build(SchedulerOutput(decodes=dec, prefills=[pre2]))
     assert b.input_ids.tolist() == [7, 1, 2, 3] and b.positions.tolist() == [20, 16, 17, 18]
     assert b.slots.tolist() == [5 * 16 + 4, 2 * 16, 2 * 16 + 1, 2 * 16 + 2]
     assert b.attn.num_decode == 1 and b.attn.kv_lens.tolist() == [21, 19] and b.attn.cu_q.tolist() == [0, 1, 4]
     assert b.attn.block_tables[0, :2].tolist() == [3, 5] and b.attn.block_tables[1, :2].tolist() == [6, 2]
-    assert b.sample_rows.tolist() == [0] and b.prefill_sampled == [False] and b.all_greedy
+    assert b.sample_rows.tolist() == [0] and b.prefill_sampled == [False] and not b.all_greedy
+    assert abs(b.temperature.tolist()[0] - 0.7) < 1e-6 and b.top_k.tolist() == [5]    # remembered from the prefill
     # page growth arrives as a tail; release drops the row
-    dec = SeqSchedule(seq_id=1, num_cached_tokens=32, token_ids=[9], bt_from=2, bt_tail=[4])
-    b = st.build(SchedulerOutput(decodes=[dec], released=[2]))
+    b = st.build(SchedulerOutput(decodes=DecodeBatch.of([(1, 9, 32, 2, [4])]), released=[2]))
     assert b.slots.tolist() == [4 * 16] and 2 not in st.row_of
     # padding to a graph bucket adds inert rows
-    b = st.build(SchedulerOutput(decodes=[SeqSchedule(seq_id=1, num_cached_tokens=33, token_ids=[9], bt_from=3)]),
-                 pad_to=4, fixed_blocks=True)
+    b = st.build(SchedulerOutput(decodes=DecodeBatch.of([(1, 9, 33, 3, [])])), pad_to=4, fixed_blocks=True)
     assert b.num_tokens == 4 and b.slots.tolist()[1:] == [-1, -1, -1] and b.attn.kv_lens.tolist() == [34, 0, 0, 0]
     assert b.attn.block_tables.shape == (4, 8) and b.num_samples == 4
 
@@ -55,9 +54,8 @@ def test_stager_python_and_native_fill_agree():
         for i in range(10):
             cached = int(rng.integers(0, 200))
             nb = cached // 16 + 1
-            entries.append(SeqSchedule(seq_id=i + 1, num_cached_tokens=cached, token_ids=[int(rng.integers(1000))],
-                                       bt_from=0, bt_tail=rng.integers(0, 99, size=nb).tolist()))
-        b = st.build(SchedulerOutput(decodes=entries))
+            entries.append((i + 1, int(rng.integers(1000)), cached, 0, rng.integers(0, 99, size=nb).tolist()))
+        b = st.build(SchedulerOutput(decodes=DecodeBatch.of(entries)))
         outs.append((b.positions.tolist(), b.slots.tolist(), b.attn.kv_lens.tolist(), b.attn.block_tables.tolist()))
     assert outs[0] == outs[1]
 

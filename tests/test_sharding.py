@@ -123,7 +123,7 @@ def _ctrl_rank(rank, world):
     import msgspec
 
     from xixi_vllm_b200.control.executor import ControlCommand
-    from xixi_vllm_b200.data.wire import SchedulerOutput, SeqSchedule
+    from xixi_vllm_b200.data.wire import DecodeBatch, SchedulerOutput
     from xixi_vllm_b200.parallel.control_channel import ControlChannel
     from xixi_vllm_b200.parallel.groups import get_world_group
     ch = ControlChannel(get_world_group().cpu_group)
@@ -131,11 +131,10 @@ def _ctrl_rank(rank, world):
     got = []
     for i in range(3):
         cmd = ControlCommand(op="execute", sched=SchedulerOutput(
-            decodes=[SeqSchedule(seq_id=i, num_cached_tokens=5, token_ids=[9], bt_from=1, bt_tail=[4, 5])],
-            released=[i + 10], step_id=i))
+            decodes=DecodeBatch.of([(i, 9, 5, 1, [4, 5])]), released=[i + 10], step_id=i))
         raw = ch.broadcast(enc.encode(cmd) if rank == 0 else None, src=0)
         c = dec.decode(raw)
-        got.append((c.op, c.sched.decodes[0].bt_tail, c.sched.released, c.sched.step_id))
+        got.append((c.op, c.sched.decodes.bt_vals, c.sched.released, c.sched.step_id))
     if rank == 1:
         ch.send(enc.encode([[1, 2], [3]]), dst=0)
         back = None

@@ -47,7 +47,9 @@ class EngineCore:
 
     def reset_kv(self, prefix_backend: str | None = None) -> None:
         self.kv = self.executor.reset_kv(prefix_backend)
+        sampled = self.scheduler.num_sampled
         self.scheduler = self._build_scheduler()
+        self.scheduler.num_sampled = sampled
         self.last_num_cached_tokens = 0
 
     def add_request(self, seq: Sequence) -> None:
@@ -86,9 +88,19 @@ class EngineCore:
         t2 = time.perf_counter()
         outputs = self.scheduler.update(sched, p_ids, d_ids)
         t3 = time.perf_counter()
+        by_id = None
+
+        def lookup(seq_id):          # built only when a request finished this step
+            nonlocal by_id
+            if by_id is None:
+                by_id = {s.seq_id: s for s in sched.decodes}
+                by_id.update((s.seq_id, s) for s in sched.prefills)
+            return by_id.get(seq_id)
+
         self.metrics.on_step(
             sched, outputs, prefill_tokens, schedule_s=t1 - t0, execute_s=t2 - t1, update_s=t3 - t2,
             kv_usage=self.kv.usage(), preemptions=self.scheduler.num_preemptions, kv=self.kv, now=t3,
+            sampled_total=self.scheduler.num_sampled, finished_lookup=lookup,
         )
         return outputs, metric
 

@@ -37,6 +37,7 @@ class Scheduler:
         self._released: list[int] = []   # seq ids whose worker-side rows can be dropped
         self._step = 0
         self.num_preemptions = 0
+        self.num_sampled = 0
 
     def is_finished(self) -> bool:
         return not self.waiting and not self.running
@@ -71,6 +72,24 @@ class Scheduler:
 
     def _take_decodes(self, prefills, decodes, used: int) -> int:
         run = self.running
+        if not run:
+            return used
+        n = min(len(run), self.max_num_seqs - len(prefills) - len(decodes), self.max_num_batched_tokens - used)
+        if n <= 0:
+            return used
+        blocks = self.kv.blocks
+        if blocks.available_slots >= n:
+            # Enough pages even if every sequence opened one: nobody can be preempted, so the
+            # queue order is untouched and the per-sequence work is one modulo.
+            bs = self.kv.block_size
+            it = iter(run)
+            for _ in range(n):
+                seq = next(it)
+                seq.num_scheduled_tokens = 1
+                if len(seq.token_ids) % bs == 1 and len(seq.block_table) < seq.num_blocks:
+                    seq.block_table.append(blocks.allocate_fresh())
+                decodes.append(seq)
+            return used + n
         while run and self._has_room(prefills, decodes) and used < self.max_num_batched_tokens:
             seq = run.popleft()
             while not self.kv.can_append(seq) and run:
@@ -149,15 +168,15 @@ class Scheduler:
         done.add(seq.seq_id)
 
     def _apply(self, seqs, token_ids, is_prefill: bool, out, done: set[int]) -> None:
+        publish = self.kv.prefix_backend != "none"
+        eos = self.eos
         for seq, tok in zip(seqs, token_ids):
             seq.num_cached_tokens += seq.num_scheduled_tokens
-            self.kv.sync_prefix(seq)
+            if publish:
+                self.kv.sync_prefix(seq)
             seq.num_scheduled_tokens = 0
-            if is_prefill and seq.num_cached_tokens < seq.num_prompt_tokens:
-                out.append(EngineCoreOutput(seq_id=seq.seq_id))      # mid-prompt chunk
-                continue
-            if is_prefill and seq.num_cached_tokens < seq.num_tokens:
-                # recomputation of a preempted sequence, chunk not at the end yet
+            if is_prefill and seq.num_cached_tokens < len(seq.token_ids):
+                # mid-prompt chunk, or recomputation of a preempted sequence not at its end yet
                 out.append(EngineCoreOutput(seq_id=seq.seq_id))
                 continue
             if seq.max_tokens <= 0:
@@ -165,8 +184,11 @@ class Scheduler:
                 out.append(EngineCoreOutput(seq_id=seq.seq_id, is_finished=True))
                 continue
             tok = int(tok)
-            seq.append_token(tok)
-            if ((not seq.ignore_eos) and tok == self.eos) or seq.num_completion_tokens >= seq.max_tokens:
+            seq.token_ids.append(tok)
+            seq.last_token = tok
+            self.num_sampled += 1
+            if (tok == eos and not seq.ignore_eos) or len(seq.token_ids) - seq.num_prompt_tokens >= seq.max_tokens:
                 self._finish(seq, done)
-            out.append(EngineCoreOutput(seq_id=seq.seq_id, new_token_ids=[tok],
-                                        is_finished=seq.seq_id in done))
+                out.append(EngineCoreOutput(seq_id=seq.seq_id, new_token_ids=[tok], is_finished=True))
+            else:
+                out.append(EngineCoreOutput(seq_id=seq.seq_id, new_token_ids=[tok]))

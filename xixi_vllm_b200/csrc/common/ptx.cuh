@@ -73,16 +73,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Polls until the phase with the given parity completes, at most `limit` times. Each
-// try_wait may itself block for a hardware-defined short interval, so the default bound
-// is on the order of a second, far beyond any legitimate wait in these kernels.
-constexpr uint32_t kDefaultSpinLimit = 1u << 22;
+// Polls until the phase with the given parity completes, for at most `timeout_ns` of wall
+// time (measured with the global nanosecond timer, so the bound does not depend on how long
+// one try_wait suspends the thread). Legitimate waits in these kernels last microseconds.
+constexpr unsigned long long kDefaultWaitNs = 2000000000ull;   // 2 s
 
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = kDefaultSpinLimit) {
-  for (uint32_t i = 0; i < limit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
+                                          unsigned long long timeout_ns = kDefaultWaitNs) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > timeout_ns) return false;
   }
-  return false;
 }
 
 // ---- TMA (cp.async.bulk.tensor) ----------------------------------------------------------------

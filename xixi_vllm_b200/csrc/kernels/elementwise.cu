@@ -96,6 +96,52 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ 
   }
 }
 
+// residual += sum_s partial[s]; y = rmsnorm(residual) * w. One CTA per row.
+__global__ void __launch_bounds__(kNormThreads)
+add_rmsnorm_partials_kernel(const float* __restrict__ partials, int splits, long long split_stride,
+                            __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ w,
+                            __nv_bfloat16* __restrict__ y, int hidden, float eps) {
+  __shared__ float scratch[32];
+  const size_t row = blockIdx.x;
+  __nv_bfloat16* rr = residual + row * hidden;
+  __nv_bfloat16* yr = y + row * hidden;
+  const int nvec = hidden >> 3;
+  float vals[kNormMaxVec][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kNormMaxVec; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    if (v < nvec) {
+      load8(rr + v * 8, vals[i]);
+      const float* src = partials + row * hidden + v * 8;
+      for (int s = 0; s < splits; ++s) {
+        const float4 a = *reinterpret_cast<const float4*>(src + s * split_stride);
+        const float4 b = *reinterpret_cast<const float4*>(src + s * split_stride + 4);
+        vals[i][0] += a.x; vals[i][1] += a.y; vals[i][2] += a.z; vals[i][3] += a.w;
+        vals[i][4] += b.x; vals[i][5] += b.y; vals[i][6] += b.z; vals[i][7] += b.w;
+      }
+      store8(rr + v * 8, vals[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        vals[i][j] = __bfloat162float(__float2bfloat16(vals[i][j]));
+        ss += vals[i][j] * vals[i][j];
+      }
+    }
+  }
+  const float inv = rsqrtf(block_sum(ss, scratch) / static_cast<float>(hidden) + eps);
+#pragma unroll
+  for (int i = 0; i < kNormMaxVec; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    if (v < nvec) {
+      float g[8], o[8];
+      load8(w + v * 8, g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * inv * g[j];
+      store8(yr + v * 8, o);
+    }
+  }
+}
+
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long long rows,
                                 int inter) {
   const int vec_per_row = inter >> 3;
@@ -110,6 +156,39 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat
 #pragma unroll
     for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
     store8(y + r * inter + c, o);
+  }
+}
+
+// Columns come in groups of 16 = [8 gate | 8 up]; input is bf16 or a sum of fp32 split-K planes.
+__global__ void silu_mul_interleaved_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ partials,
+                                            int splits, long long split_stride, __nv_bfloat16* __restrict__ y,
+                                            long long rows, int inter) {
+  const int groups = inter >> 3;
+  const long long total = rows * groups;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / groups;
+    const int gidx = static_cast<int>(i - r * groups);
+    const long long in_off = r * 2 * inter + static_cast<long long>(gidx) * 16;
+    float g[8], u[8], o[8];
+    if (partials != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g[j] = u[j] = 0.f;
+      for (int s = 0; s < splits; ++s) {
+        const float* p = partials + s * split_stride + in_off;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          g[j] += p[j];
+          u[j] += p[8 + j];
+        }
+      }
+    } else {
+      load8(x + in_off, g);
+      load8(x + in_off + 8, u);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    store8(y + r * inter + static_cast<long long>(gidx) * 8, o);
   }
 }
 
@@ -142,7 +221,8 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const in
 // the generic loop). The NeoX rotation pairs element i with i + D/2, both held by one lane.
 template <int D>
 __global__ void __launch_bounds__(256)
-qk_norm_rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ q_w,
+qk_norm_rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ partials, int splits,
+                          long long split_stride, const __nv_bfloat16* __restrict__ q_w,
                           const __nv_bfloat16* __restrict__ k_w, float eps, const float* __restrict__ cos_sin,
                           const int* __restrict__ positions, const int* __restrict__ slots,
                           __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
@@ -160,7 +240,29 @@ qk_norm_rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bflo
   const int slot = slots[t];
 
   float lo[PER], hi[PER];
-  if (PER == 2) {
+  if (partials != nullptr) {
+    // QKV arrives as split-K partial planes: sum them here instead of in a separate kernel
+    const float* ps = partials + static_cast<size_t>(t) * heads * D + static_cast<size_t>(h) * D;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) lo[i] = hi[i] = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float* q = ps + s * split_stride;
+      if (PER == 2) {
+        const float2 a = *reinterpret_cast<const float2*>(q + lane * 2);
+        const float2 b = *reinterpret_cast<const float2*>(q + HALF + lane * 2);
+        lo[0] += a.x; lo[PER - 1] += a.y; hi[0] += b.x; hi[PER - 1] += b.y;
+      } else {
+        lo[0] += q[lane];
+        hi[0] += q[HALF + lane];
+      }
+    }
+    // same rounding point as the bf16 GEMM output would have had
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      lo[i] = __bfloat162float(__float2bfloat16(lo[i]));
+      hi[i] = __bfloat162float(__float2bfloat16(hi[i]));
+    }
+  } else if (PER == 2) {
     const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + lane * 2));
     const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + HALF + lane * 2));
     lo[0] = a.x; lo[PER - 1] = a.y; hi[0] = b.x; hi[PER - 1] = b.y;
@@ -222,11 +324,13 @@ qk_norm_rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bflo
 __global__ void bounded_wait_kernel(volatile int* flag, int* status, unsigned limit) {
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     bool seen = false;
-    for (unsigned i = 0; i < limit; ++i) {
+    const unsigned long long t0 = global_timer_ns();
+    for (;;) {
       if (*flag != 0) {
         seen = true;
         break;
       }
+      if (global_timer_ns() - t0 > static_cast<unsigned long long>(limit) * 1000ull) break;   // limit in us
       __nanosleep(100);
     }
     if (!seen) report_status(status, 99, kHostFlagTimeout);
@@ -272,6 +376,18 @@ int xv_silu_mul(const void* x, void* y, int rows, int inter, cudaStream_t stream
   return launch_ok();
 }
 
+int xv_silu_mul_interleaved(const void* x, const float* partials, int splits, long long split_stride, void* y,
+                            int rows, int inter, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (inter % 8) return XV_ERR_SHAPE;
+  const long long total = static_cast<long long>(rows) * (inter / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  silu_mul_interleaved_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), partials, splits, split_stride, static_cast<__nv_bfloat16*>(y), rows, inter);
+  return launch_ok();
+}
+
 int xv_embedding(const int* ids, const void* w, void* y, int tokens, int hidden, int vocab_start, int vocab_rows,
                  cudaStream_t stream) {
   if (tokens <= 0) return 0;
@@ -289,15 +405,17 @@ int xv_gather_rows(const void* x, const int* rows, void* y, int n, int hidden, c
   return launch_ok();
 }
 
-int xv_qk_norm_rope_cache(const void* qkv, const void* q_w, const void* k_w, float eps, const float* cos_sin,
-                          const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
-                          int tokens, int hq, int hkv, int d, int block_size, cudaStream_t stream) {
+static int qk_norm_rope_launch(const void* qkv, const float* partials, int splits, long long split_stride,
+                               const void* q_w, const void* k_w, float eps, const float* cos_sin,
+                               const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
+                               int tokens, int hq, int hkv, int d, int block_size, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const long long warps = static_cast<long long>(tokens) * (hq + 2 * hkv);
   const unsigned blocks = static_cast<unsigned>((warps + 7) / 8);
 #define XV_QKR(D)                                                                                         \
   qk_norm_rope_cache_kernel<D><<<blocks, 256, 0, stream>>>(                                                \
-      static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(q_w),                      \
+      static_cast<const __nv_bfloat16*>(qkv), partials, splits, split_stride,                              \
+      static_cast<const __nv_bfloat16*>(q_w),                                                              \
       static_cast<const __nv_bfloat16*>(k_w), eps, cos_sin, positions, slots,                              \
       static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),                            \
       static_cast<__nv_bfloat16*>(v_cache), tokens, hq, hkv, block_size)
@@ -309,6 +427,32 @@ int xv_qk_norm_rope_cache(const void* qkv, const void* q_w, const void* k_w, flo
     return XV_ERR_UNSUPPORTED;
   }
 #undef XV_QKR
+  return launch_ok();
+}
+
+int xv_qk_norm_rope_cache(const void* qkv, const void* q_w, const void* k_w, float eps, const float* cos_sin,
+                          const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
+                          int tokens, int hq, int hkv, int d, int block_size, cudaStream_t stream) {
+  return qk_norm_rope_launch(qkv, nullptr, 0, 0, q_w, k_w, eps, cos_sin, positions, slots, q_out, k_cache, v_cache,
+                             tokens, hq, hkv, d, block_size, stream);
+}
+
+int xv_qk_norm_rope_cache_partials(const float* partials, int splits, long long split_stride, const void* q_w,
+                                   const void* k_w, float eps, const float* cos_sin, const int* positions,
+                                   const int* slots, void* q_out, void* k_cache, void* v_cache, int tokens, int hq,
+                                   int hkv, int d, int block_size, cudaStream_t stream) {
+  return qk_norm_rope_launch(nullptr, partials, splits, split_stride, q_w, k_w, eps, cos_sin, positions, slots,
+                             q_out, k_cache, v_cache, tokens, hq, hkv, d, block_size, stream);
+}
+
+int xv_add_rmsnorm_partials(const float* partials, int splits, long long split_stride, void* residual, const void* w,
+                            void* y, int rows, int hidden, float eps, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (hidden % 8 || hidden > kNormThreads * kNormMaxVec * 8) return XV_ERR_SHAPE;
+  add_rmsnorm_partials_kernel<<<rows, kNormThreads, 0, stream>>>(partials, splits, split_stride,
+                                                                static_cast<__nv_bfloat16*>(residual),
+                                                                static_cast<const __nv_bfloat16*>(w),
+                                                                static_cast<__nv_bfloat16*>(y), hidden, eps);
   return launch_ok();
 }
 

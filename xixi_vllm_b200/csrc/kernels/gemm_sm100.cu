@@ -51,6 +51,8 @@ struct GemmParams {
   int a_fastest;     // work order: 1 = consecutive work items walk the A tiles, 0 = the B tiles
   int transposed;    // 1: out[(b_row) * ldc + a_row], 0: out[a_row * ldc + b_row]
   int out_fp32;      // 1: fp32 partials at out + split * split_stride, 0: bf16
+  int act;           // 1: SiLU-mul epilogue. Operand rows of the weight matrix come in groups of 16 =
+                     //    [8 gate rows | 8 up rows]; output has half as many features (bf16 only)
   long long ldc;
   long long split_stride;   // elements between split-K partial planes
   void* out;
@@ -215,7 +217,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         uint32_t r[16];
         tmem_ld16(lane_addr + static_cast<uint32_t>(c), r);
         tmem_ld_wait();
-        if (p.transposed) {
+        if (p.act && p.transposed) {
+          // lanes are weight rows laid out [8 gate | 8 up | 8 gate | 8 up]: lane l pairs with l ^ 8
+          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out);
+          const int out_col = (a_row >> 4) * 8 + (a_row & 7);
+          const bool writer = (lane & 8) == 0 && a_row < p.rows_a;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float v = __uint_as_float(r[j]);
+            const float up = __shfl_xor_sync(0xffffffffu, v, 8);
+            const int b_row = b0 + c + j;
+            if (writer && b_row < p.rows_b)
+              o[static_cast<size_t>(b_row) * p.ldc + out_col] = __float2bfloat16(v / (1.f + __expf(-v)) * up);
+          }
+        } else if (p.act) {
+          // this thread's 16 columns are [8 gate | 8 up] of one feature group
+          if (a_row < p.rows_a) {
+            const int col = b0 + c;
+            if (col + 16 <= p.rows_b) {
+              float ov[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float gte = __uint_as_float(r[j]);
+                ov[j] = gte / (1.f + __expf(-gte)) * __uint_as_float(r[8 + j]);
+              }
+              uint4 v0;
+              v0.x = pack_bf16(ov[0], ov[1]);
+              v0.y = pack_bf16(ov[2], ov[3]);
+              v0.z = pack_bf16(ov[4], ov[5]);
+              v0.w = pack_bf16(ov[6], ov[7]);
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(a_row) * p.ldc +
+                                        (col >> 1)) = v0;
+            }
+          }
+        } else if (p.transposed) {
           // lanes hold consecutive output columns (a_row); tokens run along the registers
           if (a_row < p.rows_a) {
             if (p.out_fp32) {
@@ -448,9 +483,9 @@ int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan) {
 
 // Y[m,n] (bf16, row stride ldy) = X[m,k] (row stride ldx) * W[n,k]^T (row stride ldw).
 // `workspace` must hold plan.workspace_bytes when the plan splits K. `status` may be null.
-int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
-                 long long ldy, void* workspace, long long workspace_bytes, int num_sms, int* status,
-                 cudaStream_t stream) {
+static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
+                     long long ldy, void* workspace, long long workspace_bytes, int num_sms, int* status,
+                     cudaStream_t stream, bool defer_reduce, int* splits_out, int act = 0) {
   XvGemmPlan pl;
   int rc = xv_gemm_plan(m, n, k, num_sms, &pl);
   if (rc) return rc;
@@ -496,6 +531,8 @@ int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, lon
     p.out_fp32 = 0;
     p.ldc = ldy;
     p.split_stride = 0;
+    p.act = act;
+    if (act && ((n % 16) || (ldy % 8))) return XV_ERR_SHAPE;
   }
 
   static bool attr_set = false;
@@ -509,7 +546,9 @@ int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, lon
   const int grid = total_work < slots ? total_work : slots;
   gemm_tcgen05_kernel<<<grid, kGemmThreads, pl.smem_bytes, stream>>>(map_a, map_b, p);
   if (cudaGetLastError() != cudaSuccess) return XV_ERR_LAUNCH;
-  if (pl.splits > 1) {
+  if (splits_out) *splits_out = pl.splits;
+  if (act && pl.splits > 1) return XV_ERR_UNSUPPORTED;   // callers check the plan first
+  if (pl.splits > 1 && !defer_reduce) {
     const long long elems = static_cast<long long>(m) * n;
     if (ldy != n) return XV_ERR_SHAPE;   // split-K output must be dense
     const int threads = 256;
@@ -519,6 +558,29 @@ int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, lon
     if (cudaGetLastError() != cudaSuccess) return XV_ERR_LAUNCH;
   }
   return 0;
+}
+
+int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
+                 long long ldy, void* workspace, long long workspace_bytes, int num_sms, int* status,
+                 cudaStream_t stream) {
+  return gemm_impl(x, w, y, m, n, k, ldx, ldw, ldy, workspace, workspace_bytes, num_sms, status, stream, false,
+                   nullptr);
+}
+
+// Y[m, n/2] = silu(gate) * up, with W's rows interleaved in groups of 16 = [8 gate | 8 up].
+// Only for plans that do not split K (XV_ERR_UNSUPPORTED otherwise; see xv_gemm_plan).
+int xv_gemm_bf16_silu_mul(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
+                          long long ldy, int num_sms, int* status, cudaStream_t stream) {
+  return gemm_impl(x, w, y, m, n, k, ldx, ldw, ldy, nullptr, 0, num_sms, status, stream, false, nullptr, 1);
+}
+
+// Same, but when the plan splits K the fp32 partial planes [splits][m][n] are left in
+// `workspace` for the consumer kernel to sum (y is not written); *splits_out tells which.
+int xv_gemm_bf16_defer(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
+                       long long ldy, void* workspace, long long workspace_bytes, int num_sms, int* status,
+                       cudaStream_t stream, int* splits_out) {
+  return gemm_impl(x, w, y, m, n, k, ldx, ldw, ldy, workspace, workspace_bytes, num_sms, status, stream, true,
+                   splits_out);
 }
 
 }  // extern "C"

@@ -17,7 +17,7 @@
 // (so a captured CUDA graph advances it on every replay). A rank announces "my partial for
 // epoch e is complete" by storing e into its slot of every peer's flag array with a
 // system-scope release; consumers poll their own flag array with acquire loads. Polls are
-// bounded: after `spin_limit` tries the kernel records a status code and returns.
+// bounded: after `spin_limit` microseconds the kernel records a status code and returns.
 //
 // Buffer reuse rule (enforced by the caller): the buffer written for call k may be rewritten
 // only after the caller has passed the barrier of call k+1, i.e. never in two consecutive calls.
@@ -44,7 +44,7 @@ struct TpComm {
   const void* mc_buf;                // multicast address of the buffer (nullptr = no NVLS)
   uint32_t* epoch;                   // [0] current epoch, [1] finished-CTA ticket (local memory)
   int rank, world;
-  unsigned spin_limit;
+  unsigned spin_limit;               // longest wait for a peer, in microseconds
   int* status;
 };
 
@@ -87,12 +87,15 @@ __device__ bool tp_barrier(const TpComm& c, uint32_t epoch, int channel) {
   if (threadIdx.x < c.world) {
     const uint32_t* f = c.peer_flags[c.rank] + channel * kMaxRanks + threadIdx.x;
     bool seen = false;
-    for (unsigned i = 0; i < c.spin_limit; ++i) {
+    const unsigned long long t0 = global_timer_ns();
+    const unsigned long long limit = static_cast<unsigned long long>(c.spin_limit) * 1000ull;
+    for (;;) {
       // epochs only grow; signed distance tolerates wrap-around
       if (static_cast<int32_t>(ld_acquire_sys(f) - epoch) >= 0) {
         seen = true;
         break;
       }
+      if (global_timer_ns() - t0 > limit) break;
       __nanosleep(20);
     }
     if (!seen) {
@@ -294,8 +297,11 @@ tp_argmax_kernel(const TpComm c, long long slots_offset, const __nv_bfloat16* __
   if (threadIdx.x < c.world) {
     const uint32_t* f = c.peer_flags[c.rank] + 1 * kMaxRanks + threadIdx.x;
     bool seen = false;
-    for (unsigned i = 0; i < c.spin_limit; ++i) {
+    const unsigned long long t0 = global_timer_ns();
+    const unsigned long long limit = static_cast<unsigned long long>(c.spin_limit) * 1000ull;
+    for (;;) {
       if (static_cast<int32_t>(ld_acquire_sys(f) - epoch) >= 0) { seen = true; break; }
+      if (global_timer_ns() - t0 > limit) break;
       __nanosleep(20);
     }
     if (!seen) { report_status(c.status, kTpKernelId, kPeerFlagTimeout); ok_flag = 0; }

@@ -35,6 +35,21 @@ int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, lon
                  long long ldy, void* workspace, long long workspace_bytes, int num_sms, int* status,
                  cudaStream_t stream);
 
+// As xv_gemm_bf16, but a split-K plan leaves its fp32 partial planes [splits][m][n] in `workspace`
+// (y untouched) for a consumer kernel that sums them; *splits_out reports the split count.
+int xv_gemm_bf16_defer(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
+                       long long ldy, void* workspace, long long workspace_bytes, int num_sms, int* status,
+                       cudaStream_t stream, int* splits_out);
+
+// GEMM with a fused SiLU-mul epilogue: W's rows are interleaved in groups of 16 = [8 gate | 8 up],
+// Y is [m, n/2]. Only for plans that do not split K.
+int xv_gemm_bf16_silu_mul(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
+                          long long ldy, int num_sms, int* status, cudaStream_t stream);
+// SiLU-mul over activations in that interleaved layout: bf16 x [rows, 2*inter], or `splits` fp32
+// partial planes of a split-K GEMM when `partials` is non-null.
+int xv_silu_mul_interleaved(const void* x, const float* partials, int splits, long long split_stride, void* y,
+                            int rows, int inter, cudaStream_t stream);
+
 // Same GEMM for callers that must not allocate GPU memory. This entry point has no counterpart
 // in the reference project. Who needs it: code that runs where a device allocation is not
 // allowed or would stall the GPU, for example a plug-in invoked from another runtime's execution
@@ -61,12 +76,20 @@ int xv_rmsnorm(const void* x, const void* w, void* y, int rows, int hidden, floa
 // residual += x (in place), y = rmsnorm(residual) * w
 int xv_add_rmsnorm(const void* x, void* residual, const void* w, void* y, int rows, int hidden, float eps,
                    cudaStream_t stream);
+// x given as `splits` fp32 partial planes (stride split_stride elements) of a split-K GEMM.
+int xv_add_rmsnorm_partials(const float* partials, int splits, long long split_stride, void* residual, const void* w,
+                            void* y, int rows, int hidden, float eps, cudaStream_t stream);
 int xv_silu_mul(const void* x, void* y, int rows, int inter, cudaStream_t stream);
 int xv_embedding(const int* ids, const void* w, void* y, int tokens, int hidden, int vocab_start, int vocab_rows,
                  cudaStream_t stream);
 int xv_gather_rows(const void* x, const int* rows, void* y, int n, int hidden, cudaStream_t stream);
 // Per-head RMSNorm of q and k, NeoX RoPE, q written to q_out [T, hq*d], k/v appended to the
 // paged cache [blocks, hkv, block_size, d] at `slots` (negative slot = skip).
+// When `partials` is non-null the QKV activations are read as the sum of `splits` fp32 planes.
+int xv_qk_norm_rope_cache_partials(const float* partials, int splits, long long split_stride, const void* q_w,
+                                   const void* k_w, float eps, const float* cos_sin, const int* positions,
+                                   const int* slots, void* q_out, void* k_cache, void* v_cache, int tokens, int hq,
+                                   int hkv, int d, int block_size, cudaStream_t stream);
 int xv_qk_norm_rope_cache(const void* qkv, const void* q_w, const void* k_w, float eps, const float* cos_sin,
                           const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
                           int tokens, int hq, int hkv, int d, int block_size, cudaStream_t stream);

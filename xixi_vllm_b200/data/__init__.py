@@ -3,9 +3,9 @@
 from .block_manager import BlockManager
 from .kv import KVManager
 from .sequence import Sequence, SequenceStatus, slots_for_range
-from .wire import EngineCoreOutput, ScheduledBatch, SchedulerOutput, SeqSchedule
+from .wire import DecodeBatch, EngineCoreOutput, ScheduledBatch, SchedulerOutput, SeqSchedule
 
 __all__ = [
     "BlockManager", "KVManager", "Sequence", "SequenceStatus", "slots_for_range",
-    "EngineCoreOutput", "ScheduledBatch", "SchedulerOutput", "SeqSchedule",
+    "DecodeBatch", "EngineCoreOutput", "ScheduledBatch", "SchedulerOutput", "SeqSchedule",
 ]

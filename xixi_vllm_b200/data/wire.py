@@ -16,7 +16,7 @@ import msgspec
 
 from .sequence import Sequence
 
-__all__ = ["ScheduledBatch", "SeqSchedule", "SchedulerOutput", "EngineCoreOutput"]
+__all__ = ["ScheduledBatch", "SeqSchedule", "DecodeBatch", "SchedulerOutput", "EngineCoreOutput"]
 
 
 class SeqSchedule(msgspec.Struct, array_like=True):
@@ -40,9 +40,50 @@ class SeqSchedule(msgspec.Struct, array_like=True):
     min_p: float | None = None
 
 
+class DecodeBatch(msgspec.Struct, array_like=True):
+    """All decode rows of a step as parallel arrays (one new token per sequence).
+
+    A decode step of 256 sequences is 256 tiny records; building, encoding and decoding them
+    as objects costs more host time than the GPU needs for a tensor-parallel step, so they
+    travel as flat integer lists. Sampling parameters are not repeated: workers remember them
+    from the sequence's prefill message. Block-table growth is sparse (a new page every
+    ``block_size`` tokens): ``bt_index[j]`` names the row of this batch whose table gets
+    ``bt_count[j]`` entries from ``bt_vals`` starting at table position ``bt_from[j]``.
+    """
+
+    seq_ids: list[int] = []
+    tokens: list[int] = []
+    cached: list[int] = []        # KV length before this step
+    bt_index: list[int] = []
+    bt_from: list[int] = []
+    bt_count: list[int] = []
+    bt_vals: list[int] = []
+
+    def __len__(self) -> int:
+        return len(self.seq_ids)
+
+    def __bool__(self) -> bool:
+        return bool(self.seq_ids)
+
+    @classmethod
+    def of(cls, entries) -> "DecodeBatch":
+        """From ``(seq_id, token, cached, bt_from, bt_tail)`` tuples (tests, graph capture)."""
+        b = cls(seq_ids=[], tokens=[], cached=[], bt_index=[], bt_from=[], bt_count=[], bt_vals=[])
+        for i, (sid, tok, cached, start, tail) in enumerate(entries):
+            b.seq_ids.append(sid)
+            b.tokens.append(tok)
+            b.cached.append(cached)
+            if tail:
+                b.bt_index.append(i)
+                b.bt_from.append(start)
+                b.bt_count.append(len(tail))
+                b.bt_vals.extend(tail)
+        return b
+
+
 class SchedulerOutput(msgspec.Struct, array_like=True):
     prefills: list[SeqSchedule] = []
-    decodes: list[SeqSchedule] = []
+    decodes: DecodeBatch = msgspec.field(default_factory=DecodeBatch)
     # sequences that finished or were preempted since the previous message: workers
     # drop their cached block-table rows
     released: list[int] = []
@@ -79,17 +120,23 @@ class ScheduledBatch:
         return not self.prefills and not self.decodes
 
     def to_wire(self) -> SchedulerOutput:
-        decodes = []
-        for s in self.decodes:
-            if len(s.token_ids) != s.num_cached_tokens + 1:
-                raise AssertionError(
-                    f"decode invariant broken for seq {s.seq_id}: {len(s.token_ids)} tokens, "
-                    f"{s.num_cached_tokens} cached"
-                )
-            decodes.append(_entry(s, [s.last_token], True))
+        dec = self.decodes
+        d = DecodeBatch(seq_ids=[s.seq_id for s in dec], tokens=[s.last_token for s in dec],
+                        cached=[s.num_cached_tokens for s in dec], bt_index=[], bt_from=[], bt_count=[], bt_vals=[])
+        for i, s in enumerate(dec):
+            n = len(s.block_table)
+            if s.bt_synced != n:
+                if len(s.token_ids) != s.num_cached_tokens + 1:
+                    raise AssertionError(
+                        f"decode invariant broken for seq {s.seq_id}: {len(s.token_ids)} tokens, "
+                        f"{s.num_cached_tokens} cached")
+                d.bt_index.append(i)
+                d.bt_from.append(s.bt_synced)
+                d.bt_count.append(n - s.bt_synced)
+                d.bt_vals.extend(s.block_table[s.bt_synced:])
+                s.bt_synced = n
         prefills = []
         for s in self.prefills:
             lo = s.num_cached_tokens
             prefills.append(_entry(s, s.token_ids[lo: lo + s.num_scheduled_tokens], s.need_sample))
-        return SchedulerOutput(prefills=prefills, decodes=decodes, released=list(self.released),
-                               step_id=self.step_id)
+        return SchedulerOutput(prefills=prefills, decodes=d, released=list(self.released), step_id=self.step_id)

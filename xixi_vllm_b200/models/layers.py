@@ -94,24 +94,43 @@ class ColumnParallelLinear(_Linear):
 
 
 class MergedColumnParallelLinear(_Linear):
-    """Several column-parallel projections stacked on the output axis (gate | up)."""
+    """Several column-parallel projections stacked on the output axis (gate | up).
+
+    ``interleave=8`` (two equal projections only) stores the rows as repeating groups of
+    [8 of the first | 8 of the second], the layout the GPU GEMM's fused SiLU-mul epilogue
+    expects; ``forward_act`` then returns ``silu(gate) * up`` directly."""
 
     def __init__(self, in_features: int, output_sizes: list[int], *, bias: bool = False,
-                 dtype=torch.bfloat16, device="cpu") -> None:
+                 dtype=torch.bfloat16, device="cpu", interleave: int = 0) -> None:
         tp = get_tp_group()
         self.in_features = in_features
         self.output_sizes = list(output_sizes)
         self.local_sizes = [divide(s, tp.size) for s in output_sizes]
+        self.interleave = interleave
+        if interleave:
+            if len(output_sizes) != 2 or self.local_sizes[0] != self.local_sizes[1] or self.local_sizes[0] % interleave:
+                raise ValueError("interleaving needs two equal projections whose local size divides by the group")
         super().__init__(sum(self.local_sizes), in_features, bias, dtype, device)
 
     def load(self, src, name: str, shard_id: int = 0) -> None:
         n = self.local_sizes[shard_id]
-        self._copy_rows(sum(self.local_sizes[:shard_id]), src.read(name, self.tp.group_rank * n, n))
+        block = src.read(name, self.tp.group_rank * n, n)
+        if self.interleave:
+            g = self.interleave
+            self.weight.view(n // g, 2, g, self.in_features)[:, shard_id].copy_(block.reshape(n // g, g, -1))
+        else:
+            self._copy_rows(sum(self.local_sizes[:shard_id]), block)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return ops.linear(x, self.weight, self.bias)
 
     __call__ = forward
+
+    def forward_act(self, x: torch.Tensor) -> torch.Tensor:
+        """``silu(gate(x)) * up(x)``."""
+        if self.interleave and self.bias is None:
+            return ops.linear_silu_mul(x, self.weight)
+        return ops.silu_mul(self.forward(x))
 
 
 class QKVParallelLinear(_Linear):
@@ -157,8 +176,8 @@ class QKVParallelLinear(_Linear):
             s0, n, d0 = self._range(shard)
             self._copy_rows(d0, src.read(name, base + s0, n))
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear(x, self.weight, self.bias)
+    def forward(self, x: torch.Tensor, defer: bool = False) -> torch.Tensor:
+        return ops.linear(x, self.weight, self.bias, None, defer and self.bias is None)
 
     __call__ = forward
 
@@ -181,8 +200,9 @@ class RowParallelLinear(_Linear):
     def load_bias(self, src, name: str, shard_id=None) -> None:
         self.bias.copy_(src.read(name))
 
-    def forward(self, x: torch.Tensor, reduce: bool = True, out: torch.Tensor | None = None) -> torch.Tensor:
-        y = ops.linear(x, self.weight, None, out if not reduce else None)
+    def forward(self, x: torch.Tensor, reduce: bool = True, out: torch.Tensor | None = None,
+                defer: bool = False) -> torch.Tensor:
+        y = ops.linear(x, self.weight, None, out if not reduce else None, defer and not reduce and out is None)
         if not reduce:
             return y
         y = coll.all_reduce(y, self.tp)

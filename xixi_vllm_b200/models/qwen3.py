@@ -23,13 +23,14 @@ __all__ = ["Qwen3ForCausalLM", "Qwen3Model", "Qwen3DecoderLayer", "Qwen3Attentio
 
 class Qwen3MLP:
     def __init__(self, cfg, dtype, device) -> None:
+        on_gpu = torch.device(device).type == "cuda"
         self.gate_up_proj = MergedColumnParallelLinear(cfg.hidden_size, [cfg.intermediate_size] * 2,
-                                                       dtype=dtype, device=device)
+                                                       dtype=dtype, device=device, interleave=8 if on_gpu else 0)
         self.down_proj = RowParallelLinear(cfg.intermediate_size, cfg.hidden_size, dtype=dtype, device=device)
 
     def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """Returns this rank's partial sum of the MLP output."""
-        return self.down_proj(ops.silu_mul(self.gate_up_proj(x)), reduce=False, out=out)
+        return self.down_proj(self.gate_up_proj.forward_act(x), reduce=False, out=out, defer=True)
 
 
 class Qwen3Attention:
@@ -50,13 +51,13 @@ class Qwen3Attention:
 
     def forward(self, x: torch.Tensor, batch, k_cache: torch.Tensor, v_cache: torch.Tensor,
                 out: torch.Tensor | None = None) -> torch.Tensor:
-        qkv = self.qkv_proj(x)
+        qkv = self.qkv_proj(x, defer=True)      # split-K partials are summed inside the next kernel
         q = ops.qk_norm_rope_cache(qkv, self.q_norm.weight, self.k_norm.weight, self.q_norm.eps,
                                    self.rotary.cos_sin, batch.positions, batch.slots, k_cache, v_cache,
                                    self.num_heads, self.num_kv_heads, self.head_dim)
         o = ops.paged_attention(q, k_cache, v_cache, batch.attn, self.scale, self.num_heads,
                                 self.num_kv_heads, self.head_dim)
-        return self.o_proj(o, reduce=False, out=out)
+        return self.o_proj(o, reduce=False, out=out, defer=True)
 
 
 class Qwen3DecoderLayer:

@@ -51,6 +51,13 @@ def lib():
     L = ctypes.CDLL(path)
     L.xv_gemm_plan.argtypes = [_i32, _i32, _i32, _i32, ctypes.POINTER(GemmPlan)]
     L.xv_gemm_bf16.argtypes = [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _vp, _i64, _i32, _vp, _vp]
+    L.xv_gemm_bf16_defer.argtypes = [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _vp, _i64, _i32, _vp, _vp,
+                                     ctypes.POINTER(_i32)]
+    L.xv_add_rmsnorm_partials.argtypes = [_vp, _i32, _i64, _vp, _vp, _vp, _i32, _i32, _f32, _vp]
+    L.xv_qk_norm_rope_cache_partials.argtypes = [_vp, _i32, _i64, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _vp,
+                                                 _i32, _i32, _i32, _i32, _i32, _vp]
+    L.xv_gemm_bf16_silu_mul.argtypes = [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _vp, _vp]
+    L.xv_silu_mul_interleaved.argtypes = [_vp, _vp, _i32, _i64, _vp, _i32, _i32, _vp]
     L.xv_rmsnorm.argtypes = [_vp, _vp, _vp, _i32, _i32, _f32, _vp]
     L.xv_add_rmsnorm.argtypes = [_vp, _vp, _vp, _vp, _i32, _i32, _f32, _vp]
     L.xv_silu_mul.argtypes = [_vp, _vp, _i32, _i32, _vp]
@@ -140,9 +147,34 @@ def gemm_plan(m: int, n: int, k: int, num_sms: int = 148) -> GemmPlan:
 _USE_CUBLAS = os.environ.get("XV_GEMM", "") == "cublas"
 
 
+class SplitKPartial:
+    """Result of a split-K GEMM whose reduction is left to the consumer kernel: ``splits`` fp32
+    planes ``[M, N]`` in the device's GEMM workspace. Valid until the next split-K GEMM on
+    that device; ``materialize()`` reduces it to an ordinary bf16 tensor."""
+
+    __slots__ = ("ws", "splits", "shape", "device")
+
+    def __init__(self, ws: torch.Tensor, splits: int, m: int, n: int) -> None:
+        self.ws, self.splits, self.shape, self.device = ws, splits, (m, n), ws.device
+
+    @property
+    def is_cuda(self) -> bool:
+        return True
+
+    @property
+    def stride_elems(self) -> int:
+        return self.shape[0] * self.shape[1]
+
+    def materialize(self) -> torch.Tensor:
+        m, n = self.shape
+        planes = self.ws[: self.splits * m * n * 4].view(torch.float32).view(self.splits, m, n)
+        return planes.sum(0).to(torch.bfloat16)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
-           out: torch.Tensor | None = None) -> torch.Tensor:
-    """``x[M,K] @ w[N,K]^T`` on the tcgen05 GEMM; ``out`` (dense [M,N]) receives the result if given."""
+           out: torch.Tensor | None = None, defer: bool = False):
+    """``x[M,K] @ w[N,K]^T`` on the tcgen05 GEMM; ``out`` (dense [M,N]) receives the result if given.
+    ``defer=True`` may return a ``SplitKPartial`` instead of a tensor (see there)."""
     _bf16(x, w)
     if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
         raise ValueError(f"linear: bad shapes {tuple(x.shape)} x {tuple(w.shape)}")
@@ -158,6 +190,15 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
         if x.stride(1) != 1 or w.stride(1) != 1:
             x, w = x.contiguous(), w.contiguous()
         st = _state(x)
+        if defer and out is None and bias is None:
+            pl = gemm_plan(M, N, K, st.num_sms)
+            if pl.splits > 1:
+                used = _i32(0)
+                rc = lib().xv_gemm_bf16_defer(x.data_ptr(), w.data_ptr(), None, M, N, K, x.stride(0), w.stride(0), N,
+                                              st.gemm_ws.data_ptr(), st.gemm_ws.numel(), st.num_sms,
+                                              st.status.data_ptr(), _stream(), ctypes.byref(used))
+                _check(rc, f"gemm {M}x{N}x{K}")
+                return SplitKPartial(st.gemm_ws, used.value, M, N)
         y = out if out is not None else torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
         rc = lib().xv_gemm_bf16(x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K, x.stride(0), w.stride(0), N,
                                 st.gemm_ws.data_ptr(), st.gemm_ws.numel(), st.num_sms, st.status.data_ptr(),
@@ -165,6 +206,37 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
         _check(rc, f"gemm {M}x{N}x{K}")
     if bias is not None:
         y += bias
+    return y
+
+
+def linear_silu_mul(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``silu(x @ Wg^T) * (x @ Wu^T)`` where ``w`` [2*I, K] stores gate and up rows interleaved in
+    groups of 16 = [8 gate | 8 up]. The activation runs in the GEMM epilogue; when the plan
+    splits K it runs in the kernel that sums the partial planes instead."""
+    _bf16(x, w)
+    M, K = x.shape
+    N = w.shape[0]
+    inter = N // 2
+    if M == 0:
+        return x.new_empty((0, inter))
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    st = _state(x)
+    y = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
+    if _USE_CUBLAS:
+        gu = torch.matmul(x, w.t())
+        _check(lib().xv_silu_mul_interleaved(gu.data_ptr(), None, 0, 0, y.data_ptr(), M, inter, _stream()),
+               "silu_mul_interleaved")
+        return y
+    pl = gemm_plan(M, N, K, st.num_sms)
+    if pl.splits == 1:
+        _check(lib().xv_gemm_bf16_silu_mul(x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K, x.stride(0),
+                                           w.stride(0), inter, st.num_sms, st.status.data_ptr(), _stream()),
+               f"gemm+silu {M}x{N}x{K}")
+        return y
+    part = linear(x, w, defer=True)
+    _check(lib().xv_silu_mul_interleaved(None, part.ws.data_ptr(), part.splits, part.stride_elems, y.data_ptr(), M,
+                                         inter, _stream()), "silu_mul_interleaved")
     return y
 
 
@@ -178,6 +250,15 @@ def rmsnorm(x, w, eps):
 
 
 def add_rmsnorm(x, residual, w, eps):
+    if isinstance(x, SplitKPartial):
+        _bf16(residual, w)
+        if not residual.is_contiguous():
+            raise ValueError("add_rmsnorm needs a contiguous residual")
+        m, n = x.shape
+        y = torch.empty((m, n), dtype=torch.bfloat16, device=residual.device)
+        _check(lib().xv_add_rmsnorm_partials(x.ws.data_ptr(), x.splits, x.stride_elems, residual.data_ptr(),
+                                             w.data_ptr(), y.data_ptr(), m, n, eps, _stream()), "add_rmsnorm_partials")
+        return y
     _bf16(x, residual, w)
     if not (x.is_contiguous() and residual.is_contiguous()):
         raise ValueError("add_rmsnorm needs contiguous inputs (the residual is updated in place)")
@@ -221,6 +302,15 @@ def gather_rows(x, rows):
 
 def qk_norm_rope_cache(qkv, q_w, k_w, eps, cos_sin, positions, slots, k_cache, v_cache, num_q_heads,
                        num_kv_heads, head_dim):
+    if isinstance(qkv, SplitKPartial):
+        _bf16(q_w, k_w, k_cache, v_cache)
+        T = qkv.shape[0]
+        q = torch.empty((T, num_q_heads * head_dim), dtype=torch.bfloat16, device=k_cache.device)
+        _check(lib().xv_qk_norm_rope_cache_partials(
+            qkv.ws.data_ptr(), qkv.splits, qkv.stride_elems, q_w.data_ptr(), k_w.data_ptr(), eps, cos_sin.data_ptr(),
+            positions.data_ptr(), slots.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), T,
+            num_q_heads, num_kv_heads, head_dim, k_cache.shape[2], _stream()), "qk_norm_rope_cache_partials")
+        return q
     _bf16(qkv, q_w, k_w, k_cache, v_cache)
     if not (qkv.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()):
         raise ValueError("qk_norm_rope_cache needs contiguous qkv and cache tensors")

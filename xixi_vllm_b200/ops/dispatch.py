@@ -10,7 +10,7 @@ import torch
 from . import cpu_ref
 
 __all__ = [
-    "rmsnorm", "add_rmsnorm", "linear", "silu_mul", "embedding", "qk_norm_rope_cache",
+    "rmsnorm", "add_rmsnorm", "linear", "linear_silu_mul", "silu_mul", "embedding", "qk_norm_rope_cache",
     "paged_attention", "sample", "argmax", "build_cos_sin_cache", "gather_rows",
 ]
 
@@ -31,14 +31,21 @@ def add_rmsnorm(x, residual, w, eps):
     return _cuda().add_rmsnorm(x, residual, w, eps) if x.is_cuda else cpu_ref.add_rmsnorm(x, residual, w, eps)
 
 
-def linear(x, w, bias=None, out=None):
+def linear(x, w, bias=None, out=None, defer=False):
+    """``defer=True`` lets the GPU GEMM hand back unreduced split-K partials; only pass the result
+    to ``add_rmsnorm`` or ``qk_norm_rope_cache`` (they sum the partials themselves)."""
     if x.is_cuda:
-        return _cuda().linear(x, w, bias, out)
+        return _cuda().linear(x, w, bias, out, defer)
     y = cpu_ref.linear(x, w, bias)
     if out is not None:
         out.copy_(y)
         return out
     return y
+
+
+def linear_silu_mul(x, w):
+    """GPU only: fused gate/up projection + SiLU-mul over an interleaved weight (see ops.cuda)."""
+    return _cuda().linear_silu_mul(x, w)
 
 
 def silu_mul(x):

@@ -31,7 +31,7 @@ from .tp_comm import TPComm
 __all__ = ["SymmetricBuffer", "FusedTPComm"]
 
 FLAG_BYTES = 4096          # two channels x 8 ranks x 4 bytes used; one page reserved
-SPIN_LIMIT = 1 << 21       # bounded polls: a peer that never arrives is given up on after a second or two
+SPIN_LIMIT = 2_000_000     # microseconds a kernel waits for a peer before it reports and returns
 
 
 class SymmetricBuffer:

@@ -45,9 +45,16 @@ class LibraryTPComm(TPComm):
         self.group = group
 
     def all_reduce(self, x):
+        if not isinstance(x, torch.Tensor):
+            x = x.materialize()
         return coll.all_reduce(x, self.group)
 
     def reduce_add_rmsnorm(self, partial, residual, w, eps):
+        if not isinstance(partial, torch.Tensor):
+            # unreduced split-K planes from the GEMM: with one rank the add+norm kernel sums them
+            if self.group.size == 1 and residual is not None:
+                return ops.add_rmsnorm(partial, residual, w, eps), residual
+            partial = partial.materialize()
         x = coll.all_reduce(partial, self.group)
         if residual is None:
             return ops.rmsnorm(x, w, eps), x

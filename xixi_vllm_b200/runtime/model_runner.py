@@ -163,7 +163,7 @@ class ModelRunner:
 
     # --- CUDA graphs ---------------------------------------------------------------------------
     def _capture_graphs(self) -> None:
-        from ..data.wire import SchedulerOutput, SeqSchedule
+        from ..data.wire import DecodeBatch, SchedulerOutput
 
         if not (self.is_first_pp and self.is_last_pp):
             return   # with pipeline stages the p2p hand-off brackets the forward; run eagerly
@@ -171,9 +171,8 @@ class ModelRunner:
 
         def make_inputs(bs: int, greedy: bool):
             self.stager.reset()
-            entry = SeqSchedule(seq_id=-1, num_cached_tokens=0, token_ids=[0], bt_from=0, bt_tail=[0],
-                                temperature=0.0 if greedy else 1.0)
-            batch = self.stager.build(SchedulerOutput(decodes=[entry]), pad_to=bs, fixed_blocks=True)
+            batch = self.stager.build(SchedulerOutput(decodes=DecodeBatch.of([(-1, 0, 0, 0, [0])])), pad_to=bs,
+                                      fixed_blocks=True)
             batch.slots.fill_(-1)      # capture must not write real KV slots
             batch.all_greedy = greedy
             return batch

@@ -73,6 +73,11 @@ class BatchStager:
         self.num_rows = max_seqs * 2 + 8
         self.tables = np.zeros((self.num_rows, max_blocks), dtype=np.int32)
         self.row_of: dict[int, int] = {}
+        # sampling parameters remembered per row (decode messages do not repeat them)
+        self.row_temp = np.zeros(self.num_rows, dtype=np.float32)
+        self.row_topk = np.zeros(self.num_rows, dtype=np.int32)
+        self.row_topp = np.ones(self.num_rows, dtype=np.float32)
+        self.row_minp = np.zeros(self.num_rows, dtype=np.float32)
         self.free_rows = list(range(self.num_rows - 1, -1, -1))
         cap = 3 * max_tokens + 8 * (max_seqs + 1) + max_seqs * max_blocks + 64
         self.host = torch.zeros(cap, dtype=torch.int32, pin_memory=cuda)
@@ -108,7 +113,37 @@ class BatchStager:
             if end > self.max_blocks:
                 raise RuntimeError(f"sequence {entry.seq_id} needs {end} pages > max_blocks={self.max_blocks}")
             self.tables[row, entry.bt_from:end] = tail
+        self.row_temp[row] = entry.temperature
+        self.row_topk[row] = entry.top_k if entry.top_k is not None and entry.top_k > 0 else 0
+        self.row_topp[row] = entry.top_p if entry.top_p is not None else 1.0
+        self.row_minp[row] = entry.min_p if entry.min_p is not None else 0.0
         return row
+
+    def _decode_rows(self, dec) -> np.ndarray:
+        """Rows of the decode batch's sequences, after applying its sparse block-table updates."""
+        n = len(dec.seq_ids)
+        rows = self._rows_tmp[:n]
+        row_of = self.row_of
+        try:
+            rows[:] = [row_of[sid] for sid in dec.seq_ids]
+        except KeyError:
+            # first sight of a sequence in a decode message (no prefill seen by this worker)
+            for i, sid in enumerate(dec.seq_ids):
+                r = row_of.get(sid)
+                if r is None:
+                    if not self.free_rows:
+                        raise RuntimeError("out of block-table rows: more live sequences than 2*max_num_seqs")
+                    r = row_of[sid] = self.free_rows.pop()
+                    self.row_temp[r], self.row_topk[r], self.row_topp[r], self.row_minp[r] = 0.0, 0, 1.0, 0.0
+                rows[i] = r
+        off = 0
+        for i, start, cnt in zip(dec.bt_index, dec.bt_from, dec.bt_count):
+            end = start + cnt
+            if end > self.max_blocks:
+                raise RuntimeError(f"sequence {dec.seq_ids[i]} needs {end} pages > max_blocks={self.max_blocks}")
+            self.tables[rows[i], start:end] = dec.bt_vals[off:off + cnt]
+            off += cnt
+        return rows
 
     # --- packing -----------------------------------------------------------------------------
     def build(self, sched, *, pad_to: int | None = None, fixed_blocks: bool = False) -> ForwardBatch:
@@ -122,14 +157,17 @@ class BatchStager:
         B_real = n_d + n_p
         B = max(B_real, pad_to or 0)
         T_real = n_d + sum(len(e.token_ids) for e in prefills)
+        rows_d = self._decode_rows(decodes) if n_d else None
         T = T_real + (B - B_real)
         if T > self.max_tokens or B > self.max_seqs:
             raise RuntimeError(f"batch of {T} tokens / {B} sequences exceeds staging capacity")
 
-        rows = [self._row(e) for e in decodes] + [self._row(e) for e in prefills]
+        rows_p = [self._row(e) for e in prefills]
         max_kv = 1
-        for e in decodes:
-            max_kv = max(max_kv, e.num_cached_tokens + 1)
+        if n_d:
+            cached = self._cached_tmp[:n_d]
+            cached[:] = decodes.cached
+            max_kv = int(cached.max()) + 1
         for e in prefills:
             max_kv = max(max_kv, e.num_cached_tokens + len(e.token_ids))
         nblk = self.max_blocks if fixed_blocks else max(1, -(-max_kv // bsz))
@@ -155,12 +193,7 @@ class BatchStager:
 
         # decode rows
         if n_d:
-            rows_d = self._rows_tmp[:n_d]
-            cached = self._cached_tmp[:n_d]
-            for i, e in enumerate(decodes):
-                rows_d[i] = rows[i]
-                cached[i] = e.num_cached_tokens
-                ids[i] = e.token_ids[0]
+            ids[:n_d] = decodes.tokens
             if self._lib is not None:
                 p = lambda a: a.ctypes.data_as(ctypes.c_void_p)  # noqa: E731
                 self._lib.xv_fill_decode(n_d, p(rows_d), p(cached), p(self.tables), self.max_blocks, bsz,
@@ -189,7 +222,7 @@ class BatchStager:
             ids[t_off:t_off + n] = e.token_ids
             p_arr = np.arange(c, c + n, dtype=np.int32)
             pos[t_off:t_off + n] = p_arr
-            trow = self.tables[rows[b]]
+            trow = self.tables[rows_p[j]]
             slots[t_off:t_off + n] = trow[p_arr // bsz] * bsz + p_arr % bsz
             kv_lens[b] = c + n
             cu_q[b + 1] = t_off + n
@@ -215,10 +248,18 @@ class BatchStager:
 
         # sampling parameters, in sample-row order (decodes, then prefills that finish)
         greedy = True
-        k = 0
-        for e in decodes:
-            greedy &= self._put_sampling(e, k, temp, topk, topp, minp)
-            k += 1
+        k = n_d
+        if n_d:
+            temp[:n_d] = self.row_temp[rows_d]
+            greedy = bool((temp[:n_d] <= 1e-5).all())
+            if greedy:
+                topk[:n_d] = 0
+                topp[:n_d] = 1.0
+                minp[:n_d] = 0.0
+            else:
+                topk[:n_d] = self.row_topk[rows_d]
+                topp[:n_d] = self.row_topp[rows_d]
+                minp[:n_d] = self.row_minp[rows_d]
         for e in prefills:
             if e.need_sample:
                 greedy &= self._put_sampling(e, k, temp, topk, topp, minp)

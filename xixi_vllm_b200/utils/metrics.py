@@ -44,7 +44,8 @@ class EngineMetrics:
     keep_request_timings: int = 4096
 
     def on_step(self, sched, outputs, prefill_tokens: int, *, schedule_s: float, execute_s: float,
-                update_s: float, kv_usage: float, preemptions: int, kv, now: float) -> None:
+                update_s: float, kv_usage: float, preemptions: int, kv, now: float, sampled_total: int = 0,
+                finished_lookup=None) -> None:
         self.steps += 1
         self.prefill_tokens += prefill_tokens
         self.decode_tokens += len(sched.decodes)
@@ -57,28 +58,25 @@ class EngineMetrics:
         self.preemptions = preemptions
         self.prefix_hit_tokens = kv.num_prefix_hit_tokens
         self.prefix_query_tokens = kv.num_prefix_query_tokens
-        by_id = None
+        self.sampled_tokens = sampled_total
+        # decode rows that neither start nor finish a request need no per-request bookkeeping
+        for seq in sched.prefills:
+            if not seq.t_first_token and seq.num_completion_tokens > 0:
+                seq.t_first_token = now
         for o in outputs:
-            self.sampled_tokens += len(o.new_token_ids)
-            if not (o.new_token_ids or o.is_finished):
+            if not o.is_finished:
                 continue
-            if by_id is None:
-                by_id = {s.seq_id: s for s in sched.decodes}
-                by_id.update((s.seq_id, s) for s in sched.prefills)
-            seq = by_id.get(o.seq_id)
+            seq = finished_lookup(o.seq_id)
             if seq is None:
                 continue
-            if o.new_token_ids and not seq.t_first_token:
-                seq.t_first_token = now
-            if o.is_finished:
-                seq.t_finished = now
-                self.requests_finished += 1
-                if len(self.finished) < self.keep_request_timings:
-                    n = seq.num_completion_tokens
-                    first = seq.t_first_token or now
-                    self.finished.append(RequestTiming(
-                        seq.seq_id, seq.num_prompt_tokens, n, first - seq.t_arrival,
-                        (now - first) / max(1, n - 1), now - seq.t_arrival))
+            seq.t_finished = now
+            self.requests_finished += 1
+            if len(self.finished) < self.keep_request_timings:
+                n = seq.num_completion_tokens
+                first = seq.t_first_token or now
+                self.finished.append(RequestTiming(
+                    seq.seq_id, seq.num_prompt_tokens, n, first - seq.t_arrival,
+                    (now - first) / max(1, n - 1), now - seq.t_arrival))
 
     @property
     def prefix_hit_rate(self) -> float:

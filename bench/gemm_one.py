@@ -24,7 +24,10 @@ def main() -> None:
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--no-pair", action="store_true", help="force the single-CTA kernel")
     a = ap.parse_args()
+    if a.no_pair:
+        cuda.lib().xv_gemm_disable_pair(1)
     x = torch.randn(a.m, a.k, device="cuda").bfloat16()
     w = torch.randn(a.n, a.k, device="cuda").bfloat16()
     for _ in range(a.iters):

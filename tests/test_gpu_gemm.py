@@ -75,3 +75,27 @@ def test_gemm_with_fused_silu_mul(m, inter, k):
     ref = torch.nn.functional.silu(gf) * uf
     assert y.shape == (m, inter)
     assert (y.float() - ref).abs().max().item() <= 3e-2 * ref.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("m,n,k", [(2048, 4096, 1024), (4096, 6144, 4096), (1500, 9000, 512), (19 * 256, 1024, 2048)])
+def test_cta_pair_kernel_matches_single_cta_kernel(m, n, k):
+    """Large-M problems run on CTA pairs (cta_group::2); forcing the single-CTA kernel must agree."""
+    from xixi_vllm_b200.ops import cuda
+    L = cuda.lib()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert cuda.gemm_plan(m, n, k, sms).pair == 1
+    g = torch.Generator().manual_seed(m + n + k)
+    x = (torch.randn(m, k, generator=g) * 0.5).bfloat16().to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.5).bfloat16().to(DEV)
+    y_pair = cuda.linear(x, w)
+    L.xv_gemm_disable_pair(1)
+    try:
+        assert cuda.gemm_plan(m, n, k, sms).pair == 0
+        y_single = cuda.linear(x, w)
+    finally:
+        L.xv_gemm_disable_pair(0)
+    torch.cuda.synchronize()
+    cuda.check_status()
+    ref = x.float() @ w.float().t()
+    assert (y_pair.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
+    assert torch.equal(y_pair, y_single)        # same K order, same fp32 accumulation

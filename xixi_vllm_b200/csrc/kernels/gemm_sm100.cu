@@ -29,6 +29,7 @@
 #include <unordered_map>
 
 #include "../common/ptx.cuh"
+#include "tp_device.cuh"
 #include "xv_cuda.h"
 
 namespace xv {
@@ -86,7 +87,7 @@ __device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int w) {
 // is double buffered in TMEM, so the epilogue of one tile overlaps the main loop of the next.
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const GemmParams p) {
+                    const GemmParams p, const __grid_constant__ TpTail tail) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // Dynamic shared memory is only guaranteed 16-byte alignment; the swizzled tiles need 1024.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -318,6 +319,244 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
+
+  // ---------------- tensor-parallel tail: all-reduce + residual + RMSNorm in this kernel ----------------
+  // The whole grid is resident (the host clamps it to the occupancy), so grid-wide barriers
+  // are safe. Phase order: [fold split-K planes into the symmetric buffer] -> announce to
+  // peers -> wait for peers -> every CTA reduces, adds the residual and normalises its rows.
+  if (tail.enabled) {
+    __shared__ float tail_scratch[32];
+    bool ok = *abort_flag == 0;
+    if (tail.splits > 1) {
+      ok = grid_barrier(tail.grid_sync, kDefaultWaitNs) && ok;
+      if (ok) {
+        __nv_bfloat16* mine = reinterpret_cast<__nv_bfloat16*>(
+            const_cast<char*>(static_cast<const char*>(tail.comm.peer_buf[tail.comm.rank])) + tail.buf_offset);
+        const long long elems = static_cast<long long>(tail.rows) * tail.hidden;
+        for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < elems;
+             i += static_cast<long long>(gridDim.x) * blockDim.x * 4) {
+          float4 acc = *reinterpret_cast<const float4*>(tail.partials + i);
+          for (int sp = 1; sp < tail.splits; ++sp) {
+            const float4 v = *reinterpret_cast<const float4*>(tail.partials + sp * tail.split_stride + i);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+          }
+          uint2 o;
+          o.x = pack_bf16(acc.x, acc.y);
+          o.y = pack_bf16(acc.z, acc.w);
+          *reinterpret_cast<uint2*>(mine + i) = o;
+        }
+      }
+    }
+    ok = grid_barrier(tail.grid_sync, kDefaultWaitNs) && ok;
+    if (!ok) report_status(p.status, kGemmKernelId, kPeerFlagTimeout);
+    const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(tail.comm.epoch);
+    ok = tp_barrier(tail.comm, epoch, 0) && ok;
+    if (ok)
+      tp_reduce_rows<6>(tail.comm, tail.buf_offset, tail.residual_in, tail.residual_out, tail.norm_w, tail.y,
+                        tail.rows, tail.hidden, tail.eps, tail.mode, tail_scratch);
+    tp_finish(tail.comm);
+  }
+}
+
+// ---- CTA-pair variant --------------------------------------------------------------------------------
+// Two CTAs of a 2-wide cluster compute one 256 x 256 output tile with tcgen05.mma cta_group::2.
+// Each CTA loads 128 rows of A and 128 rows of B per K block (32 KB instead of the 48 KB a lone
+// CTA needs for its 128 x 256 tile), so the shared-memory fill traffic per FLOP drops by a third
+// and six stages fit. CTA rank 0 issues the MMAs for the pair; each CTA drains its own 128
+// accumulator rows. Used for the large-M (prefill) orientation.
+constexpr int kPairStages = 6;
+constexpr int kPairStageBytes = 2 * kBM * kBK * 2;   // A 16 KB + B 16 KB
+constexpr int kPairSmem = kPairStages * kPairStageBytes + 1024 + 256;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr uint32_t a_bytes = kBM * kBK * 2;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);   // used in the leader
+  uint64_t* empty_bar = full_bar + kMaxStages;
+  uint64_t* acc_full = empty_bar + kMaxStages;
+  uint64_t* acc_empty = acc_full + 2;                                                       // used in the leader
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int total_work = p.tiles_a * p.tiles_b * p.splits;
+  const int total_kb = (p.k + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&full_bar[s], 2);       // one arrive.expect_tx from each CTA's producer
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);      // four epilogue warps in each of the two CTAs
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_b);
+      const uint64_t hint = l2_policy_evict_normal();
+      uint32_t it = 0;
+      for (int w = pair; w < total_work && !*abort_flag; w += num_pairs) {
+        const WorkItem wi = decode_work(p, w);
+        const int kb_begin = wi.split * p.k_blocks_per_split;
+        const int kb_end = min(kb_begin + p.k_blocks_per_split, total_kb);
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+          const uint32_t s = it % kPairStages;
+          const uint32_t round = it / kPairStages;
+          if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
+            report_status(p.status, kGemmKernelId, kWaitEmptyTimeout);
+            *abort_flag = 1;
+            break;
+          }
+          uint8_t* sa = smem + static_cast<size_t>(s) * kPairStageBytes;
+          const uint32_t leader_full = map_to_cta(smem_u32(&full_bar[s]), 0);
+          mbar_expect_tx_cluster(leader_full, kPairStageBytes);
+          tma_load_2d_pair(sa, &map_a, leader_full, kb * kBK, wi.tile_a * 256 + static_cast<int>(rank) * kBM, hint);
+          tma_load_2d_pair(sa + a_bytes, &map_b, leader_full, kb * kBK,
+                           wi.tile_b * 256 + static_cast<int>(rank) * kBM, hint);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      uint32_t it = 0, t = 0;
+      for (int w = pair; w < total_work && !*abort_flag; w += num_pairs, ++t) {
+        const WorkItem wi = decode_work(p, w);
+        const int kb_begin = wi.split * p.k_blocks_per_split;
+        const int kb_end = min(kb_begin + p.k_blocks_per_split, total_kb);
+        const uint32_t buf = t & 1, use = t >> 1;
+        if (use > 0 && !mbar_wait(&acc_empty[buf], (use - 1) & 1)) {
+          report_status(p.status, kGemmKernelId, kWaitAccumTimeout);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * 256;
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+          const uint32_t s = it % kPairStages;
+          const uint32_t round = it / kPairStages;
+          if (!mbar_wait(&full_bar[s], round & 1)) {
+            report_status(p.status, kGemmKernelId, kWaitFullTimeout);
+            *abort_flag = 1;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + static_cast<size_t>(s) * kPairStageBytes);
+          const uint32_t sb = sa + a_bytes;
+#pragma unroll
+          for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+            umma_bf16_pair(d_tmem, umma_desc_sw128(sa + kk * kUmmaK * 2), umma_desc_sw128(sb + kk * kUmmaK * 2),
+                           p.idesc, (kb > kb_begin || kk > 0) ? 1u : 0u);
+          }
+          // the stage is free in both CTAs once these MMAs have read it
+          umma_commit_pair(map_to_cta(smem_u32(&empty_bar[s]), 0));
+          umma_commit_pair(map_to_cta(smem_u32(&empty_bar[s]), 1));
+        }
+        umma_commit_pair(map_to_cta(smem_u32(&acc_full[buf]), 0));
+        umma_commit_pair(map_to_cta(smem_u32(&acc_full[buf]), 1));
+      }
+    }
+  } else {
+    // ---------------- epilogue (both CTAs, own 128 accumulator rows) ----------------
+    const int quarter = warp & 3;
+    uint32_t t = 0;
+    for (int w = pair; w < total_work; w += num_pairs, ++t) {
+      const WorkItem wi = decode_work(p, w);
+      const uint32_t buf = t & 1, use = t >> 1;
+      bool ok = mbar_wait(&acc_full[buf], use & 1);
+      if (!ok) {
+        report_status(p.status, kGemmKernelId, kWaitAccumTimeout);
+        *abort_flag = 1;
+      }
+      tc_fence_after_sync();
+      ok = __all_sync(0xffffffffu, ok && (*abort_flag == 0));
+      if (!ok) break;
+      const int a_row = wi.tile_a * 256 + static_cast<int>(rank) * kBM + quarter * 32 + lane;
+      const uint32_t lane_addr = tmem_base + buf * 256 + (static_cast<uint32_t>(quarter * 32) << 16);
+      const int b0 = wi.tile_b * 256;
+      for (int c = 0; c < 256; c += 16) {
+        uint32_t r[16];
+        tmem_ld16(lane_addr + static_cast<uint32_t>(c), r);
+        tmem_ld_wait();
+        const int col = b0 + c;
+        if (a_row >= p.rows_a || col >= p.rows_b) continue;
+        if (p.act) {
+          if (col + 16 <= p.rows_b) {
+            float ov[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float gte = __uint_as_float(r[j]);
+              ov[j] = gte / (1.f + __expf(-gte)) * __uint_as_float(r[8 + j]);
+            }
+            uint4 v0;
+            v0.x = pack_bf16(ov[0], ov[1]);
+            v0.y = pack_bf16(ov[2], ov[3]);
+            v0.z = pack_bf16(ov[4], ov[5]);
+            v0.w = pack_bf16(ov[6], ov[7]);
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(a_row) * p.ldc +
+                                      (col >> 1)) = v0;
+          }
+        } else if (p.out_fp32) {
+          float* o = static_cast<float*>(p.out) + static_cast<size_t>(wi.split) * p.split_stride +
+                     static_cast<size_t>(a_row) * p.ldc + col;
+          for (int j = 0; j < 16; ++j)
+            if (col + j < p.rows_b) o[j] = __uint_as_float(r[j]);
+        } else {
+          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(a_row) * p.ldc + col;
+          if (col + 16 <= p.rows_b && (p.ldc & 7) == 0) {
+            uint4 v0, v1;
+            v0.x = pack_bf16(__uint_as_float(r[0]), __uint_as_float(r[1]));
+            v0.y = pack_bf16(__uint_as_float(r[2]), __uint_as_float(r[3]));
+            v0.z = pack_bf16(__uint_as_float(r[4]), __uint_as_float(r[5]));
+            v0.w = pack_bf16(__uint_as_float(r[6]), __uint_as_float(r[7]));
+            v1.x = pack_bf16(__uint_as_float(r[8]), __uint_as_float(r[9]));
+            v1.y = pack_bf16(__uint_as_float(r[10]), __uint_as_float(r[11]));
+            v1.z = pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13]));
+            v1.w = pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15]));
+            *reinterpret_cast<uint4*>(o) = v0;
+            *reinterpret_cast<uint4*>(o + 8) = v1;
+          } else {
+            for (int j = 0; j < 16; ++j)
+              if (col + j < p.rows_b) o[j] = __float2bfloat16(__uint_as_float(r[j]));
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+    }
+  }
+
+  // Both CTAs stay alive until the pair is done: the leader's MMAs read the peer's shared
+  // memory and write the peer's tensor memory.
+  tc_fence_before_sync();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
 }
 
 // out[m, n] = sum_s partial[s, m, n], rounded to bf16.
@@ -424,7 +663,12 @@ static uint32_t pow2_cols(int n) {
 
 using namespace xv;
 
+static bool g_disable_pair = false;
+
 extern "C" {
+
+// Test hook: 1 forces the single-CTA kernel for every shape (A/B comparisons), 0 restores.
+void xv_gemm_disable_pair(int disable) { g_disable_pair = disable != 0; }
 
 // Chooses orientation, tile and split-K for a problem; fills *plan. Pure host arithmetic so
 // callers (and CPU tests) can size the workspace before launching.
@@ -446,6 +690,22 @@ int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan) {
     pl.bn = n >= 256 ? 256 : round_up(n, 16);
     pl.tiles_a = (m + kBM - 1) / kBM;
     pl.tiles_b = (n + pl.bn - 1) / pl.bn;
+    // CTA pairs (256 x 256 tiles) once there are enough of them to occupy every SM pair
+    const int pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
+    if (n >= 256 && pair_tiles >= num_sms / 2 && !g_disable_pair) {
+      pl.pair = 1;
+      pl.bn = 256;
+      pl.tiles_a = (m + 255) / 256;
+      pl.tiles_b = (n + 255) / 256;
+      pl.splits = 1;
+      pl.k_blocks_per_split = total_kb;
+      pl.stages = kPairStages;
+      pl.smem_bytes = kPairSmem;
+      pl.ctas_per_sm = 1;
+      pl.workspace_bytes = 0;
+      *plan = pl;
+      return 0;
+    }
   }
   const int tiles = pl.tiles_a * pl.tiles_b;
   const int stage_bytes = kBM * kBK * 2 + pl.bn * kBK * 2;
@@ -485,10 +745,17 @@ int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan) {
 // `workspace` must hold plan.workspace_bytes when the plan splits K. `status` may be null.
 static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
                      long long ldy, void* workspace, long long workspace_bytes, int num_sms, int* status,
-                     cudaStream_t stream, bool defer_reduce, int* splits_out, int act = 0) {
+                     cudaStream_t stream, bool defer_reduce, int* splits_out, int act = 0,
+                     const TpTail* tail_in = nullptr) {
   XvGemmPlan pl;
   int rc = xv_gemm_plan(m, n, k, num_sms, &pl);
   if (rc) return rc;
+  if (tail_in && pl.pair) {        // the fused tail lives in the single-CTA kernel
+    g_disable_pair = true;
+    rc = xv_gemm_plan(m, n, k, num_sms, &pl);
+    g_disable_pair = false;
+    if (rc) return rc;
+  }
   if ((ldx % 8) || (ldw % 8) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return XV_ERR_ALIGN;
   if (pl.workspace_bytes > workspace_bytes || (pl.workspace_bytes && !workspace)) return XV_ERR_WORKSPACE;
@@ -496,7 +763,13 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
   CUtensorMap map_a, map_b;
   GemmParams p;
   std::memset(&p, 0, sizeof(p));
-  if (pl.swapped) {
+  if (pl.pair) {
+    if ((rc = get_tensor_map(&map_a, x, m, k, ldx, kBM))) return rc;
+    if ((rc = get_tensor_map(&map_b, w, n, k, ldw, kBM))) return rc;
+    p.rows_a = m;
+    p.rows_b = n;
+    p.transposed = 0;
+  } else if (pl.swapped) {
     if ((rc = get_tensor_map(&map_a, w, n, k, ldw, kBM))) return rc;
     if ((rc = get_tensor_map(&map_b, x, m, k, ldx, pl.bn))) return rc;
     p.rows_a = n;
@@ -514,7 +787,7 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
   p.stages = pl.stages;
   p.k_blocks_per_split = pl.k_blocks_per_split;
   p.status = status;
-  p.idesc = umma_idesc_bf16(kBM, pl.bn);
+  p.idesc = umma_idesc_bf16(pl.pair ? 256 : kBM, pl.bn);
   p.acc_stride = pow2_cols(pl.bn);
   p.tmem_cols = 2 * p.acc_stride;
   p.tiles_a = pl.tiles_a;
@@ -537,15 +810,51 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
 
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
     if (e != cudaSuccess) return XV_ERR_LAUNCH;
     attr_set = true;
   }
+  if (pl.pair) {
+    static bool pair_attr = false;
+    if (!pair_attr) {
+      if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024) !=
+          cudaSuccess)
+        return XV_ERR_LAUNCH;
+      pair_attr = true;
+    }
+    const int pairs_avail = (num_sms > 0 ? num_sms : 148) / 2;
+    const int work = pl.tiles_a * pl.tiles_b;
+    const int pairs = work < pairs_avail ? work : pairs_avail;
+    gemm_tcgen05_pair_kernel<<<2 * pairs, kGemmThreads, kPairSmem, stream>>>(map_a, map_b, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
+  }
   const int total_work = pl.tiles_a * pl.tiles_b * pl.splits;
-  const int slots = (num_sms > 0 ? num_sms : 148) * pl.ctas_per_sm;
-  const int grid = total_work < slots ? total_work : slots;
-  gemm_tcgen05_kernel<<<grid, kGemmThreads, pl.smem_bytes, stream>>>(map_a, map_b, p);
+  int slots = (num_sms > 0 ? num_sms : 148) * pl.ctas_per_sm;
+  TpTail tail;
+  std::memset(&tail, 0, sizeof(tail));
+  int grid = total_work < slots ? total_work : slots;
+  if (tail_in) {
+    tail = *tail_in;
+    tail.enabled = 1;
+    tail.partials = static_cast<const float*>(workspace);
+    tail.splits = pl.splits;
+    tail.split_stride = p.split_stride;
+    // grid-wide barriers need every CTA resident at once
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_tcgen05_kernel, kGemmThreads, pl.smem_bytes) !=
+            cudaSuccess || per_sm < 1)
+      return XV_ERR_LAUNCH;
+    if (per_sm > pl.ctas_per_sm) per_sm = pl.ctas_per_sm;
+    slots = (num_sms > 0 ? num_sms : 148) * per_sm;
+    // all CTAs take part in the row phase, so launch the full resident grid even for few tiles
+    grid = slots;
+    if (grid > 4 * (tail.rows > total_work ? tail.rows : total_work)) grid = 4 * (tail.rows > total_work ? tail.rows : total_work);
+    if (grid > slots) grid = slots;
+    if (grid < 1) grid = 1;
+  }
+  gemm_tcgen05_kernel<<<grid, kGemmThreads, pl.smem_bytes, stream>>>(map_a, map_b, p, tail);
   if (cudaGetLastError() != cudaSuccess) return XV_ERR_LAUNCH;
+  if (tail_in) return 0;
   if (splits_out) *splits_out = pl.splits;
   if (act && pl.splits > 1) return XV_ERR_UNSUPPORTED;   // callers check the plan first
   if (pl.splits > 1 && !defer_reduce) {
@@ -565,6 +874,44 @@ int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, lon
                  cudaStream_t stream) {
   return gemm_impl(x, w, y, m, n, k, ldx, ldw, ldy, workspace, workspace_bytes, num_sms, status, stream, false,
                    nullptr);
+}
+
+// RowParallel GEMM + all-reduce + residual add + RMSNorm as ONE kernel. The GEMM writes this
+// rank's partial [m, n] into its symmetric buffer at `buf_offset` (peer_bufs[rank]); the same
+// kernel then announces it to the peers, waits for theirs and finishes rows (see tp_fused.cu
+// for the flag protocol and the buffer-reuse rule). grid_sync: 2 zero-initialised uint32.
+int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long ldx, long long ldw, void* workspace,
+                    long long workspace_bytes, int num_sms, const void* const* peer_bufs, void* const* peer_flags,
+                    const void* mc_buf, void* epoch, int rank, int world, long long buf_offset, void* grid_sync,
+                    const void* residual_in, void* residual_out, const void* norm_w, void* y_out, float eps, int mode,
+                    unsigned spin_us, int* status, cudaStream_t stream) {
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || (n % 8) || n > 192 * 6 * 8 || (buf_offset & 15))
+    return XV_ERR_SHAPE;
+  TpTail tail;
+  std::memset(&tail, 0, sizeof(tail));
+  for (int r = 0; r < kMaxRanks; ++r) {
+    tail.comm.peer_buf[r] = r < world ? peer_bufs[r] : nullptr;
+    tail.comm.peer_flags[r] = r < world ? static_cast<uint32_t*>(peer_flags[r]) : nullptr;
+  }
+  tail.comm.mc_buf = mc_buf;
+  tail.comm.epoch = static_cast<uint32_t*>(epoch);
+  tail.comm.rank = rank;
+  tail.comm.world = world;
+  tail.comm.spin_limit = spin_us;
+  tail.comm.status = status;
+  tail.buf_offset = buf_offset;
+  tail.residual_in = static_cast<const __nv_bfloat16*>(residual_in);
+  tail.residual_out = static_cast<__nv_bfloat16*>(residual_out);
+  tail.norm_w = static_cast<const __nv_bfloat16*>(norm_w);
+  tail.y = static_cast<__nv_bfloat16*>(y_out);
+  tail.rows = m;
+  tail.hidden = n;
+  tail.eps = eps;
+  tail.mode = mode;
+  tail.grid_sync = static_cast<uint32_t*>(grid_sync);
+  void* local = const_cast<char*>(static_cast<const char*>(peer_bufs[rank])) + buf_offset;
+  return gemm_impl(x, w, local, m, n, k, ldx, ldw, n, workspace, workspace_bytes, num_sms, status, stream, true,
+                   nullptr, 0, &tail);
 }
 
 // Y[m, n/2] = silu(gate) * up, with W's rows interleaved in groups of 16 = [8 gate | 8 up].

@@ -30,114 +30,10 @@
 #include <math_constants.h>
 
 #include "../common/ptx.cuh"
+#include "tp_device.cuh"
 #include "xv_cuda.h"
 
 namespace xv {
-
-constexpr int kMaxRanks = 8;
-constexpr int kTpKernelId = 3;
-constexpr int kTpThreads = 256;
-
-struct TpComm {
-  const void* peer_buf[kMaxRanks];   // every rank's symmetric buffer base, as mapped here
-  uint32_t* peer_flags[kMaxRanks];   // every rank's flag array (kMaxRanks words per channel)
-  const void* mc_buf;                // multicast address of the buffer (nullptr = no NVLS)
-  uint32_t* epoch;                   // [0] current epoch, [1] finished-CTA ticket (local memory)
-  int rank, world;
-  unsigned spin_limit;               // longest wait for a peer, in microseconds
-  int* status;
-};
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
-// Sum over all ranks of eight bf16 values, reduced inside NVSwitch with fp32 accumulation.
-__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
-  uint4 v;
-  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc)
-               : "memory");
-  return v;
-}
-
-// Announce this rank's data for `epoch` (one thread of the grid) and wait until every rank has
-// announced. Returns false if a peer never arrived within the spin limit.
-__device__ bool tp_barrier(const TpComm& c, uint32_t epoch, int channel) {
-  __shared__ int ok_flag;
-  if (threadIdx.x == 0) ok_flag = 1;
-  __syncthreads();
-  if (blockIdx.x == 0 && threadIdx.x < c.world) {
-    __threadfence_system();   // the producer kernel's writes are ordered before the flag
-    st_release_sys(c.peer_flags[threadIdx.x] + channel * kMaxRanks + c.rank, epoch);
-  }
-  if (threadIdx.x < c.world) {
-    const uint32_t* f = c.peer_flags[c.rank] + channel * kMaxRanks + threadIdx.x;
-    bool seen = false;
-    const unsigned long long t0 = global_timer_ns();
-    const unsigned long long limit = static_cast<unsigned long long>(c.spin_limit) * 1000ull;
-    for (;;) {
-      // epochs only grow; signed distance tolerates wrap-around
-      if (static_cast<int32_t>(ld_acquire_sys(f) - epoch) >= 0) {
-        seen = true;
-        break;
-      }
-      if (global_timer_ns() - t0 > limit) break;
-      __nanosleep(20);
-    }
-    if (!seen) {
-      report_status(c.status, kTpKernelId, kPeerFlagTimeout);
-      ok_flag = 0;
-    }
-  }
-  __syncthreads();
-  return ok_flag != 0;
-}
-
-// Last CTA to finish advances the epoch for the next call and resets the ticket.
-__device__ void tp_finish(const TpComm& c) {
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    const unsigned t = atomicAdd(c.epoch + 1, 1u);
-    if (t == gridDim.x - 1) {
-      c.epoch[1] = 0;
-      __threadfence();
-      atomicAdd(c.epoch, 1u);
-    }
-  }
-}
-
-__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(h[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
-__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
-  uint4 v;
-  v.x = pack_bf16(f[0], f[1]);
-  v.y = pack_bf16(f[2], f[3]);
-  v.z = pack_bf16(f[4], f[5]);
-  v.w = pack_bf16(f[6], f[7]);
-  return v;
-}
 
 constexpr int kTpMaxVec = 4;   // hidden <= 256 * 4 * 8 = 8192
 
@@ -151,78 +47,8 @@ tp_reduce_norm_kernel(const TpComm c, long long buf_offset, const __nv_bfloat16*
   __shared__ float scratch[32];
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(c.epoch);
   const bool ok = tp_barrier(c, epoch, 0);
-  const int nvec = hidden >> 3;
-  if (ok) {
-    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-      const long long off = buf_offset + static_cast<long long>(row) * hidden * 2;
-      float vals[kTpMaxVec][8];
-      float ss = 0.f;
-#pragma unroll
-      for (int i = 0; i < kTpMaxVec; ++i) {
-        const int v = threadIdx.x + i * kTpThreads;
-        if (v < nvec) {
-          float acc[8];
-          if (c.mc_buf != nullptr) {
-            unpack8(multimem_ld_reduce_bf16x8(static_cast<const char*>(c.mc_buf) + off + v * 16), acc);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-            // fixed rank order, fp32 accumulation: every rank computes bit-identical sums
-            for (int r = 0; r < c.world; ++r) {
-              float t[8];
-              unpack8(ld_relaxed_sys_v4(static_cast<const char*>(c.peer_buf[r]) + off + v * 16), t);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) acc[j] += t[j];
-            }
-          }
-          if (mode == 0) {
-            if (residual_in != nullptr) {
-              float rr[8];
-              unpack8(*reinterpret_cast<const uint4*>(residual_in + static_cast<size_t>(row) * hidden + v * 8), rr);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) acc[j] += rr[j];
-            }
-            *reinterpret_cast<uint4*>(residual_out + static_cast<size_t>(row) * hidden + v * 8) = pack8(acc);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              acc[j] = __bfloat162float(__float2bfloat16(acc[j]));
-              ss += acc[j] * acc[j];
-            }
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) vals[i][j] = acc[j];
-        }
-      }
-      float inv = 1.f;
-      if (mode == 0) {
-        ss = warp_sum(ss);
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        if (lane == 0) scratch[warp] = ss;
-        __syncthreads();
-        float t = lane < (kTpThreads >> 5) ? scratch[lane] : 0.f;
-        t = warp_sum(t);
-        __syncthreads();
-        inv = rsqrtf(t / static_cast<float>(hidden) + eps);
-      }
-#pragma unroll
-      for (int i = 0; i < kTpMaxVec; ++i) {
-        const int v = threadIdx.x + i * kTpThreads;
-        if (v < nvec) {
-          float o[8];
-          if (mode == 0) {
-            float g[8];
-            unpack8(*reinterpret_cast<const uint4*>(w + v * 8), g);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * inv * g[j];
-          } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = vals[i][j];
-          }
-          *reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * hidden + v * 8) = pack8(o);
-        }
-      }
-    }
-  }
+  if (ok)
+    tp_reduce_rows<kTpMaxVec>(c, buf_offset, residual_in, residual_out, w, y, rows, hidden, eps, mode, scratch);
   tp_finish(c);
 }
 

@@ -27,10 +27,12 @@ typedef struct XvGemmPlan {
   int stages;
   int smem_bytes;
   int ctas_per_sm;         // resident CTAs per SM the persistent grid is sized for
+  int pair;                // 1: CTA-pair kernel (cta_group::2, 256 x 256 tiles)
   long long workspace_bytes;
 } XvGemmPlan;
 
 int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan);
+void xv_gemm_disable_pair(int disable);   // test hook: force the single-CTA kernel
 int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
                  long long ldy, void* workspace, long long workspace_bytes, int num_sms, int* status,
                  cudaStream_t stream);
@@ -121,6 +123,13 @@ int xv_tp_reduce_norm(const void* const* peer_bufs, void* const* peer_flags, con
 int xv_tp_argmax(const void* const* peer_bufs, void* const* peer_flags, void* epoch, int rank, int world,
                  long long slots_offset, const void* logits, long long ld, int local_vocab, int valid_vocab,
                  int vocab_start, long long* out, int rows, unsigned spin_limit, int* status, cudaStream_t stream);
+
+// RowParallel GEMM + all-reduce + residual add + RMSNorm in ONE kernel (see gemm_sm100.cu).
+int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long ldx, long long ldw, void* workspace,
+                    long long workspace_bytes, int num_sms, const void* const* peer_bufs, void* const* peer_flags,
+                    const void* mc_buf, void* epoch, int rank, int world, long long buf_offset, void* grid_sync,
+                    const void* residual_in, void* residual_out, const void* norm_w, void* y_out, float eps, int mode,
+                    unsigned spin_us, int* status, cudaStream_t stream);
 
 // ---- diagnostics ----
 // Waits (bounded) on a flag nobody sets and reports kHostFlagTimeout through `status`;

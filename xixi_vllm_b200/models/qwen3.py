@@ -28,9 +28,10 @@ class Qwen3MLP:
                                                        dtype=dtype, device=device, interleave=8 if on_gpu else 0)
         self.down_proj = RowParallelLinear(cfg.intermediate_size, cfg.hidden_size, dtype=dtype, device=device)
 
-    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-        """Returns this rank's partial sum of the MLP output."""
-        return self.down_proj(self.gate_up_proj.forward_act(x), reduce=False, out=out, defer=True)
+    def forward(self, x: torch.Tensor, comm: TPComm, final: bool = False):
+        """Returns this rank's partial sum of the MLP output (possibly not computed yet: the
+        communicator may run the down projection inside the kernel that reduces it)."""
+        return comm.row_linear(self.down_proj, self.gate_up_proj.forward_act(x), final)
 
 
 class Qwen3Attention:
@@ -49,15 +50,14 @@ class Qwen3Attention:
         self.num_kv_heads = self.qkv_proj.num_kv_heads
         self.scale = cfg.head_dim ** -0.5
 
-    def forward(self, x: torch.Tensor, batch, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                out: torch.Tensor | None = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, batch, k_cache: torch.Tensor, v_cache: torch.Tensor, comm: TPComm):
         qkv = self.qkv_proj(x, defer=True)      # split-K partials are summed inside the next kernel
         q = ops.qk_norm_rope_cache(qkv, self.q_norm.weight, self.k_norm.weight, self.q_norm.eps,
                                    self.rotary.cos_sin, batch.positions, batch.slots, k_cache, v_cache,
                                    self.num_heads, self.num_kv_heads, self.head_dim)
         o = ops.paged_attention(q, k_cache, v_cache, batch.attn, self.scale, self.num_heads,
                                 self.num_kv_heads, self.head_dim)
-        return self.o_proj(o, reduce=False, out=out, defer=True)
+        return comm.row_linear(self.o_proj, o)
 
 
 class Qwen3DecoderLayer:
@@ -71,13 +71,12 @@ class Qwen3DecoderLayer:
     def forward(self, partial, residual, batch, k_cache, v_cache, comm: TPComm, last: bool = False):
         """``partial`` is the previous block's unreduced output (or the embedding partial).
         ``last`` marks the layer whose MLP output feeds the forward's final reduction."""
-        T = partial.shape[0]
         ln = self.input_layernorm
         h, residual = comm.reduce_add_rmsnorm(partial, residual, ln.weight, ln.eps)
-        attn_partial = self.self_attn.forward(h, batch, k_cache, v_cache, out=comm.alloc_partial(T))
+        attn_partial = self.self_attn.forward(h, batch, k_cache, v_cache, comm)
         ln = self.post_attention_layernorm
         h, residual = comm.reduce_add_rmsnorm(attn_partial, residual, ln.weight, ln.eps)
-        return self.mlp.forward(h, out=comm.alloc_partial(T, final=last)), residual
+        return self.mlp.forward(h, comm, final=last), residual
 
 
 class Qwen3Model:
@@ -125,6 +124,9 @@ class _NoReduceOnce(TPComm):
 
     def alloc_partial(self, tokens, final=False):
         return self.inner.alloc_partial(tokens, final)
+
+    def row_linear(self, proj, x, final=False):
+        return self.inner.row_linear(proj, x, final)
 
     def reduce_add_rmsnorm(self, partial, residual, w, eps):
         if self._first:

@@ -38,8 +38,13 @@ def sources() -> list[str]:
     return sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cu")))
 
 
+def _headers() -> list[str]:
+    return (glob.glob(os.path.join(CSRC, "common", "*.cuh")) + glob.glob(os.path.join(CSRC, "kernels", "*.cuh"))
+            + glob.glob(os.path.join(CSRC, "kernels", "*.h")))
+
+
 def _deps_mtime() -> float:
-    files = sources() + glob.glob(os.path.join(CSRC, "common", "*.cuh")) + glob.glob(os.path.join(CSRC, "kernels", "*.h"))
+    files = sources() + _headers()
     return max(os.path.getmtime(f) for f in files)
 
 
@@ -53,8 +58,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     nvcc = nvcc_path()
     os.makedirs(OBJ_DIR, exist_ok=True)
     extra = ["-Xptxas", "-v"] if verbose else []
-    hdr_time = max([os.path.getmtime(f) for f in glob.glob(os.path.join(CSRC, "common", "*.cuh"))
-                    + glob.glob(os.path.join(CSRC, "kernels", "*.h"))] or [0.0])
+    hdr_time = max([os.path.getmtime(f) for f in _headers()] or [0.0])
 
     def compile_one(src: str) -> str:
         obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")

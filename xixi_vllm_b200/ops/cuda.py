@@ -38,7 +38,7 @@ launch_count = 0
 class GemmPlan(ctypes.Structure):
     _fields_ = [("swapped", _i32), ("bn", _i32), ("tiles_a", _i32), ("tiles_b", _i32), ("splits", _i32),
                 ("k_blocks_per_split", _i32), ("stages", _i32), ("smem_bytes", _i32),
-                ("ctas_per_sm", _i32), ("workspace_bytes", _i64)]
+                ("ctas_per_sm", _i32), ("pair", _i32), ("workspace_bytes", _i64)]
 
 
 def lib():
@@ -77,6 +77,8 @@ def lib():
                                     _i32, ctypes.c_uint, _vp, _vp]
     L.xv_tp_argmax.argtypes = [_vp, _vp, _vp, _i32, _i32, _i64, _vp, _i64, _i32, _i32, _i32, _vp, _i32,
                                ctypes.c_uint, _vp, _vp]
+    L.xv_gemm_bf16_tp.argtypes = [_vp, _vp, _i32, _i32, _i32, _i64, _i64, _vp, _i64, _i32, _vp, _vp, _vp, _vp, _i32,
+                                  _i32, _i64, _vp, _vp, _vp, _vp, _vp, _f32, _i32, ctypes.c_uint, _vp, _vp]
     L.xv_selftest_bounded_wait.argtypes = [_vp, _vp, ctypes.c_uint, _vp]
     L.xv_num_sms.restype = _i32
     _lib = L
@@ -395,6 +397,24 @@ def tp_argmax(peer_bufs, peer_flags, epoch, rank: int, world: int, slots_offset:
     _check(lib().xv_tp_argmax(peer_bufs, peer_flags, epoch.data_ptr(), rank, world, slots_offset, logits.data_ptr(),
                               logits.stride(0), local_vocab, valid_vocab, vocab_start, out.data_ptr(),
                               logits.shape[0], spin_limit, status.data_ptr(), _stream()), "tp_argmax")
+
+
+def gemm_tp_fused(x, w, peer_bufs, peer_flags, mc_ptr: int, epoch, rank: int, world: int, buf_offset: int,
+                  grid_sync, residual_in, residual_out, norm_w, y, eps: float, mode: int, spin_us: int) -> None:
+    """RowParallel GEMM + cross-rank sum + residual add + RMSNorm in one kernel (``xv_gemm_bf16_tp``)."""
+    _bf16(x, w)
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    M, K = x.shape
+    N = w.shape[0]
+    st = _state(x)
+    _check(lib().xv_gemm_bf16_tp(
+        x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0), w.stride(0), st.gemm_ws.data_ptr(), st.gemm_ws.numel(),
+        st.num_sms, peer_bufs, peer_flags, mc_ptr or None, epoch.data_ptr(), rank, world, buf_offset,
+        grid_sync.data_ptr(), residual_in.data_ptr() if residual_in is not None else None,
+        residual_out.data_ptr() if residual_out is not None else None,
+        norm_w.data_ptr() if norm_w is not None else None, y.data_ptr(), eps, mode, spin_us, st.status.data_ptr(),
+        _stream()), f"gemm+allreduce {M}x{N}x{K}")
 
 
 def device_status(t: torch.Tensor) -> torch.Tensor:

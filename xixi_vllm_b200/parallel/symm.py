@@ -28,7 +28,21 @@ from ..ops import cuda
 from .groups import Group
 from .tp_comm import TPComm
 
-__all__ = ["SymmetricBuffer", "FusedTPComm"]
+__all__ = ["SymmetricBuffer", "FusedTPComm", "DeferredRowGemm"]
+
+
+class DeferredRowGemm:
+    """A row-parallel projection whose GEMM has not run yet: the communicator launches it
+    together with the reduction that consumes it (one kernel)."""
+
+    __slots__ = ("x", "weight", "final")
+
+    def __init__(self, x: torch.Tensor, weight: torch.Tensor, final: bool) -> None:
+        self.x, self.weight, self.final = x, weight, final
+
+    @property
+    def shape(self):
+        return (self.x.shape[0], self.weight.shape[0])
 
 FLAG_BYTES = 4096          # two channels x 8 ranks x 4 bytes used; one page reserved
 SPIN_LIMIT = 2_000_000     # microseconds a kernel waits for a peer before it reports and returns
@@ -76,6 +90,9 @@ class FusedTPComm(TPComm):
         self.epoch = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.epoch[0] = 1
         self.status = cuda.device_status(self.epoch)
+        self.grid_sync = torch.zeros(4, dtype=torch.int32, device=self.device)
+        # XV_TP_FUSE_GEMM=0 keeps the GEMM and the reduction as two kernels
+        self.fuse_gemm = os.environ.get("XV_TP_FUSE_GEMM", "1") != "0"
         self._idx = 0
         self._base = self.symm.local.data_ptr()
         self._views = [self.symm.local[i * self.buf_bytes:(i + 1) * self.buf_bytes].view(torch.bfloat16)
@@ -106,8 +123,28 @@ class FusedTPComm(TPComm):
         buf.copy_(partial)
         return buf.data_ptr() - self._base
 
+    def row_linear(self, proj, x: torch.Tensor, final: bool = False):
+        """Output of a RowParallelLinear as something ``reduce_add_rmsnorm`` / ``all_reduce`` accept."""
+        if self.fuse_gemm and proj.bias is None:
+            return DeferredRowGemm(x, proj.weight, final)
+        return proj(x, reduce=False, out=self.alloc_partial(x.shape[0], final))
+
+    def _fused(self, d: DeferredRowGemm, residual, w, eps, mode):
+        T = d.x.shape[0]
+        buf = self.alloc_partial(T, d.final)
+        off = buf.data_ptr() - self._base
+        y = torch.empty((T, self.hidden), dtype=torch.bfloat16, device=self.device)
+        res_out = None
+        if mode == 0:
+            res_out = residual if residual is not None else torch.empty_like(y)
+        cuda.gemm_tp_fused(d.x, d.weight, self._bufs, self._flags, self.mc_ptr, self.epoch, self.rank, self.world,
+                           off, self.grid_sync, residual, res_out, w, y, eps, mode, SPIN_LIMIT)
+        return y, res_out
+
     # --- reductions -----------------------------------------------------------------------------
     def reduce_add_rmsnorm(self, partial, residual, w, eps):
+        if isinstance(partial, DeferredRowGemm):
+            return self._fused(partial, residual, w, eps, 0)
         T = partial.shape[0]
         off = self._offset_of(partial)
         y = torch.empty((T, self.hidden), dtype=torch.bfloat16, device=self.device)
@@ -117,6 +154,8 @@ class FusedTPComm(TPComm):
         return y, res_out
 
     def all_reduce(self, x):
+        if isinstance(x, DeferredRowGemm):
+            return self._fused(x, None, None, 0.0, 1)[0]
         T = x.shape[0]
         off = self._offset_of(x)
         y = torch.empty((T, self.hidden), dtype=torch.bfloat16, device=self.device)

@@ -33,6 +33,10 @@ class TPComm:
         ``final`` marks the last reduction of a forward."""
         return None
 
+    def row_linear(self, proj, x: torch.Tensor, final: bool = False):
+        """Runs (or defers) a RowParallelLinear whose output goes to the next reduction point."""
+        return proj(x, reduce=False, out=self.alloc_partial(x.shape[0], final), defer=True)
+
     def reduce_add_rmsnorm(self, partial: torch.Tensor, residual: torch.Tensor | None,
                            w: torch.Tensor, eps: float):
         """Sum ``partial`` over the TP group, add it to ``residual`` (or start the residual

@@ -16,6 +16,7 @@ from ..ops import dispatch as ops
 from ..parallel.collectives import recv_tensors, send_tensors
 from ..parallel.groups import get_pp_group, get_tp_group
 from ..parallel.pp import IntermediateTensors
+from ..utils.nvtx import nvtx_range
 from .graphs import CUDAGraphRunner, make_bs_list
 from .kv_pool import KVPool
 from .sampler import Sampler
@@ -98,13 +99,17 @@ class ModelRunner:
         with torch.no_grad():
             if use_graph:
                 bucket = self.graphs.pad_bs(n_d)
-                batch = self.stager.build(sched, pad_to=bucket, fixed_blocks=True)
+                with nvtx_range("stage"):
+                    batch = self.stager.build(sched, pad_to=bucket, fixed_blocks=True)
                 greedy = batch.all_greedy
-                tokens = self.graphs.replay(bucket, greedy)
+                with nvtx_range("decode_graph"):
+                    tokens = self.graphs.replay(bucket, greedy)
             else:
-                batch = self.stager.build(sched)
+                with nvtx_range("stage"):
+                    batch = self.stager.build(sched)
                 inter = None if self.is_first_pp else self._recv(batch.num_tokens)
-                tokens = self._forward(batch, inter)
+                with nvtx_range("forward"):
+                    tokens = self._forward(batch, inter)
                 if not self.is_last_pp:
                     self._send(tokens)
                     tokens = None

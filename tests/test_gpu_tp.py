@@ -14,6 +14,8 @@ def _need(n):
 
 def _fused_rank(rank, world, nvls):
     os.environ["XV_TP_NVLS"] = "1" if nvls else "0"
+    os.environ["XV_TP_FUSE_GEMM"] = "1"
+    os.environ["XV_TP_FUSE_GEMM_MAX_T"] = "100000"
     import torch.distributed as dist
 
     from xixi_vllm_b200.ops import cpu_ref, cuda
@@ -44,6 +46,32 @@ def _fused_rank(rank, world, nvls):
         buf2.copy_(parts[rank].to(dev))
         s = comm.all_reduce(buf2)
         errs.append(float((s.float().cpu() - total).abs().max()))
+    # GEMM + all-reduce + residual + RMSNorm as one kernel (row-parallel projection)
+    class _Proj:
+        bias = None
+
+    for it, (T, K) in enumerate([(1, 256), (40, 512), (256, 1024), (300, 2048), (512, 512)]):
+        g = torch.Generator().manual_seed(500 + it)
+        xs = [(torch.randn(T, K, generator=g) * 0.5).bfloat16() for _ in range(world)]
+        ws = [(torch.randn(H, K, generator=g) * 0.05).bfloat16() for _ in range(world)]
+        resid = torch.randn(T, H, generator=g).bfloat16()
+        nw = (1 + 0.1 * torch.randn(H, generator=g)).bfloat16()
+        proj = _Proj()
+        proj.weight = ws[rank].to(dev)
+        comm.begin_forward()
+        d = comm.row_linear(proj, xs[rank].to(dev), final=(it % 2 == 1))
+        r_dev = resid.to(dev).clone()
+        y, r_out = comm.reduce_add_rmsnorm(d, r_dev, nw.to(dev), 1e-6)
+        parts = [(x.float() @ w.float().t()).bfloat16().float() for x, w in zip(xs, ws)]
+        r_ref = (sum(parts) + resid.float()).bfloat16()
+        y_ref = cpu_ref.rmsnorm(r_ref, nw, 1e-6)
+        scale = float(r_ref.float().abs().max())
+        errs.append(float((r_out.float().cpu() - r_ref.float()).abs().max()) / max(scale, 1.0) * 2)
+        errs.append(float((y.float().cpu() - y_ref.float()).abs().max()) / 4)
+        d2 = comm.row_linear(proj, xs[rank].to(dev))
+        s2 = comm.all_reduce(d2)
+        errs.append(float((s2.float().cpu() - sum(parts)).abs().max()) / max(scale, 1.0) * 2)
+    fused_gemm = comm.fuse_gemm
     # vocab-parallel argmax: every rank must pick the global best
     g = torch.Generator().manual_seed(7)
     full = torch.randn(5, 4096, generator=g).bfloat16()
@@ -56,6 +84,7 @@ def _fused_rank(rank, world, nvls):
     torch.cuda.synchronize()
     cuda.check_status(dev)
     dist.barrier()
+    assert fused_gemm
     return max(errs), ids.tolist(), want.tolist(), bool(comm.mc_ptr)
 
 

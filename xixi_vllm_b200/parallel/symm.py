@@ -91,8 +91,12 @@ class FusedTPComm(TPComm):
         self.epoch[0] = 1
         self.status = cuda.device_status(self.epoch)
         self.grid_sync = torch.zeros(4, dtype=torch.int32, device=self.device)
-        # XV_TP_FUSE_GEMM=0 keeps the GEMM and the reduction as two kernels
-        self.fuse_gemm = os.environ.get("XV_TP_FUSE_GEMM", "1") != "0"
+        # XV_TP_FUSE_GEMM=1 runs the row-parallel GEMM and its reduction as ONE kernel (measured slower than
+        # the two-kernel form at TP=2 on Qwen3-8B, so it is opt-in)
+        self.fuse_gemm = os.environ.get("XV_TP_FUSE_GEMM", "0") == "1"
+        # Above this many tokens the projection runs on the CTA-pair GEMM and the reduction in
+        # its own kernel: at prefill sizes the faster GEMM outweighs the saved launch.
+        self.fuse_gemm_max_tokens = int(os.environ.get("XV_TP_FUSE_GEMM_MAX_T", "256"))
         self._idx = 0
         self._base = self.symm.local.data_ptr()
         self._views = [self.symm.local[i * self.buf_bytes:(i + 1) * self.buf_bytes].view(torch.bfloat16)
@@ -125,7 +129,7 @@ class FusedTPComm(TPComm):
 
     def row_linear(self, proj, x: torch.Tensor, final: bool = False):
         """Output of a RowParallelLinear as something ``reduce_add_rmsnorm`` / ``all_reduce`` accept."""
-        if self.fuse_gemm and proj.bias is None:
+        if self.fuse_gemm and proj.bias is None and x.shape[0] <= self.fuse_gemm_max_tokens:
             return DeferredRowGemm(x, proj.weight, final)
         return proj(x, reduce=False, out=self.alloc_partial(x.shape[0], final))
 

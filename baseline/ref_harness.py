@@ -22,7 +22,15 @@ def run(args, Workload, ClockSampler, flush_l2) -> dict:
 
     if HERE not in sys.path:
         sys.path.insert(0, HERE)
-    os.environ["PYTHONPATH"] = HERE + os.pathsep + os.path.dirname(HERE) + os.pathsep + os.environ.get("PYTHONPATH", "")
+    env_dir = os.path.join(HERE, "ref_env")
+    os.environ["PYTHONPATH"] = os.pathsep.join([env_dir, HERE, os.path.dirname(HERE), os.environ.get("PYTHONPATH", "")])
+    # the same aliases ref_env/sitecustomize.py installs in the spawned workers
+    import torch.distributed as dist
+
+    if not hasattr(dist, "all_gather_single"):
+        dist.all_gather_single = dist.all_gather_into_tensor
+    if not hasattr(dist, "reduce_scatter_single"):
+        dist.reduce_scatter_single = dist.reduce_scatter_tensor
     import _ref  # the reference package, unmodified
 
     from baseline.ref_model import make_reference_model_dir

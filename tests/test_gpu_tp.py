@@ -153,3 +153,14 @@ def test_engine_tp2_sampled_generation_runs(tmp_path):
     d = _tiny_dir(tmp_path)
     out = _probe(d, tp=2, comm="fused", cg=True, port=29821, temperature=0.8)
     assert all(len(x) == 10 for x in out)
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("kw", [dict(pp=2, port=29831), dict(dp=2, port=29841), dict(pp=2, cg=True, port=29851)])
+def test_engine_pp2_and_dp2_match_single_gpu(tmp_path, kw):
+    """Pipeline stages hand hidden state + residual over NCCL p2p; DP replicas are independent engines."""
+    _need(2)
+    d = _tiny_dir(tmp_path)
+    ref = _probe(d)
+    out = _probe(d, **kw)
+    assert _agree(ref, out) >= 10, (ref, out)

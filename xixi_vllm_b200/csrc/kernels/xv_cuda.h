@@ -131,6 +131,78 @@ int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long
                     const void* residual_in, void* residual_out, const void* norm_w, void* y_out, float eps, int mode,
                     unsigned spin_us, int* status, cudaStream_t stream);
 
+// ---- native forward executor (forward.cu): one call launches a whole Qwen3 forward ----
+typedef struct XvLayerWeights {
+  const void* input_norm;
+  const void* qkv;
+  const void* q_norm;
+  const void* k_norm;
+  const void* o;
+  const void* post_norm;
+  const void* gate_up;
+  const void* down;
+  void* k_cache;
+  void* v_cache;
+} XvLayerWeights;
+
+typedef struct XvModelDesc {
+  int num_layers, hidden, hq, hkv, head_dim, inter_local, qkv_rows, block_size;
+  float eps, attn_scale;
+  int gate_up_interleaved;
+  int vocab_start, vocab_rows;        // this rank's embedding / LM-head shard
+  int lm_head_rows, lm_valid;         // rows of the shard, and how many of them are real vocabulary
+  const void* embed;
+  const void* final_norm;
+  const void* lm_head;
+  const float* cos_sin;
+  const XvLayerWeights* layers;       // host array of num_layers entries
+  int tp_rank, tp_world;              // tensor parallel; with tp_world == 1 the fields below are unused
+  const void* const* peer_bufs;       // host arrays of tp_world device pointers
+  void* const* peer_flags;
+  const void* mc_buf;
+  void* epoch;
+  long long buf_bytes;                // size of each of the three symmetric partial buffers
+  long long slots_offset;             // byte offset of the argmax slots in the symmetric buffer
+  unsigned spin_us;
+} XvModelDesc;
+
+typedef struct XvBatchDesc {
+  int num_tokens, num_seqs, num_decode, max_q_len, max_blocks, num_samples, all_greedy;
+  const int* input_ids;
+  const int* positions;
+  const int* slots;
+  const int* cu_q;
+  const int* kv_lens;
+  const int* block_tables;
+  const int* sample_rows;
+} XvBatchDesc;
+
+typedef struct XvArena {              // device scratch sized for the largest step; nothing is allocated per call
+  void* h;                            // [T, hidden] normalised activations
+  void* qkv;                          // [T, qkv_rows]
+  void* q;                            // [T, hq * head_dim]
+  void* attn;                         // [T, hq * head_dim]
+  void* act;                          // [T, inter_local]
+  void* gu;                           // [T, 2 * inter_local] (only without the fused SiLU-mul epilogue)
+  void* residual;                     // [T, hidden]
+  void* partial;                      // [T, hidden] row-parallel output when tp_world == 1
+  void* hidden_out;                   // [S, hidden]
+  void* logits;                       // [S, lm_head_rows]
+  long long* tokens;                  // [S]
+  void* gemm_ws;
+  long long gemm_ws_bytes;
+  void* attn_ws;
+  long long attn_ws_bytes;
+  int* status;
+  int num_sms;
+} XvArena;
+
+// Returns 0 or the first failing launch's XV_ERR_* code (xv_forward_failed_op() names the step).
+int xv_qwen3_forward(const XvModelDesc* model, const XvBatchDesc* batch, const XvArena* arena, cudaStream_t stream);
+int xv_forward_failed_op(void);
+long long xv_forward_launch_calls(void);   // launch calls issued by forwards so far (each is at least one kernel)
+int xv_forward_decode_splits(int num_seqs, int hkv, int num_sms, int max_tokens_per_seq);
+
 // ---- diagnostics ----
 // Waits (bounded) on a flag nobody sets and reports kHostFlagTimeout through `status`;
 // proves the timeout path returns instead of hanging. `limit` polls.

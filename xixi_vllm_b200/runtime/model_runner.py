@@ -63,12 +63,32 @@ class ModelRunner:
         self._step_events: dict[int, tuple] = {}
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        # single-stage GPU models run through the native executor (one C call per forward)
+        self.native = None
+        if self.is_cuda and self.is_first_pp and self.is_last_pp and os.environ.get("XV_NATIVE_FORWARD", "1") != "0":
+            from .native_forward import NativeForward
+
+            tp = get_tp_group()
+            if tp.size == 1 or hasattr(model.comm, "symm"):
+                self.native = NativeForward(model, kv, max_tokens=self.max_tokens, max_samples=self.max_bs)
         self.graphs: CUDAGraphRunner | None = None
         if self.is_cuda and not config.enforce_eager:
             self._capture_graphs()
 
     # --- forward --------------------------------------------------------------------------
     def _forward(self, batch, intermediate=None):
+        if self.native is not None:
+            out = self.native.forward(batch)
+            if batch.all_greedy:
+                return out
+            logits = out
+            head = self.model.lm_head
+            if head.tp.size > 1:
+                from ..parallel import collectives as coll
+
+                logits = coll.all_gather(logits, head.tp, dim=-1)
+            logits = logits[..., : head.num_embeddings]
+            return self.sampler(logits, batch.temperature, batch.top_k, batch.top_p, batch.min_p, rng=batch.rng)
         out = self.model.forward(batch.input_ids, batch, self.kv, intermediate)
         if not self.is_last_pp:
             return out

@@ -174,8 +174,6 @@ def run_ours(args) -> None:
     model_dir = os.path.join(tempfile.gettempdir(), f"xv_bench_{args.model}_{os.getuid()}")
     if rank == 0:
         make_model_dir(model_dir, args.model, weights=False)
-    if world > 1:
-        time.sleep(0.0)
     context = args.prompt_max + args.out_tokens
     cfg_kwargs = dict(model=model_dir, load_format="dummy", dtype="bfloat16", context_len=context,
                       max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_batched_tokens,

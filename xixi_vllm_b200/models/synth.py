@@ -49,8 +49,12 @@ def make_model_dir(out_dir: str, arch: str = "tiny", *, weights: bool = True, se
                    **overrides) -> str:
     cfg = qwen3_arch_config(arch, **overrides)
     os.makedirs(out_dir, exist_ok=True)
-    with open(os.path.join(out_dir, "config.json"), "w", encoding="utf-8") as f:
+    # written under a temporary name and renamed, so a concurrent reader (another rank of the same
+    # launch) sees either no file or the complete one
+    tmp = os.path.join(out_dir, f".config.json.{os.getpid()}")
+    with open(tmp, "w", encoding="utf-8") as f:
         json.dump(cfg, f, indent=1)
+    os.replace(tmp, os.path.join(out_dir, "config.json"))
     if not weights:
         return out_dir
     dtype = dtype or getattr(torch, cfg["torch_dtype"])

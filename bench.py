@@ -62,6 +62,9 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--tp-comm", default="auto", choices=("auto", "fused", "nccl"),
                     help="tensor-parallel reduction path (fused peer-memory kernels or NCCL)")
+    ap.add_argument("--emulate-tp", type=int, default=1,
+                    help="single GPU, model dimensions cut to one rank's shard of this tensor-parallel degree "
+                         "(compute share of a rank without any communication; diagnostic, not a benchmark)")
     ap.add_argument("--profile", action="store_true",
                     help="bracket the timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     return ap.parse_args()
@@ -171,9 +174,18 @@ def run_ours(args) -> None:
         if world == 1 and args.gpus > 1:
             raise SystemExit(f"--gpus {args.gpus} needs torchrun with --nproc-per-node {args.gpus}")
         raise SystemExit(f"WORLD_SIZE={world} does not match --gpus {args.gpus}")
-    model_dir = os.path.join(tempfile.gettempdir(), f"xv_bench_{args.model}_{os.getuid()}")
+    model_dir = os.path.join(tempfile.gettempdir(), f"xv_bench_{args.model}_{args.emulate_tp}_{os.getuid()}")
     if rank == 0:
-        make_model_dir(model_dir, args.model, weights=False)
+        over = {}
+        if args.emulate_tp > 1:
+            from xixi_vllm_b200.config import qwen3_arch_config
+
+            full = qwen3_arch_config(args.model)
+            t = args.emulate_tp
+            over = dict(num_attention_heads=full["num_attention_heads"] // t,
+                        num_key_value_heads=max(1, full["num_key_value_heads"] // t),
+                        intermediate_size=full["intermediate_size"] // t, vocab_size=full["vocab_size"] // t)
+        make_model_dir(model_dir, args.model, weights=False, **over)
     context = args.prompt_max + args.out_tokens
     cfg_kwargs = dict(model=model_dir, load_format="dummy", dtype="bfloat16", context_len=context,
                       max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_batched_tokens,
@@ -251,6 +263,7 @@ def run_ours(args) -> None:
                    "parallelism": f"tp{args.gpus}", "prompt_len": f"U[{args.prompt_min},{args.prompt_max}]",
                    "output_len": args.out_tokens, "max_num_batched_tokens": args.max_batched_tokens,
                    "kv_block_size": 16, "decode_cuda_graph": not args.eager, "tp_comm": args.tp_comm,
+                   **({"emulate_tp_shard": args.emulate_tp} if args.emulate_tp > 1 else {}),
                    "l2": "flushed between timed steps (256 MiB write)",
                    "step": "one engine step in steady-state continuous batching"},
         "clocks": clk,

@@ -147,6 +147,17 @@ def test_engine_tp2_matches_tp1(tmp_path, comm, cg):
 
 
 @pytest.mark.timeout(600)
+def test_engine_tp2_row_sharded_reduction_matches(tmp_path, monkeypatch):
+    """The two-shot reduction (default from 4 ranks up) forced on at 2 ranks."""
+    _need(2)
+    d = _tiny_dir(tmp_path)
+    ref = _probe(d)
+    monkeypatch.setenv("XV_TP_SHARDED", "1")
+    out = _probe(d, tp=2, comm="fused", cg=True, port=29861)
+    assert _agree(ref, out) >= 10, (ref, out)
+
+
+@pytest.mark.timeout(600)
 def test_engine_tp2_sampled_generation_runs(tmp_path):
     """Non-greedy sampling under TP gathers logits and draws identical tokens on every rank."""
     _need(2)

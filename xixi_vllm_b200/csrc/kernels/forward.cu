@@ -53,6 +53,12 @@ int row_linear_reduce_norm(Ctx& c, const void* x, const void* w, int k, const vo
     ++c.call_idx;
     XV_TRY(10, xv_gemm_bf16(x, w, symm_local(c, which), T, H, k, k, k, H, c.a->gemm_ws, c.a->gemm_ws_bytes,
                             c.a->num_sms, c.a->status, c.s));
+    if (m->h_offset >= 0) {
+      XV_TRY(15, xv_tp_reduce_norm_sharded(m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch, m->tp_rank, m->tp_world,
+                                           static_cast<long long>(which) * m->buf_bytes, m->h_offset, 1,
+                                           c.a->residual, norm_w, T, H, m->eps, m->spin_us, c.a->status, c.s));
+      return 0;
+    }
     XV_TRY(11, xv_tp_reduce_norm(m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch, m->tp_rank, m->tp_world,
                                  static_cast<long long>(which) * m->buf_bytes, c.a->residual, c.a->residual, norm_w,
                                  c.a->h, T, H, m->eps, 0, m->spin_us, c.a->status, c.s));
@@ -107,6 +113,11 @@ int xv_qwen3_forward(const XvModelDesc* m, const XvBatchDesc* b, const XvArena* 
     ++c.call_idx;
     XV_TRY(1, xv_embedding(b->input_ids, m->embed, symm_local(c, which), T, H, m->vocab_start, m->vocab_rows, stream));
     const void* w0 = L > 0 ? m->layers[0].input_norm : m->final_norm;
+    if (m->h_offset >= 0) {
+      XV_TRY(5, xv_tp_reduce_norm_sharded(m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch, m->tp_rank, m->tp_world,
+                                          static_cast<long long>(which) * m->buf_bytes, m->h_offset, 0, a->residual, w0,
+                                          T, H, m->eps, m->spin_us, a->status, stream));
+    } else
     XV_TRY(2, xv_tp_reduce_norm(m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch, m->tp_rank, m->tp_world,
                                 static_cast<long long>(which) * m->buf_bytes, nullptr, a->residual, w0, a->h, T, H,
                                 m->eps, 0, m->spin_us, a->status, stream));

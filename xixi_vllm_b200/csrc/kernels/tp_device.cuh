@@ -51,6 +51,17 @@ __device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
   return v;
 }
 
+// Broadcast of eight bf16 values to the same offset on every rank through NVSwitch.
+__device__ __forceinline__ void multimem_st_bf16x8(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys_v4(void* p, const uint4& v) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
 // Announce this rank's data for `epoch` (one thread of the grid) and wait until every rank has
 // announced. Returns false if a peer never arrived within the spin limit.
 __device__ inline bool tp_barrier(const TpComm& c, uint32_t epoch, int channel) {

@@ -52,6 +52,107 @@ tp_reduce_norm_kernel(const TpComm c, long long buf_offset, const __nv_bfloat16*
   tp_finish(c);
 }
 
+// Row-sharded ("two-shot") form of the reduction point, used by the native forward:
+//   barrier -> rank r sums rows r, r + world, ... of all ranks' partials (in-switch or by peer
+//   loads), adds its shard of the residual stream (which stays sharded by rows: only the owner
+//   ever reads a residual row), normalises, and broadcasts the normalised rows into every rank's
+//   activation buffer (multimem.st or peer stores) -> barrier, so the kernel's end means the full
+//   [rows, hidden] activation is present on every rank.
+// Per reduction each GPU sends and receives about rows*hidden*2 bytes regardless of the number
+// of ranks; the one-shot kernel above moves world times more and is kept for small worlds and
+// for callers that need the full residual on every rank (pipeline hand-off).
+__global__ void __launch_bounds__(kTpThreads)
+tp_reduce_norm_sharded_kernel(const TpComm c, long long buf_offset, long long h_offset, int has_residual,
+                              __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ w, int rows,
+                              int hidden, float eps) {
+  __shared__ float scratch[32];
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(c.epoch);
+  bool ok = tp_barrier(c, epoch, 0);
+  const int nvec = hidden >> 3;
+  if (ok) {
+    for (int row = c.rank + c.world * static_cast<int>(blockIdx.x); row < rows; row += c.world * gridDim.x) {
+      const long long off = buf_offset + static_cast<long long>(row) * hidden * 2;
+      float vals[kTpMaxVec][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < kTpMaxVec; ++i) {
+        const int v = threadIdx.x + i * kTpThreads;
+        if (v < nvec) {
+          float acc[8];
+          tp_load_sum8(c, off + v * 16, acc);
+          __nv_bfloat16* rr = residual + static_cast<size_t>(row) * hidden + v * 8;
+          if (has_residual) {
+            float t[8];
+            unpack8(*reinterpret_cast<const uint4*>(rr), t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += t[j];
+          }
+          *reinterpret_cast<uint4*>(rr) = pack8(acc);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            acc[j] = __bfloat162float(__float2bfloat16(acc[j]));
+            ss += acc[j] * acc[j];
+            vals[i][j] = acc[j];
+          }
+        }
+      }
+      ss = warp_sum(ss);
+      const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+      if (lane == 0) scratch[warp] = ss;
+      __syncthreads();
+      float t = lane < (kTpThreads >> 5) ? scratch[lane] : 0.f;
+      t = warp_sum(t);
+      __syncthreads();
+      const float inv = rsqrtf(t / static_cast<float>(hidden) + eps);
+      const long long hoff = h_offset + static_cast<long long>(row) * hidden * 2;
+#pragma unroll
+      for (int i = 0; i < kTpMaxVec; ++i) {
+        const int v = threadIdx.x + i * kTpThreads;
+        if (v < nvec) {
+          float g[8], o[8];
+          unpack8(*reinterpret_cast<const uint4*>(w + v * 8), g);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * inv * g[j];
+          const uint4 packed = pack8(o);
+          if (c.mc_buf != nullptr) {
+            multimem_st_bf16x8(const_cast<char*>(static_cast<const char*>(c.mc_buf)) + hoff + v * 16, packed);
+          } else {
+            for (int r = 0; r < c.world; ++r)
+              st_relaxed_sys_v4(const_cast<char*>(static_cast<const char*>(c.peer_buf[r])) + hoff + v * 16, packed);
+          }
+        }
+      }
+    }
+  }
+  // second barrier: my rows are on every rank / every rank's rows are here
+  __shared__ int last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    last = atomicAdd(c.epoch + 2, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (last && threadIdx.x < c.world) {
+    c.epoch[2] = 0;
+    __threadfence_system();
+    st_release_sys(c.peer_flags[threadIdx.x] + 2 * kMaxRanks + c.rank, epoch);
+  }
+  if (threadIdx.x < c.world) {
+    const uint32_t* f = c.peer_flags[c.rank] + 2 * kMaxRanks + threadIdx.x;
+    const unsigned long long t0 = global_timer_ns();
+    const unsigned long long limit = static_cast<unsigned long long>(c.spin_limit) * 1000ull;
+    for (;;) {
+      if (static_cast<int32_t>(ld_acquire_sys(f) - epoch) >= 0) break;
+      if (global_timer_ns() - t0 > limit) {
+        report_status(c.status, kTpKernelId, kPeerFlagTimeout);
+        break;
+      }
+      __nanosleep(20);
+    }
+  }
+  tp_finish(c);
+}
+
 struct ArgSlot {
   float v;
   int i;
@@ -189,6 +290,27 @@ int xv_tp_reduce_norm(const void* const* peer_bufs, void* const* peer_flags, con
   tp_reduce_norm_kernel<<<grid, kTpThreads, 0, stream>>>(
       c, buf_offset, static_cast<const __nv_bfloat16*>(residual_in), static_cast<__nv_bfloat16*>(residual_out),
       static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), rows, hidden, eps, mode);
+  return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
+}
+
+// Row-sharded reduction point: partial at `buf_offset`, normalised activations broadcast to
+// `h_offset` (both byte offsets inside the symmetric buffer). `residual` holds this rank's rows
+// of the residual stream (rows rank, rank + world, ...); has_residual == 0 starts the stream.
+int xv_tp_reduce_norm_sharded(const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf, void* epoch,
+                              int rank, int world, long long buf_offset, long long h_offset, int has_residual,
+                              void* residual, const void* w, int rows, int hidden, float eps, unsigned spin_limit,
+                              int* status, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (hidden % 8 || hidden > kTpThreads * kTpMaxVec * 8 || (buf_offset & 15) || (h_offset & 15)) return XV_ERR_SHAPE;
+  TpComm c;
+  int rc = fill_comm(&c, peer_bufs, peer_flags, mc_buf, epoch, rank, world, spin_limit, status);
+  if (rc) return rc;
+  int mine = (rows + world - 1) / world;
+  int grid = mine < 148 * 4 ? mine : 148 * 4;     // every CTA waits at the end: keep the grid resident
+  if (grid < 1) grid = 1;
+  tp_reduce_norm_sharded_kernel<<<grid, kTpThreads, 0, stream>>>(
+      c, buf_offset, h_offset, has_residual, static_cast<__nv_bfloat16*>(residual),
+      static_cast<const __nv_bfloat16*>(w), rows, hidden, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
 }
 

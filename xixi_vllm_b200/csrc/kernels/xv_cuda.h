@@ -120,6 +120,10 @@ int xv_tp_reduce_norm(const void* const* peer_bufs, void* const* peer_flags, con
                       int rank, int world, long long buf_offset, const void* residual_in, void* residual_out,
                       const void* w, void* y, int rows, int hidden, float eps, int mode, unsigned spin_limit,
                       int* status, cudaStream_t stream);
+int xv_tp_reduce_norm_sharded(const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf, void* epoch,
+                              int rank, int world, long long buf_offset, long long h_offset, int has_residual,
+                              void* residual, const void* w, int rows, int hidden, float eps, unsigned spin_limit,
+                              int* status, cudaStream_t stream);
 int xv_tp_argmax(const void* const* peer_bufs, void* const* peer_flags, void* epoch, int rank, int world,
                  long long slots_offset, const void* logits, long long ld, int local_vocab, int valid_vocab,
                  int vocab_start, long long* out, int rows, unsigned spin_limit, int* status, cudaStream_t stream);
@@ -161,6 +165,8 @@ typedef struct XvModelDesc {
   void* const* peer_flags;
   const void* mc_buf;
   void* epoch;
+  long long h_offset;                 // byte offset of the activation buffer h inside the symmetric buffer
+                                      // (>= 0: row-sharded reductions broadcast h there; < 0: one-shot form)
   long long buf_bytes;                // size of each of the three symmetric partial buffers
   long long slots_offset;             // byte offset of the argmax slots in the symmetric buffer
   unsigned spin_us;

@@ -79,11 +79,17 @@ class FusedTPComm(TPComm):
         self.max_tokens = max_tokens
         self.buf_bytes = -(-max_tokens * hidden_size * 2 // 4096) * 4096
         self.slot_bytes = -(-group.size * max_tokens * 8 // 4096) * 4096
-        total = 3 * self.buf_bytes + self.slot_bytes + FLAG_BYTES
+        total = 4 * self.buf_bytes + self.slot_bytes + FLAG_BYTES
         self.symm = SymmetricBuffer(total, group, self.device)
         self.rank, self.world = self.symm.rank, self.symm.world
-        self.flags_off = 3 * self.buf_bytes + self.slot_bytes
-        self.slots_off = 3 * self.buf_bytes
+        self.h_off = 3 * self.buf_bytes              # activation buffer the row-sharded reductions broadcast into
+        self.slots_off = 4 * self.buf_bytes
+        self.flags_off = 4 * self.buf_bytes + self.slot_bytes
+        # The native forward uses the row-sharded (two-shot) reduction from 4 ranks up: its traffic per GPU
+        # does not grow with the rank count, at the price of a second barrier (measured slower at 2 ranks).
+        # XV_TP_SHARDED=0/1 forces the choice.
+        env = os.environ.get("XV_TP_SHARDED", "")
+        self.sharded_reduce = (env == "1") if env in ("0", "1") else group.size >= 4
         self._bufs = self.symm.ptr_array(0)
         self._flags = self.symm.ptr_array(self.flags_off)
         self.mc_ptr = self.symm.multicast_ptr
@@ -101,6 +107,7 @@ class FusedTPComm(TPComm):
         self._base = self.symm.local.data_ptr()
         self._views = [self.symm.local[i * self.buf_bytes:(i + 1) * self.buf_bytes].view(torch.bfloat16)
                        for i in range(3)]
+        self.h_view = self.symm.local[self.h_off: self.h_off + self.buf_bytes].view(torch.bfloat16)
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group.cpu_group)
         if self.rank == 0:

@@ -31,7 +31,7 @@ class ModelDesc(ctypes.Structure):
                 ("vocab_rows", _i32), ("lm_head_rows", _i32), ("lm_valid", _i32), ("embed", _vp), ("final_norm", _vp),
                 ("lm_head", _vp), ("cos_sin", _vp), ("layers", ctypes.POINTER(LayerWeights)), ("tp_rank", _i32),
                 ("tp_world", _i32), ("peer_bufs", _vp), ("peer_flags", _vp), ("mc_buf", _vp), ("epoch", _vp),
-                ("buf_bytes", _i64), ("slots_offset", _i64), ("spin_us", ctypes.c_uint)]
+                ("h_offset", _i64), ("buf_bytes", _i64), ("slots_offset", _i64), ("spin_us", ctypes.c_uint)]
 
 
 class BatchDesc(ctypes.Structure):
@@ -107,11 +107,13 @@ class NativeForward:
             d.mc_buf = comm.mc_ptr or None
             d.epoch = comm.epoch.data_ptr()
             d.buf_bytes, d.slots_offset = comm.buf_bytes, comm.slots_off
+            d.h_offset = comm.h_off if comm.sharded_reduce else -1
             from ..parallel.symm import SPIN_LIMIT
 
             d.spin_us = SPIN_LIMIT
         else:
             d.tp_rank, d.tp_world = 0, 1
+            d.h_offset = -1
         self.desc = d
         self.vocab_local = d.lm_head_rows
 
@@ -120,7 +122,13 @@ class NativeForward:
 
         T, S, H = max_tokens, max_samples, cfg.hidden_size
         q_cols = d.hq * d.head_dim
-        self.t = dict(h=buf(T, H), qkv=buf(T, d.qkv_rows), q=buf(T, q_cols), attn=buf(T, q_cols),
+        if d.tp_world > 1 and d.h_offset >= 0:
+            if T > comm.max_tokens:
+                raise ValueError("arena larger than the communicator's symmetric buffers")
+            h_buf = comm.h_view[: T * H].view(T, H)        # broadcast target of the row-sharded reductions
+        else:
+            h_buf = buf(T, H)
+        self.t = dict(h=h_buf, qkv=buf(T, d.qkv_rows), q=buf(T, q_cols), attn=buf(T, q_cols),
                       act=buf(T, d.inter_local), residual=buf(T, H), partial=buf(T, H), hidden_out=buf(S, H),
                       logits=buf(S, d.lm_head_rows), tokens=torch.zeros(S, dtype=torch.int64, device=dev))
         if not d.gate_up_interleaved:

@@ -724,9 +724,13 @@ int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan) {
   int splits = 1;
   if (tiles < num_sms) {
     splits = slots / tiles;
-    const int by_traffic = k / (8 * m) > 1 ? k / (8 * m) : 1;
+    // partial planes cost splits * m * n * 4 bytes written and read back: allow them up to a quarter of
+    // the weight bytes, or up to 16 MB in absolute terms (they stay in the 126 MB L2), whichever is more
+    int by_traffic = k / (8 * m) > 1 ? k / (8 * m) : 1;
+    const long long plane = static_cast<long long>(m) * n * 4;
+    const int by_bytes = static_cast<int>((16ll << 20) / (plane > 0 ? plane : 1));
+    if (by_bytes > by_traffic) by_traffic = by_bytes;
     if (splits > by_traffic) splits = by_traffic;
-    if (splits < num_sms / tiles) splits = num_sms / tiles < by_traffic ? num_sms / tiles : splits;
     while (splits > 1 && total_kb / splits < 4) --splits;
     if (splits > 16) splits = 16;
     if (splits < 1) splits = 1;

@@ -672,7 +672,7 @@ void xv_gemm_disable_pair(int disable) { g_disable_pair = disable != 0; }
 
 // Chooses orientation, tile and split-K for a problem; fills *plan. Pure host arithmetic so
 // callers (and CPU tests) can size the workspace before launching.
-int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan) {
+static int gemm_plan_impl(int m, int n, int k, int num_sms, XvGemmPlan* plan, bool allow_pair) {
   if (m <= 0 || n <= 0 || k <= 0 || (k % 8) != 0) return XV_ERR_SHAPE;
   if (num_sms <= 0) num_sms = 148;
   XvGemmPlan pl;
@@ -692,7 +692,7 @@ int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan) {
     pl.tiles_b = (n + pl.bn - 1) / pl.bn;
     // CTA pairs (256 x 256 tiles) once there are enough of them to occupy every SM pair
     const int pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
-    if (n >= 256 && pair_tiles >= num_sms / 2 && !g_disable_pair) {
+    if (n >= 256 && pair_tiles >= num_sms / 2 && allow_pair) {
       pl.pair = 1;
       pl.bn = 256;
       pl.tiles_a = (m + 255) / 256;
@@ -745,6 +745,10 @@ int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan) {
   return 0;
 }
 
+int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan) {
+  return gemm_plan_impl(m, n, k, num_sms, plan, !g_disable_pair);
+}
+
 // Y[m,n] (bf16, row stride ldy) = X[m,k] (row stride ldx) * W[n,k]^T (row stride ldw).
 // `workspace` must hold plan.workspace_bytes when the plan splits K. `status` may be null.
 static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
@@ -752,14 +756,9 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
                      cudaStream_t stream, bool defer_reduce, int* splits_out, int act = 0,
                      const TpTail* tail_in = nullptr) {
   XvGemmPlan pl;
-  int rc = xv_gemm_plan(m, n, k, num_sms, &pl);
+  // the fused tensor-parallel tail lives in the single-CTA kernel
+  int rc = gemm_plan_impl(m, n, k, num_sms, &pl, tail_in == nullptr && !g_disable_pair);
   if (rc) return rc;
-  if (tail_in && pl.pair) {        // the fused tail lives in the single-CTA kernel
-    g_disable_pair = true;
-    rc = xv_gemm_plan(m, n, k, num_sms, &pl);
-    g_disable_pair = false;
-    if (rc) return rc;
-  }
   if ((ldx % 8) || (ldw % 8) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return XV_ERR_ALIGN;
   if (pl.workspace_bytes > workspace_bytes || (pl.workspace_bytes && !workspace)) return XV_ERR_WORKSPACE;

@@ -75,6 +75,8 @@ def lib():
     L.xv_sample.argtypes = [_vp, _vp, _i32, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp]
     L.xv_tp_reduce_norm.argtypes = [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _vp, _vp, _vp, _vp, _i32, _i32, _f32,
                                     _i32, ctypes.c_uint, _vp, _vp]
+    L.xv_tp_reduce_norm_sharded.argtypes = [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _i64, _i32, _vp, _vp, _i32, _i32,
+                                            _f32, ctypes.c_uint, _vp, _vp]
     L.xv_tp_argmax.argtypes = [_vp, _vp, _vp, _i32, _i32, _i64, _vp, _i64, _i32, _i32, _i32, _vp, _i32,
                                ctypes.c_uint, _vp, _vp]
     L.xv_gemm_bf16_tp.argtypes = [_vp, _vp, _i32, _i32, _i32, _i64, _i64, _vp, _i64, _i32, _vp, _vp, _vp, _vp, _i32,

@@ -17,7 +17,7 @@ def _make_cache(num_blocks, hkv, bs, seed):
     return k, v
 
 
-def _run(q_lens, kv_lens, hq, hkv, bs=16, n_decode=0, seed=0):
+def _run(q_lens, kv_lens, hq, hkv, bs=16, n_decode=0, seed=0, q_scale=1.0):
     B = len(kv_lens)
     maxb = max(-(-l // bs) for l in kv_lens) + 1
     num_blocks = B * maxb + 3
@@ -28,7 +28,7 @@ def _run(q_lens, kv_lens, hq, hkv, bs=16, n_decode=0, seed=0):
         bt[b] = perm[b * maxb:(b + 1) * maxb].to(torch.int32)
     k, v = _make_cache(num_blocks, hkv, bs, seed)
     T = sum(q_lens)
-    q = torch.randn(T, hq * D, generator=g).bfloat16()
+    q = (torch.randn(T, hq * D, generator=g) * q_scale).bfloat16()
     cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
     kvl = torch.tensor(kv_lens, dtype=torch.int32)
     scale = D ** -0.5
@@ -38,6 +38,7 @@ def _run(q_lens, kv_lens, hq, hkv, bs=16, n_decode=0, seed=0):
                      num_decode=n_decode, max_q_len=max(q_lens), max_kv_len=max(kv_lens), num_tokens=T)
     out = cuda.paged_attention(q.to(DEV), k.to(DEV), v.to(DEV), attn, scale, hq, hkv, D)
     torch.cuda.synchronize()
+    cuda.check_status()
     torch.testing.assert_close(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
 
 
@@ -76,3 +77,32 @@ def test_prefill_with_cached_prefix():
 
 def test_mixed_decode_then_prefill():
     _run([1, 1, 1, 40, 130], [77, 16, 1, 40, 16 + 130], 32, 8, n_decode=3)
+
+
+# ---- tcgen05 prefill kernel (chunks longer than 64 rows take it by default) ----
+
+@pytest.mark.parametrize("bs", [16, 32, 64, 128, 256])
+def test_prefill_tensor_core_kernel_page_sizes(bs):
+    from xixi_vllm_b200.ops import cuda
+    assert cuda.prefill_uses_tensor_cores(D, bs, 300)
+    _run([300, 129, 70, 1], [300, 256 + 129, 70, 513], 16, 8, bs=bs, seed=bs)
+
+
+def test_prefill_tensor_core_kernel_long_sequence_with_growing_maxima():
+    # Large scores make row maxima jump by more than the lazy-rescale threshold between tiles.
+    _run([1500, 640], [1500, 2048 + 640], 8, 2, q_scale=6.0, seed=3)
+
+
+def test_prefill_tensor_core_and_warp_mma_kernels_agree_with_oracle(monkeypatch):
+    lens = [128, 127, 129, 255, 257]
+    _run(lens, lens, 16, 8, seed=5)
+    monkeypatch.setenv("XV_ATTN_PREFILL", "mma")
+    from xixi_vllm_b200.ops import cuda
+    assert not cuda.prefill_uses_tensor_cores(D, 16, 300)
+    _run(lens, lens, 16, 8, seed=5)
+
+
+def test_prefill_tensor_core_kernel_unsupported_page_size_falls_back():
+    from xixi_vllm_b200.ops import cuda
+    assert not cuda.prefill_uses_tensor_cores(D, 48, 300)
+    _run([200], [200], 16, 8, bs=48)

@@ -208,6 +208,38 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// Descriptor for an MN-major bf16 operand with the 128-byte swizzle: the contiguous dimension
+// is M (or N), 64 elements = 128 bytes per row, rows are consecutive K indices. Eight K rows
+// form a 1024-byte swizzle atom; `sbo_bytes` is the distance between 8-row K groups and
+// `lbo_bytes` the distance between 64-element blocks along M/N. (A row-major [K, N] tile that
+// TMA loaded as 64-column halves is exactly this layout.) One MMA consumes 16 K rows, so
+// advancing along K adds two atoms to the start address.
+__device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+// Same instruction descriptor as umma_idesc_bf16 with operand B read MN-major: D[M,N] += A[M,K] * B[K,N].
+__host__ __device__ inline uint32_t umma_idesc_bf16_b_mn(int m, int n) { return umma_idesc_bf16(m, n) | (1u << 16); }
+
+// Writes 16 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Makes this thread's earlier shared-memory writes visible to the async proxy (TMA, tcgen05.mma operands).
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 // ---- CTA pairs (cta_group::2): two CTAs of a 2-wide cluster drive one 256-row MMA ------------------
 // The leader CTA (cluster rank 0) issues the MMAs; operand tiles and accumulators live in both
 // CTAs' shared and tensor memory at identical offsets. Barriers that both CTAs must signal

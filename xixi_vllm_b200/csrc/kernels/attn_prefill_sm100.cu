@@ -1,0 +1,456 @@
+// Paged causal prefill attention for sm_100a on the 5th-generation tensor cores.
+//
+// One CTA owns 128 query rows of one head of one sequence and walks the sequence's KV pages
+// in tiles of 64 tokens:
+//   warp 4      - TMA producer: the Q tile once, then per tile the K and V pages named by the
+//                 block table, each page an own cp.async.bulk.tensor box (128-byte swizzle)
+//                 into a ring of 16 KiB shared-memory slots.
+//   warp 5      - allocates TMEM and issues tcgen05.mma from one thread: S = Q K^T (M=128, N=64)
+//                 into one of two S buffers in TMEM, one tile ahead of the softmax, and
+//                 O += P V (M=128, N=128; V is read MN-major exactly as the cache stores it).
+//   warps 0..3  - softmax: thread r owns query row r. tcgen05.ld of the S row, scale + causal
+//                 mask, running max and sum, P rounded to bf16 into a swizzled shared-memory tile
+//                 that the second MMA reads as its A operand. The output accumulator lives in
+//                 TMEM for the whole sequence; it is rescaled in place (tcgen05.ld/st) only when
+//                 a row's maximum grows by more than 2^8, otherwise the stale maximum is kept,
+//                 which the final division by the row sum makes exact.
+// Two CTAs share an SM (256 TMEM columns and ~112 KiB shared memory each), so one CTA's softmax
+// runs under the other's MMAs.
+//
+// Every barrier wait is bounded; a wait that runs out records a status code, the CTA stops
+// issuing work, frees its TMEM and returns.
+//
+// The reference calls flash_attn_varlen_func (an Ampere-generation mma.sync kernel) here
+// (reference: src/compute/layers/attention.py:80-90).
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <mutex>
+#include <unordered_map>
+
+#include "../common/ptx.cuh"
+#include "xv_cuda.h"
+
+namespace {
+
+using namespace xv;
+
+constexpr int kBM = 128;                       // query rows per CTA
+constexpr int kBN = 64;                        // KV tokens per tile
+constexpr int kD = 128;                        // head dimension
+constexpr int kThreads = 192;
+constexpr int kQBytes = kBM * kD * 2;          // 32 KiB, two 64-column halves of 16 KiB
+constexpr int kQHalf = kBM * 128;
+constexpr int kSlotBytes = kBN * kD * 2;       // 16 KiB, two 64-column halves of 8 KiB
+constexpr int kSlotHalf = kBN * 128;
+constexpr int kPBytes = kBM * kBN * 2;         // 16 KiB
+constexpr int kMaxSlots = 4;
+constexpr int kBarBytes = 256;
+constexpr int kSmemRequest = kQBytes + kPBytes + kMaxSlots * kSlotBytes + kBarBytes;
+constexpr uint32_t kTmemCols = 256;            // S0 [0,64) S1 [64,128) O [128,256)
+constexpr uint32_t kTmemO = 128;
+constexpr int kKernelId = 7;
+constexpr float kRescaleThreshold = 8.f;       // log2 units
+
+struct Params {
+  const int* block_tables;
+  const int* cu_q;
+  const int* kv_lens;
+  __nv_bfloat16* out;
+  int seq_begin, hq, hkv, block_size, max_blocks, num_blocks;
+  float scale_log2;
+  int* status;
+};
+
+__global__ void __launch_bounds__(kThreads, 2)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const Params p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const int b = p.seq_begin + blockIdx.z, head = blockIdx.y;
+  const int q_begin = p.cu_q[b];
+  const int q_len = p.cu_q[b + 1] - q_begin;
+  const int row0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * kBM;   // long tiles first
+  if (row0 >= q_len) return;
+  const int kv_len = p.kv_lens[b];
+  const int pos0 = kv_len - q_len;                           // absolute position of query row 0
+  const int rows_valid = min(kBM, q_len - row0);
+  const int n_tiles = (pos0 + row0 + rows_valid - 1) / kBN + 1;
+  const int hk = head / (p.hq / p.hkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // The swizzled tiles need 1024-byte alignment; the ring gets 4 slots when no padding was needed.
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw & 1023u)) & 1023u;
+  uint32_t dyn;
+  asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+  int slots = (static_cast<int>(dyn) - static_cast<int>(pad) - kBarBytes - kQBytes - kPBytes) / kSlotBytes;
+  slots = slots > kMaxSlots ? kMaxSlots : slots;
+  uint8_t* smem = smem_raw + pad;
+  uint8_t* q_s = smem;
+  uint8_t* p_s = smem + kQBytes;
+  uint8_t* ring = p_s + kPBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + slots * kSlotBytes);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;                  // [kMaxSlots]
+  uint64_t* kv_empty = kv_full + kMaxSlots;      // [kMaxSlots]
+  uint64_t* s_full = kv_empty + kMaxSlots;       // [2]
+  uint64_t* p_ready = s_full + 2;
+  uint64_t* o_done = p_ready + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  if (slots < 3) {                               // cannot happen with the launch below; never index past the ring
+    if (threadIdx.x == 0) report_status(p.status, kKernelId, kBadIndex);
+    return;
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < kMaxSlots; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
+    mbar_init(p_ready, 128);
+    mbar_init(o_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ---------------- TMA producer ----------------
+    const uint64_t pol = l2_policy_evict_normal();
+    if (lane == 0) {
+      prefetch_tensormap(&map_q);
+      prefetch_tensormap(&map_k);
+      prefetch_tensormap(&map_v);
+      mbar_expect_tx(q_full, kQBytes);
+      tma_load_2d(q_s, &map_q, q_full, head * kD, q_begin + row0, pol);
+      tma_load_2d(q_s + kQHalf, &map_q, q_full, head * kD + 64, q_begin + row0, pol);
+    }
+    const int bs = p.block_size;
+    const int rows_per_load = bs < kBN ? bs : kBN;
+    const int loads = kBN / rows_per_load;               // pages per tile (1 when a page holds >= 64 tokens)
+    const int last_page = (kv_len - 1) / bs;
+    for (int item = 0; item < 2 * n_tiles; ++item) {     // K0 V0 K1 V1 ...
+      const int j = item >> 1, is_v = item & 1;
+      const int slot = item % slots, use = item / slots;
+      int ok = 1;
+      if (lane == 0) {
+        ok = mbar_wait(&kv_empty[slot], (use & 1) ^ 1) && *abort_flag == 0;
+        if (ok) mbar_expect_tx(&kv_full[slot], kSlotBytes);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) {
+        if (lane == 0) {
+          report_status(p.status, kKernelId, kWaitEmptyTimeout);
+          *abort_flag = 1;
+        }
+        break;
+      }
+      if (lane < 2 * loads) {
+        const int i = lane >> 1, half = lane & 1;
+        const int tok = j * kBN + i * rows_per_load;
+        int pg = tok / bs;
+        pg = pg > last_page ? last_page : pg;            // past the end: any valid page, the columns are masked
+        const int within = bs > kBN ? tok % bs : 0;
+        int blk = p.block_tables[static_cast<long long>(b) * p.max_blocks + pg];
+        if (blk < 0 || blk >= p.num_blocks) {
+          report_status(p.status, kKernelId, kBadIndex);
+          blk = 0;
+        }
+        const int y = (blk * p.hkv + hk) * bs + within;
+        uint8_t* dst = ring + slot * kSlotBytes + half * kSlotHalf + i * rows_per_load * 128;
+        tma_load_2d(dst, is_v ? &map_v : &map_k, &kv_full[slot], half * 64, y, pol);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc_s = umma_idesc_bf16(kBM, kBN);
+      const uint32_t idesc_o = umma_idesc_bf16_b_mn(kBM, kD);
+      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s), ring_addr = smem_u32(ring);
+      bool ok = mbar_wait(q_full, 0);
+      int reason = kWaitFullTimeout;
+      auto issue_s = [&](int j) -> bool {
+        const int item = 2 * j, slot = item % slots, use = item / slots;
+        if (!mbar_wait(&kv_full[slot], use & 1)) return false;
+        tc_fence_after_sync();
+        const uint32_t k_addr = ring_addr + slot * kSlotBytes;
+#pragma unroll
+        for (int ks = 0; ks < kD / 16; ++ks) {
+          const uint64_t a = umma_desc_sw128(q_addr + (ks >> 2) * kQHalf + (ks & 3) * 32);
+          const uint64_t bd = umma_desc_sw128(k_addr + (ks >> 2) * kSlotHalf + (ks & 3) * 32);
+          umma_bf16(tmem_base + (j & 1) * kBN, a, bd, idesc_s, ks > 0);
+        }
+        umma_commit(&kv_empty[slot]);
+        umma_commit(&s_full[j & 1]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }
+        if (!mbar_wait(p_ready, j & 1)) { ok = false; reason = kWaitAccumTimeout; break; }
+        const int item = 2 * j + 1, slot = item % slots, use = item / slots;
+        if (!mbar_wait(&kv_full[slot], use & 1)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t v_addr = ring_addr + slot * kSlotBytes;
+#pragma unroll
+        for (int ks = 0; ks < kBN / 16; ++ks) {
+          const uint64_t a = umma_desc_sw128(p_addr + ks * 32);
+          const uint64_t bd = umma_desc_sw128_mn(v_addr + ks * 2048, kSlotHalf, 1024);
+          umma_bf16(tmem_base + kTmemO, a, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[slot]);
+        umma_commit(o_done);
+      }
+      if (!ok || *abort_flag) {
+        if (!ok) report_status(p.status, kKernelId, reason);
+        *abort_flag = 1;
+      }
+    }
+  } else {
+    // ---------------- softmax + epilogue: thread r owns query row r ----------------
+    const int r = threadIdx.x;
+    const int pos_row = pos0 + row0 + (r < rows_valid ? r : rows_valid - 1);
+    const uint32_t lane_taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t p_row = smem_u32(p_s) + r * 128;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[j & 1], (j >> 1) & 1) && *abort_flag == 0);
+      if (!ok) break;
+      tc_fence_after_sync();
+      uint32_t sr[4][16];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld16(lane_taddr + (j & 1) * kBN + c * 16, sr[c]);
+      tmem_ld_wait();
+      const int k0 = j * kBN;
+      float mt = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float s = __uint_as_float(sr[c][i]) * p.scale_log2;
+          s = (k0 + c * 16 + i <= pos_row) ? s : -INFINITY;
+          sr[c][i] = __float_as_uint(s);
+          mt = fmaxf(mt, s);
+        }
+      bool o_ready = (j == 0);
+      if (j == 0) {
+        m = mt;                                  // column 0 is never masked, so this is finite
+      } else {
+        const bool need = mt > m + kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          ok = __all_sync(0xffffffffu, mbar_wait(o_done, (j - 1) & 1));
+          if (!ok) break;
+          tc_fence_after_sync();
+          o_ready = true;
+          const float m_new = need ? mt : m;
+          const float alpha = exp2f(m - m_new);
+          l *= alpha;
+          m = m_new;
+#pragma unroll 1
+          for (int ch = 0; ch < kD / 16; ++ch) {
+            uint32_t o[16];
+            tmem_ld16(lane_taddr + kTmemO + ch * 16, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st16(lane_taddr + kTmemO + ch * 16, o);
+          }
+          tmem_st_wait();
+        }
+      }
+      uint32_t packed[32];
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+          const float p0 = exp2f(__uint_as_float(sr[c][i]) - m);
+          const float p1 = exp2f(__uint_as_float(sr[c][i + 1]) - m);
+          sum += p0 + p1;
+          packed[c * 8 + (i >> 1)] = pack_bf16(p0, p1);
+        }
+      l += sum;
+      if (!o_ready) {                            // the previous P V must have finished reading the P tile
+        ok = __all_sync(0xffffffffu, mbar_wait(o_done, (j - 1) & 1));
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint32_t addr = p_row + ((c ^ (r & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * c]),
+                     "r"(packed[4 * c + 1]), "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3])
+                     : "memory");
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(p_ready);
+    }
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_done, (n_tiles - 1) & 1) && *abort_flag == 0);
+    if (ok) {
+      tc_fence_after_sync();
+      const float inv = 1.f / l;
+      __nv_bfloat16* orow =
+          p.out + (static_cast<long long>(q_begin + row0 + r) * p.hq + head) * kD;
+#pragma unroll 1
+      for (int ch = 0; ch < kD / 16; ++ch) {
+        uint32_t o[16];
+        tmem_ld16(lane_taddr + kTmemO + ch * 16, o);
+        tmem_ld_wait();
+        if (r < rows_valid) {
+          uint4 v0, v1;
+          v0.x = pack_bf16(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
+          v0.y = pack_bf16(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
+          v0.z = pack_bf16(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv);
+          v0.w = pack_bf16(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv);
+          v1.x = pack_bf16(__uint_as_float(o[8]) * inv, __uint_as_float(o[9]) * inv);
+          v1.y = pack_bf16(__uint_as_float(o[10]) * inv, __uint_as_float(o[11]) * inv);
+          v1.z = pack_bf16(__uint_as_float(o[12]) * inv, __uint_as_float(o[13]) * inv);
+          v1.w = pack_bf16(__uint_as_float(o[14]) * inv, __uint_as_float(o[15]) * inv);
+          *reinterpret_cast<uint4*>(orow + ch * 16) = v0;
+          *reinterpret_cast<uint4*>(orow + ch * 16 + 8) = v1;
+        }
+      }
+    } else if (lane == 0) {
+      report_status(p.status, kKernelId, kWaitAccumTimeout);
+      *abort_flag = 1;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(ptr);
+  });
+  return fn;
+}
+
+struct Key {
+  const void* ptr;
+  long long rows, cols;
+  int box_rows;
+  bool operator==(const Key& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows;
+  }
+};
+struct KeyHash {
+  size_t operator()(const Key& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr) * 0x9E3779B97F4A7C15ULL;
+    h ^= static_cast<size_t>(k.rows) * 0xC2B2AE3D27D4EB4FULL + (h << 6) + (h >> 2);
+    h ^= static_cast<size_t>(k.cols * 131 + k.box_rows) + (h << 6) + (h >> 2);
+    return h;
+  }
+};
+
+// Row-major bf16 [rows, cols] viewed through boxes of 64 columns x box_rows rows, 128-byte swizzle.
+// Cached: the KV cache and the activation arena keep their addresses.
+int tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long cols, int box_rows) {
+  static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
+  static std::mutex mu;
+  const Key key{ptr, rows, cols, box_rows};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return 0;
+    }
+  }
+  EncodeFn enc = encode_fn();
+  if (!enc) return XV_ERR_DRIVER;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  if (enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return XV_ERR_TENSORMAP;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int xv_attn_prefill_tc_supported(int d, int block_size) {
+  if (d != kD || block_size <= 0 || block_size % 16) return 0;
+  return (block_size <= kBN ? kBN % block_size == 0 : block_size % kBN == 0) ? 1 : 0;
+}
+
+int xv_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                       const int* cu_q, const int* kv_lens, void* out, int seq_begin, int num_seqs, int max_q_len,
+                       int total_tokens, int num_blocks, int hq, int hkv, int d, int block_size, int max_blocks,
+                       float scale, int* status, cudaStream_t stream) {
+  if (num_seqs <= 0 || max_q_len <= 0) return 0;
+  if (!xv_attn_prefill_tc_supported(d, block_size)) return XV_ERR_UNSUPPORTED;
+  if (hq % hkv || total_tokens <= 0 || num_blocks <= 0) return XV_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+       reinterpret_cast<uintptr_t>(out)) & 15)
+    return XV_ERR_SHAPE;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemRequest) !=
+        cudaSuccess)
+      return XV_ERR_LAUNCH;
+    attr = true;
+  }
+  CUtensorMap map_q, map_k, map_v;
+  const long long kv_rows = static_cast<long long>(num_blocks) * hkv * block_size;
+  const int box_rows = block_size < kBN ? block_size : kBN;
+  if (int rc = tensor_map(&map_q, q, total_tokens, static_cast<long long>(hq) * kD, kBM)) return rc;
+  if (int rc = tensor_map(&map_k, k_cache, kv_rows, kD, box_rows)) return rc;
+  if (int rc = tensor_map(&map_v, v_cache, kv_rows, kD, box_rows)) return rc;
+  Params p;
+  p.block_tables = block_tables;
+  p.cu_q = cu_q;
+  p.kv_lens = kv_lens;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.seq_begin = seq_begin; p.hq = hq; p.hkv = hkv; p.block_size = block_size; p.max_blocks = max_blocks;
+  p.num_blocks = num_blocks;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  dim3 grid((max_q_len + kBM - 1) / kBM, hq, num_seqs);
+  attn_prefill_tc_kernel<<<grid, kThreads, kSmemRequest, stream>>>(map_q, map_k, map_v, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
+}
+
+}  // extern "C"

@@ -134,6 +134,10 @@ int xv_qwen3_forward(const XvModelDesc* m, const XvBatchDesc* b, const XvArena* 
     return XV_ERR_WORKSPACE;
   }
 
+  // Short chunks do not fill a 128-row tile; they stay on the 64-row warp-MMA kernel.
+  const bool prefill_tc = m->prefill_tc && m->num_kv_blocks > 0 && b->max_q_len > 64 &&
+                          xv_attn_prefill_tc_supported(D, m->block_size);
+
   for (int l = 0; l < L; ++l) {
     const XvLayerWeights& w = m->layers[l];
     // ---- attention block ----
@@ -152,7 +156,11 @@ int xv_qwen3_forward(const XvModelDesc* m, const XvBatchDesc* b, const XvArena* 
     if (n_dec > 0)
       XV_TRY(33, xv_attn_decode(a->q, w.k_cache, w.v_cache, b->block_tables, b->kv_lens, a->attn, n_dec, m->hq, m->hkv,
                                 D, m->block_size, b->max_blocks, m->attn_scale, splits_attn, a->attn_ws, stream));
-    if (n_pre > 0)
+    if (n_pre > 0 && prefill_tc)
+      XV_TRY(35, xv_attn_prefill_tc(a->q, w.k_cache, w.v_cache, b->block_tables, b->cu_q, b->kv_lens, a->attn, n_dec,
+                                    n_pre, b->max_q_len, T, m->num_kv_blocks, m->hq, m->hkv, D, m->block_size,
+                                    b->max_blocks, m->attn_scale, a->status, stream));
+    else if (n_pre > 0)
       XV_TRY(34, xv_attn_prefill(a->q, w.k_cache, w.v_cache, b->block_tables, b->cu_q, b->kv_lens, a->attn, n_dec,
                                  n_pre, b->max_q_len, m->hq, m->hkv, D, m->block_size, b->max_blocks, m->attn_scale,
                                  stream));

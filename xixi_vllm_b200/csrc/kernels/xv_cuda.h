@@ -108,6 +108,14 @@ int xv_attn_decode(const void* q, const void* k_cache, const void* v_cache, cons
 int xv_attn_prefill(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
                     const int* cu_q, const int* kv_lens, void* out, int seq_begin, int num_seqs, int max_q_len,
                     int hq, int hkv, int d, int block_size, int max_blocks, float scale, cudaStream_t stream);
+// The same operation on tcgen05 tensor cores (attn_prefill_sm100.cu): 128-row query tiles, K/V pages
+// fetched by TMA. `total_tokens` is the row count of q/out, `num_blocks` the page count of the caches.
+// Supported for head_dim 128 and page sizes that divide 64 or are multiples of 64.
+int xv_attn_prefill_tc_supported(int d, int block_size);
+int xv_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                       const int* cu_q, const int* kv_lens, void* out, int seq_begin, int num_seqs, int max_q_len,
+                       int total_tokens, int num_blocks, int hq, int hkv, int d, int block_size, int max_blocks,
+                       float scale, int* status, cudaStream_t stream);
 
 // ---- sampling ----
 int xv_argmax(const void* logits, long long* out, int rows, int vocab, long long ld, cudaStream_t stream);
@@ -170,6 +178,8 @@ typedef struct XvModelDesc {
   long long buf_bytes;                // size of each of the three symmetric partial buffers
   long long slots_offset;             // byte offset of the argmax slots in the symmetric buffer
   unsigned spin_us;
+  int num_kv_blocks;                  // pages in each layer's k_cache / v_cache
+  int prefill_tc;                     // 1: prefill attention on the tcgen05 kernel when the shape allows
 } XvModelDesc;
 
 typedef struct XvBatchDesc {

@@ -71,6 +71,9 @@ def lib():
                                  _vp, _vp]
     L.xv_attn_prefill.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
                                   _i32, _f32, _vp]
+    L.xv_attn_prefill_tc_supported.argtypes = [_i32, _i32]
+    L.xv_attn_prefill_tc.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
+                                     _i32, _i32, _i32, _f32, _vp, _vp]
     L.xv_argmax.argtypes = [_vp, _vp, _i32, _i32, _i64, _vp]
     L.xv_sample.argtypes = [_vp, _vp, _i32, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp]
     L.xv_tp_reduce_norm.argtypes = [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _vp, _vp, _vp, _vp, _i32, _i32, _f32,
@@ -336,6 +339,14 @@ def decode_splits(num_seqs: int, num_kv_heads: int, num_sms: int, max_blocks_tok
     return int(max(1, min(want, by_len, 16)))
 
 
+def prefill_uses_tensor_cores(head_dim: int, block_size: int, max_q_len: int) -> bool:
+    """Chunks longer than 64 rows run on the tcgen05 kernel (128-row tiles); shorter ones, unsupported
+    page sizes, or ``XV_ATTN_PREFILL=mma`` use the 64-row warp-MMA kernel."""
+    if os.environ.get("XV_ATTN_PREFILL", "tc") == "mma" or max_q_len <= 64:
+        return False
+    return bool(lib().xv_attn_prefill_tc_supported(head_dim, block_size))
+
+
 def paged_attention(q, k_cache, v_cache, attn, scale, num_q_heads, num_kv_heads, head_dim):
     """Decode rows (the first ``attn.num_decode`` sequences) and prefill chunks of one packed batch."""
     _bf16(q, k_cache, v_cache)
@@ -354,7 +365,12 @@ def paged_attention(q, k_cache, v_cache, attn, scale, num_q_heads, num_kv_heads,
                                 attn.kv_lens.data_ptr(), out.data_ptr(), n_d, num_q_heads, num_kv_heads, head_dim,
                                 bs, maxb, scale, splits, st.attn_ws.data_ptr(), _stream()), "attn_decode")
     n_p = attn.num_seqs - n_d
-    if n_p > 0:
+    if n_p > 0 and prefill_uses_tensor_cores(head_dim, bs, attn.max_q_len):
+        _check(L.xv_attn_prefill_tc(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), attn.block_tables.data_ptr(),
+                                    attn.cu_q.data_ptr(), attn.kv_lens.data_ptr(), out.data_ptr(), n_d, n_p,
+                                    attn.max_q_len, q.shape[0], k_cache.shape[0], num_q_heads, num_kv_heads, head_dim,
+                                    bs, maxb, scale, st.status.data_ptr(), _stream()), "attn_prefill_tc")
+    elif n_p > 0:
         _check(L.xv_attn_prefill(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), attn.block_tables.data_ptr(),
                                  attn.cu_q.data_ptr(), attn.kv_lens.data_ptr(), out.data_ptr(), n_d, n_p,
                                  attn.max_q_len, num_q_heads, num_kv_heads, head_dim, bs, maxb, scale, _stream()),

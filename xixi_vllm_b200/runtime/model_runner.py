@@ -40,7 +40,8 @@ class ModelRunner:
         self.max_tokens = max(config.max_num_batched_tokens, self.max_bs)
         self.max_blocks = -(-config.context_len // self.block_size)
         self.stager = BatchStager(max_seqs=self.max_bs, max_tokens=self.max_tokens,
-                                  max_blocks=self.max_blocks, block_size=self.block_size, device=self.device)
+                                  max_blocks=self.max_blocks, block_size=self.block_size, device=self.device,
+                                  seed=getattr(config, "seed", 0))
         self._pp_buf = None
         if not self.is_first_pp:
             shape = (self.max_tokens, self.hidden_size)

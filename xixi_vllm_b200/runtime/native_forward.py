@@ -9,6 +9,7 @@ module-by-module Python forward stays as the CPU path and the pipeline-parallel 
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -31,7 +32,8 @@ class ModelDesc(ctypes.Structure):
                 ("vocab_rows", _i32), ("lm_head_rows", _i32), ("lm_valid", _i32), ("embed", _vp), ("final_norm", _vp),
                 ("lm_head", _vp), ("cos_sin", _vp), ("layers", ctypes.POINTER(LayerWeights)), ("tp_rank", _i32),
                 ("tp_world", _i32), ("peer_bufs", _vp), ("peer_flags", _vp), ("mc_buf", _vp), ("epoch", _vp),
-                ("h_offset", _i64), ("buf_bytes", _i64), ("slots_offset", _i64), ("spin_us", ctypes.c_uint)]
+                ("h_offset", _i64), ("buf_bytes", _i64), ("slots_offset", _i64), ("spin_us", ctypes.c_uint),
+                ("num_kv_blocks", _i32), ("prefill_tc", _i32)]
 
 
 class BatchDesc(ctypes.Structure):
@@ -86,6 +88,8 @@ class NativeForward:
         d.inter_local = first.mlp.down_proj.in_local
         d.qkv_rows = attn0.qkv_proj.weight.shape[0]
         d.block_size = kv.block_size
+        d.num_kv_blocks = kv.k_cache(0).shape[0]
+        d.prefill_tc = int(os.environ.get("XV_ATTN_PREFILL", "tc") != "mma")
         d.eps, d.attn_scale = float(cfg.rms_norm_eps), float(attn0.scale)
         d.gate_up_interleaved = 1 if first.mlp.gate_up_proj.interleave else 0
         d.vocab_start, d.vocab_rows = m.embed_tokens.vocab_start, m.embed_tokens.weight.shape[0]

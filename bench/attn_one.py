@@ -2,6 +2,7 @@
 
     python -m bench.attn_one --mode decode --batch 64 --len 1408 [--hq 32 --hkv 8 --iters 3]
     python -m bench.attn_one --mode prefill --batch 4 --len 2048
+    python -m bench.attn_one --mode prefill --batch 4 --len 2048 --phases    # where the tcgen05 kernel's warps wait
 """
 
 from __future__ import annotations
@@ -29,6 +30,8 @@ def main() -> None:
     ap.add_argument("--hq", type=int, default=32)
     ap.add_argument("--hkv", type=int, default=8)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--phases", action="store_true",
+                    help="prefill: run the instrumented kernel once and print cycles per phase and tile")
     a = ap.parse_args()
     B, L = a.batch, a.len
     q_lens = [1] * B if a.mode == "decode" else [L] * B
@@ -43,6 +46,11 @@ def main() -> None:
     n = q_lens[0]
     ref = cpu_ref.paged_attention(q[:n].float().cpu(), k.float().cpu(), v.float().cpu(), cu[:2], kvl[:1], bt[:1],
                                   128 ** -0.5, a.hq, a.hkv, 128)
+    if a.phases and a.mode == "prefill":
+        prof = cuda.prefill_phase_profile(q, k, v, attn, 128 ** -0.5, a.hq, a.hkv, 128)
+        tiles = max(1, prof["tiles"])
+        for name, cyc in prof.items():
+            print(f"{name:32s} {cyc:14d}   {cyc / tiles:9.1f} cycles/tile")
     print("max err (seq 0)", float((out[:n].float().cpu() - ref).abs().max()))
 
 

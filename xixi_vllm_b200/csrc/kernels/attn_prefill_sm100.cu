@@ -4,7 +4,8 @@
 // in tiles of 64 tokens:
 //   warp 4      - TMA producer: the Q tile once, then per tile the K and V pages named by the
 //                 block table, each page an own cp.async.bulk.tensor box (128-byte swizzle)
-//                 into a ring of 16 KiB shared-memory slots.
+//                 into two rings of 16 KiB shared-memory slots (K runs two tiles ahead of V).
+//                 Block-table entries are read 32 pages at a time, one batch ahead of use.
 //   warp 5      - allocates TMEM and issues tcgen05.mma from one thread: S = Q K^T (M=128, N=64)
 //                 into one of two S buffers in TMEM, one tile ahead of the softmax, and
 //                 O += P V (M=128, N=128; V is read MN-major exactly as the cache stores it).
@@ -63,8 +64,38 @@ struct Params {
   int seq_begin, hq, hkv, block_size, max_blocks, num_blocks;
   float scale_log2;
   int* status;
+  unsigned long long* prof;      // profiling build only: per-phase cycle totals, see kProf* below
 };
 
+// Phase counters of the profiling instantiation (cycles summed over CTAs, one observer thread per role).
+enum ProfSlot {
+  kProfSoftWaitS = 0, kProfSoftLoad, kProfSoftMax, kProfSoftRescale, kProfSoftExp, kProfSoftWaitO, kProfSoftStore,
+  kProfSoftEpilogue, kProfMmaWaitK, kProfMmaWaitP, kProfMmaWaitV, kProfMmaIssue, kProfLoadWaitEmpty, kProfLoadIssue,
+  kProfCtaTotal, kProfTiles, kProfSetup, kProfSlots
+};
+
+template <bool kProfile>
+struct PhaseClock {
+  long long t0 = 0;
+  unsigned long long acc[kProfSlots] = {};
+  __device__ __forceinline__ void start() { t0 = clock64(); }
+  __device__ __forceinline__ void tick(int slot) {
+    const long long t1 = clock64();
+    acc[slot] += static_cast<unsigned long long>(t1 - t0);
+    t0 = t1;
+  }
+  __device__ __forceinline__ void flush(unsigned long long* out, int lo, int hi) {
+    for (int i = lo; i <= hi; ++i) atomicAdd(&out[i], acc[i]);
+  }
+};
+template <>
+struct PhaseClock<false> {
+  __device__ __forceinline__ void start() {}
+  __device__ __forceinline__ void tick(int) {}
+  __device__ __forceinline__ void flush(unsigned long long*, int, int) {}
+};
+
+template <bool kProfile>
 __global__ void __launch_bounds__(kThreads, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const Params p) {
@@ -80,6 +111,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int n_tiles = (pos0 + row0 + rows_valid - 1) / kBN + 1;
   const int hk = head / (p.hq / p.hkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  PhaseClock<kProfile> clk;
+  const long long cta_t0 = kProfile ? clock64() : 0;
+  clk.start();
 
   // The swizzled tiles need 1024-byte alignment; the ring gets 4 slots when no padding was needed.
   const uint32_t raw = smem_u32(smem_raw);
@@ -91,12 +125,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint8_t* smem = smem_raw + pad;
   uint8_t* q_s = smem;
   uint8_t* p_s = smem + kQBytes;
-  uint8_t* ring = p_s + kPBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + slots * kSlotBytes);
+  uint8_t* k_ring = p_s + kPBytes;               // 2 slots
+  uint8_t* v_ring = k_ring + 2 * kSlotBytes;     // nv = slots - 2 slots
+  const int nv = slots - 2;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(k_ring + slots * kSlotBytes);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;                  // [kMaxSlots]
-  uint64_t* kv_empty = kv_full + kMaxSlots;      // [kMaxSlots]
-  uint64_t* s_full = kv_empty + kMaxSlots;       // [2]
+  uint64_t* k_full = bars + 1;                   // [2]
+  uint64_t* v_full = k_full + 2;                 // [2]
+  uint64_t* k_empty = v_full + 2;                // [2]
+  uint64_t* v_empty = k_empty + 2;               // [2]
+  uint64_t* s_full = v_empty + 2;                // [2]
   uint64_t* p_ready = s_full + 2;
   uint64_t* o_done = p_ready + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
@@ -109,9 +147,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < kMaxSlots; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
@@ -128,6 +168,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) clk.tick(kProfSetup);
+  clk.start();
 
   if (warp == 4) {
     // ---------------- TMA producer ----------------
@@ -144,13 +186,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int rows_per_load = bs < kBN ? bs : kBN;
     const int loads = kBN / rows_per_load;               // pages per tile (1 when a page holds >= 64 tokens)
     const int last_page = (kv_len - 1) / bs;
-    for (int item = 0; item < 2 * n_tiles; ++item) {     // K0 V0 K1 V1 ...
-      const int j = item >> 1, is_v = item & 1;
-      const int slot = item % slots, use = item / slots;
+    // Block-table entries are fetched 32 pages at a time (lane l holds page 32*batch + l), one batch
+    // ahead of use, so the dependent global load never sits between two TMA issues.
+    const int* table = p.block_tables + static_cast<long long>(b) * p.max_blocks;
+    auto fetch = [&](int batch) { return __ldg(table + min(batch * 32 + lane, last_page)); };
+    int cur_batch = 0;
+    int cur = fetch(0), nxt = fetch(1);
+    const int i = lane >> 1, half = lane & 1;
+    // Loads tile `j` of K (is_v = 0) or V (is_v = 1) into slot `slot` of its ring.
+    auto load_tile = [&](int j, int is_v, int slot, int use) -> bool {
+      const int tok = j * kBN + (i < loads ? i : 0) * rows_per_load;
+      const int pg = min(tok / bs, last_page);           // past the end: any valid page, the columns are masked
+      const int from_cur = __shfl_sync(0xffffffffu, cur, pg & 31);
+      const int from_nxt = __shfl_sync(0xffffffffu, nxt, pg & 31);
+      int blk = (pg >> 5) == cur_batch ? from_cur : from_nxt;
+      if (blk < 0 || blk >= p.num_blocks) {
+        report_status(p.status, kKernelId, kBadIndex);
+        blk = 0;
+      }
+      const int y = (blk * p.hkv + hk) * bs + (bs > kBN ? tok % bs : 0);
+      uint64_t* full = is_v ? &v_full[slot] : &k_full[slot];
+      uint64_t* empty = is_v ? &v_empty[slot] : &k_empty[slot];
       int ok = 1;
       if (lane == 0) {
-        ok = mbar_wait(&kv_empty[slot], (use & 1) ^ 1) && *abort_flag == 0;
-        if (ok) mbar_expect_tx(&kv_full[slot], kSlotBytes);
+        ok = mbar_wait(empty, (use & 1) ^ 1) && *abort_flag == 0;
+        if (ok) mbar_expect_tx(full, kSlotBytes);
+        clk.tick(kProfLoadWaitEmpty);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) {
@@ -158,65 +219,78 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           report_status(p.status, kKernelId, kWaitEmptyTimeout);
           *abort_flag = 1;
         }
-        break;
+        return false;
       }
       if (lane < 2 * loads) {
-        const int i = lane >> 1, half = lane & 1;
-        const int tok = j * kBN + i * rows_per_load;
-        int pg = tok / bs;
-        pg = pg > last_page ? last_page : pg;            // past the end: any valid page, the columns are masked
-        const int within = bs > kBN ? tok % bs : 0;
-        int blk = p.block_tables[static_cast<long long>(b) * p.max_blocks + pg];
-        if (blk < 0 || blk >= p.num_blocks) {
-          report_status(p.status, kKernelId, kBadIndex);
-          blk = 0;
-        }
-        const int y = (blk * p.hkv + hk) * bs + within;
-        uint8_t* dst = ring + slot * kSlotBytes + half * kSlotHalf + i * rows_per_load * 128;
-        tma_load_2d(dst, is_v ? &map_v : &map_k, &kv_full[slot], half * 64, y, pol);
+        uint8_t* dst = (is_v ? v_ring : k_ring) + slot * kSlotBytes + half * kSlotHalf + i * rows_per_load * 128;
+        tma_load_2d(dst, is_v ? &map_v : &map_k, full, half * 64, y, pol);
       }
       __syncwarp();
+      if (lane == 0) clk.tick(kProfLoadIssue);
+      return true;
+    };
+    // K runs two tiles ahead of V: a K slot frees as soon as its S = Q K^T finishes, a V slot only
+    // after the softmax of that tile, so the order is K0 K1 V0 K2 V1 K3 ...
+    bool go = load_tile(0, 0, 0, 0);
+    if (go && n_tiles > 1) go = load_tile(1, 0, 1, 0);
+    for (int j = 0; go && j < n_tiles; ++j) {
+      const int first_pg = min(j * kBN / bs, last_page);
+      while ((first_pg >> 5) > cur_batch) {              // warp-uniform; K of tile j+2 is at most 11 pages ahead
+        cur = nxt;
+        ++cur_batch;
+        nxt = fetch(cur_batch + 1);
+      }
+      go = load_tile(j, 1, j % nv, j / nv);
+      if (go && j + 2 < n_tiles) go = load_tile(j + 2, 0, j & 1, (j + 2) >> 1);
     }
+    if (kProfile && lane == 0) clk.flush(p.prof, kProfLoadWaitEmpty, kProfLoadIssue);
   } else if (warp == 5) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc_bf16(kBM, kBN);
       const uint32_t idesc_o = umma_idesc_bf16_b_mn(kBM, kD);
-      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s), ring_addr = smem_u32(ring);
+      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      const uint32_t k_ring_addr = smem_u32(k_ring), v_ring_addr = smem_u32(v_ring);
       bool ok = mbar_wait(q_full, 0);
       int reason = kWaitFullTimeout;
       auto issue_s = [&](int j) -> bool {
-        const int item = 2 * j, slot = item % slots, use = item / slots;
-        if (!mbar_wait(&kv_full[slot], use & 1)) return false;
+        const int slot = j & 1, use = j >> 1;
+        if (!mbar_wait(&k_full[slot], use & 1)) return false;
+        clk.tick(kProfMmaWaitK);
         tc_fence_after_sync();
-        const uint32_t k_addr = ring_addr + slot * kSlotBytes;
+        const uint32_t k_addr = k_ring_addr + slot * kSlotBytes;
 #pragma unroll
         for (int ks = 0; ks < kD / 16; ++ks) {
           const uint64_t a = umma_desc_sw128(q_addr + (ks >> 2) * kQHalf + (ks & 3) * 32);
           const uint64_t bd = umma_desc_sw128(k_addr + (ks >> 2) * kSlotHalf + (ks & 3) * 32);
           umma_bf16(tmem_base + (j & 1) * kBN, a, bd, idesc_s, ks > 0);
         }
-        umma_commit(&kv_empty[slot]);
+        umma_commit(&k_empty[slot]);
         umma_commit(&s_full[j & 1]);
+        clk.tick(kProfMmaIssue);
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int j = 0; ok && j < n_tiles; ++j) {
         if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }
         if (!mbar_wait(p_ready, j & 1)) { ok = false; reason = kWaitAccumTimeout; break; }
-        const int item = 2 * j + 1, slot = item % slots, use = item / slots;
-        if (!mbar_wait(&kv_full[slot], use & 1)) { ok = false; break; }
+        clk.tick(kProfMmaWaitP);
+        const int slot = j % nv, use = j / nv;
+        if (!mbar_wait(&v_full[slot], use & 1)) { ok = false; break; }
+        clk.tick(kProfMmaWaitV);
         tc_fence_after_sync();
-        const uint32_t v_addr = ring_addr + slot * kSlotBytes;
+        const uint32_t v_addr = v_ring_addr + slot * kSlotBytes;
 #pragma unroll
         for (int ks = 0; ks < kBN / 16; ++ks) {
           const uint64_t a = umma_desc_sw128(p_addr + ks * 32);
           const uint64_t bd = umma_desc_sw128_mn(v_addr + ks * 2048, kSlotHalf, 1024);
           umma_bf16(tmem_base + kTmemO, a, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(&kv_empty[slot]);
+        umma_commit(&v_empty[slot]);
         umma_commit(o_done);
+        clk.tick(kProfMmaIssue);
       }
+      if (kProfile) clk.flush(p.prof, kProfMmaWaitK, kProfMmaIssue);
       if (!ok || *abort_flag) {
         if (!ok) report_status(p.status, kKernelId, reason);
         *abort_flag = 1;
@@ -233,22 +307,34 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int j = 0; j < n_tiles; ++j) {
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[j & 1], (j >> 1) & 1) && *abort_flag == 0);
       if (!ok) break;
+      clk.tick(kProfSoftWaitS);
       tc_fence_after_sync();
       uint32_t sr[4][16];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld16(lane_taddr + (j & 1) * kBN + c * 16, sr[c]);
       tmem_ld_wait();
+      clk.tick(kProfSoftLoad);
       const int k0 = j * kBN;
-      float mt = -INFINITY;
+      if (k0 + kBN - 1 > pos_row) {              // only tiles that cross the diagonal mask anything
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float s = __uint_as_float(sr[c][i]) * p.scale_log2;
-          s = (k0 + c * 16 + i <= pos_row) ? s : -INFINITY;
-          sr[c][i] = __float_as_uint(s);
-          mt = fmaxf(mt, s);
-        }
+          for (int i = 0; i < 16; ++i)
+            if (k0 + c * 16 + i > pos_row) sr[c][i] = 0xff800000u;      // -inf
+      }
+      // Row maximum of the raw scores (the scale is positive, so it commutes with max).
+      float mx[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float a0 = fmax3(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
+        const float a1 = fmax3(__uint_as_float(sr[c][3]), __uint_as_float(sr[c][4]), __uint_as_float(sr[c][5]));
+        const float a2 = fmax3(__uint_as_float(sr[c][6]), __uint_as_float(sr[c][7]), __uint_as_float(sr[c][8]));
+        const float a3 = fmax3(__uint_as_float(sr[c][9]), __uint_as_float(sr[c][10]), __uint_as_float(sr[c][11]));
+        const float a4 = fmax3(__uint_as_float(sr[c][12]), __uint_as_float(sr[c][13]), __uint_as_float(sr[c][14]));
+        mx[c] = fmax3(fmax3(a0, a1, a2), fmax3(a3, a4, __uint_as_float(sr[c][15])), -INFINITY);
+      }
+      const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+      clk.tick(kProfSoftMax);
       bool o_ready = (j == 0);
       if (j == 0) {
         m = mt;                                  // column 0 is never masked, so this is finite
@@ -263,34 +349,48 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const float alpha = exp2f(m - m_new);
           l *= alpha;
           m = m_new;
+          const uint64_t alpha2 = pack_f32x2(alpha, alpha);
 #pragma unroll 1
           for (int ch = 0; ch < kD / 16; ++ch) {
             uint32_t o[16];
             tmem_ld16(lane_taddr + kTmemO + ch * 16, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            for (int i = 0; i < 16; i += 2) {
+              float lo, hi;
+              unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(o[i]), __uint_as_float(o[i + 1])), alpha2), lo, hi);
+              o[i] = __float_as_uint(lo);
+              o[i + 1] = __float_as_uint(hi);
+            }
             tmem_st16(lane_taddr + kTmemO + ch * 16, o);
           }
           tmem_st_wait();
         }
       }
+      clk.tick(kProfSoftRescale);
+      // p = 2^(s * scale - m): one packed FMA per two scores, one MUFU each, four independent sums.
       uint32_t packed[32];
-      float sum = 0.f;
+      const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), negm2 = pack_f32x2(-m, -m);
+      float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int i = 0; i < 16; i += 2) {
-          const float p0 = exp2f(__uint_as_float(sr[c][i]) - m);
-          const float p1 = exp2f(__uint_as_float(sr[c][i + 1]) - m);
-          sum += p0 + p1;
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, negm2),
+                       x0, x1);
+          const float p0 = exp2f(x0), p1 = exp2f(x1);
+          sums[(i >> 1) & 3] += p0 + p1;
           packed[c * 8 + (i >> 1)] = pack_bf16(p0, p1);
         }
+      const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
       l += sum;
+      clk.tick(kProfSoftExp);
       if (!o_ready) {                            // the previous P V must have finished reading the P tile
         ok = __all_sync(0xffffffffu, mbar_wait(o_done, (j - 1) & 1));
         if (!ok) break;
       }
+      clk.tick(kProfSoftWaitO);
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         const uint32_t addr = p_row + ((c ^ (r & 7)) << 4);
@@ -301,6 +401,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(p_ready);
+      clk.tick(kProfSoftStore);
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_done, (n_tiles - 1) & 1) && *abort_flag == 0);
     if (ok) {
@@ -331,6 +432,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       report_status(p.status, kKernelId, kWaitAccumTimeout);
       *abort_flag = 1;
     }
+    clk.tick(kProfSoftEpilogue);
+    if (kProfile && threadIdx.x == 0) {
+      clk.flush(p.prof, kProfSoftWaitS, kProfSoftEpilogue);
+      atomicAdd(&p.prof[kProfTiles], static_cast<unsigned long long>(n_tiles));
+    }
   }
 
   tc_fence_before_sync();
@@ -339,6 +445,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (kProfile && threadIdx.x == 0)
+    atomicAdd(&p.prof[kProfCtaTotal], static_cast<unsigned long long>(clock64() - cta_t0));
 }
 
 // ---- host side ----------------------------------------------------------------------------------
@@ -416,10 +524,10 @@ int xv_attn_prefill_tc_supported(int d, int block_size) {
   return (block_size <= kBN ? kBN % block_size == 0 : block_size % kBN == 0) ? 1 : 0;
 }
 
-int xv_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+static int launch_prefill_tc(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
                        const int* cu_q, const int* kv_lens, void* out, int seq_begin, int num_seqs, int max_q_len,
                        int total_tokens, int num_blocks, int hq, int hkv, int d, int block_size, int max_blocks,
-                       float scale, int* status, cudaStream_t stream) {
+                       float scale, int* status, unsigned long long* prof, cudaStream_t stream) {
   if (num_seqs <= 0 || max_q_len <= 0) return 0;
   if (!xv_attn_prefill_tc_supported(d, block_size)) return XV_ERR_UNSUPPORTED;
   if (hq % hkv || total_tokens <= 0 || num_blocks <= 0) return XV_ERR_SHAPE;
@@ -428,8 +536,10 @@ int xv_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, 
     return XV_ERR_SHAPE;
   static bool attr = false;
   if (!attr) {
-    if (cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemRequest) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(attn_prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemRequest) != cudaSuccess ||
+        cudaFuncSetAttribute(attn_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemRequest) != cudaSuccess)
       return XV_ERR_LAUNCH;
     attr = true;
   }
@@ -448,9 +558,34 @@ int xv_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, 
   p.num_blocks = num_blocks;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  p.prof = prof;
   dim3 grid((max_q_len + kBM - 1) / kBM, hq, num_seqs);
-  attn_prefill_tc_kernel<<<grid, kThreads, kSmemRequest, stream>>>(map_q, map_k, map_v, p);
+  if (prof)
+    attn_prefill_tc_kernel<true><<<grid, kThreads, kSmemRequest, stream>>>(map_q, map_k, map_v, p);
+  else
+    attn_prefill_tc_kernel<false><<<grid, kThreads, kSmemRequest, stream>>>(map_q, map_k, map_v, p);
   return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
+}
+
+int xv_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                       const int* cu_q, const int* kv_lens, void* out, int seq_begin, int num_seqs, int max_q_len,
+                       int total_tokens, int num_blocks, int hq, int hkv, int d, int block_size, int max_blocks,
+                       float scale, int* status, cudaStream_t stream) {
+  return launch_prefill_tc(q, k_cache, v_cache, block_tables, cu_q, kv_lens, out, seq_begin, num_seqs, max_q_len,
+                           total_tokens, num_blocks, hq, hkv, d, block_size, max_blocks, scale, status, nullptr, stream);
+}
+
+// Same launch with per-phase cycle counters: `prof` points to xv_attn_prefill_tc_profile_slots() zeroed
+// 64-bit device counters that the kernel adds to (softmax, MMA-issue and load warps: time waiting vs working).
+int xv_attn_prefill_tc_profile_slots(void) { return kProfSlots; }
+int xv_attn_prefill_tc_profile(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                               const int* cu_q, const int* kv_lens, void* out, int seq_begin, int num_seqs,
+                               int max_q_len, int total_tokens, int num_blocks, int hq, int hkv, int d, int block_size,
+                               int max_blocks, float scale, int* status, unsigned long long* prof,
+                               cudaStream_t stream) {
+  if (!prof) return XV_ERR_SHAPE;
+  return launch_prefill_tc(q, k_cache, v_cache, block_tables, cu_q, kv_lens, out, seq_begin, num_seqs, max_q_len,
+                           total_tokens, num_blocks, hq, hkv, d, block_size, max_blocks, scale, status, prof, stream);
 }
 
 }  // extern "C"

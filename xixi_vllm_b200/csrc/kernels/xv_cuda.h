@@ -116,6 +116,14 @@ int xv_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, 
                        const int* cu_q, const int* kv_lens, void* out, int seq_begin, int num_seqs, int max_q_len,
                        int total_tokens, int num_blocks, int hq, int hkv, int d, int block_size, int max_blocks,
                        float scale, int* status, cudaStream_t stream);
+// Instrumented build of the same kernel: adds per-phase cycle totals to `prof` (xv_attn_prefill_tc_profile_slots()
+// zero-initialised 64-bit device counters). For finding where the warps of a CTA wait; slower than the plain kernel.
+int xv_attn_prefill_tc_profile_slots(void);
+int xv_attn_prefill_tc_profile(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                               const int* cu_q, const int* kv_lens, void* out, int seq_begin, int num_seqs,
+                               int max_q_len, int total_tokens, int num_blocks, int hq, int hkv, int d, int block_size,
+                               int max_blocks, float scale, int* status, unsigned long long* prof,
+                               cudaStream_t stream);
 
 // ---- sampling ----
 int xv_argmax(const void* logits, long long* out, int rows, int vocab, long long ld, cudaStream_t stream);

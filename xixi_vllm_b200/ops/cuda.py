@@ -74,6 +74,8 @@ def lib():
     L.xv_attn_prefill_tc_supported.argtypes = [_i32, _i32]
     L.xv_attn_prefill_tc.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
                                      _i32, _i32, _i32, _f32, _vp, _vp]
+    L.xv_attn_prefill_tc_profile.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
+                                             _i32, _i32, _i32, _f32, _vp, _vp, _vp]
     L.xv_argmax.argtypes = [_vp, _vp, _i32, _i32, _i64, _vp]
     L.xv_sample.argtypes = [_vp, _vp, _i32, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp]
     L.xv_tp_reduce_norm.argtypes = [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _vp, _vp, _vp, _vp, _i32, _i32, _f32,
@@ -376,6 +378,31 @@ def paged_attention(q, k_cache, v_cache, attn, scale, num_q_heads, num_kv_heads,
                                  attn.max_q_len, num_q_heads, num_kv_heads, head_dim, bs, maxb, scale, _stream()),
                "attn_prefill")
     return out
+
+
+PREFILL_PHASES = ("softmax: wait S", "softmax: tcgen05.ld S", "softmax: mask+max", "softmax: rescale O",
+                  "softmax: exp+pack", "softmax: wait previous PV", "softmax: store P", "softmax: epilogue",
+                  "mma: wait K tile", "mma: wait P", "mma: wait V tile", "mma: issue", "load: wait free slot",
+                  "load: block table + TMA issue", "CTA lifetime", "tiles", "CTA setup")
+
+
+def prefill_phase_profile(q, k_cache, v_cache, attn, scale, num_q_heads, num_kv_heads, head_dim) -> dict[str, int]:
+    """Runs the instrumented tcgen05 prefill kernel once and returns cycles per phase summed over CTAs
+    (one observer thread per warp role), plus the tile count."""
+    L = lib()
+    st = _state(q)
+    n = L.xv_attn_prefill_tc_profile_slots()
+    prof = torch.zeros(n, dtype=torch.int64, device=q.device)
+    out = torch.empty_like(q)
+    n_d = attn.num_decode
+    _check(L.xv_attn_prefill_tc_profile(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                        attn.block_tables.data_ptr(), attn.cu_q.data_ptr(), attn.kv_lens.data_ptr(),
+                                        out.data_ptr(), n_d, attn.num_seqs - n_d, attn.max_q_len, q.shape[0],
+                                        k_cache.shape[0], num_q_heads, num_kv_heads, head_dim, k_cache.shape[2],
+                                        attn.block_tables.shape[1], scale, st.status.data_ptr(), prof.data_ptr(),
+                                        _stream()), "attn_prefill_tc_profile")
+    vals = prof.cpu().tolist()
+    return dict(zip(PREFILL_PHASES, vals))
 
 
 def argmax(logits):

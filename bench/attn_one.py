@@ -32,7 +32,11 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--phases", action="store_true",
                     help="prefill: run the instrumented kernel once and print cycles per phase and tile")
+    ap.add_argument("--single-head", action="store_true",
+                    help="prefill: one head per CTA instead of two heads of a KV group")
     a = ap.parse_args()
+    if a.single_head:
+        cuda.prefill_pair_heads(False)
     B, L = a.batch, a.len
     q_lens = [1] * B if a.mode == "decode" else [L] * B
     q, k, v, cu, kvl, bt = _attn_setup(q_lens, [L] * B, a.hq, a.hkv)

@@ -106,3 +106,15 @@ def test_prefill_tensor_core_kernel_unsupported_page_size_falls_back():
     from xixi_vllm_b200.ops import cuda
     assert not cuda.prefill_uses_tensor_cores(D, 48, 300)
     _run([200], [200], 16, 8, bs=48)
+
+
+def test_prefill_tensor_core_kernel_one_head_per_cta_form():
+    """Odd KV-group sizes (and the forced single-head form) use one head per CTA, two CTAs per SM."""
+    from xixi_vllm_b200.ops import cuda
+    _run([300, 129], [300, 256 + 129], 8, 8, seed=11)            # group of 1: cannot pair heads
+    _run([200], [200], 3, 1, seed=12)                            # group of 3
+    cuda.prefill_pair_heads(False)
+    try:
+        _run([300, 129, 70, 1], [300, 256 + 129, 70, 513], 16, 8, seed=13)
+    finally:
+        cuda.prefill_pair_heads(True)

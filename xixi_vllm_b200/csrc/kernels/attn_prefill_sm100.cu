@@ -42,17 +42,17 @@ using namespace xv;
 constexpr int kBM = 128;                       // query rows per CTA
 constexpr int kBN = 64;                        // KV tokens per tile
 constexpr int kD = 128;                        // head dimension
-constexpr int kThreads = 192;
 constexpr int kQBytes = kBM * kD * 2;          // 32 KiB, two 64-column halves of 16 KiB
 constexpr int kQHalf = kBM * 128;
 constexpr int kSlotBytes = kBN * kD * 2;       // 16 KiB, two 64-column halves of 8 KiB
 constexpr int kSlotHalf = kBN * 128;
 constexpr int kPBytes = kBM * kBN * 2;         // 16 KiB
-constexpr int kMaxSlots = 4;
+constexpr int kMaxRing = 4;                    // slots per K or V ring
 constexpr int kBarBytes = 256;
-constexpr int kSmemRequest = kQBytes + kPBytes + kMaxSlots * kSlotBytes + kBarBytes;
-constexpr uint32_t kTmemCols = 256;            // S0 [0,64) S1 [64,128) O [128,256)
-constexpr uint32_t kTmemO = 128;
+// One head per CTA: 2 + 2 ring slots so that two CTAs fit an SM. Two heads: 4 + 4 slots, one CTA per SM.
+constexpr int kSmemRequest1 = kQBytes + kPBytes + 4 * kSlotBytes + kBarBytes;
+constexpr int kSmemRequest2 = 2 * (kQBytes + kPBytes) + 8 * kSlotBytes + kBarBytes;
+constexpr uint32_t kTmemO = 128;               // column offset of a unit's output accumulator
 constexpr int kKernelId = 7;
 constexpr float kRescaleThreshold = 8.f;       // log2 units
 
@@ -95,12 +95,17 @@ struct PhaseClock<false> {
   __device__ __forceinline__ void flush(unsigned long long*, int, int) {}
 };
 
-template <bool kProfile>
-__global__ void __launch_bounds__(kThreads, 2)
+// kUnits = 2: the CTA handles two query heads of one KV group (same rows, same K/V tiles), one
+// softmax warpgroup each, alone on its SM. kUnits = 1: one head per CTA, two CTAs per SM.
+template <int kUnits, bool kProfile>
+__global__ void __launch_bounds__(kUnits * 128 + 64, kUnits == 1 ? 2 : 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  const int b = p.seq_begin + blockIdx.z, head = blockIdx.y;
+  constexpr int kProducerWarp = 4 * kUnits, kMmaWarp = 4 * kUnits + 1;
+  constexpr int kFixedBytes = kUnits * (kQBytes + kPBytes);
+  constexpr uint32_t kTmemCols = 256 * kUnits;   // per unit: S0 [0,64) S1 [64,128) O [128,256)
+  const int b = p.seq_begin + blockIdx.z, head0 = blockIdx.y * kUnits;
   const int q_begin = p.cu_q[b];
   const int q_len = p.cu_q[b + 1] - q_begin;
   const int row0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * kBM;   // long tiles first
@@ -109,58 +114,61 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int pos0 = kv_len - q_len;                           // absolute position of query row 0
   const int rows_valid = min(kBM, q_len - row0);
   const int n_tiles = (pos0 + row0 + rows_valid - 1) / kBN + 1;
-  const int hk = head / (p.hq / p.hkv);
+  const int hk = head0 / (p.hq / p.hkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   PhaseClock<kProfile> clk;
   const long long cta_t0 = kProfile ? clock64() : 0;
   clk.start();
 
-  // The swizzled tiles need 1024-byte alignment; the ring gets 4 slots when no padding was needed.
+  // The swizzled tiles need 1024-byte alignment. Whatever shared memory is left after the Q and P
+  // tiles becomes K and V ring slots (at most kMaxRing each).
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw & 1023u)) & 1023u;
   uint32_t dyn;
   asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
-  int slots = (static_cast<int>(dyn) - static_cast<int>(pad) - kBarBytes - kQBytes - kPBytes) / kSlotBytes;
-  slots = slots > kMaxSlots ? kMaxSlots : slots;
+  int slots = (static_cast<int>(dyn) - static_cast<int>(pad) - kBarBytes - kFixedBytes) / kSlotBytes;
+  slots = slots > 2 * kMaxRing ? 2 * kMaxRing : slots;
+  const int nk = slots / 2, nv = slots - nk;
   uint8_t* smem = smem_raw + pad;
-  uint8_t* q_s = smem;
-  uint8_t* p_s = smem + kQBytes;
-  uint8_t* k_ring = p_s + kPBytes;               // 2 slots
-  uint8_t* v_ring = k_ring + 2 * kSlotBytes;     // nv = slots - 2 slots
-  const int nv = slots - 2;
+  uint8_t* q_s = smem;                                   // [kUnits][2 halves][128 rows][128 B]
+  uint8_t* p_s = q_s + kUnits * kQBytes;                 // [kUnits][128 rows][128 B]
+  uint8_t* k_ring = p_s + kUnits * kPBytes;
+  uint8_t* v_ring = k_ring + nk * kSlotBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(k_ring + slots * kSlotBytes);
   uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;                   // [2]
-  uint64_t* v_full = k_full + 2;                 // [2]
-  uint64_t* k_empty = v_full + 2;                // [2]
-  uint64_t* v_empty = k_empty + 2;               // [2]
-  uint64_t* s_full = v_empty + 2;                // [2]
-  uint64_t* p_ready = s_full + 2;
-  uint64_t* o_done = p_ready + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
+  uint64_t* k_full = bars + 1;                   // [kMaxRing]
+  uint64_t* v_full = k_full + kMaxRing;          // [kMaxRing]
+  uint64_t* k_empty = v_full + kMaxRing;         // [kMaxRing]
+  uint64_t* v_empty = k_empty + kMaxRing;        // [kMaxRing]
+  uint64_t* s_full = v_empty + kMaxRing;         // [kUnits][2]
+  uint64_t* p_ready = s_full + 2 * kUnits;       // [kUnits]
+  uint64_t* o_done = p_ready + kUnits;           // [kUnits]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + kUnits);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  if (slots < 3) {                               // cannot happen with the launch below; never index past the ring
+  if (nk < 2 || nv < 1) {                        // cannot happen with the launch below; never index past the rings
     if (threadIdx.x == 0) report_status(p.status, kKernelId, kBadIndex);
     return;
   }
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kMaxRing; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
     }
-    mbar_init(&s_full[0], 1);
-    mbar_init(&s_full[1], 1);
-    mbar_init(p_ready, 128);
-    mbar_init(o_done, 1);
+    for (int u = 0; u < kUnits; ++u) {
+      mbar_init(&s_full[2 * u], 1);
+      mbar_init(&s_full[2 * u + 1], 1);
+      mbar_init(&p_ready[u], 128);
+      mbar_init(&o_done[u], 1);
+    }
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -171,16 +179,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (threadIdx.x == 0) clk.tick(kProfSetup);
   clk.start();
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ---------------- TMA producer ----------------
     const uint64_t pol = l2_policy_evict_normal();
     if (lane == 0) {
       prefetch_tensormap(&map_q);
       prefetch_tensormap(&map_k);
       prefetch_tensormap(&map_v);
-      mbar_expect_tx(q_full, kQBytes);
-      tma_load_2d(q_s, &map_q, q_full, head * kD, q_begin + row0, pol);
-      tma_load_2d(q_s + kQHalf, &map_q, q_full, head * kD + 64, q_begin + row0, pol);
+      mbar_expect_tx(q_full, kUnits * kQBytes);
+      for (int u = 0; u < kUnits; ++u) {
+        tma_load_2d(q_s + u * kQBytes, &map_q, q_full, (head0 + u) * kD, q_begin + row0, pol);
+        tma_load_2d(q_s + u * kQBytes + kQHalf, &map_q, q_full, (head0 + u) * kD + 64, q_begin + row0, pol);
+      }
     }
     const int bs = p.block_size;
     const int rows_per_load = bs < kBN ? bs : kBN;
@@ -229,22 +239,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (lane == 0) clk.tick(kProfLoadIssue);
       return true;
     };
-    // K runs two tiles ahead of V: a K slot frees as soon as its S = Q K^T finishes, a V slot only
-    // after the softmax of that tile, so the order is K0 K1 V0 K2 V1 K3 ...
-    bool go = load_tile(0, 0, 0, 0);
-    if (go && n_tiles > 1) go = load_tile(1, 0, 1, 0);
+    // K runs nk tiles ahead of V: a K slot frees as soon as the S = Q K^T that read it finishes, a V
+    // slot only after the softmax of that tile. Order: K0 .. K(nk-1), then V0 K(nk) V1 K(nk+1) ...
+    // (nk <= 4 tiles = 16 pages of 16 tokens, so a K tile is never beyond the next table batch.)
+    bool go = true;
+    for (int j = 0; go && j < nk && j < n_tiles; ++j) go = load_tile(j, 0, j, 0);
     for (int j = 0; go && j < n_tiles; ++j) {
       const int first_pg = min(j * kBN / bs, last_page);
-      while ((first_pg >> 5) > cur_batch) {              // warp-uniform; K of tile j+2 is at most 11 pages ahead
+      while ((first_pg >> 5) > cur_batch) {              // warp-uniform
         cur = nxt;
         ++cur_batch;
         nxt = fetch(cur_batch + 1);
       }
       go = load_tile(j, 1, j % nv, j / nv);
-      if (go && j + 2 < n_tiles) go = load_tile(j + 2, 0, j & 1, (j + 2) >> 1);
+      if (go && j + nk < n_tiles) go = load_tile(j + nk, 0, (j + nk) % nk, (j + nk) / nk);
     }
     if (kProfile && lane == 0) clk.flush(p.prof, kProfLoadWaitEmpty, kProfLoadIssue);
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc_bf16(kBM, kBN);
@@ -253,42 +264,51 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const uint32_t k_ring_addr = smem_u32(k_ring), v_ring_addr = smem_u32(v_ring);
       bool ok = mbar_wait(q_full, 0);
       int reason = kWaitFullTimeout;
-      auto issue_s = [&](int j) -> bool {
-        const int slot = j & 1, use = j >> 1;
+      auto issue_s = [&](int j) -> bool {                // S(j) of every unit from one K tile
+        const int slot = j % nk, use = j / nk;
         if (!mbar_wait(&k_full[slot], use & 1)) return false;
         clk.tick(kProfMmaWaitK);
         tc_fence_after_sync();
         const uint32_t k_addr = k_ring_addr + slot * kSlotBytes;
 #pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks) {
-          const uint64_t a = umma_desc_sw128(q_addr + (ks >> 2) * kQHalf + (ks & 3) * 32);
-          const uint64_t bd = umma_desc_sw128(k_addr + (ks >> 2) * kSlotHalf + (ks & 3) * 32);
-          umma_bf16(tmem_base + (j & 1) * kBN, a, bd, idesc_s, ks > 0);
+        for (int u = 0; u < kUnits; ++u) {
+#pragma unroll
+          for (int ks = 0; ks < kD / 16; ++ks) {
+            const uint64_t a = umma_desc_sw128(q_addr + u * kQBytes + (ks >> 2) * kQHalf + (ks & 3) * 32);
+            const uint64_t bd = umma_desc_sw128(k_addr + (ks >> 2) * kSlotHalf + (ks & 3) * 32);
+            umma_bf16(tmem_base + u * 256 + (j & 1) * kBN, a, bd, idesc_s, ks > 0);
+          }
+          umma_commit(&s_full[2 * u + (j & 1)]);
         }
         umma_commit(&k_empty[slot]);
-        umma_commit(&s_full[j & 1]);
         clk.tick(kProfMmaIssue);
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int j = 0; ok && j < n_tiles; ++j) {
         if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }
-        if (!mbar_wait(p_ready, j & 1)) { ok = false; reason = kWaitAccumTimeout; break; }
-        clk.tick(kProfMmaWaitP);
         const int slot = j % nv, use = j / nv;
-        if (!mbar_wait(&v_full[slot], use & 1)) { ok = false; break; }
-        clk.tick(kProfMmaWaitV);
-        tc_fence_after_sync();
-        const uint32_t v_addr = v_ring_addr + slot * kSlotBytes;
 #pragma unroll
-        for (int ks = 0; ks < kBN / 16; ++ks) {
-          const uint64_t a = umma_desc_sw128(p_addr + ks * 32);
-          const uint64_t bd = umma_desc_sw128_mn(v_addr + ks * 2048, kSlotHalf, 1024);
-          umma_bf16(tmem_base + kTmemO, a, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+        for (int u = 0; u < kUnits; ++u) {
+          if (!mbar_wait(&p_ready[u], j & 1)) { ok = false; reason = kWaitAccumTimeout; break; }
+          clk.tick(kProfMmaWaitP);
+          if (u == 0) {
+            if (!mbar_wait(&v_full[slot], use & 1)) { ok = false; break; }
+            clk.tick(kProfMmaWaitV);
+          }
+          tc_fence_after_sync();
+          const uint32_t v_addr = v_ring_addr + slot * kSlotBytes;
+#pragma unroll
+          for (int ks = 0; ks < kBN / 16; ++ks) {
+            const uint64_t a = umma_desc_sw128(p_addr + u * kPBytes + ks * 32);
+            const uint64_t bd = umma_desc_sw128_mn(v_addr + ks * 2048, kSlotHalf, 1024);
+            umma_bf16(tmem_base + u * 256 + kTmemO, a, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit(&o_done[u]);
+          clk.tick(kProfMmaIssue);
         }
+        if (!ok) break;
         umma_commit(&v_empty[slot]);
-        umma_commit(o_done);
-        clk.tick(kProfMmaIssue);
       }
       if (kProfile) clk.flush(p.prof, kProfMmaWaitK, kProfMmaIssue);
       if (!ok || *abort_flag) {
@@ -297,15 +317,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
     }
   } else {
-    // ---------------- softmax + epilogue: thread r owns query row r ----------------
-    const int r = threadIdx.x;
+    // ---------------- softmax + epilogue: thread r of unit u owns query row r of head head0 + u ----------------
+    const int u = warp >> 2;
+    const int r = threadIdx.x & 127;
+    const int head = head0 + u;
     const int pos_row = pos0 + row0 + (r < rows_valid ? r : rows_valid - 1);
-    const uint32_t lane_taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    const uint32_t p_row = smem_u32(p_s) + r * 128;
+    const uint32_t lane_taddr = tmem_base + u * 256 + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const uint32_t p_row = smem_u32(p_s) + u * kPBytes + r * 128;
+    uint64_t* my_s_full = &s_full[2 * u];
+    uint64_t* my_p_ready = &p_ready[u];
+    uint64_t* my_o_done = &o_done[u];
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[j & 1], (j >> 1) & 1) && *abort_flag == 0);
+      ok = __all_sync(0xffffffffu, mbar_wait(&my_s_full[j & 1], (j >> 1) & 1) && *abort_flag == 0);
       if (!ok) break;
       clk.tick(kProfSoftWaitS);
       tc_fence_after_sync();
@@ -341,7 +366,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       } else {
         const bool need = mt > m + kRescaleThreshold;
         if (__any_sync(0xffffffffu, need)) {
-          ok = __all_sync(0xffffffffu, mbar_wait(o_done, (j - 1) & 1));
+          ok = __all_sync(0xffffffffu, mbar_wait(my_o_done, (j - 1) & 1));
           if (!ok) break;
           tc_fence_after_sync();
           o_ready = true;
@@ -383,11 +408,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           sums[(i >> 1) & 3] += p0 + p1;
           packed[c * 8 + (i >> 1)] = pack_bf16(p0, p1);
         }
-      const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
-      l += sum;
+      l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
       clk.tick(kProfSoftExp);
       if (!o_ready) {                            // the previous P V must have finished reading the P tile
-        ok = __all_sync(0xffffffffu, mbar_wait(o_done, (j - 1) & 1));
+        ok = __all_sync(0xffffffffu, mbar_wait(my_o_done, (j - 1) & 1));
         if (!ok) break;
       }
       clk.tick(kProfSoftWaitO);
@@ -400,10 +424,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(p_ready);
+      mbar_arrive(my_p_ready);
       clk.tick(kProfSoftStore);
     }
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_done, (n_tiles - 1) & 1) && *abort_flag == 0);
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(my_o_done, (n_tiles - 1) & 1) && *abort_flag == 0);
     if (ok) {
       tc_fence_after_sync();
       const float inv = 1.f / l;
@@ -441,7 +465,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -517,7 +541,12 @@ int tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long cols
 
 }  // namespace
 
+static int g_force_single_unit = 0;
+
 extern "C" {
+
+// 1: always one head per CTA (for comparing the two forms); 0: pair heads of a KV group when possible.
+void xv_attn_prefill_tc_single_unit(int on) { g_force_single_unit = on; }
 
 int xv_attn_prefill_tc_supported(int d, int block_size) {
   if (d != kD || block_size <= 0 || block_size % 16) return 0;
@@ -536,10 +565,11 @@ static int launch_prefill_tc(const void* q, const void* k_cache, const void* v_c
     return XV_ERR_SHAPE;
   static bool attr = false;
   if (!attr) {
-    if (cudaFuncSetAttribute(attn_prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemRequest) != cudaSuccess ||
-        cudaFuncSetAttribute(attn_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemRequest) != cudaSuccess)
+    const auto at = cudaFuncAttributeMaxDynamicSharedMemorySize;
+    if (cudaFuncSetAttribute(attn_prefill_tc_kernel<1, false>, at, kSmemRequest1) != cudaSuccess ||
+        cudaFuncSetAttribute(attn_prefill_tc_kernel<1, true>, at, kSmemRequest1) != cudaSuccess ||
+        cudaFuncSetAttribute(attn_prefill_tc_kernel<2, false>, at, kSmemRequest2) != cudaSuccess ||
+        cudaFuncSetAttribute(attn_prefill_tc_kernel<2, true>, at, kSmemRequest2) != cudaSuccess)
       return XV_ERR_LAUNCH;
     attr = true;
   }
@@ -559,11 +589,20 @@ static int launch_prefill_tc(const void* q, const void* k_cache, const void* v_c
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
   p.prof = prof;
-  dim3 grid((max_q_len + kBM - 1) / kBM, hq, num_seqs);
-  if (prof)
-    attn_prefill_tc_kernel<true><<<grid, kThreads, kSmemRequest, stream>>>(map_q, map_k, map_v, p);
-  else
-    attn_prefill_tc_kernel<false><<<grid, kThreads, kSmemRequest, stream>>>(map_q, map_k, map_v, p);
+  // Two heads of a KV group per CTA whenever the group size is even: K/V tiles are fetched once for both.
+  const int units = ((hq / hkv) % 2 == 0 && g_force_single_unit == 0) ? 2 : 1;
+  dim3 grid((max_q_len + kBM - 1) / kBM, hq / units, num_seqs);
+  if (units == 2) {
+    if (prof)
+      attn_prefill_tc_kernel<2, true><<<grid, 320, kSmemRequest2, stream>>>(map_q, map_k, map_v, p);
+    else
+      attn_prefill_tc_kernel<2, false><<<grid, 320, kSmemRequest2, stream>>>(map_q, map_k, map_v, p);
+  } else {
+    if (prof)
+      attn_prefill_tc_kernel<1, true><<<grid, 192, kSmemRequest1, stream>>>(map_q, map_k, map_v, p);
+    else
+      attn_prefill_tc_kernel<1, false><<<grid, 192, kSmemRequest1, stream>>>(map_q, map_k, map_v, p);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
 }
 

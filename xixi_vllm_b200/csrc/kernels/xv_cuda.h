@@ -112,6 +112,7 @@ int xv_attn_prefill(const void* q, const void* k_cache, const void* v_cache, con
 // fetched by TMA. `total_tokens` is the row count of q/out, `num_blocks` the page count of the caches.
 // Supported for head_dim 128 and page sizes that divide 64 or are multiples of 64.
 int xv_attn_prefill_tc_supported(int d, int block_size);
+void xv_attn_prefill_tc_single_unit(int on);   // 1: one head per CTA even when heads of a KV group could pair up
 int xv_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
                        const int* cu_q, const int* kv_lens, void* out, int seq_begin, int num_seqs, int max_q_len,
                        int total_tokens, int num_blocks, int hq, int hkv, int d, int block_size, int max_blocks,

@@ -20,7 +20,7 @@ from . import build as _build
 
 __all__ = [
     "lib", "rmsnorm", "add_rmsnorm", "linear", "silu_mul", "embedding", "gather_rows",
-    "qk_norm_rope_cache", "paged_attention", "argmax", "sample", "check_status", "gemm_plan",
+    "qk_norm_rope_cache", "paged_attention", "prefill_pair_heads", "prefill_phase_profile", "argmax", "sample", "check_status", "gemm_plan",
     "decode_splits", "launch_count",
 ]
 
@@ -72,6 +72,8 @@ def lib():
     L.xv_attn_prefill.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
                                   _i32, _f32, _vp]
     L.xv_attn_prefill_tc_supported.argtypes = [_i32, _i32]
+    L.xv_attn_prefill_tc_single_unit.argtypes = [_i32]
+    L.xv_attn_prefill_tc_single_unit.restype = None
     L.xv_attn_prefill_tc.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
                                      _i32, _i32, _i32, _f32, _vp, _vp]
     L.xv_attn_prefill_tc_profile.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
@@ -347,6 +349,12 @@ def prefill_uses_tensor_cores(head_dim: int, block_size: int, max_q_len: int) ->
     if os.environ.get("XV_ATTN_PREFILL", "tc") == "mma" or max_q_len <= 64:
         return False
     return bool(lib().xv_attn_prefill_tc_supported(head_dim, block_size))
+
+
+def prefill_pair_heads(on: bool) -> None:
+    """The tcgen05 prefill kernel gives one CTA two query heads of a KV group (shared K/V tiles) when the
+    group size is even; ``False`` forces one head per CTA (two CTAs per SM), for comparisons."""
+    lib().xv_attn_prefill_tc_single_unit(0 if on else 1)
 
 
 def paged_attention(q, k_cache, v_cache, attn, scale, num_q_heads, num_kv_heads, head_dim):

@@ -109,7 +109,7 @@ def test_prefill_tensor_core_kernel_unsupported_page_size_falls_back():
 
 
 def test_prefill_tensor_core_kernel_one_head_per_cta_form():
-    """Odd KV-group sizes (and the forced single-head form) use one head per CTA, two CTAs per SM."""
+    """Odd KV-group sizes (and the forced single-head form) use one head per CTA."""
     from xixi_vllm_b200.ops import cuda
     _run([300, 129], [300, 256 + 129], 8, 8, seed=11)            # group of 1: cannot pair heads
     _run([200], [200], 3, 1, seed=12)                            # group of 3

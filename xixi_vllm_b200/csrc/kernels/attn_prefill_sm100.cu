@@ -1,13 +1,13 @@
 // Paged causal prefill attention for sm_100a on the 5th-generation tensor cores.
 //
 // One CTA owns 128 query rows of one head of one sequence and walks the sequence's KV pages
-// in tiles of 64 tokens:
+// in tiles of 128 tokens (MMAs narrower than N = 128 leave the tensor pipe waiting on operand reads):
 //   warp 4      - TMA producer: the Q tile once, then per tile the K and V pages named by the
 //                 block table, each page an own cp.async.bulk.tensor box (128-byte swizzle)
 //                 into two rings of 16 KiB shared-memory slots (K runs two tiles ahead of V).
 //                 Block-table entries are read 32 pages at a time, one batch ahead of use.
-//   warp 5      - allocates TMEM and issues tcgen05.mma from one thread: S = Q K^T (M=128, N=64)
-//                 into one of two S buffers in TMEM, one tile ahead of the softmax, and
+//   warp 5      - allocates TMEM and issues tcgen05.mma from one thread: S = Q K^T (M=128, N=128)
+//                 into TMEM as soon as the softmax warps have copied the previous tile's S out, and
 //                 O += P V (M=128, N=128; V is read MN-major exactly as the cache stores it).
 //   warps 0..3  - softmax: thread r owns query row r. tcgen05.ld of the S row, scale + causal
 //                 mask, running max and sum, P rounded to bf16 into a swizzled shared-memory tile
@@ -15,8 +15,9 @@
 //                 TMEM for the whole sequence; it is rescaled in place (tcgen05.ld/st) only when
 //                 a row's maximum grows by more than 2^8, otherwise the stale maximum is kept,
 //                 which the final division by the row sum makes exact.
-// Two CTAs share an SM (256 TMEM columns and ~112 KiB shared memory each), so one CTA's softmax
-// runs under the other's MMAs.
+// A CTA normally carries two query heads of one KV group ("units": same rows, same K/V tiles, one
+// softmax warpgroup and 256 TMEM columns each), so one head's softmax runs under the other's MMAs
+// and every K/V tile is fetched once for both.
 //
 // Every barrier wait is bounded; a wait that runs out records a status code, the CTA stops
 // issuing work, frees its TMEM and returns.
@@ -40,19 +41,20 @@ namespace {
 using namespace xv;
 
 constexpr int kBM = 128;                       // query rows per CTA
-constexpr int kBN = 64;                        // KV tokens per tile
+constexpr int kBN = 128;                       // KV tokens per tile
 constexpr int kD = 128;                        // head dimension
 constexpr int kQBytes = kBM * kD * 2;          // 32 KiB, two 64-column halves of 16 KiB
 constexpr int kQHalf = kBM * 128;
-constexpr int kSlotBytes = kBN * kD * 2;       // 16 KiB, two 64-column halves of 8 KiB
+constexpr int kSlotBytes = kBN * kD * 2;       // 32 KiB, two 64-column halves of 16 KiB
 constexpr int kSlotHalf = kBN * 128;
-constexpr int kPBytes = kBM * kBN * 2;         // 16 KiB
-constexpr int kMaxRing = 4;                    // slots per K or V ring
+constexpr int kPBytes = kBM * kBN * 2;         // 32 KiB, two 64-column halves of 16 KiB
+constexpr int kPHalf = kBM * 128;
+constexpr int kMaxRing = 2;                    // slots per K or V ring
 constexpr int kBarBytes = 256;
-// One head per CTA: 2 + 2 ring slots so that two CTAs fit an SM. Two heads: 4 + 4 slots, one CTA per SM.
-constexpr int kSmemRequest1 = kQBytes + kPBytes + 4 * kSlotBytes + kBarBytes;
-constexpr int kSmemRequest2 = 2 * (kQBytes + kPBytes) + 8 * kSlotBytes + kBarBytes;
-constexpr uint32_t kTmemO = 128;               // column offset of a unit's output accumulator
+// Q and P tiles of every head plus three 32 KiB ring slots (K: 2, V: 1).
+constexpr int kSmemRequest1 = kQBytes + kPBytes + 3 * kSlotBytes + kBarBytes;
+constexpr int kSmemRequest2 = 2 * (kQBytes + kPBytes) + 3 * kSlotBytes + kBarBytes;
+constexpr uint32_t kTmemO = 128;               // per unit: S in columns [0,128), the output accumulator in [128,256)
 constexpr int kKernelId = 7;
 constexpr float kRescaleThreshold = 8.f;       // log2 units
 
@@ -71,7 +73,7 @@ struct Params {
 enum ProfSlot {
   kProfSoftWaitS = 0, kProfSoftLoad, kProfSoftMax, kProfSoftRescale, kProfSoftExp, kProfSoftWaitO, kProfSoftStore,
   kProfSoftEpilogue, kProfMmaWaitK, kProfMmaWaitP, kProfMmaWaitV, kProfMmaIssue, kProfLoadWaitEmpty, kProfLoadIssue,
-  kProfCtaTotal, kProfTiles, kProfSetup, kProfSlots
+  kProfCtaTotal, kProfTiles, kProfSetup, kProfRingSlots, kProfSlots
 };
 
 template <bool kProfile>
@@ -96,15 +98,15 @@ struct PhaseClock<false> {
 };
 
 // kUnits = 2: the CTA handles two query heads of one KV group (same rows, same K/V tiles), one
-// softmax warpgroup each, alone on its SM. kUnits = 1: one head per CTA, two CTAs per SM.
+// softmax warpgroup each. kUnits = 1: one head per CTA (odd group sizes; nothing overlaps its softmax).
 template <int kUnits, bool kProfile>
-__global__ void __launch_bounds__(kUnits * 128 + 64, kUnits == 1 ? 2 : 1)
+__global__ void __launch_bounds__(kUnits * 128 + 64, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   constexpr int kProducerWarp = 4 * kUnits, kMmaWarp = 4 * kUnits + 1;
   constexpr int kFixedBytes = kUnits * (kQBytes + kPBytes);
-  constexpr uint32_t kTmemCols = 256 * kUnits;   // per unit: S0 [0,64) S1 [64,128) O [128,256)
+  constexpr uint32_t kTmemCols = 256 * kUnits;   // per unit: S [0,128) O [128,256)
   const int b = p.seq_begin + blockIdx.z, head0 = blockIdx.y * kUnits;
   const int q_begin = p.cu_q[b];
   const int q_len = p.cu_q[b + 1] - q_begin;
@@ -128,7 +130,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
   int slots = (static_cast<int>(dyn) - static_cast<int>(pad) - kBarBytes - kFixedBytes) / kSlotBytes;
   slots = slots > 2 * kMaxRing ? 2 * kMaxRing : slots;
-  const int nk = slots / 2, nv = slots - nk;
+  const int nk = slots >= 3 ? 2 : slots - 1, nv = slots - nk;
   uint8_t* smem = smem_raw + pad;
   uint8_t* q_s = smem;                                   // [kUnits][2 halves][128 rows][128 B]
   uint8_t* p_s = q_s + kUnits * kQBytes;                 // [kUnits][128 rows][128 B]
@@ -140,8 +142,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint64_t* v_full = k_full + kMaxRing;          // [kMaxRing]
   uint64_t* k_empty = v_full + kMaxRing;         // [kMaxRing]
   uint64_t* v_empty = k_empty + kMaxRing;        // [kMaxRing]
-  uint64_t* s_full = v_empty + kMaxRing;         // [kUnits][2]
-  uint64_t* p_ready = s_full + 2 * kUnits;       // [kUnits]
+  uint64_t* s_full = v_empty + kMaxRing;         // [kUnits] S written by the MMA
+  uint64_t* s_free = s_full + kUnits;            // [kUnits] S copied to registers by the softmax warps
+  uint64_t* p_ready = s_free + kUnits;           // [kUnits]
   uint64_t* o_done = p_ready + kUnits;           // [kUnits]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + kUnits);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -160,8 +163,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_init(&v_empty[s], 1);
     }
     for (int u = 0; u < kUnits; ++u) {
-      mbar_init(&s_full[2 * u], 1);
-      mbar_init(&s_full[2 * u + 1], 1);
+      mbar_init(&s_full[u], 1);
+      mbar_init(&s_free[u], 128);
       mbar_init(&p_ready[u], 128);
       mbar_init(&o_done[u], 1);
     }
@@ -177,6 +180,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) clk.tick(kProfSetup);
+  if (kProfile && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+    p.prof[kProfRingSlots] = static_cast<unsigned long long>(slots);
   clk.start();
 
   if (warp == kProducerWarp) {
@@ -241,7 +246,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     };
     // K runs nk tiles ahead of V: a K slot frees as soon as the S = Q K^T that read it finishes, a V
     // slot only after the softmax of that tile. Order: K0 .. K(nk-1), then V0 K(nk) V1 K(nk+1) ...
-    // (nk <= 4 tiles = 16 pages of 16 tokens, so a K tile is never beyond the next table batch.)
+    // (nk = 2 tiles = 16 pages of 16 tokens, so a K tile is never beyond the next table batch.)
     bool go = true;
     for (int j = 0; go && j < nk && j < n_tiles; ++j) go = load_tile(j, 0, j, 0);
     for (int j = 0; go && j < n_tiles; ++j) {
@@ -264,24 +269,28 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const uint32_t k_ring_addr = smem_u32(k_ring), v_ring_addr = smem_u32(v_ring);
       bool ok = mbar_wait(q_full, 0);
       int reason = kWaitFullTimeout;
-      auto issue_s = [&](int j) -> bool {                // S(j) of every unit from one K tile
+      // S(j) of every unit from one K tile. A unit's S columns are free once its softmax warps
+      // have copied tile j-1 into registers.
+      auto issue_s = [&](int j) -> bool {
         const int slot = j % nk, use = j / nk;
         if (!mbar_wait(&k_full[slot], use & 1)) return false;
         clk.tick(kProfMmaWaitK);
-        tc_fence_after_sync();
         const uint32_t k_addr = k_ring_addr + slot * kSlotBytes;
 #pragma unroll
         for (int u = 0; u < kUnits; ++u) {
+          if (j > 0 && !mbar_wait(&s_free[u], (j - 1) & 1)) return false;
+          clk.tick(kProfMmaWaitP);
+          tc_fence_after_sync();
 #pragma unroll
           for (int ks = 0; ks < kD / 16; ++ks) {
             const uint64_t a = umma_desc_sw128(q_addr + u * kQBytes + (ks >> 2) * kQHalf + (ks & 3) * 32);
             const uint64_t bd = umma_desc_sw128(k_addr + (ks >> 2) * kSlotHalf + (ks & 3) * 32);
-            umma_bf16(tmem_base + u * 256 + (j & 1) * kBN, a, bd, idesc_s, ks > 0);
+            umma_bf16(tmem_base + u * 256, a, bd, idesc_s, ks > 0);
           }
-          umma_commit(&s_full[2 * u + (j & 1)]);
+          umma_commit(&s_full[u]);
+          clk.tick(kProfMmaIssue);
         }
         umma_commit(&k_empty[slot]);
-        clk.tick(kProfMmaIssue);
         return true;
       };
       if (ok) ok = issue_s(0);
@@ -300,7 +309,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const uint32_t v_addr = v_ring_addr + slot * kSlotBytes;
 #pragma unroll
           for (int ks = 0; ks < kBN / 16; ++ks) {
-            const uint64_t a = umma_desc_sw128(p_addr + u * kPBytes + ks * 32);
+            const uint64_t a = umma_desc_sw128(p_addr + u * kPBytes + (ks >> 2) * kPHalf + (ks & 3) * 32);
             const uint64_t bd = umma_desc_sw128_mn(v_addr + ks * 2048, kSlotHalf, 1024);
             umma_bf16(tmem_base + u * 256 + kTmemO, a, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
           }
@@ -324,33 +333,36 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int pos_row = pos0 + row0 + (r < rows_valid ? r : rows_valid - 1);
     const uint32_t lane_taddr = tmem_base + u * 256 + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     const uint32_t p_row = smem_u32(p_s) + u * kPBytes + r * 128;
-    uint64_t* my_s_full = &s_full[2 * u];
+    uint64_t* my_s_full = &s_full[u];
+    uint64_t* my_s_free = &s_free[u];
     uint64_t* my_p_ready = &p_ready[u];
     uint64_t* my_o_done = &o_done[u];
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(&my_s_full[j & 1], (j >> 1) & 1) && *abort_flag == 0);
+      ok = __all_sync(0xffffffffu, mbar_wait(my_s_full, j & 1) && *abort_flag == 0);
       if (!ok) break;
       clk.tick(kProfSoftWaitS);
       tc_fence_after_sync();
-      uint32_t sr[4][16];
+      uint32_t sr[8][16];                          // the whole score row: 128 fp32
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld16(lane_taddr + (j & 1) * kBN + c * 16, sr[c]);
+      for (int c = 0; c < 8; ++c) tmem_ld16(lane_taddr + c * 16, sr[c]);
       tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(my_s_free);                      // the MMA warp may overwrite S with the next tile
       clk.tick(kProfSoftLoad);
       const int k0 = j * kBN;
       if (k0 + kBN - 1 > pos_row) {              // only tiles that cross the diagonal mask anything
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 8; ++c)
 #pragma unroll
           for (int i = 0; i < 16; ++i)
             if (k0 + c * 16 + i > pos_row) sr[c][i] = 0xff800000u;      // -inf
       }
       // Row maximum of the raw scores (the scale is positive, so it commutes with max).
-      float mx[4];
+      float mx[8];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 8; ++c) {
         const float a0 = fmax3(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
         const float a1 = fmax3(__uint_as_float(sr[c][3]), __uint_as_float(sr[c][4]), __uint_as_float(sr[c][5]));
         const float a2 = fmax3(__uint_as_float(sr[c][6]), __uint_as_float(sr[c][7]), __uint_as_float(sr[c][8]));
@@ -358,7 +370,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const float a4 = fmax3(__uint_as_float(sr[c][12]), __uint_as_float(sr[c][13]), __uint_as_float(sr[c][14]));
         mx[c] = fmax3(fmax3(a0, a1, a2), fmax3(a3, a4, __uint_as_float(sr[c][15])), -INFINITY);
       }
-      const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+      const float mt = fmax3(fmax3(mx[0], mx[1], mx[2]), fmax3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) *
+                       p.scale_log2;
       clk.tick(kProfSoftMax);
       bool o_ready = (j == 0);
       if (j == 0) {
@@ -393,12 +406,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
       }
       clk.tick(kProfSoftRescale);
-      // p = 2^(s * scale - m): one packed FMA per two scores, one MUFU each, four independent sums.
-      uint32_t packed[32];
+      if (!o_ready) {                            // the previous P V must have finished reading the P tile
+        ok = __all_sync(0xffffffffu, mbar_wait(my_o_done, (j - 1) & 1));
+        if (!ok) break;
+      }
+      clk.tick(kProfSoftWaitO);
+      // p = 2^(s * scale - m): one packed FMA per two scores, one MUFU each, four independent sums;
+      // every 16 columns go to the swizzled P tile as they are produced.
       const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), negm2 = pack_f32x2(-m, -m);
       float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 8; ++c) {
+        uint32_t packed[8];
 #pragma unroll
         for (int i = 0; i < 16; i += 2) {
           float x0, x1;
@@ -406,22 +425,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        x0, x1);
           const float p0 = exp2f(x0), p1 = exp2f(x1);
           sums[(i >> 1) & 3] += p0 + p1;
-          packed[c * 8 + (i >> 1)] = pack_bf16(p0, p1);
+          packed[i >> 1] = pack_bf16(p0, p1);
         }
-      l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
-      clk.tick(kProfSoftExp);
-      if (!o_ready) {                            // the previous P V must have finished reading the P tile
-        ok = __all_sync(0xffffffffu, mbar_wait(my_o_done, (j - 1) & 1));
-        if (!ok) break;
-      }
-      clk.tick(kProfSoftWaitO);
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint32_t addr = p_row + ((c ^ (r & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * c]),
-                     "r"(packed[4 * c + 1]), "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3])
+        // columns 16c .. 16c+15 = 16-byte chunks 2c, 2c+1 of the row; chunks 0-7 live in the first half tile
+        const uint32_t half_base = p_row + (c >> 2) * kPHalf;
+        const int cc = (2 * c) & 7;
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(half_base + ((cc ^ (r & 7)) << 4)),
+                     "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3])
+                     : "memory");
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(half_base + (((cc + 1) ^ (r & 7)) << 4)),
+                     "r"(packed[4]), "r"(packed[5]), "r"(packed[6]), "r"(packed[7])
                      : "memory");
       }
+      l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
+      clk.tick(kProfSoftExp);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(my_p_ready);

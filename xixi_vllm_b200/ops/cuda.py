@@ -353,7 +353,7 @@ def prefill_uses_tensor_cores(head_dim: int, block_size: int, max_q_len: int) ->
 
 def prefill_pair_heads(on: bool) -> None:
     """The tcgen05 prefill kernel gives one CTA two query heads of a KV group (shared K/V tiles) when the
-    group size is even; ``False`` forces one head per CTA (two CTAs per SM), for comparisons."""
+    group size is even; ``False`` forces one head per CTA, for comparisons."""
     lib().xv_attn_prefill_tc_single_unit(0 if on else 1)
 
 
@@ -391,7 +391,7 @@ def paged_attention(q, k_cache, v_cache, attn, scale, num_q_heads, num_kv_heads,
 PREFILL_PHASES = ("softmax: wait S", "softmax: tcgen05.ld S", "softmax: mask+max", "softmax: rescale O",
                   "softmax: exp+pack", "softmax: wait previous PV", "softmax: store P", "softmax: epilogue",
                   "mma: wait K tile", "mma: wait P", "mma: wait V tile", "mma: issue", "load: wait free slot",
-                  "load: block table + TMA issue", "CTA lifetime", "tiles", "CTA setup")
+                  "load: block table + TMA issue", "CTA lifetime", "tiles", "CTA setup", "ring slots")
 
 
 def prefill_phase_profile(q, k_cache, v_cache, attn, scale, num_q_heads, num_kv_heads, head_dim) -> dict[str, int]:

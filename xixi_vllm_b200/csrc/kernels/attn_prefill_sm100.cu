@@ -2,11 +2,11 @@
 //
 // One CTA owns 128 query rows of one head of one sequence and walks the sequence's KV pages
 // in tiles of 128 tokens (MMAs narrower than N = 128 leave the tensor pipe waiting on operand reads):
-//   warp 4      - TMA producer: the Q tile once, then per tile the K and V pages named by the
+//   warps 4, 5  - TMA producers (K tiles, V tiles): the Q tile once, then per tile the pages named by the
 //                 block table, each page an own cp.async.bulk.tensor box (128-byte swizzle)
 //                 into two rings of 16 KiB shared-memory slots (K runs two tiles ahead of V).
 //                 Block-table entries are read 32 pages at a time, one batch ahead of use.
-//   warp 5      - allocates TMEM and issues tcgen05.mma from one thread: S = Q K^T (M=128, N=128)
+//   warp 6      - allocates TMEM and issues tcgen05.mma from one thread: S = Q K^T (M=128, N=128)
 //                 into TMEM as soon as the softmax warps have copied the previous tile's S out, and
 //                 O += P V (M=128, N=128; V is read MN-major exactly as the cache stores it).
 //   warps 0..3  - softmax: thread r owns query row r. tcgen05.ld of the S row, scale + causal
@@ -100,11 +100,11 @@ struct PhaseClock<false> {
 // kUnits = 2: the CTA handles two query heads of one KV group (same rows, same K/V tiles), one
 // softmax warpgroup each. kUnits = 1: one head per CTA (odd group sizes; nothing overlaps its softmax).
 template <int kUnits, bool kProfile>
-__global__ void __launch_bounds__(kUnits * 128 + 64, 1)
+__global__ void __launch_bounds__(kUnits * 128 + 96, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  constexpr int kProducerWarp = 4 * kUnits, kMmaWarp = 4 * kUnits + 1;
+  constexpr int kProducerWarp = 4 * kUnits, kMmaWarp = 4 * kUnits + 2;    // producers: K warp, V warp
   constexpr int kFixedBytes = kUnits * (kQBytes + kPBytes);
   constexpr uint32_t kTmemCols = 256 * kUnits;   // per unit: S [0,128) O [128,256)
   const int b = p.seq_begin + blockIdx.z, head0 = blockIdx.y * kUnits;
@@ -184,13 +184,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     p.prof[kProfRingSlots] = static_cast<unsigned long long>(slots);
   clk.start();
 
-  if (warp == kProducerWarp) {
-    // ---------------- TMA producer ----------------
+  if (warp == kProducerWarp || warp == kProducerWarp + 1) {
+    // ---------------- TMA producers: one warp streams the K tiles, the other the V tiles ----------------
+    const int is_v = warp - kProducerWarp;
     const uint64_t pol = l2_policy_evict_normal();
-    if (lane == 0) {
+    if (lane == 0 && is_v) prefetch_tensormap(&map_v);
+    if (lane == 0 && !is_v) {
       prefetch_tensormap(&map_q);
       prefetch_tensormap(&map_k);
-      prefetch_tensormap(&map_v);
       mbar_expect_tx(q_full, kUnits * kQBytes);
       for (int u = 0; u < kUnits; ++u) {
         tma_load_2d(q_s + u * kQBytes, &map_q, q_full, (head0 + u) * kD, q_begin + row0, pol);
@@ -199,7 +200,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     const int bs = p.block_size;
     const int rows_per_load = bs < kBN ? bs : kBN;
-    const int loads = kBN / rows_per_load;               // pages per tile (1 when a page holds >= 64 tokens)
+    const int loads = kBN / rows_per_load;               // pages per tile (1 when a page holds a whole tile)
     const int last_page = (kv_len - 1) / bs;
     // Block-table entries are fetched 32 pages at a time (lane l holds page 32*batch + l), one batch
     // ahead of use, so the dependent global load never sits between two TMA issues.
@@ -208,8 +209,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     int cur_batch = 0;
     int cur = fetch(0), nxt = fetch(1);
     const int i = lane >> 1, half = lane & 1;
-    // Loads tile `j` of K (is_v = 0) or V (is_v = 1) into slot `slot` of its ring.
-    auto load_tile = [&](int j, int is_v, int slot, int use) -> bool {
+    uint64_t* full_bars = is_v ? v_full : k_full;
+    uint64_t* empty_bars = is_v ? v_empty : k_empty;
+    uint8_t* ring = is_v ? v_ring : k_ring;
+    const CUtensorMap* map = is_v ? &map_v : &map_k;
+    const int depth = is_v ? nv : nk;
+    // A K slot frees as soon as the S = Q K^T that read it finishes, a V slot only after the softmax
+    // of that tile, so the K warp runs ahead of the V warp by itself.
+    for (int j = 0; j < n_tiles; ++j) {
+      const int first_pg = min(j * kBN / bs, last_page);
+      while ((first_pg >> 5) > cur_batch) {              // warp-uniform
+        cur = nxt;
+        ++cur_batch;
+        nxt = fetch(cur_batch + 1);
+      }
       const int tok = j * kBN + (i < loads ? i : 0) * rows_per_load;
       const int pg = min(tok / bs, last_page);           // past the end: any valid page, the columns are masked
       const int from_cur = __shfl_sync(0xffffffffu, cur, pg & 31);
@@ -220,13 +233,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         blk = 0;
       }
       const int y = (blk * p.hkv + hk) * bs + (bs > kBN ? tok % bs : 0);
-      uint64_t* full = is_v ? &v_full[slot] : &k_full[slot];
-      uint64_t* empty = is_v ? &v_empty[slot] : &k_empty[slot];
+      const int slot = j % depth, use = j / depth;
       int ok = 1;
       if (lane == 0) {
-        ok = mbar_wait(empty, (use & 1) ^ 1) && *abort_flag == 0;
-        if (ok) mbar_expect_tx(full, kSlotBytes);
-        clk.tick(kProfLoadWaitEmpty);
+        ok = mbar_wait(&empty_bars[slot], (use & 1) ^ 1) && *abort_flag == 0;
+        if (ok) mbar_expect_tx(&full_bars[slot], kSlotBytes);
+        if (!is_v) clk.tick(kProfLoadWaitEmpty);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) {
@@ -234,32 +246,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           report_status(p.status, kKernelId, kWaitEmptyTimeout);
           *abort_flag = 1;
         }
-        return false;
+        break;
       }
       if (lane < 2 * loads) {
-        uint8_t* dst = (is_v ? v_ring : k_ring) + slot * kSlotBytes + half * kSlotHalf + i * rows_per_load * 128;
-        tma_load_2d(dst, is_v ? &map_v : &map_k, full, half * 64, y, pol);
+        uint8_t* dst = ring + slot * kSlotBytes + half * kSlotHalf + i * rows_per_load * 128;
+        tma_load_2d(dst, map, &full_bars[slot], half * 64, y, pol);
       }
       __syncwarp();
-      if (lane == 0) clk.tick(kProfLoadIssue);
-      return true;
-    };
-    // K runs nk tiles ahead of V: a K slot frees as soon as the S = Q K^T that read it finishes, a V
-    // slot only after the softmax of that tile. Order: K0 .. K(nk-1), then V0 K(nk) V1 K(nk+1) ...
-    // (nk = 2 tiles = 16 pages of 16 tokens, so a K tile is never beyond the next table batch.)
-    bool go = true;
-    for (int j = 0; go && j < nk && j < n_tiles; ++j) go = load_tile(j, 0, j, 0);
-    for (int j = 0; go && j < n_tiles; ++j) {
-      const int first_pg = min(j * kBN / bs, last_page);
-      while ((first_pg >> 5) > cur_batch) {              // warp-uniform
-        cur = nxt;
-        ++cur_batch;
-        nxt = fetch(cur_batch + 1);
-      }
-      go = load_tile(j, 1, j % nv, j / nv);
-      if (go && j + nk < n_tiles) go = load_tile(j + nk, 0, (j + nk) % nk, (j + nk) / nk);
+      if (lane == 0 && !is_v) clk.tick(kProfLoadIssue);
     }
-    if (kProfile && lane == 0) clk.flush(p.prof, kProfLoadWaitEmpty, kProfLoadIssue);
+    if (kProfile && lane == 0 && !is_v) clk.flush(p.prof, kProfLoadWaitEmpty, kProfLoadIssue);
   } else if (warp == kMmaWarp) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
@@ -611,14 +607,14 @@ static int launch_prefill_tc(const void* q, const void* k_cache, const void* v_c
   dim3 grid((max_q_len + kBM - 1) / kBM, hq / units, num_seqs);
   if (units == 2) {
     if (prof)
-      attn_prefill_tc_kernel<2, true><<<grid, 320, kSmemRequest2, stream>>>(map_q, map_k, map_v, p);
+      attn_prefill_tc_kernel<2, true><<<grid, 352, kSmemRequest2, stream>>>(map_q, map_k, map_v, p);
     else
-      attn_prefill_tc_kernel<2, false><<<grid, 320, kSmemRequest2, stream>>>(map_q, map_k, map_v, p);
+      attn_prefill_tc_kernel<2, false><<<grid, 352, kSmemRequest2, stream>>>(map_q, map_k, map_v, p);
   } else {
     if (prof)
-      attn_prefill_tc_kernel<1, true><<<grid, 192, kSmemRequest1, stream>>>(map_q, map_k, map_v, p);
+      attn_prefill_tc_kernel<1, true><<<grid, 224, kSmemRequest1, stream>>>(map_q, map_k, map_v, p);
     else
-      attn_prefill_tc_kernel<1, false><<<grid, 192, kSmemRequest1, stream>>>(map_q, map_k, map_v, p);
+      attn_prefill_tc_kernel<1, false><<<grid, 224, kSmemRequest1, stream>>>(map_q, map_k, map_v, p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
 }

@@ -23,7 +23,7 @@ def _fused_rank(rank, world, nvls):
     from xixi_vllm_b200.parallel.symm import FusedTPComm
     dev = torch.device("cuda", rank)
     H = 1024
-    comm = FusedTPComm(get_tp_group(), dev, H, 512, torch.bfloat16)
+    comm = FusedTPComm(get_tp_group(), dev, H, 512, torch.bfloat16, logits_rows=6, logits_local_cols=4096 // world)
     errs = []
     for it, T in enumerate([1, 7, 64, 300, 512, 3, 3, 129]):
         g = torch.Generator().manual_seed(100 + it)
@@ -81,10 +81,21 @@ def _fused_rank(rank, world, nvls):
     local = full[:, rank * per:(rank + 1) * per].contiguous().to(dev)
     ids = comm.argmax(local, per, rank * per).cpu()
     want = full.float().argmax(-1)
+    # column all-gather of logit shards into every rank's full matrix (several sizes, reused buffer)
+    gather_ok = True
+    for it, rows in enumerate([5, 1, 6]):
+        g = torch.Generator().manual_seed(900 + it)
+        full = torch.randn(rows, 4096, generator=g).bfloat16()
+        padded = torch.zeros(rows, per + 8, dtype=torch.bfloat16)         # row stride wider than the shard
+        padded[:, :per] = full[:, rank * per:(rank + 1) * per]
+        got = comm.gather_logits(padded.to(dev)[:, :per])
+        torch.cuda.synchronize()
+        gather_ok = gather_ok and got is not None and torch.equal(got.cpu(), full)
+    assert comm.gather_logits(torch.zeros(7, per, dtype=torch.bfloat16, device=dev)) is None   # too many rows
     torch.cuda.synchronize()
     cuda.check_status(dev)
     dist.barrier()
-    assert fused_gemm
+    assert fused_gemm and gather_ok
     return max(errs), ids.tolist(), want.tolist(), bool(comm.mc_ptr)
 
 
@@ -158,6 +169,16 @@ def test_engine_tp2_row_sharded_reduction_matches(tmp_path, monkeypatch):
 
 
 @pytest.mark.timeout(600)
+def test_engine_tp2_sampled_tokens_same_with_fused_and_library_logits_gather(tmp_path, monkeypatch):
+    """Same seed, same logits bits: the peer-memory gather and the NCCL gather must sample the same tokens."""
+    _need(2)
+    d = _tiny_dir(tmp_path)
+    fused = _probe(d, tp=2, comm="fused", cg=True, port=29871, temperature=0.8)
+    monkeypatch.setenv("XV_TP_LOGITS_GATHER", "nccl")
+    library = _probe(d, tp=2, comm="fused", cg=True, port=29881, temperature=0.8)
+    assert fused == library
+
+
 def test_engine_tp2_sampled_generation_runs(tmp_path):
     """Non-greedy sampling under TP gathers logits and draws identical tokens on every rank."""
     _need(2)

@@ -12,6 +12,8 @@
 //                             NCCL call, no staging copy and no separate add+norm kernel.
 //   tp_argmax_kernel        - vocab-parallel greedy sampling: local argmax of this rank's logit
 //                             shard, (value, id) pushed into every peer's slot, global pick.
+//   tp_allgather_cols_kernel - full logits for sampled requests: every rank pushes its vocabulary
+//                             shard into all ranks' logits matrix (multimem.st or peer stores).
 //
 // Synchronisation: a monotonically increasing epoch per communicator, kept in device memory
 // (so a captured CUDA graph advances it on every replay). A rank announces "my partial for
@@ -253,6 +255,60 @@ tp_argmax_kernel(const TpComm c, long long slots_offset, const __nv_bfloat16* __
   tp_finish(c);
 }
 
+// All-gather along columns: every rank owns `local_cols` columns of a [rows, total_cols] matrix
+// (its LM-head logit shard) and pushes them into that position of the matrix on every rank:
+// one multimem.st per 16 bytes when the buffer has a multicast mapping (the switch replicates the
+// store), else one peer store per rank. The last CTA to finish raises this rank's flag; every CTA
+// then waits until all ranks have raised theirs, so when the kernel ends the full matrix is local.
+// The destination lives in a symmetric buffer of its own (base pointers in c.peer_buf / c.mc_buf).
+__global__ void __launch_bounds__(kTpThreads)
+tp_allgather_cols_kernel(const TpComm c, const __nv_bfloat16* __restrict__ src, long long ld, int local_cols,
+                         long long total_cols, int rows) {
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(c.epoch);
+  const int vec_per_row = local_cols >> 3;
+  const long long total = static_cast<long long>(rows) * vec_per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / vec_per_row;
+    const int v = static_cast<int>(i - row * vec_per_row);
+    const uint4 val = *reinterpret_cast<const uint4*>(src + row * ld + v * 8);
+    const long long off = (row * total_cols + static_cast<long long>(c.rank) * local_cols + v * 8) * 2;
+    if (c.mc_buf != nullptr) {
+      multimem_st_bf16x8(const_cast<char*>(static_cast<const char*>(c.mc_buf)) + off, val);
+    } else {
+      for (int r = 0; r < c.world; ++r)
+        st_relaxed_sys_v4(const_cast<char*>(static_cast<const char*>(c.peer_buf[r])) + off, val);
+    }
+  }
+  __shared__ int last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    last = atomicAdd(c.epoch + 2, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (last && threadIdx.x < c.world) {
+    c.epoch[2] = 0;
+    st_release_sys(c.peer_flags[threadIdx.x] + 1 * kMaxRanks + c.rank, epoch);
+  }
+  __shared__ int ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    const uint32_t* f = c.peer_flags[c.rank] + 1 * kMaxRanks + threadIdx.x;
+    bool seen = false;
+    const unsigned long long t0 = global_timer_ns();
+    const unsigned long long limit = static_cast<unsigned long long>(c.spin_limit) * 1000ull;
+    for (;;) {
+      if (static_cast<int32_t>(ld_acquire_sys(f) - epoch) >= 0) { seen = true; break; }
+      if (global_timer_ns() - t0 > limit) break;
+      __nanosleep(20);
+    }
+    if (!seen) { report_status(c.status, kTpKernelId, kPeerFlagTimeout); ok_flag = 0; }
+  }
+  tp_finish(c);
+}
+
 }  // namespace xv
 
 using namespace xv;
@@ -323,6 +379,27 @@ int xv_tp_argmax(const void* const* peer_bufs, void* const* peer_flags, void* ep
   if (rc) return rc;
   tp_argmax_kernel<<<rows, 1024, 0, stream>>>(c, slots_offset, static_cast<const __nv_bfloat16*>(logits), ld,
                                               local_vocab, valid_vocab, vocab_start, out, rows);
+  return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
+}
+
+// Column all-gather into the symmetric matrix whose per-rank base pointers are `peer_bufs`
+// (`mc_buf`: its multicast mapping or null). src: this rank's [rows, local_cols] shard with row
+// stride ld; the gathered matrix is [rows, total_cols] with this rank's shard at column rank * local_cols.
+int xv_tp_allgather_cols(const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf, void* epoch,
+                         int rank, int world, const void* src, long long ld, int local_cols, long long total_cols,
+                         int rows, unsigned spin_limit, int* status, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (local_cols % 8 || ld % 8 || total_cols % 8 || static_cast<long long>(local_cols) * world > total_cols ||
+      (reinterpret_cast<uintptr_t>(src) & 15))
+    return XV_ERR_SHAPE;
+  TpComm c;
+  int rc = fill_comm(&c, peer_bufs, peer_flags, mc_buf, epoch, rank, world, spin_limit, status);
+  if (rc) return rc;
+  const long long vecs = static_cast<long long>(rows) * (local_cols / 8);
+  long long want = (vecs + kTpThreads - 1) / kTpThreads;
+  const int grid = static_cast<int>(want < 1 ? 1 : (want > 148 * 4 ? 148 * 4 : want));   // every CTA waits: stay resident
+  tp_allgather_cols_kernel<<<grid, kTpThreads, 0, stream>>>(c, static_cast<const __nv_bfloat16*>(src), ld, local_cols,
+                                                            total_cols, rows);
   return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
 }
 

@@ -145,6 +145,10 @@ int xv_tp_argmax(const void* const* peer_bufs, void* const* peer_flags, void* ep
                  long long slots_offset, const void* logits, long long ld, int local_vocab, int valid_vocab,
                  int vocab_start, long long* out, int rows, unsigned spin_limit, int* status, cudaStream_t stream);
 
+int xv_tp_allgather_cols(const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf, void* epoch,
+                         int rank, int world, const void* src, long long ld, int local_cols, long long total_cols,
+                         int rows, unsigned spin_limit, int* status, cudaStream_t stream);
+
 // RowParallel GEMM + all-reduce + residual add + RMSNorm in ONE kernel (see gemm_sm100.cu).
 int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long ldx, long long ldw, void* workspace,
                     long long workspace_bytes, int num_sms, const void* const* peer_bufs, void* const* peer_flags,

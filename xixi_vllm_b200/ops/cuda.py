@@ -84,6 +84,8 @@ def lib():
                                     _i32, ctypes.c_uint, _vp, _vp]
     L.xv_tp_reduce_norm_sharded.argtypes = [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _i64, _i32, _vp, _vp, _i32, _i32,
                                             _f32, ctypes.c_uint, _vp, _vp]
+    L.xv_tp_allgather_cols.argtypes = [_vp, _vp, _vp, _vp, _i32, _i32, _vp, _i64, _i32, _i64, _i32, ctypes.c_uint,
+                                       _vp, _vp]
     L.xv_tp_argmax.argtypes = [_vp, _vp, _vp, _i32, _i32, _i64, _vp, _i64, _i32, _i32, _i32, _vp, _i32,
                                ctypes.c_uint, _vp, _vp]
     L.xv_gemm_bf16_tp.argtypes = [_vp, _vp, _i32, _i32, _i32, _i64, _i64, _vp, _i64, _i32, _vp, _vp, _vp, _vp, _i32,
@@ -450,6 +452,18 @@ def tp_argmax(peer_bufs, peer_flags, epoch, rank: int, world: int, slots_offset:
     _check(lib().xv_tp_argmax(peer_bufs, peer_flags, epoch.data_ptr(), rank, world, slots_offset, logits.data_ptr(),
                               logits.stride(0), local_vocab, valid_vocab, vocab_start, out.data_ptr(),
                               logits.shape[0], spin_limit, status.data_ptr(), _stream()), "tp_argmax")
+
+
+def tp_allgather_cols(peer_bufs, peer_flags, mc_ptr: int, epoch, rank: int, world: int, src, total_cols: int,
+                      spin_limit: int, status) -> None:
+    """Pushes this rank's ``[rows, local_cols]`` shard into column block ``rank`` of the symmetric
+    ``[rows, total_cols]`` matrix on every rank (``xv_tp_allgather_cols``)."""
+    _bf16(src)
+    if src.stride(1) != 1:
+        raise ValueError("tp_allgather_cols needs unit column stride")
+    _check(lib().xv_tp_allgather_cols(peer_bufs, peer_flags, mc_ptr or None, epoch.data_ptr(), rank, world,
+                                      src.data_ptr(), src.stride(0), src.shape[1], total_cols, src.shape[0],
+                                      spin_limit, status.data_ptr(), _stream()), "tp_allgather_cols")
 
 
 def gemm_tp_fused(x, w, peer_bufs, peer_flags, mc_ptr: int, epoch, rank: int, world: int, buf_offset: int,

@@ -70,7 +70,8 @@ class SymmetricBuffer:
 
 
 class FusedTPComm(TPComm):
-    def __init__(self, group: Group, device, hidden_size: int, max_tokens: int, dtype) -> None:
+    def __init__(self, group: Group, device, hidden_size: int, max_tokens: int, dtype,
+                 logits_rows: int = 0, logits_local_cols: int = 0) -> None:
         if dtype != torch.bfloat16:
             raise TypeError("the fused tensor-parallel path runs bfloat16")
         self.group = group
@@ -79,7 +80,11 @@ class FusedTPComm(TPComm):
         self.max_tokens = max_tokens
         self.buf_bytes = -(-max_tokens * hidden_size * 2 // 4096) * 4096
         self.slot_bytes = -(-group.size * max_tokens * 8 // 4096) * 4096
-        total = 4 * self.buf_bytes + self.slot_bytes + FLAG_BYTES
+        # optional [logits_rows, world * logits_local_cols] matrix for gathering sampled rows' logits
+        self._logit_rows, self._logit_cols = logits_rows, logits_local_cols * group.size
+        logit_bytes = -(-logits_rows * self._logit_cols * 2 // 4096) * 4096
+        self.logits_off = 4 * self.buf_bytes + self.slot_bytes + FLAG_BYTES
+        total = self.logits_off + logit_bytes
         self.symm = SymmetricBuffer(total, group, self.device)
         self.rank, self.world = self.symm.rank, self.symm.world
         self.h_off = 3 * self.buf_bytes              # activation buffer the row-sharded reductions broadcast into
@@ -104,6 +109,13 @@ class FusedTPComm(TPComm):
         # its own kernel: at prefill sizes the faster GEMM outweighs the saved launch.
         self.fuse_gemm_max_tokens = int(os.environ.get("XV_TP_FUSE_GEMM_MAX_T", "256"))
         self._idx = 0
+        self._logits_view = None
+        if logit_bytes:
+            self._logit_bufs = self.symm.ptr_array(self.logits_off)
+            self._logit_mc = self.mc_ptr + self.logits_off if self.mc_ptr else 0
+            n = logits_rows * self._logit_cols * 2
+            self._logits_view = self.symm.local[self.logits_off:self.logits_off + n].view(torch.bfloat16).view(
+                logits_rows, self._logit_cols)
         self._base = self.symm.local.data_ptr()
         self._views = [self.symm.local[i * self.buf_bytes:(i + 1) * self.buf_bytes].view(torch.bfloat16)
                        for i in range(3)]
@@ -181,6 +193,19 @@ class FusedTPComm(TPComm):
                        local_logits.shape[1], valid_vocab, vocab_start, out, SPIN_LIMIT, self.status)
         return out
 
+    # --- full logits for sampled requests ------------------------------------------------------
+    def gather_logits(self, local_logits: torch.Tensor) -> torch.Tensor | None:
+        """All ranks' vocabulary shards side by side, or None when no matching matrix was reserved
+        (the caller then uses the library collective). The result aliases the symmetric buffer and
+        stays valid until the next call."""
+        rows, cols = local_logits.shape
+        if self._logits_view is None or rows > self._logit_rows or cols * self.world != self._logit_cols:
+            return None
+        cuda.tp_allgather_cols(self._logit_bufs, self._flags, self._logit_mc, self.epoch, self.rank, self.world,
+                               local_logits, self._logit_cols, SPIN_LIMIT, self.status)
+        return self._logits_view[:rows]
+
     def destroy(self) -> None:
         self._views = []
+        self._logits_view = None
         self.symm = None

@@ -65,15 +65,18 @@ class LibraryTPComm(TPComm):
         return ops.add_rmsnorm(x, residual, w, eps), residual
 
 
-def make_tp_comm(group: Group, mode: str, device, hidden_size: int, max_tokens: int, dtype) -> TPComm:
+def make_tp_comm(group: Group, mode: str, device, hidden_size: int, max_tokens: int, dtype,
+                 logits_rows: int = 0, logits_local_cols: int = 0) -> TPComm:
     """``mode``: "nccl" forces the library path; "fused" requires the peer-memory kernels;
-    "auto" uses them when running on GPUs with more than one rank."""
+    "auto" uses them when running on GPUs with more than one rank. ``logits_rows`` x
+    ``logits_local_cols`` sizes the symmetric matrix in which the fused path gathers full logits
+    for sampled requests (0 = that gather stays on the library collective)."""
     if group.size == 1 or mode == "nccl" or torch.device(device).type != "cuda":
         return LibraryTPComm(group)
     try:
         from .symm import FusedTPComm
 
-        return FusedTPComm(group, device, hidden_size, max_tokens, dtype)
+        return FusedTPComm(group, device, hidden_size, max_tokens, dtype, logits_rows, logits_local_cols)
     except Exception:
         if mode == "fused":
             raise

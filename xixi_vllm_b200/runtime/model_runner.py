@@ -85,9 +85,12 @@ class ModelRunner:
             logits = out
             head = self.model.lm_head
             if head.tp.size > 1:
-                from ..parallel import collectives as coll
+                gathered = self._gather_logits(logits)
+                if gathered is None:
+                    from ..parallel import collectives as coll
 
-                logits = coll.all_gather(logits, head.tp, dim=-1)
+                    gathered = coll.all_gather(logits, head.tp, dim=-1)
+                logits = gathered
             logits = logits[..., : head.num_embeddings]
             return self.sampler(logits, batch.temperature, batch.top_k, batch.top_p, batch.min_p, rng=batch.rng)
         out = self.model.forward(batch.input_ids, batch, self.kv, intermediate)
@@ -98,6 +101,10 @@ class ModelRunner:
             return self.model.greedy_tokens(hidden)
         logits = self.model.compute_logits(hidden)
         return self.sampler(logits, batch.temperature, batch.top_k, batch.top_p, batch.min_p, rng=batch.rng)
+
+    def _gather_logits(self, local_logits):
+        comm = self.model.comm
+        return comm.gather_logits(local_logits) if hasattr(comm, "gather_logits") else None
 
     def _recv(self, n_tokens: int) -> IntermediateTensors:
         h, r = self._pp_buf[0][:n_tokens], self._pp_buf[1][:n_tokens]

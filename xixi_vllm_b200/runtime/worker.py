@@ -82,8 +82,13 @@ class Worker:
                 if report["skipped"] and self.rank == 0 and self.pp_size == 1:
                     print(f"[loader] {len(report['skipped'])} tensors not used, e.g. {report['skipped'][:3]}")
         max_tokens = max(cfg.max_num_batched_tokens, cfg.max_num_seqs)
+        # last pipeline stage: room for gathering the full logits of sampled rows over peer memory
+        head = getattr(self.model, "lm_head", None)
+        fused_logits = hasattr(head, "weight") and os.environ.get("XV_TP_LOGITS_GATHER", "fused") != "nccl"
         self.model.comm = make_tp_comm(groups.get_tp_group(), cfg.tp_comm, self.device,
-                                       cfg.hf_config.hidden_size, max_tokens, self.dtype)
+                                       cfg.hf_config.hidden_size, max_tokens, self.dtype,
+                                       logits_rows=cfg.max_num_seqs if fused_logits else 0,
+                                       logits_local_cols=head.weight.shape[0] if fused_logits else 0)
         if self.on_cuda:
             torch.cuda.synchronize(self.device)
             torch.cuda.empty_cache()

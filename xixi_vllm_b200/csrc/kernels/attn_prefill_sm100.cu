@@ -1,23 +1,26 @@
 // Paged causal prefill attention for sm_100a on the 5th-generation tensor cores.
 //
-// One CTA owns 128 query rows of one head of one sequence and walks the sequence's KV pages
-// in tiles of 128 tokens (MMAs narrower than N = 128 leave the tensor pipe waiting on operand reads):
-//   warps 4, 5  - TMA producers (K tiles, V tiles): the Q tile once, then per tile the pages named by the
-//                 block table, each page an own cp.async.bulk.tensor box (128-byte swizzle)
-//                 into two rings of 16 KiB shared-memory slots (K runs two tiles ahead of V).
-//                 Block-table entries are read 32 pages at a time, one batch ahead of use.
-//   warp 6      - allocates TMEM and issues tcgen05.mma from one thread: S = Q K^T (M=128, N=128)
-//                 into TMEM as soon as the softmax warps have copied the previous tile's S out, and
-//                 O += P V (M=128, N=128; V is read MN-major exactly as the cache stores it).
-//   warps 0..3  - softmax: thread r owns query row r. tcgen05.ld of the S row, scale + causal
-//                 mask, running max and sum, P rounded to bf16 into a swizzled shared-memory tile
-//                 that the second MMA reads as its A operand. The output accumulator lives in
-//                 TMEM for the whole sequence; it is rescaled in place (tcgen05.ld/st) only when
-//                 a row's maximum grows by more than 2^8, otherwise the stale maximum is kept,
-//                 which the final division by the row sum makes exact.
-// A CTA normally carries two query heads of one KV group ("units": same rows, same K/V tiles, one
-// softmax warpgroup and 256 TMEM columns each), so one head's softmax runs under the other's MMAs
-// and every K/V tile is fetched once for both.
+// A CTA owns 128 query rows of TWO query heads of one KV group of one sequence ("units": same rows,
+// same K/V tiles; 256 TMEM columns and one softmax warpgroup each) and walks the sequence's KV pages
+// in tiles of 128 tokens (MMAs narrower than N = 128 leave the tensor pipe waiting on operand reads).
+// With an odd group size a CTA carries one head. Warps of the two-head form:
+//   warps 0-3 / 4-7 - softmax of unit 0 / 1: thread r owns query row r. tcgen05.ld of the S row
+//                 (128 fp32), causal mask on diagonal tiles, three-input max, p = 2^(s*scale - m) with a
+//                 packed FMA and one MUFU per score, row sum; P rounded to bf16 and written back over the
+//                 first 64 S columns (tcgen05.st), where the second MMA reads it as its A operand from
+//                 tensor memory (no shared-memory round trip). The output accumulator lives in TMEM
+//                 for the whole sequence; it is rescaled in place (tcgen05.ld/st) only when a row's
+//                 maximum grows by more than 2^8, otherwise the stale maximum is kept, which the final
+//                 division by the row sum makes exact.
+//   warps 8, 9  - TMA producers, one for K tiles and one for V tiles (plus the Q tiles once): per tile
+//                 the pages named by the block table, each page and 64-column half its own
+//                 cp.async.bulk.tensor box (128-byte swizzle), into rings of 32 KiB shared-memory slots
+//                 (K: 3, V: 2). Block-table entries are read 32 pages at a time, one batch ahead of use.
+//   warp 10     - allocates TMEM and issues tcgen05.mma from one thread: per unit and tile
+//                 O += P V (M=128, N=128, A from TMEM, V read MN-major exactly as the cache stores it)
+//                 as soon as that unit's P is ready, then at once the unit's next S = Q K^T (M=128,
+//                 N=128) into the same columns. Units are served in the order their P tiles become
+//                 ready, so one head's softmax runs under the other head's MMAs.
 //
 // Every barrier wait is bounded; a wait that runs out records a status code, the CTA stops
 // issuing work, frees its TMEM and returns.
@@ -47,14 +50,14 @@ constexpr int kQBytes = kBM * kD * 2;          // 32 KiB, two 64-column halves o
 constexpr int kQHalf = kBM * 128;
 constexpr int kSlotBytes = kBN * kD * 2;       // 32 KiB, two 64-column halves of 16 KiB
 constexpr int kSlotHalf = kBN * 128;
-constexpr int kPBytes = kBM * kBN * 2;         // 32 KiB, two 64-column halves of 16 KiB
-constexpr int kPHalf = kBM * 128;
-constexpr int kMaxRing = 2;                    // slots per K or V ring
+constexpr int kMaxRing = 3;                    // slots per K or V ring
 constexpr int kBarBytes = 256;
-// Q and P tiles of every head plus three 32 KiB ring slots (K: 2, V: 1).
-constexpr int kSmemRequest1 = kQBytes + kPBytes + 3 * kSlotBytes + kBarBytes;
-constexpr int kSmemRequest2 = 2 * (kQBytes + kPBytes) + 3 * kSlotBytes + kBarBytes;
-constexpr uint32_t kTmemO = 128;               // per unit: S in columns [0,128), the output accumulator in [128,256)
+// The Q tile of every head plus five 32 KiB ring slots (K: 3, V: 2).
+constexpr int kSmemRequest1 = kQBytes + 5 * kSlotBytes + kBarBytes;
+constexpr int kSmemRequest2 = 2 * kQBytes + 5 * kSlotBytes + kBarBytes;
+// TMEM columns of a unit: S (fp32) in [0,128); P (bf16 pairs) overwrites [0,64) once the S row is in
+// registers; the output accumulator in [128,256).
+constexpr uint32_t kTmemO = 128;
 constexpr int kKernelId = 7;
 constexpr float kRescaleThreshold = 8.f;       // log2 units
 
@@ -105,7 +108,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, const Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   constexpr int kProducerWarp = 4 * kUnits, kMmaWarp = 4 * kUnits + 2;    // producers: K warp, V warp
-  constexpr int kFixedBytes = kUnits * (kQBytes + kPBytes);
+  constexpr int kFixedBytes = kUnits * kQBytes;
   constexpr uint32_t kTmemCols = 256 * kUnits;   // per unit: S [0,128) O [128,256)
   const int b = p.seq_begin + blockIdx.z, head0 = blockIdx.y * kUnits;
   const int q_begin = p.cu_q[b];
@@ -130,11 +133,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
   int slots = (static_cast<int>(dyn) - static_cast<int>(pad) - kBarBytes - kFixedBytes) / kSlotBytes;
   slots = slots > 2 * kMaxRing ? 2 * kMaxRing : slots;
-  const int nk = slots >= 3 ? 2 : slots - 1, nv = slots - nk;
+  const int nv = slots >= 4 ? 2 : 1, nk = slots - nv;
   uint8_t* smem = smem_raw + pad;
   uint8_t* q_s = smem;                                   // [kUnits][2 halves][128 rows][128 B]
-  uint8_t* p_s = q_s + kUnits * kQBytes;                 // [kUnits][128 rows][128 B]
-  uint8_t* k_ring = p_s + kUnits * kPBytes;
+  uint8_t* k_ring = q_s + kUnits * kQBytes;
   uint8_t* v_ring = k_ring + nk * kSlotBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(k_ring + slots * kSlotBytes);
   uint64_t* q_full = bars;
@@ -143,8 +145,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint64_t* k_empty = v_full + kMaxRing;         // [kMaxRing]
   uint64_t* v_empty = k_empty + kMaxRing;        // [kMaxRing]
   uint64_t* s_full = v_empty + kMaxRing;         // [kUnits] S written by the MMA
-  uint64_t* s_free = s_full + kUnits;            // [kUnits] S copied to registers by the softmax warps
-  uint64_t* p_ready = s_free + kUnits;           // [kUnits]
+  uint64_t* p_ready = s_full + kUnits;           // [kUnits] P written (and O rescaled) by the softmax warps
   uint64_t* o_done = p_ready + kUnits;           // [kUnits]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + kUnits);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -164,7 +165,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     for (int u = 0; u < kUnits; ++u) {
       mbar_init(&s_full[u], 1);
-      mbar_init(&s_free[u], 128);
       mbar_init(&p_ready[u], 128);
       mbar_init(&o_done[u], 1);
     }
@@ -261,59 +261,86 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc_bf16(kBM, kBN);
       const uint32_t idesc_o = umma_idesc_bf16_b_mn(kBM, kD);
-      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      const uint32_t q_addr = smem_u32(q_s);
       const uint32_t k_ring_addr = smem_u32(k_ring), v_ring_addr = smem_u32(v_ring);
       bool ok = mbar_wait(q_full, 0);
       int reason = kWaitFullTimeout;
-      // S(j) of every unit from one K tile. A unit's S columns are free once its softmax warps
-      // have copied tile j-1 into registers.
-      auto issue_s = [&](int j) -> bool {
-        const int slot = j % nk, use = j / nk;
-        if (!mbar_wait(&k_full[slot], use & 1)) return false;
-        clk.tick(kProfMmaWaitK);
-        const uint32_t k_addr = k_ring_addr + slot * kSlotBytes;
+      // S_u(j) = Q_u K(j)^T into the unit's S columns.
+      auto issue_s = [&](int u, int j) {
+        const uint32_t k_addr = k_ring_addr + (j % nk) * kSlotBytes;
 #pragma unroll
-        for (int u = 0; u < kUnits; ++u) {
-          if (j > 0 && !mbar_wait(&s_free[u], (j - 1) & 1)) return false;
-          clk.tick(kProfMmaWaitP);
-          tc_fence_after_sync();
-#pragma unroll
-          for (int ks = 0; ks < kD / 16; ++ks) {
-            const uint64_t a = umma_desc_sw128(q_addr + u * kQBytes + (ks >> 2) * kQHalf + (ks & 3) * 32);
-            const uint64_t bd = umma_desc_sw128(k_addr + (ks >> 2) * kSlotHalf + (ks & 3) * 32);
-            umma_bf16(tmem_base + u * 256, a, bd, idesc_s, ks > 0);
-          }
-          umma_commit(&s_full[u]);
-          clk.tick(kProfMmaIssue);
+        for (int ks = 0; ks < kD / 16; ++ks) {
+          const uint64_t a = umma_desc_sw128(q_addr + u * kQBytes + (ks >> 2) * kQHalf + (ks & 3) * 32);
+          const uint64_t bd = umma_desc_sw128(k_addr + (ks >> 2) * kSlotHalf + (ks & 3) * 32);
+          umma_bf16(tmem_base + u * 256, a, bd, idesc_s, ks > 0);
         }
-        umma_commit(&k_empty[slot]);
-        return true;
+        umma_commit(&s_full[u]);
       };
-      if (ok) ok = issue_s(0);
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }
-        const int slot = j % nv, use = j / nv;
+      auto wait_k = [&](int j) -> bool {
+        const bool got = mbar_wait(&k_full[j % nk], (j / nk) & 1);
+        clk.tick(kProfMmaWaitK);
+        tc_fence_after_sync();
+        return got;
+      };
+      if (ok) ok = wait_k(0);
+      if (ok) {
+#pragma unroll
+        for (int u = 0; u < kUnits; ++u) issue_s(u, 0);
+        umma_commit(&k_empty[0]);
+        clk.tick(kProfMmaIssue);
+      }
+      // Per unit and tile: O_u += P_u(j) V(j) as soon as the softmax warps have written P (over the S
+      // columns), then at once S_u(j+1) into the same columns; the tensor pipe runs them in issue order.
+      // The units are served in the order in which their P tiles become ready, so they settle into
+      // opposite phases: while one unit's pair of MMAs runs, the other unit is in its softmax.
+      int done[kUnits];
+#pragma unroll
+      for (int u = 0; u < kUnits; ++u) done[u] = 0;
+      unsigned long long idle_since = global_timer_ns();
+      while (ok) {
+        bool all_done = true, progressed = false;
 #pragma unroll
         for (int u = 0; u < kUnits; ++u) {
-          if (!mbar_wait(&p_ready[u], j & 1)) { ok = false; reason = kWaitAccumTimeout; break; }
+          const int j = done[u];
+          if (j >= n_tiles) continue;
+          all_done = false;
+          if (!mbar_try_wait(&p_ready[u], j & 1)) continue;
           clk.tick(kProfMmaWaitP);
-          if (u == 0) {
-            if (!mbar_wait(&v_full[slot], use & 1)) { ok = false; break; }
-            clk.tick(kProfMmaWaitV);
-          }
+          const int vslot = j % nv;
+          if (!mbar_wait(&v_full[vslot], (j / nv) & 1)) { ok = false; break; }
+          clk.tick(kProfMmaWaitV);
           tc_fence_after_sync();
-          const uint32_t v_addr = v_ring_addr + slot * kSlotBytes;
+          const uint32_t v_addr = v_ring_addr + vslot * kSlotBytes;
 #pragma unroll
           for (int ks = 0; ks < kBN / 16; ++ks) {
-            const uint64_t a = umma_desc_sw128(p_addr + u * kPBytes + (ks >> 2) * kPHalf + (ks & 3) * 32);
             const uint64_t bd = umma_desc_sw128_mn(v_addr + ks * 2048, kSlotHalf, 1024);
-            umma_bf16(tmem_base + u * 256 + kTmemO, a, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+            umma_bf16_a_tmem(tmem_base + u * 256 + kTmemO, tmem_base + u * 256 + ks * 8, bd, idesc_o,
+                             (j > 0 || ks > 0) ? 1u : 0u);
           }
           umma_commit(&o_done[u]);
+          // the last unit to finish tile j frees its V slot (a commit covers every MMA issued so far)
+          bool last = true;
+#pragma unroll
+          for (int o = 0; o < kUnits; ++o)
+            if (o != u && done[o] <= j) last = false;
+          if (last) umma_commit(&v_empty[vslot]);
           clk.tick(kProfMmaIssue);
+          if (j + 1 < n_tiles) {
+            if (!wait_k(j + 1)) { ok = false; break; }
+            issue_s(u, j + 1);
+            if (last) umma_commit(&k_empty[(j + 1) % nk]);
+            clk.tick(kProfMmaIssue);
+          }
+          done[u] = j + 1;
+          progressed = true;
         }
-        if (!ok) break;
-        umma_commit(&v_empty[slot]);
+        if (all_done) break;
+        if (progressed) {
+          idle_since = global_timer_ns();
+        } else if (global_timer_ns() - idle_since > kDefaultWaitNs || *abort_flag) {
+          ok = false;
+          reason = kWaitAccumTimeout;
+        }
       }
       if (kProfile) clk.flush(p.prof, kProfMmaWaitK, kProfMmaIssue);
       if (!ok || *abort_flag) {
@@ -328,9 +355,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int head = head0 + u;
     const int pos_row = pos0 + row0 + (r < rows_valid ? r : rows_valid - 1);
     const uint32_t lane_taddr = tmem_base + u * 256 + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    const uint32_t p_row = smem_u32(p_s) + u * kPBytes + r * 128;
     uint64_t* my_s_full = &s_full[u];
-    uint64_t* my_s_free = &s_free[u];
     uint64_t* my_p_ready = &p_ready[u];
     uint64_t* my_o_done = &o_done[u];
     float m = -INFINITY, l = 0.f;
@@ -344,8 +369,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
       for (int c = 0; c < 8; ++c) tmem_ld16(lane_taddr + c * 16, sr[c]);
       tmem_ld_wait();
-      tc_fence_before_sync();
-      mbar_arrive(my_s_free);                      // the MMA warp may overwrite S with the next tile
       clk.tick(kProfSoftLoad);
       const int k0 = j * kBN;
       if (k0 + kBN - 1 > pos_row) {              // only tiles that cross the diagonal mask anything
@@ -369,7 +392,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const float mt = fmax3(fmax3(mx[0], mx[1], mx[2]), fmax3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) *
                        p.scale_log2;
       clk.tick(kProfSoftMax);
-      bool o_ready = (j == 0);
       if (j == 0) {
         m = mt;                                  // column 0 is never masked, so this is finite
       } else {
@@ -378,7 +400,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           ok = __all_sync(0xffffffffu, mbar_wait(my_o_done, (j - 1) & 1));
           if (!ok) break;
           tc_fence_after_sync();
-          o_ready = true;
           const float m_new = need ? mt : m;
           const float alpha = exp2f(m - m_new);
           l *= alpha;
@@ -402,40 +423,31 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
       }
       clk.tick(kProfSoftRescale);
-      if (!o_ready) {                            // the previous P V must have finished reading the P tile
-        ok = __all_sync(0xffffffffu, mbar_wait(my_o_done, (j - 1) & 1));
-        if (!ok) break;
-      }
-      clk.tick(kProfSoftWaitO);
-      // p = 2^(s * scale - m): one packed FMA per two scores, one MUFU each, four independent sums;
-      // every 16 columns go to the swizzled P tile as they are produced.
+      // p = 2^(s * scale - m): one packed FMA per two scores, one MUFU each, four independent sums. P goes
+      // back to tensor memory as bf16 pairs over the first 64 columns of S (this thread's own lane), where
+      // the second MMA reads it as its A operand.
       const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), negm2 = pack_f32x2(-m, -m);
       float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint32_t packed[8];
+      for (int c = 0; c < 8; c += 2) {
+        uint32_t packed[16];
 #pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          float x0, x1;
-          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, negm2),
-                       x0, x1);
-          const float p0 = exp2f(x0), p1 = exp2f(x1);
-          sums[(i >> 1) & 3] += p0 + p1;
-          packed[i >> 1] = pack_bf16(p0, p1);
-        }
-        // columns 16c .. 16c+15 = 16-byte chunks 2c, 2c+1 of the row; chunks 0-7 live in the first half tile
-        const uint32_t half_base = p_row + (c >> 2) * kPHalf;
-        const int cc = (2 * c) & 7;
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(half_base + ((cc ^ (r & 7)) << 4)),
-                     "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3])
-                     : "memory");
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(half_base + (((cc + 1) ^ (r & 7)) << 4)),
-                     "r"(packed[4]), "r"(packed[5]), "r"(packed[6]), "r"(packed[7])
-                     : "memory");
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            float x0, x1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[c + h][i]), __uint_as_float(sr[c + h][i + 1])),
+                                   scale2, negm2),
+                         x0, x1);
+            const float p0 = exp2f(x0), p1 = exp2f(x1);
+            sums[(i >> 1) & 3] += p0 + p1;
+            packed[h * 8 + (i >> 1)] = pack_bf16(p0, p1);
+          }
+        tmem_st16(lane_taddr + (c >> 1) * 16, packed);   // scores 16c .. 16c+31 -> P columns 8c .. 8c+15
       }
       l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
       clk.tick(kProfSoftExp);
-      fence_proxy_async_smem();
+      tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(my_p_ready);
       clk.tick(kProfSoftStore);

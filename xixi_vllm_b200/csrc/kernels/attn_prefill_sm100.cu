@@ -16,11 +16,12 @@
 //                 the pages named by the block table, each page and 64-column half its own
 //                 cp.async.bulk.tensor box (128-byte swizzle), into rings of 32 KiB shared-memory slots
 //                 (K: 3, V: 2). Block-table entries are read 32 pages at a time, one batch ahead of use.
-//   warp 10     - allocates TMEM and issues tcgen05.mma from one thread: per unit and tile
+//   warps 10, 11 - one MMA issuer thread per unit (warp 10 also owns the TMEM allocation): per tile
 //                 O += P V (M=128, N=128, A from TMEM, V read MN-major exactly as the cache stores it)
 //                 as soon as that unit's P is ready, then at once the unit's next S = Q K^T (M=128,
-//                 N=128) into the same columns. Units are served in the order their P tiles become
-//                 ready, so one head's softmax runs under the other head's MMAs.
+//                 N=128) into the same columns. The two issuers run independently (one thread issuing
+//                 for both heads spent the whole tile period issuing and waiting), so one head's softmax
+//                 runs under the other head's MMAs.
 //
 // Every barrier wait is bounded; a wait that runs out records a status code, the CTA stops
 // issuing work, frees its TMEM and returns.
@@ -103,11 +104,11 @@ struct PhaseClock<false> {
 // kUnits = 2: the CTA handles two query heads of one KV group (same rows, same K/V tiles), one
 // softmax warpgroup each. kUnits = 1: one head per CTA (odd group sizes; nothing overlaps its softmax).
 template <int kUnits, bool kProfile>
-__global__ void __launch_bounds__(kUnits * 128 + 96, 1)
+__global__ void __launch_bounds__(kUnits * 160 + 64, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  constexpr int kProducerWarp = 4 * kUnits, kMmaWarp = 4 * kUnits + 2;    // producers: K warp, V warp
+  constexpr int kProducerWarp = 4 * kUnits, kMmaWarp = 4 * kUnits + 2;    // producers: K warp, V warp; then one MMA warp per unit
   constexpr int kFixedBytes = kUnits * kQBytes;
   constexpr uint32_t kTmemCols = 256 * kUnits;   // per unit: S [0,128) O [128,256)
   const int b = p.seq_begin + blockIdx.z, head0 = blockIdx.y * kUnits;
@@ -147,7 +148,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint64_t* s_full = v_empty + kMaxRing;         // [kUnits] S written by the MMA
   uint64_t* p_ready = s_full + kUnits;           // [kUnits] P written (and O rescaled) by the softmax warps
   uint64_t* o_done = p_ready + kUnits;           // [kUnits]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + kUnits);
+  uint64_t* xu_done = o_done + kUnits;           // [kUnits] a unit's exp phase of the tile is over
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xu_done + kUnits);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (nk < 2 || nv < 1) {                        // cannot happen with the launch below; never index past the rings
@@ -159,14 +161,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     mbar_init(q_full, 1);
     for (int s = 0; s < kMaxRing; ++s) {
       mbar_init(&k_full[s], 1);
-      mbar_init(&k_empty[s], 1);
+      mbar_init(&k_empty[s], kUnits);       // one commit per unit's MMA issuer
       mbar_init(&v_full[s], 1);
-      mbar_init(&v_empty[s], 1);
+      mbar_init(&v_empty[s], kUnits);
     }
     for (int u = 0; u < kUnits; ++u) {
       mbar_init(&s_full[u], 1);
       mbar_init(&p_ready[u], 128);
       mbar_init(&o_done[u], 1);
+      mbar_init(&xu_done[u], 128);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -256,93 +259,58 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (lane == 0 && !is_v) clk.tick(kProfLoadIssue);
     }
     if (kProfile && lane == 0 && !is_v) clk.flush(p.prof, kProfLoadWaitEmpty, kProfLoadIssue);
-  } else if (warp == kMmaWarp) {
-    // ---------------- MMA issuer ----------------
+  } else if (warp >= kMmaWarp && warp < kMmaWarp + kUnits) {
+    // ---------------- MMA issuers: one thread per unit ----------------
+    // Per tile: O_u += P_u(j) V(j) as soon as the unit's softmax warps have written P (over the S
+    // columns), then at once S_u(j+1) = Q_u K(j+1)^T into the same columns; the tensor pipe runs a
+    // thread's MMAs in issue order. The units run independently, so one head's softmax overlaps the
+    // other head's MMAs; a K or V slot is free when both issuers have committed it.
+    const int u = warp - kMmaWarp;
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc_bf16(kBM, kBN);
       const uint32_t idesc_o = umma_idesc_bf16_b_mn(kBM, kD);
-      const uint32_t q_addr = smem_u32(q_s);
+      const uint32_t q_addr = smem_u32(q_s) + u * kQBytes;
       const uint32_t k_ring_addr = smem_u32(k_ring), v_ring_addr = smem_u32(v_ring);
+      const uint32_t s_tmem = tmem_base + u * 256, o_tmem = s_tmem + kTmemO;
       bool ok = mbar_wait(q_full, 0);
       int reason = kWaitFullTimeout;
-      // S_u(j) = Q_u K(j)^T into the unit's S columns.
-      auto issue_s = [&](int u, int j) {
-        const uint32_t k_addr = k_ring_addr + (j % nk) * kSlotBytes;
+      auto issue_s = [&](int j) -> bool {
+        const int slot = j % nk;
+        if (!mbar_wait(&k_full[slot], (j / nk) & 1)) return false;
+        if (u == 0) clk.tick(kProfMmaWaitK);
+        tc_fence_after_sync();
+        const uint32_t k_addr = k_ring_addr + slot * kSlotBytes;
 #pragma unroll
         for (int ks = 0; ks < kD / 16; ++ks) {
-          const uint64_t a = umma_desc_sw128(q_addr + u * kQBytes + (ks >> 2) * kQHalf + (ks & 3) * 32);
+          const uint64_t a = umma_desc_sw128(q_addr + (ks >> 2) * kQHalf + (ks & 3) * 32);
           const uint64_t bd = umma_desc_sw128(k_addr + (ks >> 2) * kSlotHalf + (ks & 3) * 32);
-          umma_bf16(tmem_base + u * 256, a, bd, idesc_s, ks > 0);
+          umma_bf16(s_tmem, a, bd, idesc_s, ks > 0);
         }
         umma_commit(&s_full[u]);
+        umma_commit(&k_empty[slot]);
+        if (u == 0) clk.tick(kProfMmaIssue);
+        return true;
       };
-      auto wait_k = [&](int j) -> bool {
-        const bool got = mbar_wait(&k_full[j % nk], (j / nk) & 1);
-        clk.tick(kProfMmaWaitK);
+      if (ok) ok = issue_s(0);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        if (!mbar_wait(&p_ready[u], j & 1)) { ok = false; reason = kWaitAccumTimeout; break; }
+        if (u == 0) clk.tick(kProfMmaWaitP);
+        const int vslot = j % nv;
+        if (!mbar_wait(&v_full[vslot], (j / nv) & 1)) { ok = false; break; }
+        if (u == 0) clk.tick(kProfMmaWaitV);
         tc_fence_after_sync();
-        return got;
-      };
-      if (ok) ok = wait_k(0);
-      if (ok) {
+        const uint32_t v_addr = v_ring_addr + vslot * kSlotBytes;
 #pragma unroll
-        for (int u = 0; u < kUnits; ++u) issue_s(u, 0);
-        umma_commit(&k_empty[0]);
-        clk.tick(kProfMmaIssue);
-      }
-      // Per unit and tile: O_u += P_u(j) V(j) as soon as the softmax warps have written P (over the S
-      // columns), then at once S_u(j+1) into the same columns; the tensor pipe runs them in issue order.
-      // The units are served in the order in which their P tiles become ready, so they settle into
-      // opposite phases: while one unit's pair of MMAs runs, the other unit is in its softmax.
-      int done[kUnits];
-#pragma unroll
-      for (int u = 0; u < kUnits; ++u) done[u] = 0;
-      unsigned long long idle_since = global_timer_ns();
-      while (ok) {
-        bool all_done = true, progressed = false;
-#pragma unroll
-        for (int u = 0; u < kUnits; ++u) {
-          const int j = done[u];
-          if (j >= n_tiles) continue;
-          all_done = false;
-          if (!mbar_try_wait(&p_ready[u], j & 1)) continue;
-          clk.tick(kProfMmaWaitP);
-          const int vslot = j % nv;
-          if (!mbar_wait(&v_full[vslot], (j / nv) & 1)) { ok = false; break; }
-          clk.tick(kProfMmaWaitV);
-          tc_fence_after_sync();
-          const uint32_t v_addr = v_ring_addr + vslot * kSlotBytes;
-#pragma unroll
-          for (int ks = 0; ks < kBN / 16; ++ks) {
-            const uint64_t bd = umma_desc_sw128_mn(v_addr + ks * 2048, kSlotHalf, 1024);
-            umma_bf16_a_tmem(tmem_base + u * 256 + kTmemO, tmem_base + u * 256 + ks * 8, bd, idesc_o,
-                             (j > 0 || ks > 0) ? 1u : 0u);
-          }
-          umma_commit(&o_done[u]);
-          // the last unit to finish tile j frees its V slot (a commit covers every MMA issued so far)
-          bool last = true;
-#pragma unroll
-          for (int o = 0; o < kUnits; ++o)
-            if (o != u && done[o] <= j) last = false;
-          if (last) umma_commit(&v_empty[vslot]);
-          clk.tick(kProfMmaIssue);
-          if (j + 1 < n_tiles) {
-            if (!wait_k(j + 1)) { ok = false; break; }
-            issue_s(u, j + 1);
-            if (last) umma_commit(&k_empty[(j + 1) % nk]);
-            clk.tick(kProfMmaIssue);
-          }
-          done[u] = j + 1;
-          progressed = true;
+        for (int ks = 0; ks < kBN / 16; ++ks) {
+          const uint64_t bd = umma_desc_sw128_mn(v_addr + ks * 2048, kSlotHalf, 1024);
+          umma_bf16_a_tmem(o_tmem, s_tmem + ks * 8, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
         }
-        if (all_done) break;
-        if (progressed) {
-          idle_since = global_timer_ns();
-        } else if (global_timer_ns() - idle_since > kDefaultWaitNs || *abort_flag) {
-          ok = false;
-          reason = kWaitAccumTimeout;
-        }
+        umma_commit(&o_done[u]);
+        umma_commit(&v_empty[vslot]);
+        if (u == 0) clk.tick(kProfMmaIssue);
+        if (j + 1 < n_tiles && !issue_s(j + 1)) ok = false;
       }
-      if (kProfile) clk.flush(p.prof, kProfMmaWaitK, kProfMmaIssue);
+      if (kProfile && u == 0) clk.flush(p.prof, kProfMmaWaitK, kProfMmaIssue);
       if (!ok || *abort_flag) {
         if (!ok) report_status(p.status, kKernelId, reason);
         *abort_flag = 1;
@@ -423,6 +391,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
       }
       clk.tick(kProfSoftRescale);
+      // The two units take turns on the MUFU pipe (unit 0 tile j, unit 1 tile j, unit 0 tile j+1, ...):
+      // run together, both exp phases take twice as long and nothing overlaps the rest of either chain.
+      if (kUnits == 2 && (u == 1 || j > 0)) {
+        ok = __all_sync(0xffffffffu, u == 1 ? mbar_wait(&xu_done[0], j & 1) : mbar_wait(&xu_done[1], (j - 1) & 1));
+        if (!ok) break;
+      }
+      clk.tick(kProfSoftWaitO);
       // p = 2^(s * scale - m): one packed FMA per two scores, one MUFU each, four independent sums. P goes
       // back to tensor memory as bf16 pairs over the first 64 columns of S (this thread's own lane), where
       // the second MMA reads it as its A operand.
@@ -446,6 +421,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tmem_st16(lane_taddr + (c >> 1) * 16, packed);   // scores 16c .. 16c+31 -> P columns 8c .. 8c+15
       }
       l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
+      if (kUnits == 2) mbar_arrive(&xu_done[u]);
       clk.tick(kProfSoftExp);
       tmem_st_wait();
       tc_fence_before_sync();
@@ -619,9 +595,9 @@ static int launch_prefill_tc(const void* q, const void* k_cache, const void* v_c
   dim3 grid((max_q_len + kBM - 1) / kBM, hq / units, num_seqs);
   if (units == 2) {
     if (prof)
-      attn_prefill_tc_kernel<2, true><<<grid, 352, kSmemRequest2, stream>>>(map_q, map_k, map_v, p);
+      attn_prefill_tc_kernel<2, true><<<grid, 384, kSmemRequest2, stream>>>(map_q, map_k, map_v, p);
     else
-      attn_prefill_tc_kernel<2, false><<<grid, 352, kSmemRequest2, stream>>>(map_q, map_k, map_v, p);
+      attn_prefill_tc_kernel<2, false><<<grid, 384, kSmemRequest2, stream>>>(map_q, map_k, map_v, p);
   } else {
     if (prof)
       attn_prefill_tc_kernel<1, true><<<grid, 224, kSmemRequest1, stream>>>(map_q, map_k, map_v, p);

@@ -391,7 +391,7 @@ def paged_attention(q, k_cache, v_cache, attn, scale, num_q_heads, num_kv_heads,
 
 
 PREFILL_PHASES = ("softmax: wait S", "softmax: tcgen05.ld S", "softmax: mask+max", "softmax: rescale O",
-                  "softmax: exp+pack", "softmax: wait previous PV", "softmax: store P", "softmax: epilogue",
+                  "softmax: exp+pack", "softmax: wait for the MUFU turn", "softmax: store P", "softmax: epilogue",
                   "mma: wait K tile", "mma: wait P", "mma: wait V tile", "mma: issue", "load: wait free slot",
                   "load: block table + TMA issue", "CTA lifetime", "tiles", "CTA setup", "ring slots")
 

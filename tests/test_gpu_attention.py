@@ -17,7 +17,7 @@ def _make_cache(num_blocks, hkv, bs, seed):
     return k, v
 
 
-def _run(q_lens, kv_lens, hq, hkv, bs=16, n_decode=0, seed=0, q_scale=1.0):
+def _run(q_lens, kv_lens, hq, hkv, bs=16, n_decode=0, seed=0, q_scale=1.0, poison=None):
     B = len(kv_lens)
     maxb = max(-(-l // bs) for l in kv_lens) + 1
     num_blocks = B * maxb + 3
@@ -27,12 +27,28 @@ def _run(q_lens, kv_lens, hq, hkv, bs=16, n_decode=0, seed=0, q_scale=1.0):
     for b in range(B):
         bt[b] = perm[b * maxb:(b + 1) * maxb].to(torch.int32)
     k, v = _make_cache(num_blocks, hkv, bs, seed)
+    if poison is not None:
+        # Everything outside the sequences' tokens is NaN in K; in V it is NaN too, except that ``poison ==
+        # "v_tail_zero"`` leaves zeros after the last token inside its page (what the append kernel guarantees).
+        used_k = torch.zeros(num_blocks, bs, dtype=torch.bool)
+        used_v = torch.zeros(num_blocks, bs, dtype=torch.bool)
+        for b in range(B):
+            for t in range(kv_lens[b]):
+                used_k[bt[b, t // bs], t % bs] = True
+                used_v[bt[b, t // bs], t % bs] = True
+            if poison == "v_tail_zero" and kv_lens[b] % bs:
+                blk = bt[b, kv_lens[b] // bs]
+                v[blk, :, kv_lens[b] % bs:] = 0
+                used_v[blk, kv_lens[b] % bs:] = True
+        k[~used_k.unsqueeze(1).expand(-1, hkv, -1)] = float("nan")
+        v[~used_v.unsqueeze(1).expand(-1, hkv, -1)] = float("nan")
     T = sum(q_lens)
     q = (torch.randn(T, hq * D, generator=g) * q_scale).bfloat16()
     cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
     kvl = torch.tensor(kv_lens, dtype=torch.int32)
     scale = D ** -0.5
-    ref = cpu_ref.paged_attention(q.float(), k.float(), v.float(), cu, kvl, bt, scale, hq, hkv, D)
+    ref = cpu_ref.paged_attention(q.float(), torch.nan_to_num(k.float()), torch.nan_to_num(v.float()), cu, kvl, bt,
+                                  scale, hq, hkv, D)
     from xixi_vllm_b200.ops import cuda
     attn = AttnBatch(cu_q=cu.to(DEV), kv_lens=kvl.to(DEV), block_tables=bt.to(DEV), num_seqs=B,
                      num_decode=n_decode, max_q_len=max(q_lens), max_kv_len=max(kv_lens), num_tokens=T)
@@ -118,3 +134,12 @@ def test_prefill_tensor_core_kernel_one_head_per_cta_form():
         _run([300, 129, 70, 1], [300, 256 + 129, 70, 513], 16, 8, seed=13)
     finally:
         cuda.prefill_pair_heads(True)
+
+
+def test_poisoned_cache_does_not_leak_into_results():
+    """NaN everywhere outside the live tokens: pages of other sequences, unused pages, and the rest of each
+    last page. The warp-MMA kernels zero-fill what they do not need; the tcgen05 prefill kernel relies on the
+    append kernel's zeroed V tail."""
+    _run([1] * 4, [1, 15, 33, 300], 16, 8, n_decode=4, poison="all")                      # decode
+    _run([5, 40, 64], [16 + 5, 40, 128 + 64 - 7], 16, 8, poison="all")                    # short chunks (warp-MMA)
+    _run([300, 129, 70], [300, 256 + 129 - 3, 70], 16, 8, poison="v_tail_zero", seed=4)   # tcgen05

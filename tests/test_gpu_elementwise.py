@@ -73,11 +73,42 @@ def test_qk_norm_rope_cache(hq, hkv, d):
     kc_ref, vc_ref = kc.clone(), vc.clone()
     q_ref = cpu_ref.qk_norm_rope_cache(qkv, qw, kw, 1e-6, cs, pos, slots, kc_ref, vc_ref, hq, hkv, d)
     kd, vd = kc.to(DEV), vc.to(DEV)
+    # scattered slots (several rows of a page in arbitrary order): all rows count as decode rows, so no
+    # page tail is cleared; the clearing after prefill chunks has its own test below
     q = cuda.qk_norm_rope_cache(qkv.to(DEV), qw.to(DEV), kw.to(DEV), 1e-6, cs.to(DEV), pos.to(DEV),
-                                slots.to(DEV), kd, vd, hq, hkv, d)
+                                slots.to(DEV), kd, vd, hq, hkv, d, prefill_begin=T)
     _close(q, q_ref, atol=3e-2, rtol=3e-2)
     _close(kd, kc_ref, atol=3e-2, rtol=3e-2)
     assert torch.equal(vd.cpu(), vc_ref)
+
+
+def test_kv_append_clears_v_rows_after_a_prefill_chunk():
+    """Poisoned pages: after the last row a prefill chunk writes into a page the remaining V rows are
+    zero (the tcgen05 prefill kernel multiplies them by P = 0); decode rows and other pages are untouched."""
+    from xixi_vllm_b200.ops import cuda
+    hq, hkv, d, bs, nblocks = 4, 2, 128, 16, 6
+    g = torch.Generator().manual_seed(8)
+    # row 0: a decode token at slot 3 of page 5; rows 1..20: a chunk filling page 2 and 4 rows of page 0;
+    # rows 21..23: a chunk of 3 rows starting at row 6 of page 3
+    slots = torch.tensor([5 * bs + 3] + [2 * bs + i for i in range(16)] + [0 * bs + i for i in range(4)] +
+                         [3 * bs + 6 + i for i in range(3)], dtype=torch.int32)
+    T = slots.numel()
+    qkv = torch.randn(T, (hq + 2 * hkv) * d, generator=g).bfloat16()
+    w = torch.ones(d).bfloat16()
+    cs = cpu_ref.build_cos_sin_cache(d, 64, 1e6)
+    pos = torch.arange(T, dtype=torch.int32)
+    kd = torch.full((nblocks, hkv, bs, d), float("nan")).bfloat16().to(DEV)
+    vd = torch.full((nblocks, hkv, bs, d), float("nan")).bfloat16().to(DEV)
+    cuda.qk_norm_rope_cache(qkv.to(DEV), w.to(DEV), w.to(DEV), 1e-6, cs.to(DEV), pos.to(DEV), slots.to(DEV), kd, vd,
+                            hq, hkv, d, prefill_begin=1)
+    v = vd.float().cpu()
+    assert torch.isfinite(v[2]).all()                                   # page 2 fully written
+    assert torch.isfinite(v[0, :, :4]).all() and (v[0, :, 4:] == 0).all()    # chunk ended at row 3 of page 0
+    assert torch.isnan(v[3, :, :6]).all() and torch.isfinite(v[3, :, 6:9]).all() and (v[3, :, 9:] == 0).all()
+    assert torch.isfinite(v[5, :, 3]).all() and torch.isnan(v[5, :, 4:]).all()   # decode row: nothing cleared
+    assert torch.isnan(v[1]).all() and torch.isnan(v[4]).all()          # pages nobody wrote
+    k = kd.float().cpu()
+    assert torch.isnan(k[0, :, 4:]).all()                               # K rows are never cleared (they get masked)
 
 
 def test_bounded_wait_reports_instead_of_hanging():

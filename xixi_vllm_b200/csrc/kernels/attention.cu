@@ -110,7 +110,10 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) attn_decode_kernel(const De
       for (int j = 0; j < 8; ++j) {
         const int c = lane + 32 * j;          // chunk id in the page: row c/16, chunk c%16
         cp_async16(kd + swz(c >> 4, c & 15), ks + c * 16);
-        cp_async16(vd + swz(c >> 4, c & 15), vs + c * 16);
+        // V rows past the end of the sequence are zero-filled: their probabilities are zero, but whatever an
+        // earlier owner of the page left there (possibly NaN) must not reach the product. K rows only feed
+        // scores that are masked afterwards.
+        cp_async16_zfill(vd + swz(c >> 4, c & 15), vs + c * 16, tt * kTile + (c >> 4) < kv_len);
       }
     }
     cp_async_commit();

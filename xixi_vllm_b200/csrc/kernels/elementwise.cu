@@ -226,7 +226,8 @@ qk_norm_rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __
                           const __nv_bfloat16* __restrict__ k_w, float eps, const float* __restrict__ cos_sin,
                           const int* __restrict__ positions, const int* __restrict__ slots,
                           __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
-                          __nv_bfloat16* __restrict__ v_cache, int tokens, int hq, int hkv, int block_size) {
+                          __nv_bfloat16* __restrict__ v_cache, int tokens, int hq, int hkv, int block_size,
+                          int prefill_begin) {
   constexpr int HALF = D / 2;
   constexpr int PER = HALF / 32;           // elements per lane per half (2 for D=128, 1 for D=64)
   static_assert(PER == 1 || PER == 2, "head_dim must be 64 or 128");
@@ -283,6 +284,22 @@ qk_norm_rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __
       } else {
         dst[lane] = __float2bfloat16(lo[0]);
         dst[HALF + lane] = __float2bfloat16(hi[0]);
+      }
+      // Last row that a prefill chunk writes into a page: clear the V rows after it. The tcgen05 prefill
+      // kernel multiplies whole 128-token tiles, masked columns included (P = 0 there), so rows past the
+      // end of the sequence must hold finite values whatever an earlier owner of the page left behind.
+      const int r = slot % block_size;
+      if (t >= prefill_begin && r != block_size - 1 && (t == tokens - 1 || slots[t + 1] != slot + 1)) {
+        for (int z = r + 1; z < block_size; ++z) {
+          __nv_bfloat16* row = dst + static_cast<size_t>(z - r) * D;
+          if (PER == 2) {
+            *reinterpret_cast<uint32_t*>(row + lane * 2) = 0u;
+            *reinterpret_cast<uint32_t*>(row + HALF + lane * 2) = 0u;
+          } else {
+            row[lane] = __float2bfloat16(0.f);
+            row[HALF + lane] = __float2bfloat16(0.f);
+          }
+        }
       }
     }
     return;
@@ -408,7 +425,8 @@ int xv_gather_rows(const void* x, const int* rows, void* y, int n, int hidden, c
 static int qk_norm_rope_launch(const void* qkv, const float* partials, int splits, long long split_stride,
                                const void* q_w, const void* k_w, float eps, const float* cos_sin,
                                const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
-                               int tokens, int hq, int hkv, int d, int block_size, cudaStream_t stream) {
+                               int tokens, int hq, int hkv, int d, int block_size, int prefill_begin,
+                               cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const long long warps = static_cast<long long>(tokens) * (hq + 2 * hkv);
   const unsigned blocks = static_cast<unsigned>((warps + 7) / 8);
@@ -418,7 +436,7 @@ static int qk_norm_rope_launch(const void* qkv, const float* partials, int split
       static_cast<const __nv_bfloat16*>(q_w),                                                              \
       static_cast<const __nv_bfloat16*>(k_w), eps, cos_sin, positions, slots,                              \
       static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),                            \
-      static_cast<__nv_bfloat16*>(v_cache), tokens, hq, hkv, block_size)
+      static_cast<__nv_bfloat16*>(v_cache), tokens, hq, hkv, block_size, prefill_begin)
   if (d == 128) {
     XV_QKR(128);
   } else if (d == 64) {
@@ -432,17 +450,18 @@ static int qk_norm_rope_launch(const void* qkv, const float* partials, int split
 
 int xv_qk_norm_rope_cache(const void* qkv, const void* q_w, const void* k_w, float eps, const float* cos_sin,
                           const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
-                          int tokens, int hq, int hkv, int d, int block_size, cudaStream_t stream) {
+                          int tokens, int hq, int hkv, int d, int block_size, int prefill_begin,
+                          cudaStream_t stream) {
   return qk_norm_rope_launch(qkv, nullptr, 0, 0, q_w, k_w, eps, cos_sin, positions, slots, q_out, k_cache, v_cache,
-                             tokens, hq, hkv, d, block_size, stream);
+                             tokens, hq, hkv, d, block_size, prefill_begin, stream);
 }
 
 int xv_qk_norm_rope_cache_partials(const float* partials, int splits, long long split_stride, const void* q_w,
                                    const void* k_w, float eps, const float* cos_sin, const int* positions,
                                    const int* slots, void* q_out, void* k_cache, void* v_cache, int tokens, int hq,
-                                   int hkv, int d, int block_size, cudaStream_t stream) {
+                                   int hkv, int d, int block_size, int prefill_begin, cudaStream_t stream) {
   return qk_norm_rope_launch(nullptr, partials, splits, split_stride, q_w, k_w, eps, cos_sin, positions, slots,
-                             q_out, k_cache, v_cache, tokens, hq, hkv, d, block_size, stream);
+                             q_out, k_cache, v_cache, tokens, hq, hkv, d, block_size, prefill_begin, stream);
 }
 
 int xv_add_rmsnorm_partials(const float* partials, int splits, long long split_stride, void* residual, const void* w,

@@ -148,10 +148,10 @@ int xv_qwen3_forward(const XvModelDesc* m, const XvBatchDesc* b, const XvArena* 
       XV_TRY(31, xv_qk_norm_rope_cache_partials(static_cast<const float*>(a->gemm_ws), splits,
                                                 static_cast<long long>(T) * m->qkv_rows, w.q_norm, w.k_norm, m->eps,
                                                 m->cos_sin, b->positions, b->slots, a->q, w.k_cache, w.v_cache, T,
-                                                m->hq, m->hkv, D, m->block_size, stream));
+                                                m->hq, m->hkv, D, m->block_size, n_dec, stream));
     } else {
       XV_TRY(32, xv_qk_norm_rope_cache(a->qkv, w.q_norm, w.k_norm, m->eps, m->cos_sin, b->positions, b->slots, a->q,
-                                       w.k_cache, w.v_cache, T, m->hq, m->hkv, D, m->block_size, stream));
+                                       w.k_cache, w.v_cache, T, m->hq, m->hkv, D, m->block_size, n_dec, stream));
     }
     if (n_dec > 0)
       XV_TRY(33, xv_attn_decode(a->q, w.k_cache, w.v_cache, b->block_tables, b->kv_lens, a->attn, n_dec, m->hq, m->hkv,

@@ -88,13 +88,15 @@ int xv_gather_rows(const void* x, const int* rows, void* y, int n, int hidden, c
 // Per-head RMSNorm of q and k, NeoX RoPE, q written to q_out [T, hq*d], k/v appended to the
 // paged cache [blocks, hkv, block_size, d] at `slots` (negative slot = skip).
 // When `partials` is non-null the QKV activations are read as the sum of `splits` fp32 planes.
+// Tokens from index `prefill_begin` on are prefill rows: after the last row such a chunk writes into a
+// page, the remaining V rows of that page are cleared (the tcgen05 prefill kernel reads whole tiles).
 int xv_qk_norm_rope_cache_partials(const float* partials, int splits, long long split_stride, const void* q_w,
                                    const void* k_w, float eps, const float* cos_sin, const int* positions,
                                    const int* slots, void* q_out, void* k_cache, void* v_cache, int tokens, int hq,
-                                   int hkv, int d, int block_size, cudaStream_t stream);
+                                   int hkv, int d, int block_size, int prefill_begin, cudaStream_t stream);
 int xv_qk_norm_rope_cache(const void* qkv, const void* q_w, const void* k_w, float eps, const float* cos_sin,
                           const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
-                          int tokens, int hq, int hkv, int d, int block_size, cudaStream_t stream);
+                          int tokens, int hq, int hkv, int d, int block_size, int prefill_begin, cudaStream_t stream);
 
 // ---- attention ----
 // Decode: one query row per sequence (rows 0..num_seqs-1 of q) against the paged cache.

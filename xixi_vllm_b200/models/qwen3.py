@@ -54,7 +54,8 @@ class Qwen3Attention:
         qkv = self.qkv_proj(x, defer=True)      # split-K partials are summed inside the next kernel
         q = ops.qk_norm_rope_cache(qkv, self.q_norm.weight, self.k_norm.weight, self.q_norm.eps,
                                    self.rotary.cos_sin, batch.positions, batch.slots, k_cache, v_cache,
-                                   self.num_heads, self.num_kv_heads, self.head_dim)
+                                   self.num_heads, self.num_kv_heads, self.head_dim,
+                                   prefill_begin=batch.attn.num_decode)
         o = ops.paged_attention(q, k_cache, v_cache, batch.attn, self.scale, self.num_heads,
                                 self.num_kv_heads, self.head_dim)
         return comm.row_linear(self.o_proj, o)

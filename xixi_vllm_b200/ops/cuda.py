@@ -55,7 +55,7 @@ def lib():
                                      ctypes.POINTER(_i32)]
     L.xv_add_rmsnorm_partials.argtypes = [_vp, _i32, _i64, _vp, _vp, _vp, _i32, _i32, _f32, _vp]
     L.xv_qk_norm_rope_cache_partials.argtypes = [_vp, _i32, _i64, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _vp,
-                                                 _i32, _i32, _i32, _i32, _i32, _vp]
+                                                 _i32, _i32, _i32, _i32, _i32, _i32, _vp]
     L.xv_gemm_bf16_silu_mul.argtypes = [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _vp, _vp]
     L.xv_silu_mul_interleaved.argtypes = [_vp, _vp, _i32, _i64, _vp, _i32, _i32, _vp]
     L.xv_rmsnorm.argtypes = [_vp, _vp, _vp, _i32, _i32, _f32, _vp]
@@ -64,7 +64,7 @@ def lib():
     L.xv_embedding.argtypes = [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]
     L.xv_gather_rows.argtypes = [_vp, _vp, _vp, _i32, _i32, _vp]
     L.xv_qk_norm_rope_cache.argtypes = [_vp, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
-                                        _i32, _i32, _vp]
+                                        _i32, _i32, _i32, _vp]
     L.xv_attn_decode_workspace_bytes.argtypes = [_i32, _i32, _i32, _i32]
     L.xv_attn_decode_workspace_bytes.restype = _i64
     L.xv_attn_decode.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _i32,
@@ -314,7 +314,7 @@ def gather_rows(x, rows):
 
 
 def qk_norm_rope_cache(qkv, q_w, k_w, eps, cos_sin, positions, slots, k_cache, v_cache, num_q_heads,
-                       num_kv_heads, head_dim):
+                       num_kv_heads, head_dim, prefill_begin: int = 0):
     if isinstance(qkv, SplitKPartial):
         _bf16(q_w, k_w, k_cache, v_cache)
         T = qkv.shape[0]
@@ -322,7 +322,8 @@ def qk_norm_rope_cache(qkv, q_w, k_w, eps, cos_sin, positions, slots, k_cache, v
         _check(lib().xv_qk_norm_rope_cache_partials(
             qkv.ws.data_ptr(), qkv.splits, qkv.stride_elems, q_w.data_ptr(), k_w.data_ptr(), eps, cos_sin.data_ptr(),
             positions.data_ptr(), slots.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), T,
-            num_q_heads, num_kv_heads, head_dim, k_cache.shape[2], _stream()), "qk_norm_rope_cache_partials")
+            num_q_heads, num_kv_heads, head_dim, k_cache.shape[2], prefill_begin, _stream()),
+            "qk_norm_rope_cache_partials")
         return q
     _bf16(qkv, q_w, k_w, k_cache, v_cache)
     if not (qkv.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()):
@@ -332,7 +333,7 @@ def qk_norm_rope_cache(qkv, q_w, k_w, eps, cos_sin, positions, slots, k_cache, v
     _check(lib().xv_qk_norm_rope_cache(qkv.data_ptr(), q_w.data_ptr(), k_w.data_ptr(), eps, cos_sin.data_ptr(),
                                        positions.data_ptr(), slots.data_ptr(), q.data_ptr(), k_cache.data_ptr(),
                                        v_cache.data_ptr(), T, num_q_heads, num_kv_heads, head_dim,
-                                       k_cache.shape[2], _stream()), "qk_norm_rope_cache")
+                                       k_cache.shape[2], prefill_begin, _stream()), "qk_norm_rope_cache")
     return q
 
 

@@ -63,10 +63,14 @@ def embedding(ids, w, vocab_start=0, out=None):
 
 
 def qk_norm_rope_cache(qkv, q_w, k_w, eps, cos_sin, positions, slots, k_cache, v_cache,
-                       num_q_heads, num_kv_heads, head_dim):
-    f = _cuda().qk_norm_rope_cache if qkv.is_cuda else cpu_ref.qk_norm_rope_cache
-    return f(qkv, q_w, k_w, eps, cos_sin, positions, slots, k_cache, v_cache,
-             num_q_heads, num_kv_heads, head_dim)
+                       num_q_heads, num_kv_heads, head_dim, prefill_begin: int = 0):
+    """``prefill_begin``: index of the first prefill row of the packed batch (decode rows come first).
+    The GPU kernel clears the V rows that follow a prefill chunk's last row inside its page."""
+    if qkv.is_cuda:
+        return _cuda().qk_norm_rope_cache(qkv, q_w, k_w, eps, cos_sin, positions, slots, k_cache, v_cache,
+                                          num_q_heads, num_kv_heads, head_dim, prefill_begin)
+    return cpu_ref.qk_norm_rope_cache(qkv, q_w, k_w, eps, cos_sin, positions, slots, k_cache, v_cache,
+                                      num_q_heads, num_kv_heads, head_dim)
 
 
 def paged_attention(q, k_cache, v_cache, attn, scale, num_q_heads, num_kv_heads, head_dim):

@@ -340,6 +340,9 @@ def qk_norm_rope_cache(qkv, q_w, k_w, eps, cos_sin, positions, slots, k_cache, v
 def decode_splits(num_seqs: int, num_kv_heads: int, num_sms: int, max_blocks_tokens: int) -> int:
     """KV splits so that a small batch still fills the GPU; depends only on launch-shape
     constants (never on sequence lengths) so it is stable under CUDA-graph replay."""
+    forced = os.environ.get("XV_DECODE_SPLITS")
+    if forced:
+        return int(forced)
     ctas = max(1, num_seqs * num_kv_heads)
     want = -(-2 * num_sms // ctas)
     by_len = max(1, max_blocks_tokens // 256)      # at least ~256 tokens per split

@@ -23,6 +23,7 @@
 #include <cuda_runtime.h>
 #include <math_constants.h>
 
+#include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "xv_cuda.h"
 
@@ -60,6 +61,8 @@ struct DecodeParams {
 };
 
 __global__ void __launch_bounds__(kDecWarps * 32, 2) attn_decode_kernel(const DecodeParams p) {
+  grid_dep_launch();
+  grid_dep_wait();
   extern __shared__ __align__(128) uint8_t smem[];
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -255,6 +258,8 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) attn_decode_kernel(const De
 // out[seq, head, :] = sum_s w_s * O_s with w_s = 2^(lse_s - max) / sum.
 __global__ void attn_combine_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_lse,
                                     __nv_bfloat16* __restrict__ out, int splits) {
+  grid_dep_launch();
+  grid_dep_wait();
   const size_t row = blockIdx.x;      // seq * hq + head
   const int d = threadIdx.x;
   float M = -CUDART_INF_F;
@@ -290,6 +295,8 @@ struct PrefillParams {
 };
 
 __global__ void __launch_bounds__(kPfWarps * 32, 2) attn_prefill_kernel(const PrefillParams p) {
+  grid_dep_launch();
+  grid_dep_wait();
   extern __shared__ __align__(128) uint8_t smem[];
   const int qt = blockIdx.x, head = blockIdx.y, b = p.seq_begin + blockIdx.z;
   const int q_begin = p.cu_q[b];
@@ -501,10 +508,10 @@ int xv_attn_decode(const void* q, const void* k_cache, const void* v_cache, cons
   p.hq = hq; p.hkv = hkv; p.block_size = block_size; p.max_blocks = max_blocks; p.splits = splits;
   p.scale_log2 = scale * kLog2e;
   dim3 grid(splits, hkv, num_seqs);
-  attn_decode_kernel<<<grid, kDecWarps * 32, kDecSmem, stream>>>(p);
+  launch_pdl(attn_decode_kernel, dim3(grid), dim3(kDecWarps * 32), kDecSmem, stream, p);
   if (cudaGetLastError() != cudaSuccess) return XV_ERR_LAUNCH;
   if (splits > 1) {
-    attn_combine_kernel<<<num_seqs * hq, kD, 0, stream>>>(p.ws_o, p.ws_lse, p.out, splits);
+    launch_pdl(attn_combine_kernel, dim3(num_seqs * hq), dim3(kD), 0, stream, p.ws_o, p.ws_lse, p.out, splits);
     if (cudaGetLastError() != cudaSuccess) return XV_ERR_LAUNCH;
   }
   return 0;
@@ -533,7 +540,7 @@ int xv_attn_prefill(const void* q, const void* k_cache, const void* v_cache, con
   p.seq_begin = seq_begin; p.hq = hq; p.hkv = hkv; p.block_size = block_size; p.max_blocks = max_blocks;
   p.scale_log2 = scale * kLog2e;
   dim3 grid((max_q_len + kPfBM - 1) / kPfBM, hq, num_seqs);
-  attn_prefill_kernel<<<grid, kPfWarps * 32, kPfSmem, stream>>>(p);
+  launch_pdl(attn_prefill_kernel, dim3(grid), dim3(kPfWarps * 32), kPfSmem, stream, p);
   return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
 }
 

@@ -11,6 +11,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "xv_cuda.h"
 
@@ -55,6 +56,8 @@ template <bool ADD>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,
                const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int hidden, float eps) {
+  grid_dep_launch();
+  grid_dep_wait();
   __shared__ float scratch[32];
   const size_t row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * hidden;
@@ -101,6 +104,8 @@ __global__ void __launch_bounds__(kNormThreads)
 add_rmsnorm_partials_kernel(const float* __restrict__ partials, int splits, long long split_stride,
                             __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ w,
                             __nv_bfloat16* __restrict__ y, int hidden, float eps) {
+  grid_dep_launch();
+  grid_dep_wait();
   __shared__ float scratch[32];
   const size_t row = blockIdx.x;
   __nv_bfloat16* rr = residual + row * hidden;
@@ -144,6 +149,8 @@ add_rmsnorm_partials_kernel(const float* __restrict__ partials, int splits, long
 
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long long rows,
                                 int inter) {
+  grid_dep_launch();
+  grid_dep_wait();
   const int vec_per_row = inter >> 3;
   const long long total = rows * vec_per_row;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -163,6 +170,8 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat
 __global__ void silu_mul_interleaved_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ partials,
                                             int splits, long long split_stride, __nv_bfloat16* __restrict__ y,
                                             long long rows, int inter) {
+  grid_dep_launch();
+  grid_dep_wait();
   const int groups = inter >> 3;
   const long long total = rows * groups;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -195,6 +204,8 @@ __global__ void silu_mul_interleaved_kernel(const __nv_bfloat16* __restrict__ x,
 // out[t] = w[ids[t] - vocab_start] when the id is inside this rank's shard, zeros otherwise.
 __global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ w,
                                  __nv_bfloat16* __restrict__ y, int hidden, int vocab_start, int vocab_rows) {
+  grid_dep_launch();
+  grid_dep_wait();
   const size_t t = blockIdx.x;
   const int local = ids[t] - vocab_start;
   const bool mine = local >= 0 && local < vocab_rows;
@@ -209,6 +220,8 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat1
 
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ rows,
                                    __nv_bfloat16* __restrict__ y, int hidden) {
+  grid_dep_launch();
+  grid_dep_wait();
   const size_t i = blockIdx.x;
   const size_t src = static_cast<size_t>(rows[i]);
   const int nvec = hidden >> 3;
@@ -228,6 +241,8 @@ qk_norm_rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __
                           __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
                           __nv_bfloat16* __restrict__ v_cache, int tokens, int hq, int hkv, int block_size,
                           int prefill_begin) {
+  grid_dep_launch();
+  grid_dep_wait();
   constexpr int HALF = D / 2;
   constexpr int PER = HALF / 32;           // elements per lane per half (2 for D=128, 1 for D=64)
   static_assert(PER == 1 || PER == 2, "head_dim must be 64 or 128");
@@ -365,7 +380,7 @@ extern "C" {
 int xv_rmsnorm(const void* x, const void* w, void* y, int rows, int hidden, float eps, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (hidden % 8 || hidden > kNormThreads * kNormMaxVec * 8) return XV_ERR_SHAPE;
-  rmsnorm_kernel<false><<<rows, kNormThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), nullptr,
+  launch_pdl(rmsnorm_kernel<false>, dim3(rows), dim3(kNormThreads), 0, stream, static_cast<const __nv_bfloat16*>(x), nullptr,
                                                           static_cast<const __nv_bfloat16*>(w),
                                                           static_cast<__nv_bfloat16*>(y), hidden, eps);
   return launch_ok();
@@ -375,7 +390,7 @@ int xv_add_rmsnorm(const void* x, void* residual, const void* w, void* y, int ro
                    cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (hidden % 8 || hidden > kNormThreads * kNormMaxVec * 8) return XV_ERR_SHAPE;
-  rmsnorm_kernel<true><<<rows, kNormThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
+  launch_pdl(rmsnorm_kernel<true>, dim3(rows), dim3(kNormThreads), 0, stream, static_cast<const __nv_bfloat16*>(x),
                                                          static_cast<__nv_bfloat16*>(residual),
                                                          static_cast<const __nv_bfloat16*>(w),
                                                          static_cast<__nv_bfloat16*>(y), hidden, eps);
@@ -388,7 +403,7 @@ int xv_silu_mul(const void* x, void* y, int rows, int inter, cudaStream_t stream
   const long long total = static_cast<long long>(rows) * (inter / 8);
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  silu_mul_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
+  launch_pdl(silu_mul_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x),
                                                                      static_cast<__nv_bfloat16*>(y), rows, inter);
   return launch_ok();
 }
@@ -400,7 +415,7 @@ int xv_silu_mul_interleaved(const void* x, const float* partials, int splits, lo
   const long long total = static_cast<long long>(rows) * (inter / 8);
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  silu_mul_interleaved_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+  launch_pdl(silu_mul_interleaved_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, 
       static_cast<const __nv_bfloat16*>(x), partials, splits, split_stride, static_cast<__nv_bfloat16*>(y), rows, inter);
   return launch_ok();
 }
@@ -409,7 +424,7 @@ int xv_embedding(const int* ids, const void* w, void* y, int tokens, int hidden,
                  cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (hidden % 8) return XV_ERR_SHAPE;
-  embedding_kernel<<<tokens, 128, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(w),
+  launch_pdl(embedding_kernel, dim3(tokens), dim3(128), 0, stream, ids, static_cast<const __nv_bfloat16*>(w),
                                                static_cast<__nv_bfloat16*>(y), hidden, vocab_start, vocab_rows);
   return launch_ok();
 }
@@ -417,7 +432,7 @@ int xv_embedding(const int* ids, const void* w, void* y, int tokens, int hidden,
 int xv_gather_rows(const void* x, const int* rows, void* y, int n, int hidden, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (hidden % 8) return XV_ERR_SHAPE;
-  gather_rows_kernel<<<n, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows,
+  launch_pdl(gather_rows_kernel, dim3(n), dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(x), rows,
                                             static_cast<__nv_bfloat16*>(y), hidden);
   return launch_ok();
 }
@@ -431,7 +446,7 @@ static int qk_norm_rope_launch(const void* qkv, const float* partials, int split
   const long long warps = static_cast<long long>(tokens) * (hq + 2 * hkv);
   const unsigned blocks = static_cast<unsigned>((warps + 7) / 8);
 #define XV_QKR(D)                                                                                         \
-  qk_norm_rope_cache_kernel<D><<<blocks, 256, 0, stream>>>(                                                \
+  launch_pdl(qk_norm_rope_cache_kernel<D>, dim3(blocks), dim3(256), 0, stream,                                                 \
       static_cast<const __nv_bfloat16*>(qkv), partials, splits, split_stride,                              \
       static_cast<const __nv_bfloat16*>(q_w),                                                              \
       static_cast<const __nv_bfloat16*>(k_w), eps, cos_sin, positions, slots,                              \
@@ -468,7 +483,7 @@ int xv_add_rmsnorm_partials(const float* partials, int splits, long long split_s
                             void* y, int rows, int hidden, float eps, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (hidden % 8 || hidden > kNormThreads * kNormMaxVec * 8) return XV_ERR_SHAPE;
-  add_rmsnorm_partials_kernel<<<rows, kNormThreads, 0, stream>>>(partials, splits, split_stride,
+  launch_pdl(add_rmsnorm_partials_kernel, dim3(rows), dim3(kNormThreads), 0, stream, partials, splits, split_stride,
                                                                 static_cast<__nv_bfloat16*>(residual),
                                                                 static_cast<const __nv_bfloat16*>(w),
                                                                 static_cast<__nv_bfloat16*>(y), hidden, eps);

@@ -28,6 +28,7 @@
 #include <mutex>
 #include <unordered_map>
 
+#include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "tp_device.cuh"
 #include "xv_cuda.h"
@@ -89,6 +90,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p, const __grid_constant__ TpTail tail) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+  grid_dep_launch();           // the next kernel of the stream may start its prologue (see launch.cuh)
   // Dynamic shared memory is only guaranteed 16-byte alignment; the swizzled tiles need 1024.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -127,6 +129,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything up to here touched only this CTA's shared and tensor memory. The producer thread first
+  // starts the weight stream, which no earlier kernel writes; every other thread waits now for the
+  // previous kernel of the stream (its outputs are this kernel's activations, and this kernel's
+  // outputs may overwrite buffers it still reads).
+  if (threadIdx.x != 0) grid_dep_wait();
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -137,6 +144,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // activations) is re-read by every CTA. Hints follow that.
       const uint64_t hint_a = p.transposed ? l2_policy_evict_first() : l2_policy_evict_normal();
       const uint64_t hint_b = p.transposed ? l2_policy_evict_last() : l2_policy_evict_normal();
+      // Weight tiles of the first stages of the first work item go out before the wait.
+      uint32_t pre = 0;
+      if (static_cast<int>(blockIdx.x) < total_work) {
+        const WorkItem wi = decode_work(p, blockIdx.x);
+        const int kb_begin = wi.split * p.k_blocks_per_split;
+        const int kb_end = min(kb_begin + p.k_blocks_per_split, total_kb);
+        pre = static_cast<uint32_t>(min(kb_end - kb_begin, p.stages));
+        for (uint32_t i = 0; i < pre; ++i) {
+          uint8_t* sa = smem + static_cast<size_t>(i) * stage_bytes;
+          mbar_expect_tx(&full_bar[i], stage_bytes);
+          if (p.transposed)
+            tma_load_2d(sa, &map_a, &full_bar[i], (kb_begin + i) * kBK, wi.tile_a * kBM, hint_a);
+          else
+            tma_load_2d(sa + a_bytes, &map_b, &full_bar[i], (kb_begin + i) * kBK, wi.tile_b * p.bn, hint_b);
+        }
+      }
+      grid_dep_wait();
       uint32_t it = 0;                   // K blocks issued so far by this CTA, across work items
       for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
         const WorkItem wi = decode_work(p, w);
@@ -151,9 +175,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             break;
           }
           uint8_t* sa = smem + static_cast<size_t>(s) * stage_bytes;
-          mbar_expect_tx(&full_bar[s], stage_bytes);
-          tma_load_2d(sa, &map_a, &full_bar[s], kb * kBK, wi.tile_a * kBM, hint_a);
-          tma_load_2d(sa + a_bytes, &map_b, &full_bar[s], kb * kBK, wi.tile_b * p.bn, hint_b);
+          const bool weights_out = it < pre;      // expect_tx and the weight tile were issued above
+          if (!weights_out) mbar_expect_tx(&full_bar[s], stage_bytes);
+          if (!(weights_out && p.transposed))
+            tma_load_2d(sa, &map_a, &full_bar[s], kb * kBK, wi.tile_a * kBM, hint_a);
+          if (!(weights_out && !p.transposed))
+            tma_load_2d(sa + a_bytes, &map_b, &full_bar[s], kb * kBK, wi.tile_b * p.bn, hint_b);
         }
       }
     }
@@ -562,6 +589,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 // out[m, n] = sum_s partial[s, m, n], rounded to bf16.
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
                                      long long elems, int splits, long long split_stride) {
+  grid_dep_launch();
+  grid_dep_wait();
   const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
   if (i >= elems) return;
   if (i + 4 <= elems) {
@@ -855,7 +884,7 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
     if (grid > slots) grid = slots;
     if (grid < 1) grid = 1;
   }
-  gemm_tcgen05_kernel<<<grid, kGemmThreads, pl.smem_bytes, stream>>>(map_a, map_b, p, tail);
+  launch_pdl(gemm_tcgen05_kernel, dim3(grid), dim3(kGemmThreads), pl.smem_bytes, stream, map_a, map_b, p, tail);
   if (cudaGetLastError() != cudaSuccess) return XV_ERR_LAUNCH;
   if (tail_in) return 0;
   if (splits_out) *splits_out = pl.splits;
@@ -865,7 +894,7 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
     if (ldy != n) return XV_ERR_SHAPE;   // split-K output must be dense
     const int threads = 256;
     const long long blocks = (elems / 4 + threads) / threads;
-    splitk_reduce_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+    launch_pdl(splitk_reduce_kernel, dim3(static_cast<unsigned>(blocks)), dim3(threads), 0, stream,
         static_cast<const float*>(workspace), static_cast<__nv_bfloat16*>(y), elems, pl.splits, p.split_stride);
     if (cudaGetLastError() != cudaSuccess) return XV_ERR_LAUNCH;
   }

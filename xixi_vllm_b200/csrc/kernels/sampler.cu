@@ -17,6 +17,7 @@
 #include <cuda_runtime.h>
 #include <math_constants.h>
 
+#include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "xv_cuda.h"
 
@@ -85,6 +86,8 @@ __device__ float block_sum_f(float v, float* scratch) {
 
 __global__ void __launch_bounds__(kSampThreads)
 argmax_kernel(const __nv_bfloat16* __restrict__ logits, long long* __restrict__ out, int vocab, long long ld) {
+  grid_dep_launch();
+  grid_dep_wait();
   __shared__ ArgPair scratch[32];
   const __nv_bfloat16* row = logits + static_cast<size_t>(blockIdx.x) * ld;
   ArgPair best{-CUDART_INF_F, 0x7fffffff};
@@ -110,6 +113,8 @@ __global__ void __launch_bounds__(kSampThreads)
 sample_kernel(const __nv_bfloat16* __restrict__ logits, long long* __restrict__ out, int vocab, long long ld,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const float* __restrict__ min_p, const int* __restrict__ rng) {
+  grid_dep_launch();
+  grid_dep_wait();
   __shared__ ArgPair scratch[32];
   __shared__ float fscratch[32];
   __shared__ unsigned hist_cnt[256];
@@ -235,14 +240,14 @@ extern "C" {
 
 int xv_argmax(const void* logits, long long* out, int rows, int vocab, long long ld, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  argmax_kernel<<<rows, kSampThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), out, vocab, ld);
+  launch_pdl(argmax_kernel, dim3(rows), dim3(kSampThreads), 0, stream, static_cast<const __nv_bfloat16*>(logits), out, vocab, ld);
   return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
 }
 
 int xv_sample(const void* logits, long long* out, int rows, int vocab, long long ld, const float* temperature,
               const int* top_k, const float* top_p, const float* min_p, const int* rng, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  sample_kernel<<<rows, kSampThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), out, vocab, ld,
+  launch_pdl(sample_kernel, dim3(rows), dim3(kSampThreads), 0, stream, static_cast<const __nv_bfloat16*>(logits), out, vocab, ld,
                                                    temperature, top_k, top_p, min_p, rng);
   return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
 }

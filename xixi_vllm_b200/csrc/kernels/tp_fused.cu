@@ -31,6 +31,7 @@
 #include <cuda_runtime.h>
 #include <math_constants.h>
 
+#include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "tp_device.cuh"
 #include "xv_cuda.h"
@@ -46,6 +47,8 @@ __global__ void __launch_bounds__(kTpThreads)
 tp_reduce_norm_kernel(const TpComm c, long long buf_offset, const __nv_bfloat16* __restrict__ residual_in,
                       __nv_bfloat16* __restrict__ residual_out, const __nv_bfloat16* __restrict__ w,
                       __nv_bfloat16* __restrict__ y, int rows, int hidden, float eps, int mode) {
+  grid_dep_launch();
+  grid_dep_wait();
   __shared__ float scratch[32];
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(c.epoch);
   const bool ok = tp_barrier(c, epoch, 0);
@@ -67,6 +70,8 @@ __global__ void __launch_bounds__(kTpThreads)
 tp_reduce_norm_sharded_kernel(const TpComm c, long long buf_offset, long long h_offset, int has_residual,
                               __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ w, int rows,
                               int hidden, float eps) {
+  grid_dep_launch();
+  grid_dep_wait();
   __shared__ float scratch[32];
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(c.epoch);
   bool ok = tp_barrier(c, epoch, 0);
@@ -165,6 +170,8 @@ struct ArgSlot {
 __global__ void __launch_bounds__(1024)
 tp_argmax_kernel(const TpComm c, long long slots_offset, const __nv_bfloat16* __restrict__ logits, long long ld,
                  int local_vocab, int valid_vocab, int vocab_start, long long* __restrict__ out, int rows) {
+  grid_dep_launch();
+  grid_dep_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
   const int row = blockIdx.x;
@@ -264,6 +271,8 @@ tp_argmax_kernel(const TpComm c, long long slots_offset, const __nv_bfloat16* __
 __global__ void __launch_bounds__(kTpThreads)
 tp_allgather_cols_kernel(const TpComm c, const __nv_bfloat16* __restrict__ src, long long ld, int local_cols,
                          long long total_cols, int rows) {
+  grid_dep_launch();
+  grid_dep_wait();
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(c.epoch);
   const int vec_per_row = local_cols >> 3;
   const long long total = static_cast<long long>(rows) * vec_per_row;
@@ -343,7 +352,7 @@ int xv_tp_reduce_norm(const void* const* peer_bufs, void* const* peer_flags, con
   int rc = fill_comm(&c, peer_bufs, peer_flags, mc_buf, epoch, rank, world, spin_limit, status);
   if (rc) return rc;
   int grid = rows < 148 * 4 ? rows : 148 * 4;
-  tp_reduce_norm_kernel<<<grid, kTpThreads, 0, stream>>>(
+  launch_pdl(tp_reduce_norm_kernel, dim3(grid), dim3(kTpThreads), 0, stream, 
       c, buf_offset, static_cast<const __nv_bfloat16*>(residual_in), static_cast<__nv_bfloat16*>(residual_out),
       static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), rows, hidden, eps, mode);
   return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
@@ -364,7 +373,7 @@ int xv_tp_reduce_norm_sharded(const void* const* peer_bufs, void* const* peer_fl
   int mine = (rows + world - 1) / world;
   int grid = mine < 148 * 4 ? mine : 148 * 4;     // every CTA waits at the end: keep the grid resident
   if (grid < 1) grid = 1;
-  tp_reduce_norm_sharded_kernel<<<grid, kTpThreads, 0, stream>>>(
+  launch_pdl(tp_reduce_norm_sharded_kernel, dim3(grid), dim3(kTpThreads), 0, stream, 
       c, buf_offset, h_offset, has_residual, static_cast<__nv_bfloat16*>(residual),
       static_cast<const __nv_bfloat16*>(w), rows, hidden, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
@@ -377,7 +386,7 @@ int xv_tp_argmax(const void* const* peer_bufs, void* const* peer_flags, void* ep
   TpComm c;
   int rc = fill_comm(&c, peer_bufs, peer_flags, nullptr, epoch, rank, world, spin_limit, status);
   if (rc) return rc;
-  tp_argmax_kernel<<<rows, 1024, 0, stream>>>(c, slots_offset, static_cast<const __nv_bfloat16*>(logits), ld,
+  launch_pdl(tp_argmax_kernel, dim3(rows), dim3(1024), 0, stream, c, slots_offset, static_cast<const __nv_bfloat16*>(logits), ld,
                                               local_vocab, valid_vocab, vocab_start, out, rows);
   return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
 }
@@ -398,7 +407,7 @@ int xv_tp_allgather_cols(const void* const* peer_bufs, void* const* peer_flags, 
   const long long vecs = static_cast<long long>(rows) * (local_cols / 8);
   long long want = (vecs + kTpThreads - 1) / kTpThreads;
   const int grid = static_cast<int>(want < 1 ? 1 : (want > 148 * 4 ? 148 * 4 : want));   // every CTA waits: stay resident
-  tp_allgather_cols_kernel<<<grid, kTpThreads, 0, stream>>>(c, static_cast<const __nv_bfloat16*>(src), ld, local_cols,
+  launch_pdl(tp_allgather_cols_kernel, dim3(grid), dim3(kTpThreads), 0, stream, c, static_cast<const __nv_bfloat16*>(src), ld, local_cols,
                                                             total_cols, rows);
   return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
 }

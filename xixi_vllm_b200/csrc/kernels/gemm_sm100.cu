@@ -24,6 +24,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -761,6 +762,11 @@ static int gemm_plan_impl(int m, int n, int k, int num_sms, XvGemmPlan* plan, bo
     if (by_bytes > by_traffic) by_traffic = by_bytes;
     if (splits > by_traffic) splits = by_traffic;
     while (splits > 1 && total_kb / splits < 4) --splits;
+    static const int max_splits = [] {
+      const char* e = std::getenv("XV_GEMM_MAX_SPLITS");      // experiment knob: cap on split-K
+      return e ? std::atoi(e) : 16;
+    }();
+    if (splits > max_splits) splits = max_splits;
     if (splits > 16) splits = 16;
     if (splits < 1) splits = 1;
   }

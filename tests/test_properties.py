@@ -1,0 +1,125 @@
+"""Property tests (Hypothesis) for the CPU control plane: whatever the scheduler does with a
+workload (chunking, mixing, preemption, prefix reuse), every request must end with the tokens a
+scheduling-independent "model" assigns to it, budgets must hold at every step and the page ledger must
+stay consistent."""
+import random
+
+from hypothesis import HealthCheck, given, settings
+from hypothesis import strategies as st
+
+from xixi_vllm_b200.control.scheduler import Scheduler
+from xixi_vllm_b200.data import KVManager, Sequence
+from xixi_vllm_b200.data.sequence import slots_for_range
+from xixi_vllm_b200.sampling_params import SamplingParams
+
+EOS = 2
+BS = 16
+
+
+def fake_model(token_ids) -> int:
+    """Next token as a pure function of the token history: the same request yields the same text however
+    its prompt was chunked, cached, preempted or batched. Emits EOS now and then."""
+    h = 0
+    for t in token_ids:
+        h = (h * 1000003 + t + 1) % 2147483647
+    t = h % 37
+    return EOS if t == 0 else t + 3
+
+
+def expected_completion(prompt, max_tokens, ignore_eos):
+    toks = list(prompt)
+    out = []
+    while len(out) < max_tokens:
+        t = fake_model(toks)
+        toks.append(t)
+        out.append(t)
+        if t == EOS and not ignore_eos:
+            break
+    return out
+
+
+request = st.tuples(st.integers(1, 70),          # prompt length
+                    st.integers(0, 3),           # which shared prefix (0 = none)
+                    st.integers(0, 12),          # max_tokens
+                    st.booleans())               # ignore_eos
+
+
+@settings(max_examples=120, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@given(reqs=st.lists(request, min_size=1, max_size=10),
+       num_blocks=st.integers(6, 40), max_seqs=st.integers(1, 6), budget=st.integers(8, 96),
+       mix=st.booleans(), backend=st.sampled_from(["none", "hash", "radix"]), seed=st.integers(0, 1000),
+       arrivals=st.integers(1, 4))
+def test_any_schedule_yields_the_models_tokens(reqs, num_blocks, max_seqs, budget, mix, backend, seed, arrivals):
+    rnd = random.Random(seed)
+    prefixes = [[], [7] * 32, list(range(100, 148)), [9, 8] * 20]
+    kv = KVManager(num_blocks=num_blocks, block_size=BS, prefix_backend=backend)
+    sch = Scheduler(kv, max_num_seqs=max_seqs, max_num_batched_tokens=budget, eos_token_id=EOS,
+                    mix_prefill_decode=mix)
+    pending = []
+    for n, which, max_tokens, ignore_eos in reqs:
+        prompt = (prefixes[which] + [rnd.randrange(3, 60) for _ in range(n)])
+        # a request must fit the pool on its own, or no scheduler could ever run it
+        if -(-(len(prompt) + max_tokens) // BS) > num_blocks:
+            prompt = prompt[: max(1, num_blocks * BS - max_tokens - 1)]
+        seq = Sequence.from_prompt(prompt, block_size=BS,
+                                   sampling=SamplingParams(max_tokens=max_tokens, ignore_eos=ignore_eos))
+        pending.append((seq, list(prompt), max_tokens, ignore_eos))
+    todo = list(pending)
+    steps = 0
+    while todo or not sch.is_finished():
+        for _ in range(arrivals):                  # requests trickle in while others run
+            if todo:
+                sch.add(todo.pop(0)[0])
+        batch = sch.schedule()
+        # per-step budgets
+        assert len(batch.prefills) + len(batch.decodes) <= max_seqs
+        assert sum(s.num_scheduled_tokens for s in batch.prefills) + len(batch.decodes) <= budget
+        assert sum(1 for s in batch.prefills if not s.need_sample) <= 1       # one partial chunk per step
+        for s in batch.prefills + batch.decodes:
+            assert len(s.block_table) >= -(-(s.num_cached_tokens + s.num_scheduled_tokens) // BS)
+        batch.to_wire()
+        p_ids = [fake_model(s.token_ids) for s in batch.prefills]
+        d_ids = [fake_model(s.token_ids) for s in batch.decodes]
+        sch.update(batch, p_ids, d_ids)
+        kv.blocks.check_invariants()
+        steps += 1
+        assert steps < 5000, "the workload does not terminate"
+    for seq, prompt, max_tokens, ignore_eos in pending:
+        assert seq.is_finished
+        assert seq.token_ids[len(prompt):] == expected_completion(prompt, max_tokens, ignore_eos)
+    assert kv.blocks.num_used == 0
+
+
+@settings(max_examples=200, deadline=None)
+@given(table=st.lists(st.integers(0, 500), min_size=1, max_size=12, unique=True),
+       start=st.integers(0, 150), count=st.integers(0, 150), bs=st.sampled_from([16, 32, 64]))
+def test_slots_for_range_matches_definition(table, start, count, bs):
+    end = min(start + count, len(table) * bs)
+    start = min(start, end)
+    got = [int(x) for x in slots_for_range(table, start, end, bs)]
+    assert got == [table[i // bs] * bs + i % bs for i in range(start, end)]
+
+
+@settings(max_examples=60, deadline=None)
+@given(prompts=st.lists(st.tuples(st.integers(0, 2), st.integers(0, 80), st.integers(1, 40)), min_size=1, max_size=25),
+       seed=st.integers(0, 100))
+def test_hash_and_radix_backends_report_the_same_hits(prompts, seed):
+    """Both prefix indexes implement the same contract (full pages, chained identity): with a pool large
+    enough that nothing is evicted they must find exactly the same cached prefix for every request."""
+    rnd = random.Random(seed)
+    bases = [[rnd.randrange(50) for _ in range(96)] for _ in range(3)]
+    kvs = {b: KVManager(num_blocks=4096, block_size=BS, prefix_backend=b) for b in ("hash", "radix")}
+    for which, cut, tail in prompts:
+        toks = bases[which][:cut] + [rnd.randrange(50, 99) for _ in range(tail)]
+        hits = {}
+        for name, kv in kvs.items():
+            s = Sequence.from_prompt(toks, block_size=BS)
+            kv.allocate(s)
+            hits[name] = s.num_cached_tokens
+            assert s.num_cached_tokens % BS == 0 and s.num_cached_tokens < len(toks)
+            s.num_scheduled_tokens = s.num_tokens - s.num_cached_tokens
+            s.num_cached_tokens = s.num_tokens
+            kv.sync_prefix(s)
+            kv.deallocate(s)
+            kv.blocks.check_invariants()
+        assert hits["hash"] == hits["radix"]

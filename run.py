@@ -118,6 +118,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--pp", type=int, default=None, help="pipeline-parallel degree")
     p.add_argument("--dp", type=int, default=None, help="data-parallel replicas")
     p.add_argument("--pp-layer-counts", type=str, default=None, help="layers per stage, comma separated")
+    p.add_argument("--pp-microbatches", type=int, default=None,
+                   help="pipeline stages work on this many pieces of a step in turn (default 1: lockstep)")
     p.add_argument("--device-ids", type=str, default=None, help="GPU ids, comma separated (dp*tp*pp entries)")
     p.add_argument("--load-format", choices=("auto", "dummy"), default=None)
     p.add_argument("--device", choices=("cuda", "cpu"), default=None)
@@ -138,6 +140,8 @@ def config_from_args(args) -> dict:
             cfg[key] = getattr(args, flag)
     if args.pp_layer_counts is not None:
         cfg["pp_layer_counts"] = [int(x) for x in args.pp_layer_counts.split(",")]
+    if args.pp_microbatches is not None:
+        cfg["pp_microbatches"] = args.pp_microbatches
     if args.device_ids is not None:
         cfg["device_ids"] = [int(x) for x in args.device_ids.split(",")]
     if args.cg:

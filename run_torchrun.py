@@ -69,6 +69,8 @@ def main(argv=None) -> None:
         cfg["torch_compile"] = True
     if args.pp_layer_counts is not None:
         cfg["pp_layer_counts"] = [int(x) for x in args.pp_layer_counts.split(",")]
+    if args.pp_microbatches is not None:
+        cfg["pp_microbatches"] = args.pp_microbatches
     if args.device_ids is not None:
         cfg["device_ids"] = [int(x) for x in args.device_ids.split(",")]
     engine = launch_from_env(engine_config_from(cfg, resolve_model_path(cfg["model"])))

@@ -21,6 +21,7 @@ def main() -> None:
     ap.add_argument("--prefix-backend", default="hash")
     ap.add_argument("--prompt-lens", default="5,16,40,100")
     ap.add_argument("--temperature", type=float, default=0.0)
+    ap.add_argument("--pp-microbatches", type=int, default=1)
     a = ap.parse_args()
     import torch
 
@@ -28,7 +29,8 @@ def main() -> None:
     g = torch.Generator().manual_seed(0)
     cfg = EngineConfig(model=a.model, dtype="bfloat16", num_kvcache_blocks=256, max_num_seqs=16,
                        max_num_batched_tokens=256, context_len=512, tp_size=a.tp, pp_size=a.pp, dp_size=a.dp,
-                       tp_comm=a.comm, enforce_eager=not a.cg, nccl_port=a.port, prefix_backend=a.prefix_backend)
+                       tp_comm=a.comm, enforce_eager=not a.cg, nccl_port=a.port, prefix_backend=a.prefix_backend,
+                       pp_microbatches=a.pp_microbatches)
     vocab = cfg.hf_config.vocab_size
     prompts = [torch.randint(0, vocab, (int(n),), generator=g).tolist() for n in a.prompt_lens.split(",")]
     eng = Engine(cfg)

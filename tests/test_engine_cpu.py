@@ -109,6 +109,17 @@ def test_pp2_and_tp2pp2_equal_single_rank(tiny_model_dir):
     assert _generate(tiny_model_dir, prompts, tp_size=2, pp_size=2, nccl_port=29731) == base
 
 
+@pytest.mark.parametrize("kw", [dict(pp_size=2, pp_microbatches=2, nccl_port=29761),
+                                dict(pp_size=2, pp_microbatches=3, max_num_batched_tokens=24, nccl_port=29771),
+                                dict(tp_size=2, pp_size=2, pp_microbatches=2, nccl_port=29781)])
+def test_pp_microbatches_equal_single_rank(tiny_model_dir, kw):
+    """Pipeline stages that work on pieces of every step (decodes, whole prompts and mid-prompt chunks end up
+    in different pieces) must produce the tokens of the single-rank engine."""
+    prompts = _prompts(5, 20, seed=4) + _prompts(1, 50, seed=5)
+    base = _generate(tiny_model_dir, prompts, max_tokens=6)
+    assert _generate(tiny_model_dir, prompts, max_tokens=6, **kw) == base
+
+
 def test_uneven_pp_layer_counts(tmp_path):
     from xixi_vllm_b200.models.synth import make_model_dir
     d = make_model_dir(str(tmp_path / "m3"), "tiny", num_hidden_layers=3)

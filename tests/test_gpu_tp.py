@@ -196,3 +196,12 @@ def test_engine_pp2_and_dp2_match_single_gpu(tmp_path, kw):
     ref = _probe(d)
     out = _probe(d, **kw)
     assert _agree(ref, out) >= 10, (ref, out)
+
+
+def test_engine_pp2_microbatched_stages_match_single_gpu(tmp_path):
+    """Two pipeline stages working on two pieces of every step give the single-GPU tokens."""
+    _need(2)
+    d = _tiny_dir(tmp_path)
+    ref = _probe(d)
+    out = _probe(d, pp=2, pp_microbatches=2, port=29891)
+    assert _agree(ref, out) >= 10, (ref, out)

@@ -120,3 +120,43 @@ def test_cli_precedence_and_cleanup(tmp_path):
                 else:
                     fn(dict(cfg, prompt="hi", temperature=0.0, top_p=None, top_k=None))
                 assert engine.destroy.call_count == 1
+
+
+def test_split_forward_batch_pieces_cover_the_batch_in_order():
+    """Micro-batches for pipeline stages: whole sequences, rebased offsets, samples in the original order."""
+    import numpy as np
+    from xixi_vllm_b200.data import KVManager, Sequence
+    from xixi_vllm_b200.control.scheduler import Scheduler
+    from xixi_vllm_b200.runtime.staging import split_forward_batch
+    from xixi_vllm_b200.sampling_params import SamplingParams
+    kv = KVManager(num_blocks=64, block_size=16, prefix_backend="none")
+    sch = Scheduler(kv, max_num_seqs=8, max_num_batched_tokens=40, eos_token_id=1)
+    for n in (5, 9, 30, 40):
+        sch.add(Sequence.from_prompt(list(range(3, 3 + n)), block_size=16,
+                                     sampling=SamplingParams(max_tokens=4, ignore_eos=True)))
+    st = BatchStager(max_seqs=8, max_tokens=128, max_blocks=8, block_size=16, device="cpu")
+    seen_partial = False
+    for _ in range(4):                       # prefill-only step, then mixed steps with a mid-prompt chunk
+        b = sch.schedule()
+        full = st.build(b.to_wire())
+        for parts in (1, 2, 3, 16):
+            pieces = split_forward_batch(full, parts)
+            assert len(pieces) <= max(1, min(parts, full.attn.num_seqs))
+            assert pieces[0][1] == 0 and pieces[-1][2] == full.num_tokens
+            rows, samples, seqs = [], [], 0
+            for sub, t0, t1 in pieces:
+                assert t1 - t0 == sub.num_tokens == int(sub.attn.cu_q[-1]) and int(sub.attn.cu_q[0]) == 0
+                assert torch.equal(sub.input_ids, full.input_ids[t0:t1])
+                assert sub.attn.num_seqs == sub.attn.kv_lens.numel() == sub.attn.block_tables.shape[0]
+                assert sub.n_decode + sub.n_prefill == sub.attn.num_seqs and sub.attn.num_decode == sub.n_decode
+                assert sub.attn.max_q_len == int(np.diff(sub.attn.cu_q_host).max())
+                assert len(sub.prefill_sampled) == sub.n_prefill and sub.num_samples == sub.sample_rows.numel()
+                rows.append(sub.sample_rows + t0)
+                samples.append(sub.temperature)
+                seqs += sub.attn.num_seqs
+            assert seqs == full.attn.num_seqs
+            assert torch.equal(torch.cat(rows), full.sample_rows)
+            assert torch.cat(samples).numel() == full.num_samples
+        seen_partial |= not all(full.prefill_sampled)
+        sch.update(b, [7] * len(b.prefills), [7] * len(b.decodes))
+    assert seen_partial

@@ -139,6 +139,7 @@ class EngineConfig:
     seed: int = 0
     tp_comm: str = "auto"            # "auto" | "fused" | "nccl": tensor-parallel reduction path
     dp_ready_timeout_s: float = 0.0  # 0 = scale with model size
+    pp_microbatches: int = 1         # pipeline stages work on this many pieces of a step in turn (1 = lockstep)
 
     hf_config: ModelConfig = field(init=False, repr=False)
 
@@ -162,6 +163,8 @@ class EngineConfig:
             raise ValueError(f"device must be cuda|cpu, got {self.device!r}")
         if self.tp_comm not in ("auto", "fused", "nccl"):
             raise ValueError(f"tp_comm must be auto|fused|nccl, got {self.tp_comm!r}")
+        if self.pp_microbatches < 1:
+            raise ValueError("pp_microbatches must be >= 1")
         self.hf_config = load_model_config(self.model)
         if self.pp_layer_counts is not None:
             if len(self.pp_layer_counts) != self.pp_size:

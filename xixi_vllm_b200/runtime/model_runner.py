@@ -20,7 +20,7 @@ from ..utils.nvtx import nvtx_range
 from .graphs import CUDAGraphRunner, make_bs_list
 from .kv_pool import KVPool
 from .sampler import Sampler
-from .staging import BatchStager
+from .staging import BatchStager, split_forward_batch
 
 __all__ = ["ModelRunner"]
 
@@ -39,6 +39,7 @@ class ModelRunner:
         self.max_bs = config.max_num_seqs
         self.max_tokens = max(config.max_num_batched_tokens, self.max_bs)
         self.max_blocks = -(-config.context_len // self.block_size)
+        self.pp_microbatches = max(1, int(getattr(config, "pp_microbatches", 1)))
         self.stager = BatchStager(max_seqs=self.max_bs, max_tokens=self.max_tokens,
                                   max_blocks=self.max_blocks, block_size=self.block_size, device=self.device,
                                   seed=getattr(config, "seed", 0))
@@ -96,6 +97,8 @@ class ModelRunner:
         out = self.model.forward(batch.input_ids, batch, self.kv, intermediate)
         if not self.is_last_pp:
             return out
+        if batch.num_samples == 0:      # only a mid-prompt chunk: the forward wrote its KV, nothing to sample
+            return torch.empty(0, dtype=torch.int64, device=self.device)
         hidden = ops.gather_rows(out, batch.sample_rows)
         if batch.all_greedy:
             return self.model.greedy_tokens(hidden)
@@ -114,6 +117,30 @@ class ModelRunner:
     def _send(self, inter: IntermediateTensors) -> None:
         for w in send_tensors([inter["hidden_states"], inter["residual"]], group=self._pp):
             w.wait()
+
+    def _forward_microbatched(self, batch):
+        """Pipeline stages work on several pieces of the step in turn: while this stage computes piece k+1,
+        its output for piece k is already on its way and the next stage is computing it. Sends are not waited
+        for until every piece has been launched; receives land in disjoint row ranges of the hand-off buffers.
+        (The reference runs its stages in lockstep on the whole step.)"""
+        pending, pieces = [], []
+        for sub, t0, t1 in split_forward_batch(batch, self.pp_microbatches):
+            inter = None
+            if not self.is_first_pp:
+                h, r = self._pp_buf[0][t0:t1], self._pp_buf[1][t0:t1]
+                recv_tensors([h, r], group=self._pp)
+                inter = IntermediateTensors(hidden_states=h, residual=r)
+            with nvtx_range("forward"):
+                out = self._forward(sub, inter)
+            if not self.is_last_pp:
+                pending.extend(send_tensors([out["hidden_states"], out["residual"]], group=self._pp))
+            elif sub.num_samples:
+                pieces.append(out)
+        for w in pending:
+            w.wait()
+        if not self.is_last_pp:
+            return None
+        return torch.cat(pieces) if len(pieces) != 1 else pieces[0]
 
     def run_forward(self, sched) -> tuple[int, int]:
         """Launches the step (no host wait). Returns (#prefill sequences, #decode sequences)."""
@@ -135,12 +162,15 @@ class ModelRunner:
             else:
                 with nvtx_range("stage"):
                     batch = self.stager.build(sched)
-                inter = None if self.is_first_pp else self._recv(batch.num_tokens)
-                with nvtx_range("forward"):
-                    tokens = self._forward(batch, inter)
-                if not self.is_last_pp:
-                    self._send(tokens)
-                    tokens = None
+                if self.pp_microbatches > 1 and not (self.is_first_pp and self.is_last_pp):
+                    tokens = self._forward_microbatched(batch)
+                else:
+                    inter = None if self.is_first_pp else self._recv(batch.num_tokens)
+                    with nvtx_range("forward"):
+                        tokens = self._forward(batch, inter)
+                    if not self.is_last_pp:
+                        self._send(tokens)
+                        tokens = None
         self._last = (n_p, n_d, batch.prefill_sampled)
         self.h2d_bytes = self.stager.last_h2d_bytes
         if ev is not None:

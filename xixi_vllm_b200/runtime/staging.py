@@ -19,7 +19,7 @@ import torch
 
 from ..ops import hostlib
 
-__all__ = ["AttnBatch", "ForwardBatch", "BatchStager"]
+__all__ = ["AttnBatch", "ForwardBatch", "BatchStager", "split_forward_batch"]
 
 
 @dataclass
@@ -55,6 +55,55 @@ class ForwardBatch:
     n_prefill: int
     n_decode: int
     prefill_sampled: list[bool]
+
+
+def split_forward_batch(batch: ForwardBatch, parts: int) -> list[tuple[ForwardBatch, int, int]]:
+    """Cuts a staged batch into at most ``parts`` micro-batches of whole sequences with about equal token
+    counts, for pipeline stages that want several pieces of a step in flight. Returns ``(sub, t0, t1)``
+    triples: ``sub`` views rows ``t0:t1`` of the packed token arrays and the matching sequence range, with
+    its query offsets and sample rows rebased to the piece. Concatenating the pieces' samples in order gives
+    the full batch's sample order (decodes first, then the prefills that finish their prompt)."""
+    a = batch.attn
+    B = a.num_seqs
+    cu = a.cu_q_host
+    if parts <= 1 or B < 2 or cu is None:
+        return [(batch, 0, batch.num_tokens)]
+    parts = min(parts, B)
+    T = int(cu[B])
+    bounds = [0]
+    for k in range(1, parts):
+        s = int(np.searchsorted(cu[1:B + 1], T * k / parts, side="left")) + 1     # first boundary at/after the target
+        s = min(max(s, bounds[-1] + 1), B - (parts - k))                           # every piece keeps a sequence
+        bounds.append(s)
+    bounds.append(B)
+    n_d = a.num_decode
+    # samples before each sequence: every decode row samples, a prefill only when it finishes its prompt
+    flags = [1] * n_d + [1 if f else 0 for f in batch.prefill_sampled]
+    flags += [0] * (B - len(flags))
+    before = np.concatenate(([0], np.cumsum(flags)))
+    out: list[tuple[ForwardBatch, int, int]] = []
+    kv_host = a.kv_lens_host
+    for s0, s1 in zip(bounds[:-1], bounds[1:]):
+        if s1 <= s0:
+            continue
+        t0, t1 = int(cu[s0]), int(cu[s1])
+        r0, r1 = int(before[s0]), min(int(before[s1]), batch.num_samples)
+        q_lens = np.diff(cu[s0:s1 + 1])
+        sub_attn = AttnBatch(cu_q=a.cu_q[s0:s1 + 1] - t0, kv_lens=a.kv_lens[s0:s1], block_tables=a.block_tables[s0:s1],
+                             num_seqs=s1 - s0, num_decode=max(0, min(n_d, s1) - s0),
+                             max_q_len=int(q_lens.max()) if q_lens.size else 1,
+                             max_kv_len=int(kv_host[s0:s1].max()) if kv_host is not None else a.max_kv_len,
+                             num_tokens=t1 - t0, cu_q_host=cu[s0:s1 + 1] - t0,
+                             kv_lens_host=kv_host[s0:s1] if kv_host is not None else None)
+        n_dec = sub_attn.num_decode
+        sub = ForwardBatch(input_ids=batch.input_ids[t0:t1], positions=batch.positions[t0:t1], slots=batch.slots[t0:t1],
+                           attn=sub_attn, sample_rows=batch.sample_rows[r0:r1] - t0,
+                           temperature=batch.temperature[r0:r1], top_k=batch.top_k[r0:r1], top_p=batch.top_p[r0:r1],
+                           min_p=batch.min_p[r0:r1], rng=batch.rng, num_tokens=t1 - t0, num_samples=r1 - r0,
+                           all_greedy=batch.all_greedy, n_prefill=(s1 - s0) - n_dec, n_decode=n_dec,
+                           prefill_sampled=batch.prefill_sampled[max(0, s0 - n_d):max(0, s1 - n_d)])
+        out.append((sub, t0, t1))
+    return out
 
 
 class BatchStager:

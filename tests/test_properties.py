@@ -44,7 +44,7 @@ request = st.tuples(st.integers(1, 70),          # prompt length
                     st.booleans())               # ignore_eos
 
 
-@settings(max_examples=120, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@settings(max_examples=150, deadline=None, suppress_health_check=[HealthCheck.too_slow])
 @given(reqs=st.lists(request, min_size=1, max_size=10),
        num_blocks=st.integers(6, 40), max_seqs=st.integers(1, 6), budget=st.integers(8, 96),
        mix=st.booleans(), backend=st.sampled_from(["none", "hash", "radix"]), seed=st.integers(0, 1000),

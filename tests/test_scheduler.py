@@ -112,6 +112,43 @@ def test_preemption_recomputes_and_output_is_complete():
     assert a.num_completion_tokens == 40 and b.num_completion_tokens == 40
 
 
+def _drain(sch, kv, limit=2000):
+    steps = 0
+    while not sch.is_finished():
+        run_step(sch)
+        kv.blocks.check_invariants()
+        steps += 1
+        assert steps < limit, "the scheduler makes no progress"
+    return steps
+
+
+def test_decode_out_of_pages_takes_them_from_a_half_prefilled_prompt():
+    """A decoding sequence that needs one more page while a later prompt, cut into chunks, holds the rest of
+    the pool: the prompt gives its pages back. (Preempting the decoding sequence instead queued it in front
+    of the prompt and restarted it with the pages still missing, forever.)"""
+    sch, kv = make(num_blocks=14, max_seqs=2, budget=8)
+    a, b = req(105, max_tokens=9, ignore_eos=True), req(97, max_tokens=0)
+    sch.add(a)
+    run_step(sch)
+    sch.add(b)
+    _drain(sch, kv)
+    assert a.num_completion_tokens == 9 and b.is_finished and kv.blocks.num_used == 0
+
+
+def test_blocked_prompt_does_not_stop_a_later_prompt_that_already_holds_pages():
+    """Queue [page-less prompt that does not fit, half-prefilled prompt holding pages]: the second one must
+    still be scheduled, otherwise both wait for each other until the idle guard fires."""
+    sch, kv = make(num_blocks=8, max_seqs=4, budget=16)
+    big, held = req(100, max_tokens=2, ignore_eos=True), req(60, max_tokens=2, ignore_eos=True)
+    sch.add(held)
+    run_step(sch)                                   # first 16-token chunk of `held`: it now owns 4 pages
+    assert held.block_table and not held.is_finished
+    sch.waiting.appendleft(big)                     # a preempted sequence is re-queued at the front like this
+    big.status = SequenceStatus.WAITING
+    _drain(sch, kv)
+    assert big.num_completion_tokens == 2 and held.num_completion_tokens == 2
+
+
 def test_released_ids_reach_the_wire():
     sch, _ = make()
     s = req(5, max_tokens=1, ignore_eos=True)

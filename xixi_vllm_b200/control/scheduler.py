@@ -95,6 +95,12 @@ class Scheduler:
             while not self.kv.can_append(seq) and run:
                 self.preempt(run.pop())
             if not self.kv.can_append(seq):
+                # Nobody left to preempt among the running sequences: a half-prefilled prompt in the waiting
+                # queue may still be sitting on pages. It arrived later than anything that is decoding, so it
+                # gives them back and starts over; preempting `seq` instead would put it in front of that
+                # prompt, restart it with the pages still missing, and repeat forever.
+                self._reset_partial_prefills()
+            if not self.kv.can_append(seq):
                 self.preempt(seq)
                 break
             seq.num_scheduled_tokens = 1
@@ -106,6 +112,7 @@ class Scheduler:
         return used
 
     def _take_prefills(self, prefills, decodes, used: int, *, allow_trailing_partial: bool) -> int:
+        blocked = False
         for seq in list(self.waiting):
             if not self._has_room(prefills, decodes):
                 break
@@ -113,8 +120,15 @@ class Scheduler:
             if budget <= 0:
                 break
             if not seq.block_table:
+                # First come, first served: once a prompt does not fit, no later prompt may take pages ahead
+                # of it. A prompt further back that already holds its pages (it was cut into chunks and a
+                # preempted sequence was queued in front of it) must still be allowed to finish, or the two
+                # would wait for each other.
+                if blocked:
+                    continue
                 if not self.kv.can_allocate(seq):
-                    break
+                    blocked = True
+                    continue
                 self.kv.allocate(seq)
             need = seq.num_tokens - seq.num_cached_tokens
             if need <= 0:   # nothing to compute (cannot happen with the last-page rule, kept as a guard)
@@ -133,6 +147,15 @@ class Scheduler:
                 seq.need_sample = False
                 break   # one partial chunk per step
         return used
+
+    def _reset_partial_prefills(self) -> None:
+        """Takes the pages back from waiting sequences that hold some (prompts cut into chunks); they keep
+        their place in the queue and recompute from their first token."""
+        for w in self.waiting:
+            if w.block_table:
+                self.kv.deallocate(w, publish=False)
+                self._released.append(w.seq_id)
+                self.num_preemptions += 1
 
     def _promote(self, seq: Sequence) -> None:
         seq.status = SequenceStatus.RUNNING

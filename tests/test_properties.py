@@ -123,3 +123,48 @@ def test_hash_and_radix_backends_report_the_same_hits(prompts, seed):
             kv.deallocate(s)
             kv.blocks.check_invariants()
         assert hits["hash"] == hits["radix"]
+
+
+op = st.one_of(
+    st.tuples(st.just("insert"), st.lists(st.integers(0, 3), min_size=1, max_size=8)),
+    st.tuples(st.just("match"), st.lists(st.integers(0, 3), min_size=0, max_size=9)),
+    st.tuples(st.just("evict"), st.integers(1, 6)),
+)
+
+
+@settings(max_examples=300, deadline=None)
+@given(ops=st.lists(op, min_size=1, max_size=40))
+def test_radix_tree_behaves_like_a_prefix_dictionary(ops):
+    """Model: a dict from every stored key prefix to the value first stored for it. Matching returns the
+    values along the longest stored prefix; eviction only ever removes prefixes nothing longer hangs on."""
+    from xixi_vllm_b200.data.prefix.radix_tree import RadixTree
+    tree, model, fresh = RadixTree(), {}, iter(range(10 ** 6))
+    for kind, arg in ops:
+        if kind == "insert":
+            vals = [next(fresh) for _ in arg]
+            known = 0
+            while known < len(arg) and tuple(arg[:known + 1]) in model:
+                known += 1
+            matched, _ = tree.insert(arg, vals)
+            assert matched == known
+            for i in range(known, len(arg)):
+                model[tuple(arg[:i + 1])] = vals[i]
+        elif kind == "match":
+            want = []
+            for i in range(len(arg)):
+                if tuple(arg[:i + 1]) not in model:
+                    break
+                want.append(model[tuple(arg[:i + 1])])
+            assert tree.match_prefix(arg)[0] == want
+        else:
+            freed = set(tree.evict(arg))
+            assert len(freed) <= max(arg, 0) + 8            # whole edges go at once, never the whole tree by accident
+            gone = [p for p, v in model.items() if v in freed]
+            assert len(gone) == len(freed)
+            for p in gone:
+                del model[p]
+            for p in model:                                  # what is left is still closed under taking prefixes
+                assert all(p[:i] in model for i in range(1, len(p)))
+        for v in model.values():
+            assert tree.contains_block(v)
+    assert sum(1 for _ in model) == sum(1 for v in set(model.values()))

@@ -82,6 +82,7 @@ def test_any_schedule_yields_the_models_tokens(reqs, num_blocks, max_seqs, budge
         d_ids = [fake_model(s.token_ids) for s in batch.decodes]
         sch.update(batch, p_ids, d_ids)
         kv.blocks.check_invariants()
+        assert sch._holders == sum(1 for w in sch.waiting if w.block_table)
         steps += 1
         assert steps < 5000, "the workload does not terminate"
     for seq, prompt, max_tokens, ignore_eos in pending:

@@ -38,6 +38,7 @@ class Scheduler:
         self._step = 0
         self.num_preemptions = 0
         self.num_sampled = 0
+        self._holders = 0          # waiting sequences that hold pages (prompts in the middle of their chunks)
 
     def is_finished(self) -> bool:
         return not self.waiting and not self.running
@@ -124,12 +125,13 @@ class Scheduler:
                 # of it. A prompt further back that already holds its pages (it was cut into chunks and a
                 # preempted sequence was queued in front of it) must still be allowed to finish, or the two
                 # would wait for each other.
-                if blocked:
-                    continue
-                if not self.kv.can_allocate(seq):
+                if blocked or not self.kv.can_allocate(seq):
                     blocked = True
+                    if self._holders == 0:        # nobody further back holds pages: nothing else can run
+                        break
                     continue
                 self.kv.allocate(seq)
+                self._holders += 1
             need = seq.num_tokens - seq.num_cached_tokens
             if need <= 0:   # nothing to compute (cannot happen with the last-page rule, kept as a guard)
                 self._promote(seq)
@@ -156,8 +158,10 @@ class Scheduler:
                 self.kv.deallocate(w, publish=False)
                 self._released.append(w.seq_id)
                 self.num_preemptions += 1
+                self._holders -= 1
 
     def _promote(self, seq: Sequence) -> None:
+        self._holders -= 1
         seq.status = SequenceStatus.RUNNING
         self.waiting.remove(seq)
         self.running.append(seq)

@@ -65,6 +65,9 @@ def parse_args():
     ap.add_argument("--emulate-tp", type=int, default=1,
                     help="single GPU, model dimensions cut to one rank's shard of this tensor-parallel degree "
                          "(compute share of a rank without any communication; diagnostic, not a benchmark)")
+    ap.add_argument("--pp", type=int, default=1,
+                    help="pipeline stages (must divide --gpus; the rest is tensor parallel). The headline is tp = gpus")
+    ap.add_argument("--pp-microbatches", type=int, default=1, help="pieces of a step the stages work on in turn")
     ap.add_argument("--profile", action="store_true",
                     help="bracket the timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     return ap.parse_args()
@@ -190,7 +193,8 @@ def run_ours(args) -> None:
     cfg_kwargs = dict(model=model_dir, load_format="dummy", dtype="bfloat16", context_len=context,
                       max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_batched_tokens,
                       kvcache_block_size=16, prefix_backend="none", enforce_eager=args.eager,
-                      tp_size=args.gpus, seed=args.seed, gpu_memory_utilization=0.9, tp_comm=args.tp_comm)
+                      tp_size=args.gpus // args.pp, pp_size=args.pp, pp_microbatches=args.pp_microbatches,
+                      seed=args.seed, gpu_memory_utilization=0.9, tp_comm=args.tp_comm)
     # rank 0 writes config.json before the others read it
     if world > 1:
         import torch.distributed as dist  # noqa: F401
@@ -260,7 +264,8 @@ def run_ours(args) -> None:
         "higher_is_better": True, "scaling": "strong", "vs_baseline": baseline_number(), "dtype": "bf16",
         "data": "synthetic (random-init weights, uniform random token prompts)", "impl": "ours",
         "config": {"model": args.model, "global_batch": args.max_num_seqs, "seq_len": context,
-                   "parallelism": f"tp{args.gpus}", "prompt_len": f"U[{args.prompt_min},{args.prompt_max}]",
+                   "parallelism": (f"tp{args.gpus}" if args.pp == 1 else
+                                   f"tp{args.gpus // args.pp}pp{args.pp}mb{args.pp_microbatches}"), "prompt_len": f"U[{args.prompt_min},{args.prompt_max}]",
                    "output_len": args.out_tokens, "max_num_batched_tokens": args.max_batched_tokens,
                    "kv_block_size": 16, "decode_cuda_graph": not args.eager, "tp_comm": args.tp_comm,
                    **({"emulate_tp_shard": args.emulate_tp} if args.emulate_tp > 1 else {}),

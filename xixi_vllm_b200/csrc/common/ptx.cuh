@@ -48,7 +48,8 @@ __device__ __forceinline__ bool elect_one() {
 // Compiled out by default: with the trigger at the top of every kernel a decode step of a
 // tensor-parallel shard (about 400 kernels of 4-35 us) ran 4 % slower than without programmatic
 // launch, while the launch attribute alone (the dependent kernel starts when the last block of this
-// one exits, its launch latency already paid) ran 4 % faster. Build with -DXV_PDL_TRIGGER=1 to try it.
+// one exits, its launch latency already paid) ran 4 % faster. A trigger placed late, after a GEMM CTA's
+// last load, was also slower (6.08 against 5.85 ms per step). Build with -DXV_PDL_TRIGGER=1 to try it.
 #ifndef XV_PDL_TRIGGER
 #define XV_PDL_TRIGGER 0
 #endif

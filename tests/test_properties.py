@@ -169,3 +169,45 @@ def test_radix_tree_behaves_like_a_prefix_dictionary(ops):
         for v in model.values():
             assert tree.contains_block(v)
     assert sum(1 for _ in model) == sum(1 for v in set(model.values()))
+
+
+_isolated: dict = {}
+
+
+@settings(max_examples=12, deadline=None, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@given(lens=st.lists(st.integers(1, 70), min_size=2, max_size=6), shared=st.integers(0, 40),
+       blocks=st.integers(8, 24), budget=st.integers(16, 64), max_seqs=st.integers(1, 4),
+       backend=st.sampled_from(["none", "hash", "radix"]), new=st.integers(1, 6))
+def test_engine_output_of_a_request_does_not_depend_on_its_neighbours(tiny_model_dir, lens, shared, blocks, budget,
+                                                                     max_seqs, backend, new):
+    """The whole CPU engine (scheduler, page ledger, prefix caches, staging with persistent block-table rows,
+    paged oracle attention): under any pool size, token budget and prefix backend, with chunked prefills and
+    preemptions, each request generates exactly what it generates when it runs alone in a roomy engine."""
+    import torch
+
+    from xixi_vllm_b200 import Engine, EngineConfig, SamplingParams
+    g = torch.Generator().manual_seed(shared * 131 + len(lens))
+    common = torch.randint(0, 1024, (shared,), generator=g).tolist()
+    prompts = [common + torch.randint(0, 1024, (n,), generator=g).tolist() for n in lens]
+    need = max(-(-(len(p) + new) // 16) for p in prompts)
+
+    def run(ps, **kw):
+        eng = Engine(EngineConfig(model=tiny_model_dir, device="cpu", dtype="float32", context_len=256, **kw))
+        try:
+            seqs = [eng.add_request(p, SamplingParams(max_tokens=new, ignore_eos=True)) for p in ps]
+            while eng.has_unfinished():
+                eng.step()
+            return [s.token_ids[s.num_prompt_tokens:] for s in seqs]
+        finally:
+            eng.destroy()
+
+    want = []
+    for p in prompts:
+        key = (tuple(p), new)
+        if key not in _isolated:
+            _isolated[key] = run([p], num_kvcache_blocks=64, max_num_seqs=1, max_num_batched_tokens=256,
+                                 prefix_backend="none")[0]
+        want.append(_isolated[key])
+    got = run(prompts, num_kvcache_blocks=max(blocks, need), max_num_seqs=max_seqs, max_num_batched_tokens=budget,
+              prefix_backend=backend)
+    assert got == want

@@ -722,7 +722,13 @@ static int gemm_plan_impl(int m, int n, int k, int num_sms, XvGemmPlan* plan, bo
     pl.tiles_b = (n + pl.bn - 1) / pl.bn;
     // CTA pairs (256 x 256 tiles) once there are enough of them to occupy every SM pair
     const int pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
-    if (n >= 256 && pair_tiles >= num_sms / 2 && allow_pair) {
+    // Both kernels are persistent with one tile (pair) per SM (pair): time goes in whole waves. A 256 x 256
+    // pair tile takes about 0.88 of the time of a 128 x 256 single tile (measured: 35 us against 39 us at
+    // K = 4096), so the pair kernel wins unless it needs more waves, e.g. M = 1100, N = 4096: 80 pair tiles on
+    // 74 pairs are two waves, 144 single tiles on 148 SMs one (measured 156 us against 109 us).
+    const int pair_waves = (pair_tiles + num_sms / 2 - 1) / (num_sms / 2);
+    const int single_waves = (pl.tiles_a * pl.tiles_b + num_sms - 1) / num_sms;
+    if (n >= 256 && pair_tiles >= num_sms / 2 && allow_pair && pair_waves * 0.88 <= single_waves) {
       pl.pair = 1;
       pl.bn = 256;
       pl.tiles_a = (m + 255) / 256;

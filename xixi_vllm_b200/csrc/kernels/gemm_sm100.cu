@@ -720,28 +720,6 @@ static int gemm_plan_impl(int m, int n, int k, int num_sms, XvGemmPlan* plan, bo
     pl.bn = n >= 256 ? 256 : round_up(n, 16);
     pl.tiles_a = (m + kBM - 1) / kBM;
     pl.tiles_b = (n + pl.bn - 1) / pl.bn;
-    // CTA pairs (256 x 256 tiles) once there are enough of them to occupy every SM pair
-    const int pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
-    // Both kernels are persistent with one tile (pair) per SM (pair): time goes in whole waves. A 256 x 256
-    // pair tile takes about 0.88 of the time of a 128 x 256 single tile (measured: 35 us against 39 us at
-    // K = 4096), so the pair kernel wins unless it needs more waves, e.g. M = 1100, N = 4096: 80 pair tiles on
-    // 74 pairs are two waves, 144 single tiles on 148 SMs one (measured 156 us against 109 us).
-    const int pair_waves = (pair_tiles + num_sms / 2 - 1) / (num_sms / 2);
-    const int single_waves = (pl.tiles_a * pl.tiles_b + num_sms - 1) / num_sms;
-    if (n >= 256 && pair_tiles >= num_sms / 2 && allow_pair && pair_waves * 0.88 <= single_waves) {
-      pl.pair = 1;
-      pl.bn = 256;
-      pl.tiles_a = (m + 255) / 256;
-      pl.tiles_b = (n + 255) / 256;
-      pl.splits = 1;
-      pl.k_blocks_per_split = total_kb;
-      pl.stages = kPairStages;
-      pl.smem_bytes = kPairSmem;
-      pl.ctas_per_sm = 1;
-      pl.workspace_bytes = 0;
-      *plan = pl;
-      return 0;
-    }
   }
   const int tiles = pl.tiles_a * pl.tiles_b;
   const int stage_bytes = kBM * kBK * 2 + pl.bn * kBK * 2;
@@ -782,6 +760,30 @@ static int gemm_plan_impl(int m, int n, int k, int num_sms, XvGemmPlan* plan, bo
   pl.stages = stages;
   pl.smem_bytes = stages * stage_bytes + 1024 + 256;
   pl.workspace_bytes = pl.splits > 1 ? static_cast<long long>(pl.splits) * m * n * 4 : 0;
+  // CTA pairs (256 x 256 tiles, cta_group::2) instead of the plan above? Both kernels are persistent with one
+  // tile per SM (pair of SMs), so time goes in whole waves, and a pair tile takes about 0.88 of the time of a
+  // 128 x 256 tile (measured: 35 us against 39 us at K = 4096). Pairs win unless they need more waves
+  // (M = 1100, N = 4096: 80 pair tiles on 74 pairs are two waves, 144 single tiles on 148 SMs one: measured 156
+  // against 109 us). With fewer pair tiles than SM pairs they still win by 5-13 % (M = 384..832, N = 4096 or 6144)
+  // as long as the single-CTA plan would not split K; where it does (M <= 512 with K = 12288), split-K is faster.
+  if (!pl.swapped && allow_pair && n >= 256) {
+    const int pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
+    const int pair_waves = (pair_tiles + num_sms / 2 - 1) / (num_sms / 2);
+    const int single_waves = (tiles + num_sms - 1) / num_sms;
+    const bool enough = pair_tiles >= num_sms / 2 || (pl.splits == 1 && pair_tiles >= 24);
+    if (enough && pair_waves * 0.88 <= single_waves) {
+      pl.pair = 1;
+      pl.bn = 256;
+      pl.tiles_a = (m + 255) / 256;
+      pl.tiles_b = (n + 255) / 256;
+      pl.splits = 1;
+      pl.k_blocks_per_split = total_kb;
+      pl.stages = kPairStages;
+      pl.smem_bytes = kPairSmem;
+      pl.ctas_per_sm = 1;
+      pl.workspace_bytes = 0;
+    }
+  }
   *plan = pl;
   return 0;
 }

@@ -156,7 +156,7 @@ def emit(record: dict) -> None:
 
 
 def baseline_number():
-    """BASELINE.md publishes no number for this metric, so vs_baseline is null."""
+    """The reference publishes no number for this metric and configuration, so vs_baseline is null."""
     return None
 
 
@@ -292,7 +292,7 @@ def run_ours(args) -> None:
 def run_reference(args) -> None:
     ref_root = os.path.join(ROOT, "baseline")
     if not os.path.isfile(os.path.join(ref_root, "_ref", "control", "engine.py")):
-        emit({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --target install of /root/reference)"})
+        emit({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --target install of the reference package)"})
         return
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:

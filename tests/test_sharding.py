@@ -163,3 +163,41 @@ def test_pp_indices_and_helpers():
         divide(10, 4)
     x = torch.ones(2)
     assert PPMissingLayer()(x) is x
+
+
+def _ctl_rank(rank, world, use_shm):
+    """Driver broadcasts more messages than the ring has slots, one larger than a slot, then a sentinel."""
+    import torch.distributed as dist
+
+    from xixi_vllm_b200.parallel.control_channel import ControlChannel
+    from xixi_vllm_b200.parallel.groups import get_world_group
+    ch = ControlChannel(get_world_group().cpu_group, shm=use_shm)
+    msgs = [bytes([i % 251]) * (1 + 37 * i) for i in range(40)] + [b"x" * ((1 << 20) + 5), b"", b"end"]
+    got = []
+    for m in msgs:
+        got.append(ch.broadcast(m if rank == 0 else None, src=0))
+    # point-to-point replies still work next to the ring
+    if rank == 1:
+        ch.send(b"reply", dst=0)
+    reply = ch.recv(1) if rank == 0 else None
+    dist.barrier(group=get_world_group().cpu_group)
+    shared = ch.uses_shared_memory
+    ch.close()
+    return got == msgs, shared, reply
+
+
+def test_control_channel_ring_and_gloo_paths_deliver_the_same_messages():
+    import os
+
+    from dist_utils import run_ranks
+    before = {f for f in os.listdir("/dev/shm") if f.startswith("xv_ctl_")} if os.path.isdir("/dev/shm") else set()
+    for use_shm in (True, False):
+        res = run_ranks(_ctl_rank, world=3, tp=3, args=(use_shm,))
+        assert all(ok for ok, _, _ in res)
+        assert res[0][2] == b"reply"
+        if use_shm and os.path.isdir("/dev/shm"):
+            assert all(shared for _, shared, _ in res)
+        if not use_shm:
+            assert not any(shared for _, shared, _ in res)
+    after = {f for f in os.listdir("/dev/shm") if f.startswith("xv_ctl_")} if os.path.isdir("/dev/shm") else set()
+    assert after <= before            # the driver removed its ring file

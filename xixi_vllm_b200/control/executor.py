@@ -108,6 +108,7 @@ def worker_loop(worker) -> None:
     while True:
         cmd = dec.decode(channel.broadcast(None, src=0))
         if cmd.op == "shutdown":
+            channel.close()
             return
         if cmd.op == "reset_kv":
             worker.reset_kv(cmd.prefix_backend)
@@ -272,7 +273,10 @@ class MultiprocExecutor(Executor):
             for p in self._procs:
                 p.join(timeout=10)
             _terminate_procs(self._procs)
+            self._channel.close()
             self.worker.destroy_environment()
+        else:
+            self._channel.close()      # ranks started externally: only the shared-memory ring is ours to drop
         self.kv = None
 
 

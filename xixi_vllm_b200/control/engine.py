@@ -106,6 +106,14 @@ class Engine:
         outputs, metric = self._client.step()
         mirror = not isinstance(self._client, InprocClient)
         finished: list[tuple[int, list[int]]] = []
+        if not mirror:
+            # in-process core: the Sequence objects are shared and already up to date; only ends matter
+            for out in outputs:
+                if out.is_finished:
+                    seq = self._seqs.pop(out.seq_id, None)
+                    if seq is not None:
+                        finished.append((out.seq_id, seq.token_ids[seq.num_prompt_tokens:]))
+            return finished, metric
         for out in outputs:
             seq = self._seqs.get(out.seq_id)
             if seq is None:

@@ -181,7 +181,7 @@ class Scheduler:
         out: list[EngineCoreOutput] = []
         done: set[int] = set()
         if sched.decodes:
-            self._apply(sched.decodes, d_ids, False, out, done)
+            self._apply_decodes(sched.decodes, d_ids, out, done)
         if sched.prefills:
             self._apply(sched.prefills, p_ids, True, out, done)
         if done:
@@ -193,6 +193,29 @@ class Scheduler:
         seq.status = SequenceStatus.FINISHED
         self.kv.deallocate(seq, publish=True)
         done.add(seq.seq_id)
+
+    def _apply_decodes(self, seqs, token_ids, out, done: set[int]) -> None:
+        """``_apply`` for decode rows (one scheduled token, always sampled, ``max_tokens`` >= 2): the loop runs
+        once per running sequence per step, so it keeps to the few operations a decode row needs."""
+        publish = self.kv.prefix_backend != "none"
+        sync = self.kv.sync_prefix
+        eos = self.eos
+        make = EngineCoreOutput
+        emit = out.append
+        for seq, tok in zip(seqs, token_ids):
+            seq.num_cached_tokens += seq.num_scheduled_tokens
+            if publish:
+                sync(seq)
+            seq.num_scheduled_tokens = 0
+            ids = seq.token_ids
+            ids.append(tok)
+            seq.last_token = tok
+            if (tok == eos and not seq.ignore_eos) or len(ids) - seq.num_prompt_tokens >= seq.max_tokens:
+                self._finish(seq, done)
+                emit(make(seq_id=seq.seq_id, new_token_ids=[tok], is_finished=True))
+            else:
+                emit(make(seq_id=seq.seq_id, new_token_ids=[tok]))
+        self.num_sampled += len(seqs)
 
     def _apply(self, seqs, token_ids, is_prefill: bool, out, done: set[int]) -> None:
         publish = self.kv.prefix_backend != "none"

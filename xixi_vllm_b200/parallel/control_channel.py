@@ -113,27 +113,35 @@ class _ShmRing:
         seq = self.seq + 1
         off = self._slot(seq)
         cell = off // 8
-        spins = 0
-        waited_since = None
-        while self.q[cell] != seq:
-            spins += 1
-            if spins < 4000:
-                continue
-            if spins < 20000:
-                time.sleep(0)
-                continue
-            time.sleep(0.0002)
-            now = time.monotonic()
-            if waited_since is None:
-                waited_since = now
-            elif now - waited_since > 1.0:
-                waited_since = now
-                try:
-                    os.kill(self.driver_pid(), 0)
-                except ProcessLookupError:
-                    raise RuntimeError("the driver process is gone; leaving the control loop") from None
-                except PermissionError:
-                    pass
+        # Poll hot while the engine is busy (a step takes 5-30 ms and every rank's launch waits for this
+        # message), yield the core between bursts, and back off to short sleeps only when nothing has come
+        # for a while, so an idle engine costs next to nothing.
+        q = self.q
+        t0 = 0.0
+        last_check = 0.0
+        while q[cell] != seq:
+            for _ in range(256):
+                if q[cell] == seq:
+                    break
+            else:
+                now = time.monotonic()
+                if not t0:
+                    t0 = last_check = now
+                idle = now - t0
+                if idle < 0.05:
+                    os.sched_yield()
+                elif idle < 2.0:
+                    time.sleep(0.0002)
+                else:
+                    time.sleep(0.001)
+                if now - last_check > 1.0:
+                    last_check = now
+                    try:
+                        os.kill(self.driver_pid(), 0)
+                    except ProcessLookupError:
+                        raise RuntimeError("the driver process is gone; leaving the control loop") from None
+                    except PermissionError:
+                        pass
         self._barrier()
         n = self.q[cell + 1]
         out = (None, n) if n & _VIA_GLOO else (bytes(self.map[off + _HDR: off + _HDR + n]), 0)

@@ -171,15 +171,25 @@ def _ctl_rank(rank, world, use_shm):
 
     from xixi_vllm_b200.parallel.control_channel import ControlChannel
     from xixi_vllm_b200.parallel.groups import get_world_group
-    ch = ControlChannel(get_world_group().cpu_group, shm=use_shm)
+    ch = ControlChannel(get_world_group().cpu_group, shm=use_shm, reply_from=1)
     msgs = [bytes([i % 251]) * (1 + 37 * i) for i in range(40)] + [b"x" * ((1 << 20) + 5), b"", b"end"]
     got = []
     for m in msgs:
         got.append(ch.broadcast(m if rank == 0 else None, src=0))
     # point-to-point replies still work next to the ring
+    # replies of the designated rank (ring of its own towards rank 0), small, empty and larger than a slot
+    replies = [b"reply", b"", b"y" * ((1 << 20) + 9)] + [bytes([i]) * 100 for i in range(20)]
     if rank == 1:
-        ch.send(b"reply", dst=0)
-    reply = ch.recv(1) if rank == 0 else None
+        for m in replies:
+            ch.send(m, dst=0)
+    reply = None
+    if rank == 0:
+        reply = b"reply" if [ch.recv(1) for _ in replies] == replies else b"mismatch"
+    # any other pair still talks over gloo
+    if rank == 2:
+        ch.send(b"side", dst=0)
+    if rank == 0:
+        assert ch.recv(2) == b"side"
     dist.barrier(group=get_world_group().cpu_group)
     shared = ch.uses_shared_memory
     ch.close()

@@ -101,10 +101,10 @@ def _spawn_worker(config: EngineConfig, rank: int, tp_rank: int, pp_rank: int, r
 
 def worker_loop(worker) -> None:
     """Ranks >= 1: wait for broadcast commands until ``shutdown``."""
-    channel = ControlChannel(get_world_group().cpu_group)
+    sampler_rank = _sampler_rank(worker.tp_size, worker.pp_size)
+    channel = ControlChannel(get_world_group().cpu_group, reply_from=sampler_rank)
     enc = msgspec.msgpack.Encoder()
     dec = msgspec.msgpack.Decoder(ControlCommand)
-    sampler_rank = _sampler_rank(worker.tp_size, worker.pp_size)
     while True:
         cmd = dec.decode(channel.broadcast(None, src=0))
         if cmd.op == "shutdown":
@@ -184,7 +184,7 @@ class MultiprocExecutor(Executor):
             worker = self._spawn_world()
         self.worker = worker
         self.num_blocks = worker.get_kv_cache_size()
-        self._channel = ControlChannel(get_world_group().cpu_group)
+        self._channel = ControlChannel(get_world_group().cpu_group, reply_from=self.sampler_rank)
 
     def _spawn_world(self):
         import torch.distributed as dist

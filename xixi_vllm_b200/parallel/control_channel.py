@@ -10,7 +10,9 @@ all ranks share a host the broadcast therefore goes through a single-writer ring
 (a file under /dev/shm mapped by every rank): the driver copies the bytes into the next slot and
 publishes a sequence number, the workers poll for it (busy first, then yielding, then sleeping, so
 idle engines cost next to nothing) and acknowledge, which is what lets the driver reuse slots.
-Messages larger than a slot, hosts without /dev/shm and multi-node groups use the gloo path.
+The rank that answers the driver every step (the sampler rank of a pipeline) gets a second ring of its
+own towards rank 0. Messages larger than a slot, other point-to-point pairs, hosts without /dev/shm
+and multi-node groups use the gloo path.
 ``XV_CTL_SHM=0`` disables the ring.
 """
 
@@ -39,8 +41,11 @@ _VIA_GLOO = (1 << 63)              # length marker: this message follows on the 
 class _ShmRing:
     """Single-writer, many-reader message ring in a shared mapping."""
 
-    def __init__(self, path: str, world: int, rank: int, create: bool) -> None:
+    def __init__(self, path: str, world: int, rank: int, create: bool, writer: int = 0,
+                 readers: list[int] | None = None) -> None:
         self.path, self.world, self.rank, self.owner = path, world, rank, create
+        self.writer = writer
+        self.readers = readers if readers is not None else [r for r in range(world) if r != writer]
         self.slots_off = _ACK_OFF + 64 * world
         size = self.slots_off + _SLOTS * (_HDR + _SLOT_BYTES)
         flags = os.O_RDWR | (os.O_CREAT | os.O_EXCL if create else 0)
@@ -55,10 +60,11 @@ class _ShmRing:
         self.seq = 0                                     # last message written (driver) / read (worker)
         self._fence = threading.Lock()
         if create:
-            struct.pack_into("<Q", self.map, 0, os.getpid())
             atexit.register(self._unlink)            # a driver that exits without close() leaves no file behind
-        else:
-            self.q[(_ACK_OFF + 64 * rank) // 8 + 1] = os.getpid()     # lets the driver notice a dead reader
+        if rank == writer:
+            struct.pack_into("<Q", self.map, 0, os.getpid())          # lets readers notice a dead writer
+        elif rank in self.readers:
+            self.q[(_ACK_OFF + 64 * rank) // 8 + 1] = os.getpid()     # lets the writer notice a dead reader
 
     def _barrier(self) -> None:
         # a lock round trip orders this thread's earlier stores before its later ones on any CPU
@@ -68,7 +74,7 @@ class _ShmRing:
     def _slot(self, seq: int) -> int:
         return self.slots_off + (seq % _SLOTS) * (_HDR + _SLOT_BYTES)
 
-    def driver_pid(self) -> int:
+    def writer_pid(self) -> int:
         return struct.unpack_from("<Q", self.map, 0)[0]
 
     # --- driver ------------------------------------------------------------------------------
@@ -78,7 +84,7 @@ class _ShmRing:
             need = seq - _SLOTS
             spins = 0
             checked = time.monotonic()
-            while min(self.q[(_ACK_OFF + 64 * r) // 8] for r in range(1, self.world)) < need:
+            while min(self.q[(_ACK_OFF + 64 * r) // 8] for r in self.readers) < need:
                 spins += 1
                 if spins > 2000:
                     time.sleep(0.0001)
@@ -96,14 +102,14 @@ class _ShmRing:
         self.seq = seq
 
     def _check_readers(self, need: int) -> None:
-        for r in range(1, self.world):
+        for r in self.readers:
             cell = (_ACK_OFF + 64 * r) // 8
             pid = self.q[cell + 1]
             if self.q[cell] < need and pid:
                 try:
                     os.kill(pid, 0)
                 except ProcessLookupError:
-                    raise RuntimeError(f"worker rank {r} (pid {pid}) is gone with control messages unread") from None
+                    raise RuntimeError(f"rank {r} (pid {pid}) is gone with control messages unread") from None
                 except PermissionError:
                     pass
 
@@ -136,10 +142,12 @@ class _ShmRing:
                     time.sleep(0.001)
                 if now - last_check > 1.0:
                     last_check = now
+                    pid = self.writer_pid()
                     try:
-                        os.kill(self.driver_pid(), 0)
+                        if pid:
+                            os.kill(pid, 0)
                     except ProcessLookupError:
-                        raise RuntimeError("the driver process is gone; leaving the control loop") from None
+                        raise RuntimeError("the sending process is gone; leaving the control loop") from None
                     except PermissionError:
                         pass
         self._barrier()
@@ -166,11 +174,15 @@ class _ShmRing:
 
 
 class ControlChannel:
-    def __init__(self, cpu_group, shm: bool | None = None) -> None:
+    def __init__(self, cpu_group, shm: bool | None = None, reply_from: int = 0) -> None:
         """Collective when shared memory is enabled: every rank of the group constructs its channel at
-        the same point (the driver after its workers are up, the workers when they enter their loop)."""
+        the same point (the driver after its workers are up, the workers when they enter their loop).
+        ``reply_from``: the rank whose ``send(..., dst=0)`` answers the driver every step (the sampler rank
+        of a pipeline); it gets a ring of its own towards rank 0. 0 = no such rank."""
         self.group = cpu_group
+        self.reply_from = reply_from
         self._ring: _ShmRing | None = None
+        self._reply: _ShmRing | None = None
         if shm is None:
             shm = os.environ.get("XV_CTL_SHM", "1") != "0"
         world = dist.get_world_size(group=cpu_group)
@@ -180,13 +192,19 @@ class ControlChannel:
     def _setup_ring(self, world: int) -> None:
         me = dist.get_rank(group=self.group)
         info = [None]
-        ring = None
+        ring = reply = None
+        rf = self.reply_from if 0 < self.reply_from < world else 0
         if me == 0:
             path = f"/dev/shm/xv_ctl_{os.getpid()}_{int(time.time() * 1e6) & 0xFFFFFFFF:x}"
             try:
                 ring = _ShmRing(path, world, 0, create=True)
+                if rf:
+                    reply = _ShmRing(path + "_r", world, 0, create=True, writer=rf, readers=[0])
                 info = [(path, socket.gethostname())]
             except OSError:
+                if ring is not None:
+                    ring.close()
+                    ring = None
                 info = [None]
         dist.broadcast_object_list(info, src=dist.get_global_rank(self.group, 0), group=self.group)
         ok = 1
@@ -198,14 +216,18 @@ class ControlChannel:
                 if host != socket.gethostname():
                     raise OSError("different host")
                 ring = _ShmRing(path, world, me, create=False)
+                if rf and me == rf:
+                    reply = _ShmRing(path + "_r", world, me, create=False, writer=rf, readers=[0])
             except OSError:
                 ok = 0
         flag = torch.tensor([ok], dtype=torch.int64)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
         if int(flag.item()) == 1:
-            self._ring = ring
-        elif ring is not None:
-            ring.close()
+            self._ring, self._reply = ring, reply
+        else:
+            for r in (ring, reply):
+                if r is not None:
+                    r.close()
 
     @property
     def uses_shared_memory(self) -> bool:
@@ -245,11 +267,20 @@ class ControlChannel:
         return payload if me == src else bytes(buf.numpy())
 
     def send(self, payload: bytes, dst: int) -> None:
+        if self._reply is not None and dst == 0 and dist.get_rank(group=self.group) == self.reply_from:
+            if len(payload) <= _SLOT_BYTES:
+                self._reply.write(payload)
+                return
+            self._reply.write(None, _VIA_GLOO | len(payload))
         dist.send(torch.tensor([len(payload)], dtype=torch.int64), dst=dst, group=self.group)
         if payload:
             dist.send(torch.frombuffer(bytearray(payload), dtype=torch.uint8), dst=dst, group=self.group)
 
     def recv(self, src: int) -> bytes:
+        if self._reply is not None and src == self.reply_from and dist.get_rank(group=self.group) == 0:
+            data, _ = self._reply.read()
+            if data is not None:
+                return data
         n = torch.zeros(1, dtype=torch.int64)
         dist.recv(n, src=src, group=self.group)
         size = int(n.item())
@@ -260,6 +291,7 @@ class ControlChannel:
         return bytes(buf.numpy())
 
     def close(self) -> None:
-        if self._ring is not None:
-            self._ring.close()
-            self._ring = None
+        for ring in (self._ring, self._reply):
+            if ring is not None:
+                ring.close()
+        self._ring = self._reply = None

@@ -12,7 +12,6 @@ page ``s // block_size``, offset ``s % block_size``.
 
 from __future__ import annotations
 
-import math
 
 import torch
 

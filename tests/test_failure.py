@@ -93,3 +93,57 @@ def test_config_validation(tmp_path, tiny_model_dir):
     cfg = EngineConfig(model=tiny_model_dir, context_len=10 ** 9, tp_size=2, pp_size=2, dp_size=3)
     assert cfg.context_len == cfg.hf_config.max_position_embeddings
     assert (cfg.world_size, cfg.num_gpus, cfg.block_size) == (4, 12, 16)
+
+
+def _ring_reader(path, world, rank, n, q):
+    from xixi_vllm_b200.parallel.control_channel import _ShmRing
+    ring = _ShmRing(path, world, rank, create=False)
+    q.put(("attached", rank))
+    try:
+        got = [ring.read()[0] for _ in range(n)]
+        q.put(("read", got))
+    except RuntimeError as e:
+        q.put(("error", str(e)))
+
+
+def test_control_ring_notices_a_dead_reader_and_a_dead_writer(tmp_path):
+    """Shared-memory control ring, host-side failure detection: a writer whose reader died stops with an
+    error once the ring is full instead of waiting for acknowledgements forever; a reader whose writer
+    died leaves its polling loop."""
+    import multiprocessing as mp
+    import os
+
+    from xixi_vllm_b200.parallel.control_channel import _SLOTS, _ShmRing
+    ctx = mp.get_context("spawn")
+    # 1. reader reads two messages and exits; the writer fills the ring and must then raise
+    path = str(tmp_path / "ring_a")
+    ring = _ShmRing(path, 2, 0, create=True)
+    q = ctx.Queue()
+    p = ctx.Process(target=_ring_reader, args=(path, 2, 1, 2, q))
+    p.start()
+    assert q.get(timeout=60)[0] == "attached"
+    ring.write(b"one")
+    ring.write(b"two")
+    assert q.get(timeout=60) == ("read", [b"one", b"two"])
+    p.join(timeout=30)
+    with pytest.raises(RuntimeError, match="is gone"):
+        for i in range(_SLOTS + 2):
+            ring.write(b"x%d" % i)
+    ring.close()
+    assert not os.path.exists(path)
+    # 2. the writer side disappears (its pid in the header no longer exists): a waiting reader gives up
+    path = str(tmp_path / "ring_b")
+    ring = _ShmRing(path, 2, 0, create=True)
+    dead = ctx.Process(target=int)          # a process that has exited: its pid is free
+    dead.start()
+    dead.join()
+    import struct
+    struct.pack_into("<Q", ring.map, 0, dead.pid)
+    q = ctx.Queue()
+    p = ctx.Process(target=_ring_reader, args=(path, 2, 1, 1, q))
+    p.start()
+    assert q.get(timeout=60)[0] == "attached"
+    kind, msg = q.get(timeout=60)
+    assert kind == "error" and "gone" in msg
+    p.join(timeout=30)
+    ring.close()

@@ -48,6 +48,8 @@ def main(argv=None) -> None:
     p.add_argument("--cg", action="store_true")
     p.add_argument("--compile", action="store_true", help="accepted for compatibility")
     p.add_argument("--pp-layer-counts", type=str, default=None)
+    p.add_argument("--pp-microbatches", type=int, default=None,
+                   help="pipeline stages work on this many pieces of a step in turn (default 1: lockstep)")
     p.add_argument("--device-ids", type=str, default=None)
     p.add_argument("--load-format", choices=("auto", "dummy"), default=None)
     p.add_argument("--device", choices=("cuda", "cpu"), default=None)

@@ -168,3 +168,26 @@ def test_sampled_generation_is_seeded(tiny_model_dir):
             eng.destroy()
     assert run(1) == run(1)
     assert run(1) != run(2)
+
+
+def _cli(args, timeout=300):
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable] + args, cwd=root, capture_output=True, text=True, timeout=timeout)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    lines = [ln for ln in p.stdout.splitlines() if ln.startswith("hello world")]
+    assert lines, p.stdout[-2000:]
+    return lines[-1]
+
+
+def test_command_lines_generate_the_same_text(tiny_model_dir):
+    """``run.py`` in one process, ``run_torchrun.py`` under torchrun with TP=2 and with two pipeline stages
+    working on pieces of each step: the same greedy continuation of the same prompt."""
+    common = ["--model", tiny_model_dir, "--device", "cpu", "--max-new-tokens", "5", "--prompt", "hello world"]
+    single = _cli(["run.py"] + common)
+    launch = ["-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1"]
+    assert _cli(launch + ["--master-port", "29921", "run_torchrun.py", "--tp", "2"] + common) == single
+    assert _cli(launch + ["--master-port", "29922", "run_torchrun.py", "--tp", "1", "--pp", "2",
+                          "--pp-microbatches", "2"] + common) == single

@@ -98,4 +98,5 @@ def test_cta_pair_kernel_matches_single_cta_kernel(m, n, k):
     cuda.check_status()
     ref = x.float() @ w.float().t()
     assert (y_pair.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
-    assert torch.equal(y_pair, y_single)        # same K order, same fp32 accumulation
+    # tiles that the pairs deal in K blocks are summed from two or three fp32 partial sums
+    assert (y_pair.float() - y_single.float()).abs().max().item() <= 1e-2 * ref.abs().max().item()

@@ -1,4 +1,4 @@
-"""Tensor-parallel GPU paths on 2 GPUs: fused peer-memory kernels vs NCCL + separate ops."""
+"""Tensor-parallel GPU paths on 2, 4 and 8 GPUs: fused peer-memory kernels vs NCCL + separate ops."""
 import os
 
 import pytest
@@ -14,7 +14,6 @@ def _need(n):
 
 def _fused_rank(rank, world, nvls):
     os.environ["XV_TP_NVLS"] = "1" if nvls else "0"
-    os.environ["XV_TP_FUSE_GEMM"] = "1"
     os.environ["XV_TP_FUSE_GEMM_MAX_T"] = "100000"
     import torch.distributed as dist
 
@@ -23,7 +22,7 @@ def _fused_rank(rank, world, nvls):
     from xixi_vllm_b200.parallel.symm import FusedTPComm
     dev = torch.device("cuda", rank)
     H = 1024
-    comm = FusedTPComm(get_tp_group(), dev, H, 512, torch.bfloat16, logits_rows=6, logits_local_cols=4096 // world)
+    comm = FusedTPComm(get_tp_group(), dev, H, 1024, torch.bfloat16, logits_rows=6, logits_local_cols=4096 // world)
     errs = []
     for it, T in enumerate([1, 7, 64, 300, 512, 3, 3, 129]):
         g = torch.Generator().manual_seed(100 + it)
@@ -46,7 +45,8 @@ def _fused_rank(rank, world, nvls):
         buf2.copy_(parts[rank].to(dev))
         s = comm.all_reduce(buf2)
         errs.append(float((s.float().cpu() - total).abs().max()))
-    # GEMM + all-reduce + residual + RMSNorm as one kernel (row-parallel projection)
+    # GEMM + cross-rank sum + residual + RMSNorm as one kernel (row-parallel projection), module path:
+    # every rank reduces every row
     class _Proj:
         bias = None
 
@@ -60,6 +60,7 @@ def _fused_rank(rank, world, nvls):
         proj.weight = ws[rank].to(dev)
         comm.begin_forward()
         d = comm.row_linear(proj, xs[rank].to(dev), final=(it % 2 == 1))
+        assert not isinstance(d, torch.Tensor)          # deferred: the GEMM runs inside the reduction kernel
         r_dev = resid.to(dev).clone()
         y, r_out = comm.reduce_add_rmsnorm(d, r_dev, nw.to(dev), 1e-6)
         parts = [(x.float() @ w.float().t()).bfloat16().float() for x, w in zip(xs, ws)]
@@ -81,6 +82,13 @@ def _fused_rank(rank, world, nvls):
     local = full[:, rank * per:(rank + 1) * per].contiguous().to(dev)
     ids = comm.argmax(local, per, rank * per).cpu()
     want = full.float().argmax(-1)
+    # more rows than CTAs can be resident at once: the grid is capped and walks the rows
+    g = torch.Generator().manual_seed(8)
+    many = torch.randn(400, 4096, generator=g).bfloat16()
+    many[17, 5] = 11.0
+    many[17, 4090] = 11.0
+    ids_many = comm.argmax(many[:, rank * per:(rank + 1) * per].contiguous().to(dev), per, rank * per).cpu()
+    many_ok = torch.equal(ids_many, many.float().argmax(-1)) and int(ids_many[17]) == 5
     # column all-gather of logit shards into every rank's full matrix (several sizes, reused buffer)
     gather_ok = True
     for it, rows in enumerate([5, 1, 6]):
@@ -95,22 +103,114 @@ def _fused_rank(rank, world, nvls):
     torch.cuda.synchronize()
     cuda.check_status(dev)
     dist.barrier()
-    assert fused_gemm and gather_ok
+    assert fused_gemm and gather_ok and many_ok
     return max(errs), ids.tolist(), want.tolist(), bool(comm.mc_ptr)
 
 
+def _world_or_skip(world):
+    _need(world)
+    return world
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("nvls", [False, True])
-def test_fused_reduce_norm_and_argmax(nvls):
-    _need(2)
+def test_fused_reduce_norm_and_argmax(nvls, world):
+    _world_or_skip(world)
     from dist_utils import run_ranks_gpu
-    for err, ids, want, has_mc in run_ranks_gpu(_fused_rank, world=2, tp=2, args=(nvls,)):
+    for err, ids, want, has_mc in run_ranks_gpu(_fused_rank, world=world, tp=world, args=(nvls,)):
         assert err < 0.08, err
         assert ids[2] == 100
         assert ids == want or all(a == b for i, (a, b) in enumerate(zip(ids, want)) if i != 2)
 
 
+def _push_rank(rank, world, nvls):
+    """The one-kernel row-parallel projection in both forms, chained without host synchronisation, then
+    replayed from a CUDA graph: residual rows and activations against an fp32 reference."""
+    os.environ["XV_TP_NVLS"] = "1" if nvls else "0"
+    import torch.distributed as dist
+
+    from xixi_vllm_b200.ops import cpu_ref, cuda
+    from xixi_vllm_b200.parallel.groups import get_tp_group
+    from xixi_vllm_b200.parallel.symm import FusedTPComm
+    dev = torch.device("cuda", rank)
+    H = 1024
+    comm = FusedTPComm(get_tp_group(), dev, H, 2048, torch.bfloat16)
+    worst = 0.0
+    cases = [(256, 512, True), (256, 1536, True), (1, 256, False), (32, 512, False), (33, 512, True),
+             (7, 1024, True), (130, 2048, True), (700, 512, True), (1500, 1024, True), (2048, 256, True),
+             (64, 512, False), (256, 512, True)]
+    pending = []
+    comm.begin_forward()       # once: the slot arrays then alternate from call to call, as within a model forward
+    for it, (T, K, two_shot) in enumerate(cases):
+        g = torch.Generator().manual_seed(700 + it)
+        xs = [(torch.randn(T, K, generator=g) * 0.5).bfloat16() for _ in range(world)]
+        ws = [(torch.randn(H, K, generator=g) * 0.05).bfloat16() for _ in range(world)]
+        resid = torch.randn(T, H, generator=g).bfloat16()
+        nw = (1 + 0.1 * torch.randn(H, generator=g)).bfloat16()
+        first = it % 4 == 3
+        r_dev = resid.to(dev).clone()
+        y, r_out = comm.gemm_reduce_norm(xs[rank].to(dev), ws[rank].to(dev), r_dev, nw.to(dev), 1e-6,
+                                         two_shot=two_shot, final=(it % 3 == 2), first=first)
+        pending.append((T, two_shot, first, xs, ws, resid, nw, y.clone(), r_out.clone()))
+    torch.cuda.synchronize()
+    cuda.check_status(dev)
+    for T, two_shot, first, xs, ws, resid, nw, y, r_out in pending:
+        parts = [(x.float() @ w.float().t()).bfloat16().float() for x, w in zip(xs, ws)]
+        r_ref = (sum(parts) + (0 if first else resid.float())).bfloat16()
+        y_ref = cpu_ref.rmsnorm(r_ref, nw, 1e-6)
+        scale = max(float(r_ref.float().abs().max()), 1.0)
+        rows = slice(rank, None, world) if two_shot else slice(None)
+        worst = max(worst, float((r_out.float().cpu()[rows] - r_ref.float()[rows]).abs().max()) / scale * 2)
+        worst = max(worst, float((y.float().cpu() - y_ref.float()).abs().max()) / 4)
+    # a captured chain of four reduction points replayed many times: the counters' history must keep step
+    T, K = 48, 512
+    g = torch.Generator().manual_seed(42)
+    xs = [(torch.randn(T, K, generator=g) * 0.5).bfloat16() for _ in range(world)]
+    ws = [(torch.randn(H, K, generator=g) * 0.05).bfloat16() for _ in range(world)]
+    nw = (1 + 0.1 * torch.randn(H, generator=g)).bfloat16().to(dev)
+    x_d, w_d = xs[rank].to(dev), ws[rank].to(dev)
+    res = torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
+    outs = []
+
+    def chain():
+        comm.begin_forward()
+        for j in range(4):
+            y, _ = comm.gemm_reduce_norm(x_d, w_d, res, nw, 1e-6, two_shot=(j % 2 == 0), final=(j == 3), first=True)
+            outs.append(y)
+        return outs[-1]
+
+    chain()
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    outs.clear()
+    with torch.cuda.graph(graph):
+        last = chain()
+    for _ in range(300):
+        graph.replay()
+    torch.cuda.synchronize()
+    cuda.check_status(dev)
+    parts = [(x.float() @ w.float().t()).bfloat16().float() for x, w in zip(xs, ws)]
+    y_ref = cpu_ref.rmsnorm(sum(parts).bfloat16(), nw.cpu(), 1e-6)
+    worst = max(worst, float((last.float().cpu() - y_ref.float()).abs().max()) / 4)
+    dist.barrier()
+    return worst, bool(comm.mc_ptr)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("nvls", [False, True])
+def test_one_kernel_row_parallel_projection(nvls, world):
+    _world_or_skip(world)
+    from dist_utils import run_ranks_gpu
+    for err, has_mc in run_ranks_gpu(_push_rank, world=world, tp=world, args=(nvls,)):
+        assert err < 0.08, err
+
+
 def _probe(model_dir, timeout=240, **kw):
-    """Generate with a fresh process tree; the whole tree is killed if it exceeds ``timeout``."""
+    """Generate with a fresh process tree. The ranks run without NVLink multicast (plain peer loads and stores,
+    NCCL without NVLS): a tree that has to be ended after ``timeout`` must not hold memory bound to a multicast
+    object. It is asked to stop first (SIGTERM, so the workers tear their communicators down) and only killed
+    if that does not end it."""
     import json
     import signal
     import subprocess
@@ -122,12 +222,18 @@ def _probe(model_dir, timeout=240, **kw):
             cmd.append(f"--{k.replace('_', '-')}")
         elif v is not False:
             cmd += [f"--{k.replace('_', '-')}", str(v)]
-    p = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, start_new_session=True)
+    env = dict(os.environ, XV_TP_NVLS="0", NCCL_NVLS_ENABLE="0")
+    p = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, start_new_session=True,
+                         env=env)
     try:
         out, _ = p.communicate(timeout=timeout)
     except subprocess.TimeoutExpired:
-        os.killpg(p.pid, signal.SIGKILL)       # the process group this test started
-        out, _ = p.communicate()
+        os.killpg(p.pid, signal.SIGTERM)       # the process group this test started
+        try:
+            out, _ = p.communicate(timeout=20)
+        except subprocess.TimeoutExpired:
+            os.killpg(p.pid, signal.SIGKILL)
+            out, _ = p.communicate()
         raise AssertionError(f"engine probe timed out:\n{out[-3000:]}")
     for line in out.splitlines():
         if line.startswith("RESULT "):
@@ -155,6 +261,23 @@ def test_engine_tp2_matches_tp1(tmp_path, comm, cg):
     out = _probe(d, tp=2, comm=comm, cg=cg, port=29811)
     # first tokens agree; later ones may flip on bf16 near-ties between different reduction orders
     assert _agree(ref, out) >= 10, (ref, out)
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("tp", [4, 8])
+def test_engine_tp4_tp8_match_tp1(tmp_path, tp):
+    """The sizes the scaling benchmark runs: first tokens of TP=4 / TP=8 (fused kernels, decode graphs) against
+    one GPU, on a model whose head counts divide by 8."""
+    _need(tp)
+    from xixi_vllm_b200.models.synth import make_model_dir
+    d = make_model_dir(str(tmp_path / "m8"), "tiny", std=0.08, num_hidden_layers=2, hidden_size=1024,
+                       num_attention_heads=8, num_key_value_heads=8, head_dim=128, intermediate_size=2048,
+                       vocab_size=4096, torch_dtype="bfloat16", tie_word_embeddings=False)
+    ref = _probe(d)
+    out = _probe(d, tp=tp, comm="fused", cg=True, port=29901 + tp)
+    assert _agree(ref, out) >= 10, (ref, out)
+    eager = _probe(d, tp=tp, comm="fused", port=29921 + tp)
+    assert _agree(ref, eager) >= 10, (ref, eager)
 
 
 @pytest.mark.timeout(600)

@@ -51,7 +51,7 @@ def test_noalloc_gemm_rejects_oversized_problem(capfd):
     from xixi_vllm_b200.ops import cuda
     L, f = _sym()
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    m, n, k = 256, 9216, 8192
+    m, n, k = 128, 16640, 8192          # two split-K planes of 8.1 MiB each
     need = cuda.gemm_plan(m, n, k, sms).workspace_bytes
     assert need > L.xv_gemm_noalloc_max_scratch_bytes()
     x = torch.zeros(m, k, dtype=torch.bfloat16, device="cuda")

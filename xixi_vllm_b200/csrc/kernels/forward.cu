@@ -27,6 +27,8 @@ struct Ctx {
   const XvArena* a;
   cudaStream_t s;
   int call_idx;      // reduction points issued so far in this forward (symmetric-buffer rotation)
+  bool two_shot;     // this forward's reductions deal the rows to the ranks (residual stream sharded by rows)
+  bool push;         // row-parallel GEMM and its reduction run as one kernel
 };
 
 #define XV_TRY(opid, expr)      \
@@ -45,23 +47,34 @@ inline char* symm_local(const Ctx& c, int which) {
 
 // Row-parallel projection followed by the reduction point that consumes it:
 //   residual += sum_over_ranks(x W^T);  h = rmsnorm(residual) * norm_w
+// Under tensor parallelism this is ONE kernel (xv_gemm_bf16_tp: tiles pushed from the GEMM epilogue to
+// the ranks that reduce them); the two-kernel form (GEMM into the symmetric buffer, then a reduction
+// kernel that pulls) remains for shapes whose slot array does not fit and for XV_TP_PUSH=0.
 int row_linear_reduce_norm(Ctx& c, const void* x, const void* w, int k, const void* norm_w, bool final_call) {
   const XvModelDesc* m = c.m;
   const int T = c.b->num_tokens, H = m->hidden;
   if (m->tp_world > 1) {
     const int which = final_call ? 2 : (c.call_idx & 1);
     ++c.call_idx;
-    XV_TRY(10, xv_gemm_bf16(x, w, symm_local(c, which), T, H, k, k, k, H, c.a->gemm_ws, c.a->gemm_ws_bytes,
-                            c.a->num_sms, c.a->status, c.s));
-    if (m->h_offset >= 0) {
-      XV_TRY(15, xv_tp_reduce_norm_sharded(m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch, m->tp_rank, m->tp_world,
-                                           static_cast<long long>(which) * m->buf_bytes, m->h_offset, 1,
-                                           c.a->residual, norm_w, T, H, m->eps, m->spin_us, c.a->status, c.s));
+    const long long slot_off = static_cast<long long>(which) * m->buf_bytes;
+    if (c.push) {
+      XV_TRY(16, xv_gemm_bf16_tp(x, w, T, H, k, k, k, c.a->num_sms, m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch,
+                                 m->tp_rank, m->tp_world, slot_off, m->buf_bytes, c.two_shot ? 1 : 0, m->h_offset,
+                                 c.a->residual, c.a->residual, norm_w, c.a->h, m->eps, 0, m->spin_us, c.a->status,
+                                 c.s));
       return 0;
     }
-    XV_TRY(11, xv_tp_reduce_norm(m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch, m->tp_rank, m->tp_world,
-                                 static_cast<long long>(which) * m->buf_bytes, c.a->residual, c.a->residual, norm_w,
-                                 c.a->h, T, H, m->eps, 0, m->spin_us, c.a->status, c.s));
+    XV_TRY(10, xv_gemm_bf16(x, w, symm_local(c, which), T, H, k, k, k, H, c.a->gemm_ws, c.a->gemm_ws_bytes,
+                            c.a->num_sms, c.a->status, c.s));
+    if (c.two_shot) {
+      XV_TRY(15, xv_tp_reduce_norm_sharded(m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch, m->tp_rank, m->tp_world,
+                                           slot_off, m->h_offset, 1, c.a->residual, norm_w, T, H, m->eps, m->spin_us,
+                                           c.a->status, c.s));
+      return 0;
+    }
+    XV_TRY(11, xv_tp_reduce_norm(m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch, m->tp_rank, m->tp_world, slot_off,
+                                 c.a->residual, c.a->residual, norm_w, c.a->h, T, H, m->eps, 0, m->spin_us,
+                                 c.a->status, c.s));
     return 0;
   }
   int splits = 1;
@@ -101,19 +114,30 @@ int xv_forward_decode_splits(int num_seqs, int hkv, int num_sms, int max_tokens_
 }
 
 int xv_qwen3_forward(const XvModelDesc* m, const XvBatchDesc* b, const XvArena* a, cudaStream_t stream) {
-  Ctx c{m, b, a, stream, 0};
+  Ctx c{m, b, a, stream, 0, false, false};
   const int T = b->num_tokens, H = m->hidden, D = m->head_dim;
   if (T <= 0) return 0;
   const int q_cols = m->hq * D;
   const int L = m->num_layers;
-
-  // ---- embedding and the first normalisation point ----
   if (m->tp_world > 1) {
+    // Few rows: every rank reduces every row (one wait per reduction point). More rows: the rows are dealt
+    // to the ranks (traffic per GPU independent of the rank count, a second wait for the broadcast).
+    c.two_shot = m->h_offset >= 0 && T > m->tp_one_shot_max;
+    const long long cap = c.two_shot ? (T + m->tp_world - 1) / m->tp_world : T;
+    c.push = m->tp_push != 0 && static_cast<long long>(m->tp_world) * cap * H * 2 <= m->buf_bytes;
+    // both members of a stage pair must agree on the form: it fixes the layout of the residual they exchange
+  }
+
+  // ---- embedding and the first normalisation point (first pipeline stage) ----
+  if (!m->is_first) {
+    // h (normalised by the sender with this stage's first input norm) and the residual stream were received
+    // into the arena; after a two-shot reduction each rank holds only its rows of the residual.
+  } else if (m->tp_world > 1) {
     const int which = (L == 0) ? 2 : (c.call_idx & 1);
     ++c.call_idx;
     XV_TRY(1, xv_embedding(b->input_ids, m->embed, symm_local(c, which), T, H, m->vocab_start, m->vocab_rows, stream));
     const void* w0 = L > 0 ? m->layers[0].input_norm : m->final_norm;
-    if (m->h_offset >= 0) {
+    if (c.two_shot) {
       XV_TRY(5, xv_tp_reduce_norm_sharded(m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch, m->tp_rank, m->tp_world,
                                           static_cast<long long>(which) * m->buf_bytes, m->h_offset, 0, a->residual, w0,
                                           T, H, m->eps, m->spin_us, a->status, stream));
@@ -190,6 +214,7 @@ int xv_qwen3_forward(const XvModelDesc* m, const XvBatchDesc* b, const XvArena* 
                               a->num_sms, a->status, stream));
       XV_TRY(45, xv_silu_mul(a->gu, a->act, T, I, stream));
     }
+    // the stage's last point normalises with the next stage's first input norm (a copy of it is loaded here)
     const void* next_norm = (l + 1 < L) ? m->layers[l + 1].input_norm : m->final_norm;
     {
       int rc = row_linear_reduce_norm(c, a->act, w.down, I, next_norm, l + 1 == L);
@@ -197,9 +222,9 @@ int xv_qwen3_forward(const XvModelDesc* m, const XvBatchDesc* b, const XvArena* 
     }
   }
 
-  // ---- sampling rows -> LM head ----
+  // ---- sampling rows -> LM head (last pipeline stage) ----
   const int S = b->num_samples;
-  if (S <= 0) return 0;
+  if (S <= 0 || !m->is_last) return 0;
   XV_TRY(50, xv_gather_rows(a->h, b->sample_rows, a->hidden_out, S, H, stream));
   XV_TRY(51, xv_gemm_bf16(a->hidden_out, m->lm_head, a->logits, S, m->lm_head_rows, H, H, H, m->lm_head_rows,
                           a->gemm_ws, a->gemm_ws_bytes, a->num_sms, a->status, stream));

@@ -42,12 +42,14 @@ constexpr int kUmmaK = 16;        // K per tcgen05.mma for 16-bit inputs
 constexpr int kGemmThreads = 192;
 constexpr int kMaxStages = 8;
 constexpr int kGemmKernelId = 1;
+constexpr int kStagingBytes = 4 * 2048;   // per epilogue warp: [32 tokens][32 features] bf16 transpose buffer
+constexpr int kTailMaxVec = 6;            // hidden <= 192 * 6 * 8 = 9216 in the tensor-parallel tail
 
 struct GemmParams {
   int rows_a;        // valid rows of operand A (M axis of the MMA)
   int rows_b;        // valid rows of operand B (N axis of the MMA)
   int k;             // reduction length
-  int bn;            // MMA N = rows of B per CTA (multiple of 16, <= 256)
+  int bn;            // MMA N = rows of B per CTA (pair: per CTA pair); multiple of 16, <= 256
   int stages;
   int k_blocks_per_split;
   int tiles_a, tiles_b, splits;
@@ -56,6 +58,7 @@ struct GemmParams {
   int out_fp32;      // 1: fp32 partials at out + split * split_stride, 0: bf16
   int act;           // 1: SiLU-mul epilogue. Operand rows of the weight matrix come in groups of 16 =
                      //    [8 gate rows | 8 up rows]; output has half as many features (bf16 only)
+  int vec_ok;        // output rows may be written with 16-byte stores (alignment and row stride allow it)
   long long ldc;
   long long split_stride;   // elements between split-K partial planes
   void* out;
@@ -84,12 +87,156 @@ __device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int w) {
   return it;
 }
 
+__device__ __forceinline__ uint4 pack8_regs(const uint32_t* r) {
+  uint4 v;
+  v.x = pack_bf16(__uint_as_float(r[0]), __uint_as_float(r[1]));
+  v.y = pack_bf16(__uint_as_float(r[2]), __uint_as_float(r[3]));
+  v.z = pack_bf16(__uint_as_float(r[4]), __uint_as_float(r[5]));
+  v.w = pack_bf16(__uint_as_float(r[6]), __uint_as_float(r[7]));
+  return v;
+}
+
+__device__ __forceinline__ float silu_mul_f(float gate, float up) { return gate / (1.f + __expf(-gate)) * up; }
+
+// One thread's share of an accumulator tile in the normal orientation: 32 consecutive output columns
+// (col .. col + 31) of output row `a_row`, in registers. Stores them as bf16, as an fp32 split-K plane,
+// through the SiLU-mul epilogue, or into the reducing ranks' slots (tensor-parallel push).
+__device__ __forceinline__ void store_row32(const GemmParams& p, const TpPush& push, int a_row, int col, int b_end,
+                                            int split, const uint32_t (&r)[32]) {
+  // b_end: first column that is not this tile's (the accumulator holds nothing valid from there on)
+  if (a_row >= p.rows_a || col >= b_end) return;
+  if (push.enabled) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      if (col + g * 8 < b_end) tp_push_store8(push, a_row, col + g * 8, split, pack8_regs(r + g * 8));
+  } else if (p.act) {
+    // 16 columns are [8 gate | 8 up] of one feature group -> 8 outputs
+    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(a_row) * p.ldc + (col >> 1);
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      if (col + g * 16 + 16 <= b_end) {
+        float ov[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          ov[j] = silu_mul_f(__uint_as_float(r[g * 16 + j]), __uint_as_float(r[g * 16 + 8 + j]));
+        uint4 v;
+        v.x = pack_bf16(ov[0], ov[1]);
+        v.y = pack_bf16(ov[2], ov[3]);
+        v.z = pack_bf16(ov[4], ov[5]);
+        v.w = pack_bf16(ov[6], ov[7]);
+        *reinterpret_cast<uint4*>(o + g * 8) = v;
+      }
+    }
+  } else if (p.out_fp32) {
+    float* o = static_cast<float*>(p.out) + static_cast<size_t>(split) * p.split_stride +
+               static_cast<size_t>(a_row) * p.ldc + col;
+    if (col + 32 <= b_end && (p.ldc & 3) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(o + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                        __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col + j < b_end) o[j] = __uint_as_float(r[j]);
+    }
+  } else {
+    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(a_row) * p.ldc + col;
+    if (col + 32 <= b_end && p.vec_ok) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) *reinterpret_cast<uint4*>(o + g * 8) = pack8_regs(r + g * 8);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col + j < b_end) o[j] = __float2bfloat16(__uint_as_float(r[j]));
+    }
+  }
+}
+
+// One warp's share of an accumulator tile in the swapped orientation: lane = output feature
+// (a_row0 + lane), registers = 32 consecutive tokens (tok0 ..). The tile is turned through a
+// per-warp shared-memory buffer so that global (or peer) memory sees 16-byte stores of eight
+// consecutive features of one token instead of 2-byte stores.
+__device__ __forceinline__ void store_swapped32(const GemmParams& p, const TpPush& push, uint8_t* stage_w, int lane,
+                                                int a_row0, int tok0, int b_end, int split,
+                                                const uint32_t (&r)[32]) {
+  const int a_row = a_row0 + lane;
+  if (p.out_fp32) {
+    if (a_row < p.rows_a) {
+      float* o = static_cast<float*>(p.out) + static_cast<size_t>(split) * p.split_stride;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (tok0 + j < b_end) o[static_cast<size_t>(tok0 + j) * p.ldc + a_row] = __uint_as_float(r[j]);
+    }
+    return;
+  }
+  if (p.act) {
+    // lanes are weight rows laid out [8 gate | 8 up | 8 gate | 8 up]: lane l pairs with l ^ 8;
+    // the 16 lanes with (l & 8) == 0 end up with one output feature each
+    __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage_w);     // [32 tokens][16 features]
+    const bool writer = (lane & 8) == 0;
+    const int of = ((lane >> 4) << 3) + (lane & 7);
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float v = __uint_as_float(r[j]);
+      const float up = __shfl_xor_sync(0xffffffffu, v, 8);
+      if (writer) st[j * 16 + of] = __float2bfloat16(silu_mul_f(v, up));
+    }
+    __syncwarp();
+    const int out_col = (a_row0 >> 1) + (lane & 1) * 8;
+    if (p.vec_ok && a_row0 + 32 <= p.rows_a) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int tl = (lane >> 1) + 16 * i;
+        const uint4 v = *reinterpret_cast<const uint4*>(stage_w + tl * 32 + (lane & 1) * 16);
+        if (tok0 + tl < b_end)
+          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(tok0 + tl) * p.ldc +
+                                    out_col) = v;
+      }
+    } else if (writer && a_row < p.rows_a) {
+      __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out);
+      const int oc = (a_row >> 4) * 8 + (a_row & 7);
+      for (int j = 0; j < 32; ++j)
+        if (tok0 + j < b_end) o[static_cast<size_t>(tok0 + j) * p.ldc + oc] = st[j * 16 + of];
+    }
+    return;
+  }
+  if (!(p.vec_ok || push.enabled)) {
+    if (a_row < p.rows_a) {
+      __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out);
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (tok0 + j < b_end) o[static_cast<size_t>(tok0 + j) * p.ldc + a_row] = __float2bfloat16(__uint_as_float(r[j]));
+    }
+    return;
+  }
+  __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage_w);       // [32 tokens][32 features]
+  __syncwarp();                  // the readers of the previous chunk are done with the buffer
+#pragma unroll
+  for (int j = 0; j < 32; ++j) st[j * 32 + lane] = __float2bfloat16(__uint_as_float(r[j]));
+  __syncwarp();
+  const int col = a_row0 + (lane & 3) * 8;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int tl = (lane >> 2) + 8 * i;
+    const int tok = tok0 + tl;
+    const uint4 v = *reinterpret_cast<const uint4*>(stage_w + tl * 64 + (lane & 3) * 16);
+    if (tok < b_end && col < p.rows_a) {       // rows_a is a multiple of 8 on this path
+      if (push.enabled)
+        tp_push_store8(push, tok, col, split, v);
+      else
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(tok) * p.ldc + col) = v;
+    }
+  }
+}
+
 // Persistent kernel: every CTA walks work items (output tile x K split) with stride gridDim.x.
 // The shared-memory stage ring and its phases run on across work items, and the accumulator
 // is double buffered in TMEM, so the epilogue of one tile overlaps the main loop of the next.
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads, 2)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const GemmParams p, const __grid_constant__ TpTail tail) {
+                    const GemmParams p, const __grid_constant__ TpPush push) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   grid_dep_launch();           // the next kernel of the stream may start its prologue (see launch.cuh)
   // Dynamic shared memory is only guaranteed 16-byte alignment; the swizzled tiles need 1024.
@@ -104,6 +251,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   uint64_t* acc_empty = acc_full + 2;              // [2] accumulator drained, MMA may overwrite
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* staging = reinterpret_cast<uint8_t*>(full_bar) + 256;   // kStagingBytes, swapped orientation only
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -162,14 +310,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       }
       grid_dep_wait();
-      uint32_t it = 0;                   // K blocks issued so far by this CTA, across work items
+      // K blocks issued so far by this CTA, across work items: `it` counts them, `s` is the stage the
+      // next one goes to and `round` how often the ring has wrapped (kept incrementally: no division
+      // in the loop)
+      uint32_t it = 0, s = 0, round = 0;
+      const uint32_t nst = static_cast<uint32_t>(p.stages);
       for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
         const WorkItem wi = decode_work(p, w);
         const int kb_begin = wi.split * p.k_blocks_per_split;
         const int kb_end = min(kb_begin + p.k_blocks_per_split, total_kb);
+        const int ya = wi.tile_a * kBM, yb = wi.tile_b * p.bn;
         for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
-          const uint32_t s = it % p.stages;
-          const uint32_t round = it / p.stages;
           if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
             report_status(p.status, kGemmKernelId, kWaitEmptyTimeout);
             *abort_flag = 1;
@@ -179,16 +330,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const bool weights_out = it < pre;      // expect_tx and the weight tile were issued above
           if (!weights_out) mbar_expect_tx(&full_bar[s], stage_bytes);
           if (!(weights_out && p.transposed))
-            tma_load_2d(sa, &map_a, &full_bar[s], kb * kBK, wi.tile_a * kBM, hint_a);
+            tma_load_2d(sa, &map_a, &full_bar[s], kb * kBK, ya, hint_a);
           if (!(weights_out && !p.transposed))
-            tma_load_2d(sa + a_bytes, &map_b, &full_bar[s], kb * kBK, wi.tile_b * p.bn, hint_b);
+            tma_load_2d(sa + a_bytes, &map_b, &full_bar[s], kb * kBK, yb, hint_b);
+          if (++s == nst) {
+            s = 0;
+            ++round;
+          }
         }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      uint32_t it = 0, t = 0;
+      uint32_t t = 0, s = 0, parity = 0;
+      const uint32_t nst = static_cast<uint32_t>(p.stages);
+      // descriptors of stage 0; a stage further on adds stage_bytes / 16, a K step of 16 elements adds 2
+      const uint64_t desc_a0 = umma_desc_sw128(smem_u32(smem));
+      const uint64_t desc_b0 = umma_desc_sw128(smem_u32(smem) + a_bytes);
+      const uint32_t idesc = p.idesc;
       for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x, ++t) {
         const WorkItem wi = decode_work(p, w);
         const int kb_begin = wi.split * p.k_blocks_per_split;
@@ -201,24 +361,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
-        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
-          const uint32_t s = it % p.stages;
-          const uint32_t round = it / p.stages;
-          if (!mbar_wait(&full_bar[s], round & 1)) {
+        uint32_t accumulate = 0;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          if (!mbar_wait(&full_bar[s], parity)) {
             report_status(p.status, kGemmKernelId, kWaitFullTimeout);
             *abort_flag = 1;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
-          const uint32_t sb = sa + a_bytes;
+          const uint64_t soff = static_cast<uint64_t>((s * stage_bytes) >> 4);
 #pragma unroll
           for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
-            const uint64_t da = umma_desc_sw128(sa + kk * kUmmaK * 2);
-            const uint64_t db = umma_desc_sw128(sb + kk * kUmmaK * 2);
-            umma_bf16(d_tmem, da, db, p.idesc, (kb > kb_begin || kk > 0) ? 1u : 0u);
+            umma_bf16(d_tmem, desc_a0 + soff + kk * 2, desc_b0 + soff + kk * 2, idesc, accumulate);
+            accumulate = 1;
           }
           umma_commit(&empty_bar[s]);   // stage is free once these MMAs have read it
+          if (++s == nst) {
+            s = 0;
+            parity ^= 1;
+          }
         }
         umma_commit(&acc_full[buf]);     // accumulator complete
       }
@@ -226,6 +387,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   } else {
     // ---------------- epilogue ----------------
     const int quarter = warp & 3;                       // TMEM lane quarter this warp may read
+    uint8_t* stage_w = staging + quarter * 2048;
+    const int nchunks = (p.bn + 31) >> 5;               // 32 accumulator columns per tcgen05.ld
     uint32_t t = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++t) {
       const WorkItem wi = decode_work(p, w);
@@ -239,105 +402,44 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // warp-uniform: the aligned TMEM loads below must be executed by all 32 lanes or none
       ok = __all_sync(0xffffffffu, ok && (*abort_flag == 0));
       if (!ok) break;
-      const int a_row = wi.tile_a * kBM + quarter * 32 + lane;
+      const int a_row0 = wi.tile_a * kBM + quarter * 32;
       const uint32_t lane_addr = tmem_base + buf * p.acc_stride + (static_cast<uint32_t>(quarter * 32) << 16);
       const int b0 = wi.tile_b * p.bn;
-      for (int c = 0; c < p.bn; c += 16) {
-        uint32_t r[16];
-        tmem_ld16(lane_addr + static_cast<uint32_t>(c), r);
+      const int b_end = min(p.rows_b, b0 + p.bn);
+      // Two register sets: the load of the next 32 columns is in flight while this one is stored.
+      uint32_t ra[32], rb[32];
+      tmem_ld32(lane_addr, ra);
+      for (int ch = 0; ch < nchunks; ch += 2) {
         tmem_ld_wait();
-        if (p.act && p.transposed) {
-          // lanes are weight rows laid out [8 gate | 8 up | 8 gate | 8 up]: lane l pairs with l ^ 8
-          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out);
-          const int out_col = (a_row >> 4) * 8 + (a_row & 7);
-          const bool writer = (lane & 8) == 0 && a_row < p.rows_a;
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float v = __uint_as_float(r[j]);
-            const float up = __shfl_xor_sync(0xffffffffu, v, 8);
-            const int b_row = b0 + c + j;
-            if (writer && b_row < p.rows_b)
-              o[static_cast<size_t>(b_row) * p.ldc + out_col] = __float2bfloat16(v / (1.f + __expf(-v)) * up);
-          }
-        } else if (p.act) {
-          // this thread's 16 columns are [8 gate | 8 up] of one feature group
-          if (a_row < p.rows_a) {
-            const int col = b0 + c;
-            if (col + 16 <= p.rows_b) {
-              float ov[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float gte = __uint_as_float(r[j]);
-                ov[j] = gte / (1.f + __expf(-gte)) * __uint_as_float(r[8 + j]);
-              }
-              uint4 v0;
-              v0.x = pack_bf16(ov[0], ov[1]);
-              v0.y = pack_bf16(ov[2], ov[3]);
-              v0.z = pack_bf16(ov[4], ov[5]);
-              v0.w = pack_bf16(ov[6], ov[7]);
-              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(a_row) * p.ldc +
-                                        (col >> 1)) = v0;
-            }
-          }
-        } else if (p.transposed) {
-          // lanes hold consecutive output columns (a_row); tokens run along the registers
-          if (a_row < p.rows_a) {
-            if (p.out_fp32) {
-              float* o = static_cast<float*>(p.out) + static_cast<size_t>(wi.split) * p.split_stride;
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int b_row = b0 + c + j;
-                if (b_row < p.rows_b) o[static_cast<size_t>(b_row) * p.ldc + a_row] = __uint_as_float(r[j]);
-              }
-            } else {
-              __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out);
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int b_row = b0 + c + j;
-                if (b_row < p.rows_b)
-                  o[static_cast<size_t>(b_row) * p.ldc + a_row] = __float2bfloat16(__uint_as_float(r[j]));
-              }
-            }
-          }
-        } else if (a_row < p.rows_a) {
-          const int col = b0 + c;
-          if (p.out_fp32) {
-            float* o = static_cast<float*>(p.out) + static_cast<size_t>(wi.split) * p.split_stride +
-                       static_cast<size_t>(a_row) * p.ldc + col;
-            if (col + 16 <= p.rows_b && (p.ldc & 3) == 0) {
-#pragma unroll
-              for (int j = 0; j < 16; j += 4)
-                *reinterpret_cast<float4*>(o + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                                __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-            } else {
-              for (int j = 0; j < 16; ++j)
-                if (col + j < p.rows_b) o[j] = __uint_as_float(r[j]);
-            }
-          } else {
-            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(a_row) * p.ldc + col;
-            if (col + 16 <= p.rows_b && (p.ldc & 7) == 0) {
-              uint4 v0, v1;
-              v0.x = pack_bf16(__uint_as_float(r[0]), __uint_as_float(r[1]));
-              v0.y = pack_bf16(__uint_as_float(r[2]), __uint_as_float(r[3]));
-              v0.z = pack_bf16(__uint_as_float(r[4]), __uint_as_float(r[5]));
-              v0.w = pack_bf16(__uint_as_float(r[6]), __uint_as_float(r[7]));
-              v1.x = pack_bf16(__uint_as_float(r[8]), __uint_as_float(r[9]));
-              v1.y = pack_bf16(__uint_as_float(r[10]), __uint_as_float(r[11]));
-              v1.z = pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13]));
-              v1.w = pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15]));
-              *reinterpret_cast<uint4*>(o) = v0;
-              *reinterpret_cast<uint4*>(o + 8) = v1;
-            } else {
-              for (int j = 0; j < 16; ++j)
-                if (col + j < p.rows_b) o[j] = __float2bfloat16(__uint_as_float(r[j]));
-            }
-          }
+        tmem_ld_fence_regs(ra);
+        if (ch + 1 < nchunks) tmem_ld32(lane_addr + static_cast<uint32_t>((ch + 1) * 32), rb);
+        if (p.transposed)
+          store_swapped32(p, push, stage_w, lane, a_row0, b0 + ch * 32, b_end, wi.split, ra);
+        else
+          store_row32(p, push, a_row0 + lane, b0 + ch * 32, b_end, wi.split, ra);
+        if (ch + 1 < nchunks) {
+          tmem_ld_wait();
+          tmem_ld_fence_regs(rb);
+          if (ch + 2 < nchunks) tmem_ld32(lane_addr + static_cast<uint32_t>((ch + 2) * 32), ra);
+          if (p.transposed)
+            store_swapped32(p, push, stage_w, lane, a_row0, b0 + (ch + 1) * 32, b_end, wi.split, rb);
+          else
+            store_row32(p, push, a_row0 + lane, b0 + (ch + 1) * 32, b_end, wi.split, rb);
         }
       }
       // this warp has drained its quarter of the accumulator
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+    if (push.enabled) {
+      // "this CTA's tiles are in the reducing ranks' slots": once per CTA that had GEMM work, also when the
+      // pipeline gave up (the peers' waits then still end; the status word says what happened)
+      if (static_cast<int>(blockIdx.x) < total_work) {
+        named_barrier(1, 128);                        // all four epilogue warps have issued their stores
+        const int et = static_cast<int>(threadIdx.x) - 64;
+        if (et < push.comm.world) tp_push_signal_tiles(push, et);
+      }
     }
   }
 
@@ -347,62 +449,100 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
-
-  // ---------------- tensor-parallel tail: all-reduce + residual + RMSNorm in this kernel ----------------
-  // The whole grid is resident (the host clamps it to the occupancy), so grid-wide barriers
-  // are safe. Phase order: [fold split-K planes into the symmetric buffer] -> announce to
-  // peers -> wait for peers -> every CTA reduces, adds the residual and normalises its rows.
-  if (tail.enabled) {
-    __shared__ float tail_scratch[32];
-    bool ok = *abort_flag == 0;
-    if (tail.splits > 1) {
-      ok = grid_barrier(tail.grid_sync, kDefaultWaitNs) && ok;
-      if (ok) {
-        __nv_bfloat16* mine = reinterpret_cast<__nv_bfloat16*>(
-            const_cast<char*>(static_cast<const char*>(tail.comm.peer_buf[tail.comm.rank])) + tail.buf_offset);
-        const long long elems = static_cast<long long>(tail.rows) * tail.hidden;
-        for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < elems;
-             i += static_cast<long long>(gridDim.x) * blockDim.x * 4) {
-          float4 acc = *reinterpret_cast<const float4*>(tail.partials + i);
-          for (int sp = 1; sp < tail.splits; ++sp) {
-            const float4 v = *reinterpret_cast<const float4*>(tail.partials + sp * tail.split_stride + i);
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-          }
-          uint2 o;
-          o.x = pack_bf16(acc.x, acc.y);
-          o.y = pack_bf16(acc.z, acc.w);
-          *reinterpret_cast<uint2*>(mine + i) = o;
-        }
-      }
-    }
-    ok = grid_barrier(tail.grid_sync, kDefaultWaitNs) && ok;
-    if (!ok) report_status(p.status, kGemmKernelId, kPeerFlagTimeout);
-    const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(tail.comm.epoch);
-    ok = tp_barrier(tail.comm, epoch, 0) && ok;
-    if (ok)
-      tp_reduce_rows<6>(tail.comm, tail.buf_offset, tail.residual_in, tail.residual_out, tail.norm_w, tail.y,
-                        tail.rows, tail.hidden, tail.eps, tail.mode, tail_scratch);
-    tp_finish(tail.comm);
-  }
+  if (push.enabled) tp_push_tail<kTailMaxVec>(push);
 }
 
 // ---- CTA-pair variant --------------------------------------------------------------------------------
-// Two CTAs of a 2-wide cluster compute one 256 x 256 output tile with tcgen05.mma cta_group::2.
-// Each CTA loads 128 rows of A and 128 rows of B per K block (32 KB instead of the 48 KB a lone
-// CTA needs for its 128 x 256 tile), so the shared-memory fill traffic per FLOP drops by a third
-// and six stages fit. CTA rank 0 issues the MMAs for the pair; each CTA drains its own 128
-// accumulator rows. Used for the large-M (prefill) orientation.
-constexpr int kPairStages = 6;
-constexpr int kPairStageBytes = 2 * kBM * kBK * 2;   // A 16 KB + B 16 KB
-constexpr int kPairSmem = kPairStages * kPairStageBytes + 1024 + 256;
+// Two CTAs of a 2-wide cluster compute 256 x BN output tiles with tcgen05.mma cta_group::2 (BN a
+// multiple of 16 up to 256). Each CTA loads 128 rows of A and BN/2 rows of B per K block, so the
+// shared-memory fill traffic per FLOP is a third lower than for a lone CTA's 128 x BN tile. CTA rank 0
+// issues the MMAs for the pair; each CTA drains its own 128 accumulator rows.
+//
+// Tiles are dealt whole and round-robin as long as they fill all SM pairs; what is left over (96 tiles on
+// 74 pairs: the last wave, or the last two) is dealt in K blocks ("stream-K"): that region's tiles x
+// K-blocks units are numbered tile by tile and every pair takes one contiguous range of them, so all pairs
+// finish together. A range covers at most one tile's end, whole tiles, and one tile's beginning; it is at
+// least half a tile long, so at most three pairs share a tile. A pair walks its range from the top: the
+// beginning of its last tile first, whose fp32 accumulator it adds (red.add.f32) into the slot of the pair
+// that will finish that tile, then raises that pair's counter; whole tiles next; the end of its first tile
+// last, where it adds what the other pairs left in its own slot to its accumulator, runs the normal
+// epilogue, and clears slot and counter for the next launch. With at most two contributions added to a slot
+// that starts at zero the sum does not depend on their order.
+constexpr int kPairAccStride = 256;
+constexpr long long kSkReserveBytes = 20ll << 20;   // tail of the workspace kept zero for partial tiles + counters
+constexpr long long kSkCounterBytes = 4096;         // the very end of it: two counters per SM pair
+
+struct StreamK {
+  int units_per_pair;      // K blocks of the stream-K region each pair takes
+  int dp_tiles;            // tiles [0, dp_tiles) are dealt whole, round-robin over the pairs
+  int sk_units;            // (tiles - dp_tiles) * K blocks per tile
+  int slot_floats;         // floats per slot: 256 rows x BN rounded up to whole 32-column chunks
+  float* slots;            // [pairs][slot_floats], indexed by the pair that finishes the tile; zero between launches
+  uint32_t* counters;      // [pairs][2] (finishing pair, CTA rank); zero between launches
+};
+
+struct Segment {
+  int tile, kb_begin, kb_end;
+  int sk_tile;             // index of the tile inside the stream-K region, -1 for a whole tile dealt round-robin
+};
+
+// A pair's work: first its contiguous range [lo, hi) of the stream-K region's K blocks, from the top (the
+// beginning of its last tile, whole tiles, the end of its first tile), then its whole tiles pair, pair + pairs, ...
+// of the round-robin region, so that the pairs running at the same time work on neighbouring tiles there.
+struct PairWork {
+  int lo, u_hi, total_kb, sk_tile0, dp_next, dp_tiles, stride;
+  __device__ PairWork(const GemmParams& p, const StreamK& sk, int pair, int num_pairs, int kb_per_tile) {
+    total_kb = kb_per_tile;
+    lo = min(pair * sk.units_per_pair, sk.sk_units);
+    u_hi = min(lo + sk.units_per_pair, sk.sk_units);
+    sk_tile0 = sk.dp_tiles;
+    dp_next = pair;
+    dp_tiles = sk.dp_tiles;
+    stride = num_pairs;
+  }
+  __device__ bool any() const { return u_hi > lo || dp_next < dp_tiles; }
+  __device__ bool next(Segment& sg) {
+    if (u_hi > lo) {
+      sg.sk_tile = (u_hi - 1) / total_kb;
+      const int t0 = sg.sk_tile * total_kb;
+      const int seg_lo = lo > t0 ? lo : t0;
+      sg.kb_begin = seg_lo - t0;
+      sg.kb_end = u_hi - t0;
+      sg.tile = sk_tile0 + sg.sk_tile;
+      u_hi = seg_lo;
+      return true;
+    }
+    if (dp_next < dp_tiles) {
+      sg.tile = dp_next;
+      sg.sk_tile = -1;
+      sg.kb_begin = 0;
+      sg.kb_end = total_kb;
+      dp_next += stride;
+      return true;
+    }
+    return false;
+  }
+};
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tile_a, int& tile_b) {
+  tile_b = tile / p.tiles_a;            // consecutive tiles walk the A (row) tiles and share the B tile
+  tile_a = tile - tile_b * p.tiles_a;
+}
+__device__ __forceinline__ void red_add_f32x4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                         const GemmParams p) {
+                         const GemmParams p, const StreamK sk, const __grid_constant__ TpPush push) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+  grid_dep_launch();
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr uint32_t a_bytes = kBM * kBK * 2;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);   // used in the leader
+  const uint32_t half_bn = static_cast<uint32_t>(p.bn) >> 1;
+  const uint32_t stage_bytes = a_bytes + half_bn * kBK * 2;      // this CTA's share of a K block
+  const uint32_t nstages = static_cast<uint32_t>(p.stages);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(nstages) * stage_bytes);   // used in the leader
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* acc_full = empty_bar + kMaxStages;
   uint64_t* acc_empty = acc_full + 2;                                                       // used in the leader
@@ -414,11 +554,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const uint32_t rank = cluster_ctarank();
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int total_work = p.tiles_a * p.tiles_b * p.splits;
   const int total_kb = (p.k + kBK - 1) / kBK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kPairStages; ++s) {
+    for (uint32_t s = 0; s < nstages; ++s) {
       mbar_init(&full_bar[s], 2);       // one arrive.expect_tx from each CTA's producer
       mbar_init(&empty_bar[s], 1);
     }
@@ -437,6 +576,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  grid_dep_wait();
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
@@ -444,36 +584,45 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       prefetch_tensormap(&map_a);
       prefetch_tensormap(&map_b);
       const uint64_t hint = l2_policy_evict_normal();
-      uint32_t it = 0;
-      for (int w = pair; w < total_work && !*abort_flag; w += num_pairs) {
-        const WorkItem wi = decode_work(p, w);
-        const int kb_begin = wi.split * p.k_blocks_per_split;
-        const int kb_end = min(kb_begin + p.k_blocks_per_split, total_kb);
-        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
-          const uint32_t s = it % kPairStages;
-          const uint32_t round = it / kPairStages;
+      uint32_t s = 0, round = 0;
+      const uint32_t leader_full0 = map_to_cta(smem_u32(&full_bar[0]), 0);
+      PairWork work(p, sk, pair, num_pairs, total_kb);
+      Segment sg;
+      while (!*abort_flag && work.next(sg)) {
+        int tile_a, tile_b;
+        tile_coords(p, sg.tile, tile_a, tile_b);
+        const int ya = tile_a * 256 + static_cast<int>(rank) * kBM;
+        const int yb = tile_b * p.bn + static_cast<int>(rank * half_bn);
+        for (int kb = sg.kb_begin; kb < sg.kb_end; ++kb) {
           if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
             report_status(p.status, kGemmKernelId, kWaitEmptyTimeout);
             *abort_flag = 1;
             break;
           }
-          uint8_t* sa = smem + static_cast<size_t>(s) * kPairStageBytes;
-          const uint32_t leader_full = map_to_cta(smem_u32(&full_bar[s]), 0);
-          mbar_expect_tx_cluster(leader_full, kPairStageBytes);
-          tma_load_2d_pair(sa, &map_a, leader_full, kb * kBK, wi.tile_a * 256 + static_cast<int>(rank) * kBM, hint);
-          tma_load_2d_pair(sa + a_bytes, &map_b, leader_full, kb * kBK,
-                           wi.tile_b * 256 + static_cast<int>(rank) * kBM, hint);
+          uint8_t* sa = smem + static_cast<size_t>(s) * stage_bytes;
+          const uint32_t leader_full = leader_full0 + s * 8;
+          mbar_expect_tx_cluster(leader_full, stage_bytes);
+          tma_load_2d_pair(sa, &map_a, leader_full, kb * kBK, ya, hint);
+          tma_load_2d_pair(sa + a_bytes, &map_b, leader_full, kb * kBK, yb, hint);
+          if (++s == nstages) {
+            s = 0;
+            ++round;
+          }
         }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer (leader CTA only) ----------------
     if (lane == 0 && rank == 0) {
-      uint32_t it = 0, t = 0;
-      for (int w = pair; w < total_work && !*abort_flag; w += num_pairs, ++t) {
-        const WorkItem wi = decode_work(p, w);
-        const int kb_begin = wi.split * p.k_blocks_per_split;
-        const int kb_end = min(kb_begin + p.k_blocks_per_split, total_kb);
+      uint32_t t = 0, s = 0, parity = 0;
+      const uint64_t desc_a0 = umma_desc_sw128(smem_u32(smem));
+      const uint64_t desc_b0 = umma_desc_sw128(smem_u32(smem) + a_bytes);
+      const uint32_t idesc = p.idesc;
+      const uint32_t empty0_cta0 = map_to_cta(smem_u32(&empty_bar[0]), 0);
+      const uint32_t empty0_cta1 = map_to_cta(smem_u32(&empty_bar[0]), 1);
+      PairWork work(p, sk, pair, num_pairs, total_kb);
+      Segment sg;
+      for (; !*abort_flag && work.next(sg); ++t) {
         const uint32_t buf = t & 1, use = t >> 1;
         if (use > 0 && !mbar_wait(&acc_empty[buf], (use - 1) & 1)) {
           report_status(p.status, kGemmKernelId, kWaitAccumTimeout);
@@ -481,26 +630,28 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           break;
         }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * 256;
-        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
-          const uint32_t s = it % kPairStages;
-          const uint32_t round = it / kPairStages;
-          if (!mbar_wait(&full_bar[s], round & 1)) {
+        const uint32_t d_tmem = tmem_base + buf * kPairAccStride;
+        uint32_t accumulate = 0;
+        for (int kb = sg.kb_begin; kb < sg.kb_end; ++kb) {
+          if (!mbar_wait(&full_bar[s], parity)) {
             report_status(p.status, kGemmKernelId, kWaitFullTimeout);
             *abort_flag = 1;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + static_cast<size_t>(s) * kPairStageBytes);
-          const uint32_t sb = sa + a_bytes;
+          const uint64_t soff = static_cast<uint64_t>((s * stage_bytes) >> 4);
 #pragma unroll
           for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
-            umma_bf16_pair(d_tmem, umma_desc_sw128(sa + kk * kUmmaK * 2), umma_desc_sw128(sb + kk * kUmmaK * 2),
-                           p.idesc, (kb > kb_begin || kk > 0) ? 1u : 0u);
+            umma_bf16_pair(d_tmem, desc_a0 + soff + kk * 2, desc_b0 + soff + kk * 2, idesc, accumulate);
+            accumulate = 1;
           }
           // the stage is free in both CTAs once these MMAs have read it
-          umma_commit_pair(map_to_cta(smem_u32(&empty_bar[s]), 0));
-          umma_commit_pair(map_to_cta(smem_u32(&empty_bar[s]), 1));
+          umma_commit_pair(empty0_cta0 + s * 8);
+          umma_commit_pair(empty0_cta1 + s * 8);
+          if (++s == nstages) {
+            s = 0;
+            parity ^= 1;
+          }
         }
         umma_commit_pair(map_to_cta(smem_u32(&acc_full[buf]), 0));
         umma_commit_pair(map_to_cta(smem_u32(&acc_full[buf]), 1));
@@ -509,71 +660,114 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   } else {
     // ---------------- epilogue (both CTAs, own 128 accumulator rows) ----------------
     const int quarter = warp & 3;
+    const int nchunks = (p.bn + 31) >> 5;
+    const int row_in_tile = static_cast<int>(rank) * kBM + quarter * 32 + lane;
     uint32_t t = 0;
-    for (int w = pair; w < total_work; w += num_pairs, ++t) {
-      const WorkItem wi = decode_work(p, w);
+    bool dead = false;      // a wait ran out: no more data work, but this warp keeps meeting the others at the barriers
+    PairWork work(p, sk, pair, num_pairs, total_kb);
+    const bool has_work = work.any();
+    Segment sg;
+    for (; work.next(sg); ++t) {
+      int tile_a, tile_b;
+      tile_coords(p, sg.tile, tile_a, tile_b);
       const uint32_t buf = t & 1, use = t >> 1;
-      bool ok = mbar_wait(&acc_full[buf], use & 1);
-      if (!ok) {
-        report_status(p.status, kGemmKernelId, kWaitAccumTimeout);
-        *abort_flag = 1;
+      const bool contributes = sg.kb_end < total_kb;                  // the tile's end belongs to another pair
+      const bool finishes = !contributes && sg.kb_begin > 0;          // other pairs hold the tile's beginning
+      if (!dead) {
+        bool ok = mbar_wait(&acc_full[buf], use & 1);
+        if (!ok) {
+          report_status(p.status, kGemmKernelId, kWaitAccumTimeout);
+          *abort_flag = 1;
+        }
+        tc_fence_after_sync();
+        // warp-uniform: the aligned TMEM loads below must be executed by all 32 lanes or none
+        dead = !__all_sync(0xffffffffu, ok && (*abort_flag == 0));
       }
-      tc_fence_after_sync();
-      ok = __all_sync(0xffffffffu, ok && (*abort_flag == 0));
-      if (!ok) break;
-      const int a_row = wi.tile_a * 256 + static_cast<int>(rank) * kBM + quarter * 32 + lane;
-      const uint32_t lane_addr = tmem_base + buf * 256 + (static_cast<uint32_t>(quarter * 32) << 16);
-      const int b0 = wi.tile_b * 256;
-      for (int c = 0; c < 256; c += 16) {
-        uint32_t r[16];
-        tmem_ld16(lane_addr + static_cast<uint32_t>(c), r);
-        tmem_ld_wait();
-        const int col = b0 + c;
-        if (a_row >= p.rows_a || col >= p.rows_b) continue;
-        if (p.act) {
-          if (col + 16 <= p.rows_b) {
-            float ov[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float gte = __uint_as_float(r[j]);
-              ov[j] = gte / (1.f + __expf(-gte)) * __uint_as_float(r[8 + j]);
+      if (!dead) {
+        const int a_row = tile_a * 256 + row_in_tile;
+        const uint32_t lane_addr = tmem_base + buf * kPairAccStride + (static_cast<uint32_t>(quarter * 32) << 16);
+        const int b0 = tile_b * p.bn;
+        const int b_end = min(p.rows_b, b0 + p.bn);
+        // The pair that holds the tile's last K block finishes the tile; its slot collects the others' sums.
+        // Slot layout: [32-column chunk][4-float group j][256 rows][4 floats]: the 32 rows of a warp are
+        // consecutive 16-byte pieces, so every vector access of a warp is 512 contiguous bytes.
+        const int fin_pair = finishes ? pair : ((sg.sk_tile + 1) * total_kb - 1) / sk.units_per_pair;
+        float* slot = sk.slots + static_cast<size_t>(fin_pair) * sk.slot_floats;
+        if (finishes) {
+          const int first_pair = (sg.sk_tile * total_kb) / sk.units_per_pair;
+          const uint32_t want = static_cast<uint32_t>(pair - first_pair);
+          const uint32_t* ctr = sk.counters + 2 * pair + rank;
+          if (lane == 0) {
+            const unsigned long long t0 = global_timer_ns();
+            while (ld_acquire_gpu(ctr) < want) {
+              if (global_timer_ns() - t0 > kDefaultWaitNs) {
+                report_status(p.status, kGemmKernelId, kWaitAccumTimeout);
+                break;
+              }
+              __nanosleep(64);
             }
-            uint4 v0;
-            v0.x = pack_bf16(ov[0], ov[1]);
-            v0.y = pack_bf16(ov[2], ov[3]);
-            v0.z = pack_bf16(ov[4], ov[5]);
-            v0.w = pack_bf16(ov[6], ov[7]);
-            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(a_row) * p.ldc +
-                                      (col >> 1)) = v0;
           }
-        } else if (p.out_fp32) {
-          float* o = static_cast<float*>(p.out) + static_cast<size_t>(wi.split) * p.split_stride +
-                     static_cast<size_t>(a_row) * p.ldc + col;
-          for (int j = 0; j < 16; ++j)
-            if (col + j < p.rows_b) o[j] = __uint_as_float(r[j]);
-        } else {
-          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(a_row) * p.ldc + col;
-          if (col + 16 <= p.rows_b && (p.ldc & 7) == 0) {
-            uint4 v0, v1;
-            v0.x = pack_bf16(__uint_as_float(r[0]), __uint_as_float(r[1]));
-            v0.y = pack_bf16(__uint_as_float(r[2]), __uint_as_float(r[3]));
-            v0.z = pack_bf16(__uint_as_float(r[4]), __uint_as_float(r[5]));
-            v0.w = pack_bf16(__uint_as_float(r[6]), __uint_as_float(r[7]));
-            v1.x = pack_bf16(__uint_as_float(r[8]), __uint_as_float(r[9]));
-            v1.y = pack_bf16(__uint_as_float(r[10]), __uint_as_float(r[11]));
-            v1.z = pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13]));
-            v1.w = pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15]));
-            *reinterpret_cast<uint4*>(o) = v0;
-            *reinterpret_cast<uint4*>(o + 8) = v1;
-          } else {
-            for (int j = 0; j < 16; ++j)
-              if (col + j < p.rows_b) o[j] = __float2bfloat16(__uint_as_float(r[j]));
+          __syncwarp();
+        }
+        uint32_t ra[32], rb[32];
+        tmem_ld32(lane_addr, ra);
+        for (int ch = 0; ch < nchunks; ch += 2) {
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            if (ch + half < nchunks) {
+              uint32_t(&r)[32] = half == 0 ? ra : rb;
+              uint32_t(&rn)[32] = half == 0 ? rb : ra;
+              tmem_ld_wait();
+              tmem_ld_fence_regs(r);
+              if (ch + half + 1 < nchunks) tmem_ld32(lane_addr + static_cast<uint32_t>((ch + half + 1) * 32), rn);
+              float* sl = slot + (static_cast<size_t>(ch + half) * 8 * 256 + row_in_tile) * 4;
+              if (contributes) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  red_add_f32x4(sl + j * 1024, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+              } else {
+                if (finishes) {
+                  float4 v[8];
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) v[j] = ld_cg_f4(reinterpret_cast<const float4*>(sl + j * 1024));
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    *reinterpret_cast<float4*>(sl + j * 1024) = make_float4(0.f, 0.f, 0.f, 0.f);   // for the next launch
+                    r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v[j].x);
+                    r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v[j].y);
+                    r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v[j].z);
+                    r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v[j].w);
+                  }
+                }
+                store_row32(p, push, a_row, b0 + (ch + half) * 32, b_end, 0, r);
+              }
+            }
           }
         }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+      if (contributes || finishes) {
+        // all four epilogue warps of this CTA are done with the slot / the counter (also after a failed wait:
+        // the other pairs' waits must still end, the status word says that the numbers are not to be used)
+        __threadfence();
+        named_barrier(2, 128);
+        if (threadIdx.x == 64) {
+          const int fin_pair = finishes ? pair : ((sg.sk_tile + 1) * total_kb - 1) / sk.units_per_pair;
+          uint32_t* ctr = sk.counters + 2 * fin_pair + rank;
+          if (contributes)
+            red_release_gpu_add(ctr, 1u);
+          else
+            *reinterpret_cast<volatile uint32_t*>(ctr) = 0u;     // ready for the next launch
+        }
+      }
+    }
+    if (push.enabled && has_work) {
+      named_barrier(1, 128);
+      const int et = static_cast<int>(threadIdx.x) - 64;
+      if (et < push.comm.world) tp_push_signal_tiles(push, et);
     }
   }
 
@@ -585,6 +779,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     tc_fence_after_sync();
     tmem_dealloc_pair(tmem_base, 512);
   }
+  if (push.enabled) tp_push_tail<kTailMaxVec>(push);
 }
 
 // out[m, n] = sum_s partial[s, m, n], rounded to bf16.
@@ -695,18 +890,50 @@ using namespace xv;
 
 static bool g_disable_pair = false;
 
-extern "C" {
+namespace {
 
-// Test hook: 1 forces the single-CTA kernel for every shape (A/B comparisons), 0 restores.
-void xv_gemm_disable_pair(int disable) { g_disable_pair = disable != 0; }
+constexpr int kMaxDevices = 64;
 
-// Chooses orientation, tile and split-K for a problem; fills *plan. Pure host arithmetic so
-// callers (and CPU tests) can size the workspace before launching.
-static int gemm_plan_impl(int m, int n, int k, int num_sms, XvGemmPlan* plan, bool allow_pair) {
-  if (m <= 0 || n <= 0 || k <= 0 || (k % 8) != 0) return XV_ERR_SHAPE;
-  if (num_sms <= 0) num_sms = 148;
-  XvGemmPlan pl;
-  std::memset(&pl, 0, sizeof(pl));
+struct PlanOverride {
+  int active, kind, bn, splits, stages;
+};
+PlanOverride g_override = {0, 0, 0, 0, 0};
+
+constexpr unsigned kPlanNoPair = 1u;     // single-CTA kernels only
+constexpr unsigned kPlanNoSplit = 2u;    // the caller cannot take fp32 partial planes
+
+struct PlanKey {
+  int m, n, k, sms;
+  unsigned flags;
+  int max_splits;
+  bool operator==(const PlanKey& o) const {
+    return m == o.m && n == o.n && k == o.k && sms == o.sms && flags == o.flags && max_splits == o.max_splits;
+  }
+};
+struct PlanKeyHash {
+  size_t operator()(const PlanKey& k) const {
+    size_t h = static_cast<size_t>(k.m) * 0x9E3779B97F4A7C15ULL;
+    h ^= static_cast<size_t>(k.n) * 0xC2B2AE3D27D4EB4FULL + (h << 6) + (h >> 2);
+    h ^= static_cast<size_t>(k.k) * 0x165667B19E3779F9ULL + (h << 6) + (h >> 2);
+    h ^= static_cast<size_t>(k.sms * 131 + k.flags * 7 + k.max_splits) + (h << 6) + (h >> 2);
+    return h;
+  }
+};
+
+int env_int(const char* name, int dflt) {
+  const char* e = std::getenv(name);
+  return e ? std::atoi(e) : dflt;
+}
+
+void fill_single_smem(XvGemmPlan& pl, int stages) {
+  const int stage_bytes = kBM * kBK * 2 + pl.bn * kBK * 2;
+  pl.stages = stages;
+  pl.smem_bytes = stages * stage_bytes + 256 + (pl.swapped ? kStagingBytes : 0) + 1024;
+}
+
+// Swapped (weights on the MMA M axis) or normal single-CTA plan, with split-K when the output tiles
+// alone cannot occupy the machine.
+void plan_single(int m, int n, int k, int num_sms, unsigned flags, int max_splits, XvGemmPlan& pl) {
   const int total_kb = (k + kBK - 1) / kBK;
   if (m <= 256) {
     pl.swapped = 1;
@@ -725,93 +952,275 @@ static int gemm_plan_impl(int m, int n, int k, int num_sms, XvGemmPlan* plan, bo
   const int stage_bytes = kBM * kBK * 2 + pl.bn * kBK * 2;
   // small-token tiles leave room for two resident CTAs per SM (more loads in flight while
   // another CTA drains its epilogue); big tiles take the whole SM
-  const int smem_budget = (pl.swapped && pl.bn <= 128) ? 100 * 1024 : 200 * 1024;
-  int stages = smem_budget / stage_bytes;
+  const int extra = 256 + (pl.swapped ? kStagingBytes : 0) + 1024;
+  const int smem_budget = (pl.swapped && pl.bn <= 128) ? 112 * 1024 : 220 * 1024;
+  int stages = (smem_budget - extra) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) stages = 2;
-  const int smem_bytes = stages * stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  pl.ctas_per_sm = (smem_bytes <= 110 * 1024 && 2 * pow2_cols(pl.bn) <= 256) ? 2 : 1;
-  // Split K when the output tiles alone cannot occupy the machine. Bounds: at least 4 K blocks
-  // per split, at most 16 splits, and fp32 partials (written and read back once) no larger
-  // than about a quarter of the weight bytes.
+  const int smem_bytes = stages * stage_bytes + extra;
+  pl.ctas_per_sm = (smem_bytes <= 113 * 1024 && 2 * pow2_cols(pl.bn) <= 256) ? 2 : 1;
+  // Split K bounds: at least 4 K blocks per split, at most 16 splits, and fp32 partials (written and
+  // read back once) no larger than about a quarter of the weight bytes or 16 MB (they stay in L2).
   const int slots = num_sms * pl.ctas_per_sm;
   int splits = 1;
-  if (tiles < num_sms) {
+  if (tiles < num_sms && !(flags & kPlanNoSplit)) {
     splits = slots / tiles;
-    // partial planes cost splits * m * n * 4 bytes written and read back: allow them up to a quarter of
-    // the weight bytes, or up to 16 MB in absolute terms (they stay in the 126 MB L2), whichever is more
     int by_traffic = k / (8 * m) > 1 ? k / (8 * m) : 1;
     const long long plane = static_cast<long long>(m) * n * 4;
     const int by_bytes = static_cast<int>((16ll << 20) / (plane > 0 ? plane : 1));
     if (by_bytes > by_traffic) by_traffic = by_bytes;
     if (splits > by_traffic) splits = by_traffic;
     while (splits > 1 && total_kb / splits < 4) --splits;
-    static const int max_splits = [] {
-      const char* e = std::getenv("XV_GEMM_MAX_SPLITS");      // experiment knob: cap on split-K
-      return e ? std::atoi(e) : 16;
-    }();
-    if (splits > max_splits) splits = max_splits;
+    static const int env_max = env_int("XV_GEMM_MAX_SPLITS", 16);      // experiment knob: cap on split-K
+    if (splits > env_max) splits = env_max;
     if (splits > 16) splits = 16;
+    if (max_splits > 0 && splits > max_splits) splits = max_splits;
     if (splits < 1) splits = 1;
   }
   pl.k_blocks_per_split = (total_kb + splits - 1) / splits;
   pl.splits = (total_kb + pl.k_blocks_per_split - 1) / pl.k_blocks_per_split;
   if (stages > pl.k_blocks_per_split && pl.k_blocks_per_split >= 2) stages = pl.k_blocks_per_split;
-  pl.stages = stages;
-  pl.smem_bytes = stages * stage_bytes + 1024 + 256;
+  fill_single_smem(pl, stages);
   pl.workspace_bytes = pl.splits > 1 ? static_cast<long long>(pl.splits) * m * n * 4 : 0;
-  // CTA pairs (256 x 256 tiles, cta_group::2) instead of the plan above? Both kernels are persistent with one
-  // tile per SM (pair of SMs), so time goes in whole waves, and a pair tile takes about 0.88 of the time of a
-  // 128 x 256 tile (measured: 35 us against 39 us at K = 4096). Pairs win unless they need more waves
-  // (M = 1100, N = 4096: 80 pair tiles on 74 pairs are two waves, 144 single tiles on 148 SMs one: measured 156
-  // against 109 us). With fewer pair tiles than SM pairs they still win by 5-13 % (M = 384..832, N = 4096 or 6144)
-  // as long as the single-CTA plan would not split K; where it does (M <= 512 with K = 12288), split-K is faster.
-  if (!pl.swapped && allow_pair && n >= 256) {
-    const int pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
-    const int pair_waves = (pair_tiles + num_sms / 2 - 1) / (num_sms / 2);
-    const int single_waves = (tiles + num_sms - 1) / num_sms;
-    const bool enough = pair_tiles >= num_sms / 2 || (pl.splits == 1 && pair_tiles >= 24);
-    if (enough && pair_waves * 0.88 <= single_waves) {
-      pl.pair = 1;
-      pl.bn = 256;
-      pl.tiles_a = (m + 255) / 256;
-      pl.tiles_b = (n + 255) / 256;
-      pl.splits = 1;
-      pl.k_blocks_per_split = total_kb;
-      pl.stages = kPairStages;
-      pl.smem_bytes = kPairSmem;
-      pl.ctas_per_sm = 1;
-      pl.workspace_bytes = 0;
+}
+
+// CTA-pair plan: 256 x bn tiles. Whole waves of tiles are dealt round-robin; the rest (`sk_tiles` at the
+// end of the tile order) is dealt in contiguous ranges of `units_per_pair` K blocks (stream-K). The last
+// whole wave joins the stream-K region when that evens the pairs' loads out better. bn <= 0 picks the
+// widest tile that splits N evenly; units_override: > 0 fixes the range length, < 0 deals whole tiles only.
+void fill_pair(int m, int n, int k, int bn, int num_sms, int units_override, XvGemmPlan& pl) {
+  const int total_kb = (k + kBK - 1) / kBK;
+  if (bn <= 0) {
+    const int tiles_b = (n + 255) / 256;
+    bn = round_up((n + tiles_b - 1) / tiles_b, 16);
+  }
+  if (bn > 256) bn = 256;
+  if (bn < 16) bn = 16;
+  pl.pair = 1;
+  pl.swapped = 0;
+  pl.bn = bn;
+  pl.tiles_a = (m + 255) / 256;
+  pl.tiles_b = (n + bn - 1) / bn;
+  pl.splits = 1;
+  pl.k_blocks_per_split = total_kb;
+  const int stage_bytes = kBM * kBK * 2 + (bn / 2) * kBK * 2;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  pl.stages = stages;
+  pl.smem_bytes = stages * stage_bytes + 256 + 1024;
+  pl.ctas_per_sm = 1;
+  const int pairs = num_sms / 2;
+  const int tiles = pl.tiles_a * pl.tiles_b;
+  const int min_units = (total_kb + 1) / 2;          // at most three pairs share a tile
+  const int waves = tiles / pairs, rest = tiles % pairs;
+  pl.sk_tiles = 0;
+  pl.units_per_pair = 0;
+  pl.workspace_bytes = 0;
+  if (units_override < 0 || rest == 0 || total_kb < 16) return;         // whole tiles only (short K: the fix-up would cost more than it evens out)
+  // K blocks on the busiest pair: whole waves, then the stream-K region's ranges
+  auto range_len = [&](int sk_tiles) {
+    long long u = (static_cast<long long>(sk_tiles) * total_kb + pairs - 1) / pairs;
+    if (u < min_units) u = min_units;
+    if (u > static_cast<long long>(sk_tiles) * total_kb) u = static_cast<long long>(sk_tiles) * total_kb;
+    return static_cast<int>(u);
+  };
+  int sk_tiles = rest;
+  int u = range_len(rest);
+  if (waves >= 1) {
+    const int u2 = range_len(rest + pairs);
+    if ((waves - 1) * total_kb + u2 < waves * total_kb + u) {
+      sk_tiles = rest + pairs;
+      u = u2;
     }
   }
+  if (units_override > 0) {
+    u = units_override < min_units ? min_units : units_override;
+    const long long need = (static_cast<long long>(sk_tiles) * total_kb + u - 1) / u;
+    if (need > pairs) u = range_len(sk_tiles);
+  }
+  if (u >= total_kb && u % total_kb == 0 && static_cast<long long>(sk_tiles) * total_kb <= static_cast<long long>(u) * pairs &&
+      sk_tiles <= pairs * (u / total_kb) && (sk_tiles % pairs == 0))
+    return;                                                                 // the ranges are whole tiles anyway
+  pl.sk_tiles = sk_tiles;
+  pl.units_per_pair = u;
+  const int chunks = (bn + 31) / 32;
+  pl.workspace_bytes = static_cast<long long>(pairs) * chunks * 256 * 32 * 4 + kSkCounterBytes;
+}
+
+std::unordered_map<PlanKey, XvGemmPlan, PlanKeyHash> g_plan_cache;
+std::mutex g_plan_mu;
+
+// Chooses kernel, orientation, tile and split-K for a problem. Pure host arithmetic so callers (and
+// CPU tests) can size the workspace before launching.
+int gemm_plan_impl(int m, int n, int k, int num_sms, XvGemmPlan* plan, unsigned flags, int max_splits) {
+  if (m <= 0 || n <= 0 || k <= 0 || (k % 8) != 0) return XV_ERR_SHAPE;
+  if (num_sms <= 0) num_sms = 148;
+  if (g_disable_pair) flags |= kPlanNoPair;
+  const PlanKey key{m, n, k, num_sms, flags, max_splits};
+  if (!g_override.active) {
+    std::lock_guard<std::mutex> g(g_plan_mu);
+    auto it = g_plan_cache.find(key);
+    if (it != g_plan_cache.end()) {
+      *plan = it->second;
+      return 0;
+    }
+  }
+  XvGemmPlan pl;
+  std::memset(&pl, 0, sizeof(pl));
+  if (g_override.active) {
+    // test and tuning hook: a fixed kernel / tile / split instead of the planner's choice
+    const int total_kb = (k + kBK - 1) / kBK;
+    int sp = g_override.splits > 0 ? g_override.splits : 1;
+    if (sp > total_kb) sp = total_kb;
+    if (g_override.kind == 2) {
+      // `splits` of the hook means K blocks per pair in the stream-K region (0: planner, -1: whole tiles only)
+      const int bn = g_override.bn > 0 ? round_up(g_override.bn, 16) : 0;
+      fill_pair(m, n, k, bn, num_sms, g_override.splits, pl);
+      if (g_override.stages > 1 && g_override.stages <= pl.stages) {
+        pl.smem_bytes -= (pl.stages - g_override.stages) * (kBM * kBK * 2 + (pl.bn / 2) * kBK * 2);
+        pl.stages = g_override.stages;
+      }
+    } else {
+      plan_single(m, n, k, num_sms, flags | kPlanNoSplit, 0, pl);
+      if (g_override.kind == 1 && m <= 256) {       // normal orientation for a small batch
+        pl.swapped = 0;
+        pl.bn = n >= 256 ? 256 : round_up(n, 16);
+        pl.tiles_a = (m + kBM - 1) / kBM;
+        pl.tiles_b = (n + pl.bn - 1) / pl.bn;
+      }
+      if (g_override.bn > 0 && !pl.swapped) {
+        pl.bn = round_up(g_override.bn > 256 ? 256 : g_override.bn, 16);
+        pl.tiles_b = (n + pl.bn - 1) / pl.bn;
+      }
+      pl.k_blocks_per_split = (total_kb + sp - 1) / sp;
+      pl.splits = (total_kb + pl.k_blocks_per_split - 1) / pl.k_blocks_per_split;
+      const int stage_bytes = kBM * kBK * 2 + pl.bn * kBK * 2;
+      int stages = g_override.stages > 1 ? g_override.stages : (200 * 1024) / stage_bytes;
+      if (stages > kMaxStages) stages = kMaxStages;
+      while (stages > 2 && stages * stage_bytes + 256 + kStagingBytes + 1024 > 222 * 1024) --stages;
+      fill_single_smem(pl, stages);
+      pl.ctas_per_sm = (pl.smem_bytes <= 113 * 1024 && 2 * pow2_cols(pl.bn) <= 256) ? 2 : 1;
+      pl.workspace_bytes = pl.splits > 1 ? static_cast<long long>(pl.splits) * m * n * 4 : 0;
+    }
+    *plan = pl;
+    return 0;
+  }
+  plan_single(m, n, k, num_sms, flags, max_splits, pl);
+  // CTA pairs (cta_group::2, 256-row tiles) instead? Measured on a B200 (bench/gemm_sweep.py): a pair's K block
+  // takes 0.30 us + 0.55 ns per tile column almost independently of the shape (the operand stream from L2
+  // bounds it, not the MMA), pairs work in waves of SMs / 2 tiles, so the tile width is picked to make the
+  // tile count fit the waves; among equal costs the wider tile wins (fewer operand bytes per FLOP).
+  //  * above 256 rows the pairs beat lone CTAs on every measured shape;
+  //  * from 161 to 256 rows (a decode batch) the swapped single-CTA kernel with split-K wins unless there
+  //    are enough output columns for the pairs to fill the machine without splitting K.
+  static const int pair_min_m = env_int("XV_GEMM_PAIR_MIN_M", 161);
+  static const int streamk = env_int("XV_GEMM_STREAMK", 0);
+  const int total_kb = (k + kBK - 1) / kBK;
+  if (!(flags & kPlanNoPair) && m >= pair_min_m && n >= 64 && (m > 256 || (n >= 6144 && total_kb <= 80))) {
+    const int pairs = num_sms / 2;
+    const int tiles_a = (m + 255) / 256;
+    double best = 1e30, widest = 0.0;
+    int best_bn = 256;
+    for (int bn = 256; bn >= 96; bn -= 16) {
+      if (bn > round_up(n, 16) && bn != 256) continue;
+      const int tiles = tiles_a * ((n + bn - 1) / bn);
+      const int waves = (tiles + pairs - 1) / pairs;
+      const double cost = waves * (total_kb * (0.30 + 0.00055 * bn) + 1.5);
+      if (bn == 256) widest = cost;
+      // a narrower tile has to win by more than the run-to-run spread of the measurements
+      if (cost < best && (bn == 256 || cost < 0.94 * widest)) {
+        best = cost;
+        best_bn = bn;
+      }
+    }
+    if (n < 256) best_bn = round_up(n, 16);
+    std::memset(&pl, 0, sizeof(pl));
+    fill_pair(m, n, k, best_bn, num_sms, streamk ? 0 : -1, pl);
+  }
   *plan = pl;
+  std::lock_guard<std::mutex> g(g_plan_mu);
+  if (g_plan_cache.size() > (1u << 18)) g_plan_cache.clear();
+  g_plan_cache.emplace(key, pl);
   return 0;
 }
 
+bool g_attr_single[kMaxDevices] = {false};
+bool g_attr_pair[kMaxDevices] = {false};
+std::mutex g_attr_mu;
+
+// The opt-in to more than 48 KB of dynamic shared memory is a per-device property of a kernel.
+int ensure_smem_attr(bool pair) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return XV_ERR_DRIVER;
+  std::lock_guard<std::mutex> g(g_attr_mu);
+  bool* done = pair ? g_attr_pair : g_attr_single;
+  if (!done[dev]) {
+    const cudaError_t e =
+        pair ? cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024)
+             : cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+    if (e != cudaSuccess) return XV_ERR_LAUNCH;
+    done[dev] = true;
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Test hook: 1 forces the single-CTA kernel for every shape (A/B comparisons), 0 restores.
+void xv_gemm_disable_pair(int disable) { g_disable_pair = disable != 0; }
+
+// Test and tuning hook: kind 0 = single CTA, swapped where the planner would; 1 = single CTA, normal
+// orientation; 2 = CTA pairs. bn / splits / stages <= 0 keep that kernel's default. kind < 0 clears.
+void xv_gemm_plan_override(int kind, int bn, int splits, int stages) {
+  g_override.active = kind >= 0;
+  g_override.kind = kind;
+  g_override.bn = bn;
+  g_override.splits = splits;
+  g_override.stages = stages;
+}
+
 int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan) {
-  return gemm_plan_impl(m, n, k, num_sms, plan, !g_disable_pair);
+  return gemm_plan_impl(m, n, k, num_sms, plan, 0u, 0);
 }
 
 // Y[m,n] (bf16, row stride ldy) = X[m,k] (row stride ldx) * W[n,k]^T (row stride ldw).
 // `workspace` must hold plan.workspace_bytes when the plan splits K. `status` may be null.
+// Every argument is checked before the first launch.
 static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
                      long long ldy, void* workspace, long long workspace_bytes, int num_sms, int* status,
                      cudaStream_t stream, bool defer_reduce, int* splits_out, int act = 0,
-                     const TpTail* tail_in = nullptr) {
+                     const TpPush* push_in = nullptr, int push_max_splits = 1) {
   XvGemmPlan pl;
-  // the fused tensor-parallel tail lives in the single-CTA kernel
-  int rc = gemm_plan_impl(m, n, k, num_sms, &pl, tail_in == nullptr && !g_disable_pair);
+  if (num_sms <= 0) num_sms = 148;
+  unsigned flags = 0;
+  if (act && !defer_reduce) flags |= 0u;     // callers of the fused activation check the plan first
+  int rc = gemm_plan_impl(m, n, k, num_sms, &pl, flags, push_in ? push_max_splits : 0);
   if (rc) return rc;
   if ((ldx % 8) || (ldw % 8) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return XV_ERR_ALIGN;
-  if (pl.workspace_bytes > workspace_bytes || (pl.workspace_bytes && !workspace)) return XV_ERR_WORKSPACE;
+  // A workspace of at least twice the stream-K reserve has its tail set aside (and kept zero) for the pair
+  // kernel's partial tiles; split-K planes use the front part. Smaller workspaces are all planes and the
+  // pair kernel deals whole tiles (its pairs then finish unevenly).
+  const bool sk_ok = workspace != nullptr && workspace_bytes >= 2 * kSkReserveBytes;
+  if (pl.pair && pl.sk_tiles > 0 && (!sk_ok || pl.workspace_bytes > kSkReserveBytes))
+    fill_pair(m, n, k, pl.bn, num_sms, -1, pl);
+  const bool to_planes = pl.splits > 1 && push_in == nullptr;
+  if (to_planes && (!workspace || pl.workspace_bytes > (sk_ok ? workspace_bytes - kSkReserveBytes : workspace_bytes)))
+    return XV_ERR_WORKSPACE;
+  if (act && pl.splits > 1) return XV_ERR_UNSUPPORTED;       // callers check the plan first
+  if (act && ((n % 16) || (ldy % 8))) return XV_ERR_SHAPE;
+  if (to_planes && !defer_reduce && ldy != n) return XV_ERR_SHAPE;   // the reduce kernel writes a dense output
+  if (push_in != nullptr && ((n % 8) || pl.splits > push_max_splits)) return XV_ERR_SHAPE;
+  if ((rc = ensure_smem_attr(pl.pair != 0))) return rc;
 
   CUtensorMap map_a, map_b;
   GemmParams p;
   std::memset(&p, 0, sizeof(p));
   if (pl.pair) {
     if ((rc = get_tensor_map(&map_a, x, m, k, ldx, kBM))) return rc;
-    if ((rc = get_tensor_map(&map_b, w, n, k, ldw, kBM))) return rc;
+    if ((rc = get_tensor_map(&map_b, w, n, k, ldw, pl.bn / 2))) return rc;
     p.rows_a = m;
     p.rows_b = n;
     p.transposed = 0;
@@ -834,13 +1243,13 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
   p.k_blocks_per_split = pl.k_blocks_per_split;
   p.status = status;
   p.idesc = umma_idesc_bf16(pl.pair ? 256 : kBM, pl.bn);
-  p.acc_stride = pow2_cols(pl.bn);
+  p.acc_stride = pl.pair ? kPairAccStride : pow2_cols(pl.bn);
   p.tmem_cols = 2 * p.acc_stride;
   p.tiles_a = pl.tiles_a;
   p.tiles_b = pl.tiles_b;
   p.splits = pl.splits;
   p.a_fastest = pl.swapped ? 0 : 1;
-  if (pl.splits > 1) {
+  if (to_planes) {
     p.out = workspace;
     p.out_fp32 = 1;
     p.ldc = n;
@@ -851,61 +1260,77 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
     p.ldc = ldy;
     p.split_stride = 0;
     p.act = act;
-    if (act && ((n % 16) || (ldy % 8))) return XV_ERR_SHAPE;
+    p.vec_ok = (ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0) && (act || (n % 8) == 0);
   }
 
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
-    if (e != cudaSuccess) return XV_ERR_LAUNCH;
-    attr_set = true;
-  }
-  if (pl.pair) {
-    static bool pair_attr = false;
-    if (!pair_attr) {
-      if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024) !=
-          cudaSuccess)
-        return XV_ERR_LAUNCH;
-      pair_attr = true;
-    }
-    const int pairs_avail = (num_sms > 0 ? num_sms : 148) / 2;
-    const int work = pl.tiles_a * pl.tiles_b;
-    const int pairs = work < pairs_avail ? work : pairs_avail;
-    gemm_tcgen05_pair_kernel<<<2 * pairs, kGemmThreads, kPairSmem, stream>>>(map_a, map_b, p);
-    return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
-  }
+  TpPush push;
+  std::memset(&push, 0, sizeof(push));
   const int total_work = pl.tiles_a * pl.tiles_b * pl.splits;
-  int slots = (num_sms > 0 ? num_sms : 148) * pl.ctas_per_sm;
-  TpTail tail;
-  std::memset(&tail, 0, sizeof(tail));
-  int grid = total_work < slots ? total_work : slots;
-  if (tail_in) {
-    tail = *tail_in;
-    tail.enabled = 1;
-    tail.partials = static_cast<const float*>(workspace);
-    tail.splits = pl.splits;
-    tail.split_stride = p.split_stride;
-    // grid-wide barriers need every CTA resident at once
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_tcgen05_kernel, kGemmThreads, pl.smem_bytes) !=
-            cudaSuccess || per_sm < 1)
+  if (pl.pair) {
+    const int pairs_avail = num_sms / 2;
+    const int total_kb = (k + kBK - 1) / kBK;
+    const int tiles = pl.tiles_a * pl.tiles_b;
+    StreamK sk;
+    std::memset(&sk, 0, sizeof(sk));
+    sk.dp_tiles = tiles - pl.sk_tiles;
+    sk.sk_units = pl.sk_tiles * total_kb;
+    sk.units_per_pair = pl.sk_tiles > 0 ? pl.units_per_pair : 1;
+    int used_pairs = sk.dp_tiles < pairs_avail ? sk.dp_tiles : pairs_avail;
+    if (pl.sk_tiles > 0) {
+      const int sk_pairs = (sk.sk_units + sk.units_per_pair - 1) / sk.units_per_pair;
+      if (sk_pairs > pairs_avail) return XV_ERR_SHAPE;
+      if (sk_pairs > used_pairs) used_pairs = sk_pairs;
+      sk.slot_floats = ((pl.bn + 31) / 32) * 256 * 32;
+      char* tail = static_cast<char*>(workspace) + workspace_bytes - kSkReserveBytes;
+      sk.slots = reinterpret_cast<float*>(tail);
+      sk.counters = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + workspace_bytes - kSkCounterBytes);
+    }
+    int pairs = used_pairs;
+    if (push_in) {
+      push = *push_in;
+      push.enabled = 1;
+      push.splits = pl.splits;
+      // every CTA takes part in the row phase and waits for the others: the whole grid must be resident
+      int per_sm = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_tcgen05_pair_kernel, kGemmThreads,
+                                                        pl.smem_bytes) != cudaSuccess || per_sm < 1)
+        return XV_ERR_LAUNCH;
+      pairs = pairs_avail;
+      push.signal_ctas = 2 * used_pairs;
+    }
+    if (launch_pdl(gemm_tcgen05_pair_kernel, dim3(2 * pairs), dim3(kGemmThreads), pl.smem_bytes, stream, map_a, map_b,
+                   p, sk, push) != cudaSuccess)
       return XV_ERR_LAUNCH;
-    if (per_sm > pl.ctas_per_sm) per_sm = pl.ctas_per_sm;
-    slots = (num_sms > 0 ? num_sms : 148) * per_sm;
-    // all CTAs take part in the row phase, so launch the full resident grid even for few tiles
-    grid = slots;
-    if (grid > 4 * (tail.rows > total_work ? tail.rows : total_work)) grid = 4 * (tail.rows > total_work ? tail.rows : total_work);
-    if (grid > slots) grid = slots;
-    if (grid < 1) grid = 1;
+  } else {
+    int slots = num_sms * pl.ctas_per_sm;
+    int grid = total_work < slots ? total_work : slots;
+    if (push_in) {
+      push = *push_in;
+      push.enabled = 1;
+      push.splits = pl.splits;
+      int per_sm = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_tcgen05_kernel, kGemmThreads, pl.smem_bytes) !=
+              cudaSuccess || per_sm < 1)
+        return XV_ERR_LAUNCH;
+      if (per_sm > pl.ctas_per_sm) per_sm = pl.ctas_per_sm;
+      slots = num_sms * per_sm;
+      if (grid > slots) grid = slots;
+      // CTAs beyond the GEMM tiles take the rows this rank reduces
+      const int n_mine = push.two_shot ? (push.rows + push.comm.world - 1) / push.comm.world : push.rows;
+      grid = (total_work < slots ? total_work : slots) + n_mine;
+      if (grid > slots) grid = slots;
+      if (grid < 1) grid = 1;
+      push.signal_ctas = total_work < grid ? total_work : grid;
+    }
+    if (launch_pdl(gemm_tcgen05_kernel, dim3(grid), dim3(kGemmThreads), pl.smem_bytes, stream, map_a, map_b, p,
+                   push) != cudaSuccess)
+      return XV_ERR_LAUNCH;
   }
-  launch_pdl(gemm_tcgen05_kernel, dim3(grid), dim3(kGemmThreads), pl.smem_bytes, stream, map_a, map_b, p, tail);
   if (cudaGetLastError() != cudaSuccess) return XV_ERR_LAUNCH;
-  if (tail_in) return 0;
+  if (push_in) return 0;
   if (splits_out) *splits_out = pl.splits;
-  if (act && pl.splits > 1) return XV_ERR_UNSUPPORTED;   // callers check the plan first
-  if (pl.splits > 1 && !defer_reduce) {
+  if (to_planes && !defer_reduce) {
     const long long elems = static_cast<long long>(m) * n;
-    if (ldy != n) return XV_ERR_SHAPE;   // split-K output must be dense
     const int threads = 256;
     const long long blocks = (elems / 4 + threads) / threads;
     launch_pdl(splitk_reduce_kernel, dim3(static_cast<unsigned>(blocks)), dim3(threads), 0, stream,
@@ -922,42 +1347,55 @@ int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, lon
                    nullptr);
 }
 
-// RowParallel GEMM + all-reduce + residual add + RMSNorm as ONE kernel. The GEMM writes this
-// rank's partial [m, n] into its symmetric buffer at `buf_offset` (peer_bufs[rank]); the same
-// kernel then announces it to the peers, waits for theirs and finishes rows (see tp_fused.cu
-// for the flag protocol and the buffer-reuse rule). grid_sync: 2 zero-initialised uint32.
-int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long ldx, long long ldw, void* workspace,
-                    long long workspace_bytes, int num_sms, const void* const* peer_bufs, void* const* peer_flags,
-                    const void* mc_buf, void* epoch, int rank, int world, long long buf_offset, void* grid_sync,
+// RowParallel GEMM + cross-rank sum + residual add + RMSNorm as ONE kernel (push protocol, see
+// tp_device.cuh). The GEMM epilogue writes this rank's partial [m, n] into the slot array at
+// `slot_offset` (`slot_bytes` long) of the symmetric buffers of the ranks that reduce it.
+//   two_shot = 1: rank r reduces rows r, r + world, ...; `residual_in` / `residual_out` are local
+//                 [m, n] buffers of which only those rows are touched; the finished rows are broadcast to
+//                 byte offset `h_offset` of every rank's symmetric buffer (y_out unused).
+//   two_shot = 0: every rank reduces all rows into its local `y_out` (and `residual_out`).
+//   mode 0: residual_out = sum (+ residual_in, may be null); out = rmsnorm(residual_out) * norm_w.   mode 1: out = sum.
+// `epoch`: 32 uint32 words of local device memory, zero-initialised once (the kernels keep their counters'
+// history there). Returns XV_ERR_WORKSPACE when the slot array is too small for the problem.
+int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long ldx, long long ldw, int num_sms,
+                    const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf, void* epoch, int rank,
+                    int world, long long slot_offset, long long slot_bytes, int two_shot, long long h_offset,
                     const void* residual_in, void* residual_out, const void* norm_w, void* y_out, float eps, int mode,
                     unsigned spin_us, int* status, cudaStream_t stream) {
-  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || (n % 8) || n > 192 * 6 * 8 || (buf_offset & 15))
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || (n % 8) || n > kGemmThreads * kTailMaxVec * 8 ||
+      (slot_offset & 15) || (two_shot && (h_offset & 15)) || m <= 0)
     return XV_ERR_SHAPE;
-  TpTail tail;
-  std::memset(&tail, 0, sizeof(tail));
+  if (mode == 0 && (residual_out == nullptr || norm_w == nullptr)) return XV_ERR_SHAPE;
+  if (!two_shot && y_out == nullptr) return XV_ERR_SHAPE;
+  TpPush t;
+  std::memset(&t, 0, sizeof(t));
   for (int r = 0; r < kMaxRanks; ++r) {
-    tail.comm.peer_buf[r] = r < world ? peer_bufs[r] : nullptr;
-    tail.comm.peer_flags[r] = r < world ? static_cast<uint32_t*>(peer_flags[r]) : nullptr;
+    t.comm.peer_buf[r] = r < world ? peer_bufs[r] : nullptr;
+    t.comm.peer_flags[r] = r < world ? static_cast<uint32_t*>(peer_flags[r]) : nullptr;
   }
-  tail.comm.mc_buf = mc_buf;
-  tail.comm.epoch = static_cast<uint32_t*>(epoch);
-  tail.comm.rank = rank;
-  tail.comm.world = world;
-  tail.comm.spin_limit = spin_us;
-  tail.comm.status = status;
-  tail.buf_offset = buf_offset;
-  tail.residual_in = static_cast<const __nv_bfloat16*>(residual_in);
-  tail.residual_out = static_cast<__nv_bfloat16*>(residual_out);
-  tail.norm_w = static_cast<const __nv_bfloat16*>(norm_w);
-  tail.y = static_cast<__nv_bfloat16*>(y_out);
-  tail.rows = m;
-  tail.hidden = n;
-  tail.eps = eps;
-  tail.mode = mode;
-  tail.grid_sync = static_cast<uint32_t*>(grid_sync);
-  void* local = const_cast<char*>(static_cast<const char*>(peer_bufs[rank])) + buf_offset;
-  return gemm_impl(x, w, local, m, n, k, ldx, ldw, n, workspace, workspace_bytes, num_sms, status, stream, true,
-                   nullptr, 0, &tail);
+  t.comm.mc_buf = mc_buf;
+  t.comm.epoch = static_cast<uint32_t*>(epoch);
+  t.comm.rank = rank;
+  t.comm.world = world;
+  t.comm.spin_limit = spin_us;
+  t.comm.status = status;
+  t.two_shot = two_shot ? 1 : 0;
+  t.slot_offset = slot_offset;
+  t.cap_rows = two_shot ? (m + world - 1) / world : m;
+  t.h_offset = h_offset;
+  t.y = static_cast<__nv_bfloat16*>(y_out);
+  t.residual_in = static_cast<const __nv_bfloat16*>(residual_in);
+  t.residual_out = static_cast<__nv_bfloat16*>(residual_out);
+  t.norm_w = static_cast<const __nv_bfloat16*>(norm_w);
+  t.rows = m;
+  t.hidden = n;
+  t.eps = eps;
+  t.mode = mode;
+  const long long per_split = static_cast<long long>(world) * t.cap_rows * n * 2;
+  const long long max_splits = slot_bytes / per_split;
+  if (max_splits < 1) return XV_ERR_WORKSPACE;
+  return gemm_impl(x, w, nullptr, m, n, k, ldx, ldw, n, nullptr, 0, num_sms, status, stream, true, nullptr, 0, &t,
+                   static_cast<int>(max_splits > 4 ? 4 : max_splits));
 }
 
 // Y[m, n/2] = silu(gate) * up, with W's rows interleaved in groups of 16 = [8 gate | 8 up].
@@ -985,7 +1423,6 @@ int xv_gemm_bf16_defer(const void* x, const void* w, void* y, int m, int n, int 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[XV_NOALLOC_SCRATCH_BYTES];
 
 namespace {
-constexpr int kMaxDevices = 64;
 void* g_scratch_ptr[kMaxDevices] = {nullptr};
 int g_scratch_sms[kMaxDevices] = {0};
 std::mutex g_scratch_mu;
@@ -1024,7 +1461,8 @@ int xv_gemm_bf16_noalloc(const void* x, const void* w, void* y, int m, int n, in
   if (rc) return rc;
   XvGemmPlan pl;
   if ((rc = xv_gemm_plan(m, n, k, sms, &pl))) return rc;
-  if (pl.workspace_bytes > XV_NOALLOC_SCRATCH_BYTES) {
+  // Split-K planes have to fit; the CTA-pair kernel deals whole tiles when given a buffer this small.
+  if (!pl.pair && pl.workspace_bytes > XV_NOALLOC_SCRATCH_BYTES) {
     std::fprintf(stderr,
                  "xv_gemm_bf16_noalloc: %d x %d x %d needs %lld bytes of split-K scratch, the built-in buffer "
                  "holds %lld; use xv_gemm_bf16 with a caller-provided workspace\n",

@@ -245,22 +245,237 @@ __device__ inline void tp_reduce_rows(const TpComm& c, long long buf_offset, con
   }
 }
 
-// Everything a GEMM needs to finish with the cross-rank reduction in the same kernel.
-struct TpTail {
+// ---- push protocol: GEMM epilogue -> row owners' slots -> sum + residual + RMSNorm -> broadcast ----------
+//
+// A row-parallel projection under tensor parallelism is ONE kernel. Its GEMM epilogue writes every
+// finished tile of this rank's partial product straight into the memory of the ranks that will reduce
+// it ("slots": one copy of the rows per source), then raises an arrival counter there. Rows are dealt
+// round-robin: rank r owns rows r, r + world, ... (two-shot form; traffic per GPU does not grow with the
+// number of ranks). The owner sums the sources in a fixed order, adds its rows of the residual stream,
+// normalises and broadcasts the result into every rank's activation buffer (multimem.st through
+// NVSwitch, or one peer store per rank), then raises a second counter. With few rows the one-shot form
+// is cheaper: every rank receives all rows from all sources and reduces all of them itself; there is no
+// broadcast and no second wait.
+//
+// Counters only grow. Each rank keeps, in local device memory, the value every counter had reached
+// when the previous call ended; a call waits for that value plus the number of arrivals it expects.
+// A rank cannot leave call k before every rank has delivered its part of call k, so arrivals that
+// belong to call k + 1 can only come on top of a complete call k and never satisfy a wait early.
+// Every wait is bounded by `spin_limit`; on expiry the kernel records a status code and carries on to
+// its end (its output is then garbage, the host raises).
+//
+// Slot array of one call, at byte `slot_offset` of the symmetric buffer of the reducing rank:
+//   [world * splits sources][cap_rows][hidden] bf16, source index = rank * splits + k_split.
+// The caller alternates between two arrays, so the array written in call k is not written again
+// before call k + 2, by which time its owner has finished reading it (same argument as above).
+constexpr int kPushArriveWord = 32;   // flag words [32, 40): tiles arrived from source rank s
+constexpr int kPushBcastWord = 64;    // flag words [64, 72): rows arrived from owner rank o
+constexpr int kPushTicketWord = 6;    // TpComm::epoch word: CTAs of the running call that have finished
+constexpr int kPushArriveBase = 8;    // TpComm::epoch words [8, 16): arrive counters at the end of the last call
+constexpr int kPushBcastBase = 16;    // TpComm::epoch words [16, 24): broadcast counters at the end of the last call
+constexpr int kTpPushKernelId = 4;
+
+struct TpPush {
   int enabled;
+  int two_shot;                        // 1: rows dealt to owners; 0: every rank reduces every row
   TpComm comm;
-  long long buf_offset;                 // byte offset of the [rows, hidden] bf16 partial in the symmetric buffer
-  const __nv_bfloat16* residual_in;
+  long long slot_offset;
+  int cap_rows;                        // rows per source in the slot array
+  int splits;                          // K splits of the GEMM, pushed as separate sources
+  long long h_offset;                  // two-shot: byte offset (symmetric buffer) the finished rows are broadcast to
+  __nv_bfloat16* y;                    // one-shot: local [rows, hidden] output
+  const __nv_bfloat16* residual_in;    // [rows, hidden] local; two-shot touches only this rank's rows; may be null
   __nv_bfloat16* residual_out;
   const __nv_bfloat16* norm_w;
-  __nv_bfloat16* y;
   int rows, hidden;
   float eps;
-  int mode;
-  uint32_t* grid_sync;                  // two words of local device memory, zero-initialised once
-  const float* partials;                // split-K planes to fold first (splits > 1)
-  int splits;
-  long long split_stride;
+  int mode;                            // 0: residual add + RMSNorm; 1: plain sum
+  int signal_ctas;                     // CTAs of this launch that own GEMM work (each raises its counter once)
 };
+
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Polls until the counter at `f` has reached `target` (signed distance, so wrap-around is harmless).
+__device__ __forceinline__ bool tp_wait_counter(const uint32_t* f, uint32_t target, unsigned spin_us) {
+  unsigned long long t0 = 0;
+  const unsigned long long limit = static_cast<unsigned long long>(spin_us) * 1000ull;
+  for (int polls = 0;; ++polls) {
+    if (static_cast<int32_t>(ld_acquire_sys(f) - target) >= 0) return true;
+    if (polls == 64) t0 = global_timer_ns();
+    if (polls > 64) {
+      if (global_timer_ns() - t0 > limit) return false;
+      __nanosleep(32);
+    }
+  }
+}
+
+__device__ __forceinline__ int tp_rows_owned(int rows, int owner, int world) {
+  return rows > owner ? (rows - owner + world - 1) / world : 0;
+}
+
+// Eight bf16 values of row `row`, columns col .. col + 7, of this rank's partial (K split `split`)
+// to wherever they will be reduced.
+__device__ __forceinline__ void tp_push_store8(const TpPush& t, int row, int col, int split, const uint4& v) {
+  const int src = t.comm.rank * t.splits + split;
+  if (t.two_shot) {
+    const int owner = row % t.comm.world;
+    const int slot_row = row / t.comm.world;
+    char* dst = const_cast<char*>(static_cast<const char*>(t.comm.peer_buf[owner])) + t.slot_offset +
+                ((static_cast<long long>(src) * t.cap_rows + slot_row) * t.hidden + col) * 2;
+    st_relaxed_sys_v4(dst, v);
+  } else {
+    const long long off = t.slot_offset + ((static_cast<long long>(src) * t.cap_rows + row) * t.hidden + col) * 2;
+    if (t.comm.mc_buf != nullptr) {
+      multimem_st_bf16x8(const_cast<char*>(static_cast<const char*>(t.comm.mc_buf)) + off, v);
+    } else {
+      for (int r = 0; r < t.comm.world; ++r)
+        st_relaxed_sys_v4(const_cast<char*>(static_cast<const char*>(t.comm.peer_buf[r])) + off, v);
+    }
+  }
+}
+
+// Called by threads 0 .. world-1 of the group that pushed, after a barrier among that group:
+// "this CTA's tiles have been written" on every rank.
+__device__ __forceinline__ void tp_push_signal_tiles(const TpPush& t, int peer) {
+  __threadfence_system();
+  red_release_sys_add(t.comm.peer_flags[peer] + kPushArriveWord + t.comm.rank, 1u);
+}
+
+// Second half of the kernel, run by all threads of every CTA once the CTA's GEMM work is done.
+template <int MAXVEC>
+__device__ __noinline__ void tp_push_tail(const TpPush& t) {
+  __shared__ float scratch[32];
+  const int world = t.comm.world, rank = t.comm.rank;
+  const int nthreads = blockDim.x;
+  volatile uint32_t* st = t.comm.epoch;
+  const int n_mine = t.two_shot ? tp_rows_owned(t.rows, rank, world) : t.rows;
+  // rows go to the CTAs from the end of the grid first: those are the ones without GEMM tiles
+  const int first = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+  if (first < n_mine) {
+    if (threadIdx.x < world) {
+      const uint32_t target = st[kPushArriveBase + threadIdx.x] + static_cast<uint32_t>(t.signal_ctas);
+      if (!tp_wait_counter(t.comm.peer_flags[rank] + kPushArriveWord + threadIdx.x, target, t.comm.spin_limit))
+        report_status(t.comm.status, kTpPushKernelId, kPeerFlagTimeout);
+    }
+    __syncthreads();
+    const char* slots = static_cast<const char*>(t.comm.peer_buf[rank]) + t.slot_offset;
+    const int n_src = world * t.splits;
+    const int nvec = t.hidden >> 3;
+    for (int i = first; i < n_mine; i += gridDim.x) {
+      const int row = t.two_shot ? rank + i * world : i;
+      float vals[MAXVEC][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int u = 0; u < MAXVEC; ++u) {
+        const int v = threadIdx.x + u * nthreads;
+        if (v < nvec) {
+          float acc[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+          const char* p0 = slots + (static_cast<long long>(i) * t.hidden + v * 8) * 2;
+          const long long src_stride = static_cast<long long>(t.cap_rows) * t.hidden * 2;
+#pragma unroll 4
+          for (int s = 0; s < n_src; ++s) {       // fixed order, fp32: the result does not depend on arrival order
+            float x[8];
+            unpack8(ld_relaxed_sys_v4(p0 + s * src_stride), x);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += x[j];
+          }
+          if (t.mode == 0) {
+            const size_t ro = static_cast<size_t>(row) * t.hidden + v * 8;
+            if (t.residual_in != nullptr) {
+              float rr[8];
+              unpack8(*reinterpret_cast<const uint4*>(t.residual_in + ro), rr);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[j] += rr[j];
+            }
+            *reinterpret_cast<uint4*>(t.residual_out + ro) = pack8(acc);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              acc[j] = __bfloat162float(__float2bfloat16(acc[j]));
+              ss += acc[j] * acc[j];
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) vals[u][j] = acc[j];
+        }
+      }
+      float inv = 1.f;
+      if (t.mode == 0) {
+        ss = warp_sum(ss);
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        if (lane == 0) scratch[warp] = ss;
+        __syncthreads();
+        float tot = lane < (nthreads >> 5) ? scratch[lane] : 0.f;
+        tot = warp_sum(tot);
+        __syncthreads();
+        inv = rsqrtf(tot / static_cast<float>(t.hidden) + t.eps);
+      }
+#pragma unroll
+      for (int u = 0; u < MAXVEC; ++u) {
+        const int v = threadIdx.x + u * nthreads;
+        if (v < nvec) {
+          float o[8];
+          if (t.mode == 0) {
+            float g[8];
+            unpack8(*reinterpret_cast<const uint4*>(t.norm_w + v * 8), g);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = vals[u][j] * inv * g[j];
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = vals[u][j];
+          }
+          const uint4 packed = pack8(o);
+          if (!t.two_shot) {
+            *reinterpret_cast<uint4*>(t.y + static_cast<size_t>(row) * t.hidden + v * 8) = packed;
+          } else {
+            const long long off = t.h_offset + (static_cast<long long>(row) * t.hidden + v * 8) * 2;
+            if (t.comm.mc_buf != nullptr) {
+              multimem_st_bf16x8(const_cast<char*>(static_cast<const char*>(t.comm.mc_buf)) + off, packed);
+            } else {
+              for (int r = 0; r < world; ++r)
+                st_relaxed_sys_v4(const_cast<char*>(static_cast<const char*>(t.comm.peer_buf[r])) + off, packed);
+            }
+          }
+        }
+      }
+    }
+    if (t.two_shot) {
+      __syncthreads();
+      if (threadIdx.x < world) {
+        __threadfence_system();
+        red_release_sys_add(t.comm.peer_flags[threadIdx.x] + kPushBcastWord + rank, 1u);
+      }
+    }
+  }
+  // One CTA keeps the kernel open until every owner's rows have landed in this rank's activation
+  // buffer: the kernel's end then means "the whole [rows, hidden] activation is here".
+  if (t.two_shot && blockIdx.x == 0 && threadIdx.x < world) {
+    const int owned = tp_rows_owned(t.rows, threadIdx.x, world);
+    const int expect = owned < static_cast<int>(gridDim.x) ? owned : static_cast<int>(gridDim.x);
+    const uint32_t target = st[kPushBcastBase + threadIdx.x] + static_cast<uint32_t>(expect);
+    if (!tp_wait_counter(t.comm.peer_flags[rank] + kPushBcastWord + threadIdx.x, target, t.comm.spin_limit))
+      report_status(t.comm.status, kTpPushKernelId, kPeerFlagTimeout);
+  }
+  // The last CTA to get here moves the per-counter bases on for the next call.
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(t.comm.epoch + kPushTicketWord, 1u) == gridDim.x - 1) {
+      t.comm.epoch[kPushTicketWord] = 0;
+      for (int r = 0; r < world; ++r) {
+        t.comm.epoch[kPushArriveBase + r] += static_cast<uint32_t>(t.signal_ctas);
+        if (t.two_shot) {
+          const int owned = tp_rows_owned(t.rows, r, world);
+          t.comm.epoch[kPushBcastBase + r] +=
+              static_cast<uint32_t>(owned < static_cast<int>(gridDim.x) ? owned : static_cast<int>(gridDim.x));
+        }
+      }
+      __threadfence();
+    }
+  }
+}
 
 }  // namespace xv

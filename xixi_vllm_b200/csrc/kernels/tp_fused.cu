@@ -66,7 +66,7 @@ tp_reduce_norm_kernel(const TpComm c, long long buf_offset, const __nv_bfloat16*
 // Per reduction each GPU sends and receives about rows*hidden*2 bytes regardless of the number
 // of ranks; the one-shot kernel above moves world times more and is kept for small worlds and
 // for callers that need the full residual on every rank (pipeline hand-off).
-__global__ void __launch_bounds__(kTpThreads)
+__global__ void __launch_bounds__(kTpThreads, 4)
 tp_reduce_norm_sharded_kernel(const TpComm c, long long buf_offset, long long h_offset, int has_residual,
                               __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ w, int rows,
                               int hidden, float eps) {
@@ -165,8 +165,9 @@ struct ArgSlot {
   int i;
 };
 
-// One CTA per row. slots: symmetric [world][rows] ArgSlot array; each rank writes its local
-// best into slot [rank][row] of every peer, then all ranks pick the same winner.
+// slots: symmetric [world][rows] ArgSlot array; each rank writes its local best of every row into slot
+// [rank][row] of every peer, then all ranks pick the same winner. The grid is capped at what can be
+// resident at once (every CTA waits for the peers before it picks) and walks the rows with its stride.
 __global__ void __launch_bounds__(1024)
 tp_argmax_kernel(const TpComm c, long long slots_offset, const __nv_bfloat16* __restrict__ logits, long long ld,
                  int local_vocab, int valid_vocab, int vocab_start, long long* __restrict__ out, int rows) {
@@ -174,49 +175,49 @@ tp_argmax_kernel(const TpComm c, long long slots_offset, const __nv_bfloat16* __
   grid_dep_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
-  const int row = blockIdx.x;
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(c.epoch);
-  const __nv_bfloat16* lr = logits + static_cast<size_t>(row) * ld;
-  float bv = -CUDART_INF_F;
-  int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < valid_vocab && i < local_vocab; i += blockDim.x) {
-    const float x = __bfloat162float(lr[i]);
-    if (x > bv || (x == bv && i < bi)) { bv = x; bi = i; }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
-  __syncthreads();
-  if (warp == 0) {
-    bv = lane < (blockDim.x >> 5) ? sv[lane] : -CUDART_INF_F;
-    bi = lane < (blockDim.x >> 5) ? si[lane] : 0x7fffffff;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const __nv_bfloat16* lr = logits + static_cast<size_t>(row) * ld;
+    float bv = -CUDART_INF_F;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < valid_vocab && i < local_vocab; i += blockDim.x) {
+      const float x = __bfloat162float(lr[i]);
+      if (x > bv || (x == bv && i < bi)) { bv = x; bi = i; }
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
-    if (lane < c.world) {
-      // push (value, global id) into slot [my rank][row] on peer `lane`
-      ArgSlot* dst = reinterpret_cast<ArgSlot*>(const_cast<char*>(static_cast<const char*>(c.peer_buf[lane])) +
-                                                slots_offset) + static_cast<size_t>(c.rank) * rows + row;
-      ArgSlot s;
-      s.v = bv;
-      s.i = bi == 0x7fffffff ? -1 : bi + vocab_start;
-      asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(s.v)), "r"(s.i)
-                   : "memory");
-      __threadfence_system();
+    if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+      bv = lane < (blockDim.x >> 5) ? sv[lane] : -CUDART_INF_F;
+      bi = lane < (blockDim.x >> 5) ? si[lane] : 0x7fffffff;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (lane < c.world) {
+        // push (value, global id) into slot [my rank][row] on peer `lane`
+        ArgSlot* dst = reinterpret_cast<ArgSlot*>(const_cast<char*>(static_cast<const char*>(c.peer_buf[lane])) +
+                                                  slots_offset) + static_cast<size_t>(c.rank) * rows + row;
+        const int gi = bi == 0x7fffffff ? -1 : bi + vocab_start;
+        asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(bv)), "r"(gi)
+                     : "memory");
+      }
     }
+    __syncthreads();
   }
-  __syncthreads();
-  // per-row flags would need rows x world words; one barrier per kernel is enough because the
-  // flag is raised by block 0 only after a grid-wide ticket says every row has been pushed
+  // one flag per kernel: raised by whichever CTA finishes last, after a grid-wide ticket says every row
+  // has been pushed
   __shared__ int last;
+  if (threadIdx.x < 32 && threadIdx.x < c.world) __threadfence_system();
+  __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
     last = atomicAdd(c.epoch + 2, 1u) == gridDim.x - 1;
@@ -224,6 +225,7 @@ tp_argmax_kernel(const TpComm c, long long slots_offset, const __nv_bfloat16* __
   __syncthreads();
   if (last && threadIdx.x < c.world) {
     c.epoch[2] = 0;
+    __threadfence_system();
     st_release_sys(c.peer_flags[threadIdx.x] + 1 * kMaxRanks + c.rank, epoch);
   }
   // wait for every rank's pushes
@@ -243,10 +245,10 @@ tp_argmax_kernel(const TpComm c, long long slots_offset, const __nv_bfloat16* __
     if (!seen) { report_status(c.status, kTpKernelId, kPeerFlagTimeout); ok_flag = 0; }
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  const ArgSlot* mine = reinterpret_cast<const ArgSlot*>(static_cast<const char*>(c.peer_buf[c.rank]) + slots_offset);
+  for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < rows; row += gridDim.x * blockDim.x) {
     long long pick = 0;
     if (ok_flag) {
-      const ArgSlot* mine = reinterpret_cast<const ArgSlot*>(static_cast<const char*>(c.peer_buf[c.rank]) + slots_offset);
       float best = -CUDART_INF_F;
       int id = 0x7fffffff;
       for (int r = 0; r < c.world; ++r) {
@@ -268,7 +270,7 @@ tp_argmax_kernel(const TpComm c, long long slots_offset, const __nv_bfloat16* __
 // store), else one peer store per rank. The last CTA to finish raises this rank's flag; every CTA
 // then waits until all ranks have raised theirs, so when the kernel ends the full matrix is local.
 // The destination lives in a symmetric buffer of its own (base pointers in c.peer_buf / c.mc_buf).
-__global__ void __launch_bounds__(kTpThreads)
+__global__ void __launch_bounds__(kTpThreads, 4)
 tp_allgather_cols_kernel(const TpComm c, const __nv_bfloat16* __restrict__ src, long long ld, int local_cols,
                          long long total_cols, int rows) {
   grid_dep_launch();
@@ -338,6 +340,23 @@ static int fill_comm(TpComm* c, const void* const* peer_bufs, void* const* peer_
   return 0;
 }
 
+// How many CTAs of `kernel` can be resident on the current device at once (0 on error). Kernels whose CTAs
+// wait for one another must not be launched with more; the figure comes from the occupancy calculator and
+// the device's SM count, cached per device and kernel.
+template <typename K>
+static int resident_ctas(K kernel, int threads, int slot) {
+  constexpr int kMaxDev = 64;
+  static int cache[4][kMaxDev] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return 0;
+  if (cache[slot][dev] > 0) return cache[slot][dev];
+  int per_sm = 0, sms = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  cache[slot][dev] = per_sm * sms;
+  return cache[slot][dev];
+}
+
 extern "C" {
 
 // peer_bufs / peer_flags: HOST arrays of `world` device pointers (as mapped on this rank).
@@ -351,7 +370,9 @@ int xv_tp_reduce_norm(const void* const* peer_bufs, void* const* peer_flags, con
   TpComm c;
   int rc = fill_comm(&c, peer_bufs, peer_flags, mc_buf, epoch, rank, world, spin_limit, status);
   if (rc) return rc;
-  int grid = rows < 148 * 4 ? rows : 148 * 4;
+  const int cap = resident_ctas(tp_reduce_norm_kernel, kTpThreads, 0);
+  if (cap < 1) return XV_ERR_LAUNCH;
+  int grid = rows < cap ? rows : cap;
   launch_pdl(tp_reduce_norm_kernel, dim3(grid), dim3(kTpThreads), 0, stream, 
       c, buf_offset, static_cast<const __nv_bfloat16*>(residual_in), static_cast<__nv_bfloat16*>(residual_out),
       static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), rows, hidden, eps, mode);
@@ -370,8 +391,10 @@ int xv_tp_reduce_norm_sharded(const void* const* peer_bufs, void* const* peer_fl
   TpComm c;
   int rc = fill_comm(&c, peer_bufs, peer_flags, mc_buf, epoch, rank, world, spin_limit, status);
   if (rc) return rc;
+  const int cap = resident_ctas(tp_reduce_norm_sharded_kernel, kTpThreads, 1);
+  if (cap < 1) return XV_ERR_LAUNCH;
   int mine = (rows + world - 1) / world;
-  int grid = mine < 148 * 4 ? mine : 148 * 4;     // every CTA waits at the end: keep the grid resident
+  int grid = mine < cap ? mine : cap;     // every CTA waits at the end: keep the grid resident
   if (grid < 1) grid = 1;
   launch_pdl(tp_reduce_norm_sharded_kernel, dim3(grid), dim3(kTpThreads), 0, stream, 
       c, buf_offset, h_offset, has_residual, static_cast<__nv_bfloat16*>(residual),
@@ -386,7 +409,9 @@ int xv_tp_argmax(const void* const* peer_bufs, void* const* peer_flags, void* ep
   TpComm c;
   int rc = fill_comm(&c, peer_bufs, peer_flags, nullptr, epoch, rank, world, spin_limit, status);
   if (rc) return rc;
-  launch_pdl(tp_argmax_kernel, dim3(rows), dim3(1024), 0, stream, c, slots_offset, static_cast<const __nv_bfloat16*>(logits), ld,
+  const int cap = resident_ctas(tp_argmax_kernel, 1024, 2);
+  if (cap < 1) return XV_ERR_LAUNCH;
+  launch_pdl(tp_argmax_kernel, dim3(rows < cap ? rows : cap), dim3(1024), 0, stream, c, slots_offset, static_cast<const __nv_bfloat16*>(logits), ld,
                                               local_vocab, valid_vocab, vocab_start, out, rows);
   return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
 }
@@ -406,7 +431,9 @@ int xv_tp_allgather_cols(const void* const* peer_bufs, void* const* peer_flags, 
   if (rc) return rc;
   const long long vecs = static_cast<long long>(rows) * (local_cols / 8);
   long long want = (vecs + kTpThreads - 1) / kTpThreads;
-  const int grid = static_cast<int>(want < 1 ? 1 : (want > 148 * 4 ? 148 * 4 : want));   // every CTA waits: stay resident
+  const int cap = resident_ctas(tp_allgather_cols_kernel, kTpThreads, 3);
+  if (cap < 1) return XV_ERR_LAUNCH;
+  const int grid = static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));   // every CTA waits: stay resident
   launch_pdl(tp_allgather_cols_kernel, dim3(grid), dim3(kTpThreads), 0, stream, c, static_cast<const __nv_bfloat16*>(src), ld, local_cols,
                                                             total_cols, rows);
   return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;

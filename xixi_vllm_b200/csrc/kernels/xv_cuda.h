@@ -27,12 +27,22 @@ typedef struct XvGemmPlan {
   int stages;
   int smem_bytes;
   int ctas_per_sm;         // resident CTAs per SM the persistent grid is sized for
-  int pair;                // 1: CTA-pair kernel (cta_group::2, 256 x 256 tiles)
+  int pair;                // 1: CTA-pair kernel (cta_group::2, 256 x bn tiles, stream-K)
+  int sk_tiles;            // pair kernel: tiles at the end of the tile order that are dealt in K blocks (stream-K)
+  int units_per_pair;      // pair kernel: K blocks of that region each SM pair takes
   long long workspace_bytes;
 } XvGemmPlan;
 
 int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan);
 void xv_gemm_disable_pair(int disable);   // test hook: force the single-CTA kernel
+// Test and tuning hook: fixed kernel (0 single CTA, 1 single CTA normal orientation, 2 CTA pairs), tile width,
+// split-K and stage count instead of the planner's choice; values <= 0 keep the default, kind < 0 clears.
+void xv_gemm_plan_override(int kind, int bn, int splits, int stages);
+// `workspace`: fp32 partial planes of a split-K plan (plan.workspace_bytes). A workspace of 40 MiB or more also
+// serves the CTA-pair kernel's stream-K: its last 20 MiB then hold partial tiles and counters, must be zero
+// before the first call that uses the buffer, and are left zero by every call; planes use the part in front.
+// With a smaller workspace the pair kernel deals whole tiles. Calls that overlap on the GPU must not share a
+// workspace.
 int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
                  long long ldy, void* workspace, long long workspace_bytes, int num_sms, int* status,
                  cudaStream_t stream);
@@ -151,10 +161,15 @@ int xv_tp_allgather_cols(const void* const* peer_bufs, void* const* peer_flags, 
                          int rank, int world, const void* src, long long ld, int local_cols, long long total_cols,
                          int rows, unsigned spin_limit, int* status, cudaStream_t stream);
 
-// RowParallel GEMM + all-reduce + residual add + RMSNorm in ONE kernel (see gemm_sm100.cu).
-int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long ldx, long long ldw, void* workspace,
-                    long long workspace_bytes, int num_sms, const void* const* peer_bufs, void* const* peer_flags,
-                    const void* mc_buf, void* epoch, int rank, int world, long long buf_offset, void* grid_sync,
+// RowParallel GEMM + cross-rank sum + residual add + RMSNorm in ONE kernel (gemm_sm100.cu, tp_device.cuh):
+// the GEMM epilogue pushes its tiles into the slot array (`slot_offset`, `slot_bytes`, inside the
+// symmetric buffer) of the ranks that reduce them. two_shot = 1: rows are dealt to the ranks, the
+// finished rows are broadcast to byte offset `h_offset` of every rank's symmetric buffer and the
+// residual buffers hold only this rank's rows; two_shot = 0: every rank reduces all rows into its own
+// y_out. `epoch`: 32 zero-initialised uint32 words of local device memory kept across calls.
+int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long ldx, long long ldw, int num_sms,
+                    const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf, void* epoch, int rank,
+                    int world, long long slot_offset, long long slot_bytes, int two_shot, long long h_offset,
                     const void* residual_in, void* residual_out, const void* norm_w, void* y_out, float eps, int mode,
                     unsigned spin_us, int* status, cudaStream_t stream);
 
@@ -195,6 +210,11 @@ typedef struct XvModelDesc {
   unsigned spin_us;
   int num_kv_blocks;                  // pages in each layer's k_cache / v_cache
   int prefill_tc;                     // 1: prefill attention on the tcgen05 kernel when the shape allows
+  int tp_push;                        // 1: row-parallel GEMM + reduction + norm as one kernel (xv_gemm_bf16_tp)
+  int tp_one_shot_max;                // forwards of at most this many tokens reduce every row on every rank
+  int is_first, is_last;              // pipeline stage: the first owns the embedding, the last the LM head; on
+                                      // other stages `final_norm` is the next stage's first input norm and the
+                                      // arena's h / residual are received from / sent to the neighbours
 } XvModelDesc;
 
 typedef struct XvBatchDesc {

@@ -90,6 +90,10 @@ class Qwen3Model:
                              if self.is_first else PPMissingLayer())
         self.layers = [Qwen3DecoderLayer(cfg, i, dtype, device) for i in range(self.start_layer, self.end_layer)]
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device) if self.is_last else PPMissingLayer()
+        # A stage that hands over to another one keeps a copy of that stage's first input norm: the native
+        # executor ends the stage with "reduce + residual add + that norm", so the receiver starts at its QKV GEMM.
+        self.boundary_norm = (None if self.is_last else
+                              RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device))
 
     def forward(self, input_ids, batch, kv, comm: TPComm, intermediate: IntermediateTensors | None = None):
         """Returns final-normed hidden states on the last stage, else ``IntermediateTensors``."""
@@ -191,6 +195,8 @@ class Qwen3ForCausalLM:
             yield p + "mlp.down_proj.weight", f.down_proj.weight
             yield p + "input_layernorm.weight", layer.input_layernorm.weight
             yield p + "post_attention_layernorm.weight", layer.post_attention_layernorm.weight
+        if m.boundary_norm is not None:
+            yield "model.boundary_norm.weight", m.boundary_norm.weight
         if m.is_last:
             yield "model.norm.weight", m.norm.weight
             yield "lm_head.weight", self.lm_head.weight
@@ -216,6 +222,8 @@ class Qwen3ForCausalLM:
         if len(parts) < 5 or parts[0] != "model" or parts[1] != "layers":
             return None
         idx = int(parts[2])
+        if idx == m.end_layer and m.boundary_norm is not None and parts[3] == "input_layernorm":
+            return m.boundary_norm, "load", None
         if not m.start_layer <= idx < m.end_layer:
             return None
         layer = m.layers[idx - m.start_layer]

@@ -38,7 +38,7 @@ launch_count = 0
 class GemmPlan(ctypes.Structure):
     _fields_ = [("swapped", _i32), ("bn", _i32), ("tiles_a", _i32), ("tiles_b", _i32), ("splits", _i32),
                 ("k_blocks_per_split", _i32), ("stages", _i32), ("smem_bytes", _i32),
-                ("ctas_per_sm", _i32), ("pair", _i32), ("workspace_bytes", _i64)]
+                ("ctas_per_sm", _i32), ("pair", _i32), ("sk_tiles", _i32), ("units_per_pair", _i32), ("workspace_bytes", _i64)]
 
 
 def lib():
@@ -88,8 +88,10 @@ def lib():
                                        _vp, _vp]
     L.xv_tp_argmax.argtypes = [_vp, _vp, _vp, _i32, _i32, _i64, _vp, _i64, _i32, _i32, _i32, _vp, _i32,
                                ctypes.c_uint, _vp, _vp]
-    L.xv_gemm_bf16_tp.argtypes = [_vp, _vp, _i32, _i32, _i32, _i64, _i64, _vp, _i64, _i32, _vp, _vp, _vp, _vp, _i32,
-                                  _i32, _i64, _vp, _vp, _vp, _vp, _vp, _f32, _i32, ctypes.c_uint, _vp, _vp]
+    L.xv_gemm_bf16_tp.argtypes = [_vp, _vp, _i32, _i32, _i32, _i64, _i64, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i64,
+                                  _i64, _i32, _i64, _vp, _vp, _vp, _vp, _f32, _i32, ctypes.c_uint, _vp, _vp]
+    L.xv_gemm_plan_override.argtypes = [_i32, _i32, _i32, _i32]
+    L.xv_gemm_plan_override.restype = None
     L.xv_selftest_bounded_wait.argtypes = [_vp, _vp, ctypes.c_uint, _vp]
     L.xv_num_sms.restype = _i32
     _lib = L
@@ -119,7 +121,9 @@ class _DeviceState:
     def __init__(self, device: torch.device) -> None:
         self.device = device
         self.num_sms = torch.cuda.get_device_properties(device).multi_processor_count
-        self.gemm_ws = torch.empty(32 << 20, dtype=torch.uint8, device=device)
+        # zero-filled: the last 20 MiB serve the pair GEMM's stream-K (partial tiles and counters, kept at zero
+        # by the kernels), the front part holds split-K planes
+        self.gemm_ws = torch.zeros(56 << 20, dtype=torch.uint8, device=device)
         self.attn_ws = torch.empty(16 << 20, dtype=torch.uint8, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
 
@@ -470,9 +474,11 @@ def tp_allgather_cols(peer_bufs, peer_flags, mc_ptr: int, epoch, rank: int, worl
                                       spin_limit, status.data_ptr(), _stream()), "tp_allgather_cols")
 
 
-def gemm_tp_fused(x, w, peer_bufs, peer_flags, mc_ptr: int, epoch, rank: int, world: int, buf_offset: int,
-                  grid_sync, residual_in, residual_out, norm_w, y, eps: float, mode: int, spin_us: int) -> None:
-    """RowParallel GEMM + cross-rank sum + residual add + RMSNorm in one kernel (``xv_gemm_bf16_tp``)."""
+def gemm_tp_fused(x, w, peer_bufs, peer_flags, mc_ptr: int, epoch, rank: int, world: int, slot_offset: int,
+                  slot_bytes: int, two_shot: bool, h_offset: int, residual_in, residual_out, norm_w, y, eps: float,
+                  mode: int, spin_us: int) -> None:
+    """RowParallel GEMM + cross-rank sum + residual add + RMSNorm in one kernel (``xv_gemm_bf16_tp``): the GEMM
+    epilogue pushes its tiles into the slot array of the ranks that reduce them."""
     _bf16(x, w)
     if x.stride(1) != 1:
         x = x.contiguous()
@@ -480,12 +486,18 @@ def gemm_tp_fused(x, w, peer_bufs, peer_flags, mc_ptr: int, epoch, rank: int, wo
     N = w.shape[0]
     st = _state(x)
     _check(lib().xv_gemm_bf16_tp(
-        x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0), w.stride(0), st.gemm_ws.data_ptr(), st.gemm_ws.numel(),
-        st.num_sms, peer_bufs, peer_flags, mc_ptr or None, epoch.data_ptr(), rank, world, buf_offset,
-        grid_sync.data_ptr(), residual_in.data_ptr() if residual_in is not None else None,
+        x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0), w.stride(0), st.num_sms, peer_bufs, peer_flags,
+        mc_ptr or None, epoch.data_ptr(), rank, world, slot_offset, slot_bytes, 1 if two_shot else 0, h_offset,
+        residual_in.data_ptr() if residual_in is not None else None,
         residual_out.data_ptr() if residual_out is not None else None,
-        norm_w.data_ptr() if norm_w is not None else None, y.data_ptr(), eps, mode, spin_us, st.status.data_ptr(),
-        _stream()), f"gemm+allreduce {M}x{N}x{K}")
+        norm_w.data_ptr() if norm_w is not None else None, y.data_ptr() if y is not None else None, eps, mode,
+        spin_us, st.status.data_ptr(), _stream()), f"gemm+allreduce {M}x{N}x{K}")
+
+
+def gemm_plan_override(kind: int = -1, bn: int = 0, splits: int = 0, stages: int = 0) -> None:
+    """Tuning hook: force kernel kind (0 single CTA, 1 single CTA normal orientation, 2 CTA pairs), tile width,
+    split-K and stages for every following GEMM; ``kind < 0`` restores the planner."""
+    lib().xv_gemm_plan_override(kind, bn, splits, stages)
 
 
 def device_status(t: torch.Tensor) -> torch.Tensor:

@@ -44,7 +44,7 @@ class DeferredRowGemm:
     def shape(self):
         return (self.x.shape[0], self.weight.shape[0])
 
-FLAG_BYTES = 4096          # two channels x 8 ranks x 4 bytes used; one page reserved
+FLAG_BYTES = 4096          # epoch flags (three channels x 8 ranks) and the push protocol's arrival counters
 SPIN_LIMIT = 2_000_000     # microseconds a kernel waits for a peer before it reports and returns
 
 
@@ -78,7 +78,8 @@ class FusedTPComm(TPComm):
         self.device = torch.device(device)
         self.hidden = hidden_size
         self.max_tokens = max_tokens
-        self.buf_bytes = -(-max_tokens * hidden_size * 2 // 4096) * 4096
+        # room for the push protocol's slot array: world sources x ceil(tokens / world) rows
+        self.buf_bytes = -(-(max_tokens + group.size) * hidden_size * 2 // 4096) * 4096
         self.slot_bytes = -(-group.size * max_tokens * 8 // 4096) * 4096
         # optional [logits_rows, world * logits_local_cols] matrix for gathering sampled rows' logits
         self._logit_rows, self._logit_cols = logits_rows, logits_local_cols * group.size
@@ -98,16 +99,17 @@ class FusedTPComm(TPComm):
         self._bufs = self.symm.ptr_array(0)
         self._flags = self.symm.ptr_array(self.flags_off)
         self.mc_ptr = self.symm.multicast_ptr
-        self.epoch = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.epoch = torch.zeros(32, dtype=torch.int32, device=self.device)   # [0] epoch, the rest: counter history
         self.epoch[0] = 1
         self.status = cuda.device_status(self.epoch)
-        self.grid_sync = torch.zeros(4, dtype=torch.int32, device=self.device)
-        # XV_TP_FUSE_GEMM=1 runs the row-parallel GEMM and its reduction as ONE kernel (measured slower than
-        # the two-kernel form at TP=2 on Qwen3-8B, so it is opt-in)
-        self.fuse_gemm = os.environ.get("XV_TP_FUSE_GEMM", "0") == "1"
-        # Above this many tokens the projection runs on the CTA-pair GEMM and the reduction in
-        # its own kernel: at prefill sizes the faster GEMM outweighs the saved launch.
+        # The row-parallel GEMM and its reduction run as ONE kernel (tiles pushed from the GEMM epilogue into the
+        # reducing ranks' slots); XV_TP_PUSH=0 goes back to GEMM + reduction kernel. This module-by-module path
+        # (pipeline stages, tests) reduces every row on every rank, which costs NVLink traffic proportional to
+        # the rank count, so it is used up to XV_TP_FUSE_GEMM_MAX_T tokens.
+        self.fuse_gemm = os.environ.get("XV_TP_PUSH", "1") != "0"
         self.fuse_gemm_max_tokens = int(os.environ.get("XV_TP_FUSE_GEMM_MAX_T", "256"))
+        # forwards of at most this many tokens use the one-shot form in the native executor
+        self.one_shot_max_tokens = int(os.environ.get("XV_TP_ONE_SHOT_MAX_T", "32"))
         self._idx = 0
         self._logits_view = None
         if logit_bytes:
@@ -148,7 +150,9 @@ class FusedTPComm(TPComm):
 
     def row_linear(self, proj, x: torch.Tensor, final: bool = False):
         """Output of a RowParallelLinear as something ``reduce_add_rmsnorm`` / ``all_reduce`` accept."""
-        if self.fuse_gemm and proj.bias is None and x.shape[0] <= self.fuse_gemm_max_tokens:
+        T = x.shape[0]
+        if (self.fuse_gemm and proj.bias is None and 0 < T <= self.fuse_gemm_max_tokens
+                and self.world * T * self.hidden * 2 <= self.buf_bytes):
             return DeferredRowGemm(x, proj.weight, final)
         return proj(x, reduce=False, out=self.alloc_partial(x.shape[0], final))
 
@@ -161,7 +165,33 @@ class FusedTPComm(TPComm):
         if mode == 0:
             res_out = residual if residual is not None else torch.empty_like(y)
         cuda.gemm_tp_fused(d.x, d.weight, self._bufs, self._flags, self.mc_ptr, self.epoch, self.rank, self.world,
-                           off, self.grid_sync, residual, res_out, w, y, eps, mode, SPIN_LIMIT)
+                           off, self.buf_bytes, False, 0, residual, res_out, w, y, eps, mode, SPIN_LIMIT)
+        return y, res_out
+
+    def gemm_reduce_norm(self, x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | None,
+                         w: torch.Tensor | None, eps: float, *, two_shot: bool, final: bool = False,
+                         first: bool = False, mode: int = 0):
+        """Row-parallel projection, cross-rank sum, residual add and RMSNorm as one kernel.
+
+        ``two_shot``: rank r reduces rows r, r + world, ...; ``residual`` is a local [T, H] buffer of which
+        only those rows are read and written (``first`` starts the stream instead of adding), and the
+        result is the view of the symmetric activation buffer every rank's rows were broadcast into.
+        Otherwise every rank reduces all rows and gets a fresh [T, H] tensor.
+        Returns ``(y, residual)``."""
+        T = x.shape[0]
+        buf = self.alloc_partial(T, final)
+        off = buf.data_ptr() - self._base
+        if two_shot:
+            y = self.h_view[: T * self.hidden].view(T, self.hidden)
+        else:
+            y = torch.empty((T, self.hidden), dtype=torch.bfloat16, device=self.device)
+        res_out = None
+        if mode == 0:
+            res_out = residual if residual is not None else torch.empty((T, self.hidden), dtype=torch.bfloat16,
+                                                                        device=self.device)
+        cuda.gemm_tp_fused(x, weight, self._bufs, self._flags, self.mc_ptr, self.epoch, self.rank, self.world,
+                           off, self.buf_bytes, two_shot, self.h_off, None if first else residual, res_out, w,
+                           None if two_shot else y, eps, mode, SPIN_LIMIT)
         return y, res_out
 
     # --- reductions -----------------------------------------------------------------------------

@@ -65,9 +65,9 @@ class ModelRunner:
         self._step_events: dict[int, tuple] = {}
         self.h2d_bytes = 0
         self.d2h_bytes = 0
-        # single-stage GPU models run through the native executor (one C call per forward)
+        # GPU models run through the native executor: one C call launches a pipeline stage's whole forward
         self.native = None
-        if self.is_cuda and self.is_first_pp and self.is_last_pp and os.environ.get("XV_NATIVE_FORWARD", "1") != "0":
+        if self.is_cuda and os.environ.get("XV_NATIVE_FORWARD", "1") != "0":
             from .native_forward import NativeForward
 
             tp = get_tp_group()
@@ -80,7 +80,9 @@ class ModelRunner:
     # --- forward --------------------------------------------------------------------------
     def _forward(self, batch, intermediate=None):
         if self.native is not None:
-            out = self.native.forward(batch)
+            out = self.native.forward(batch)      # a stage that is not the first reads what _recv put in the arena
+            if not self.is_last_pp:
+                return IntermediateTensors(hidden_states=out[0], residual=out[1])
             if batch.all_greedy:
                 return out
             logits = out
@@ -110,7 +112,12 @@ class ModelRunner:
         return comm.gather_logits(local_logits) if hasattr(comm, "gather_logits") else None
 
     def _recv(self, n_tokens: int) -> IntermediateTensors:
-        h, r = self._pp_buf[0][:n_tokens], self._pp_buf[1][:n_tokens]
+        """Receives the previous stage's hidden states and residual stream for a whole step: straight into
+        the native executor's arena when it runs this stage, else into the runner's own pair."""
+        if self.native is not None:
+            h, r = self.native.stage_inputs(n_tokens)
+        else:
+            h, r = self._pp_buf[0][:n_tokens], self._pp_buf[1][:n_tokens]
         recv_tensors([h, r], group=self._pp)
         return IntermediateTensors(hidden_states=h, residual=r)
 
@@ -130,10 +137,19 @@ class ModelRunner:
                 h, r = self._pp_buf[0][t0:t1], self._pp_buf[1][t0:t1]
                 recv_tensors([h, r], group=self._pp)
                 inter = IntermediateTensors(hidden_states=h, residual=r)
+                if self.native is not None:
+                    # the native executor reads a stage's input at the start of its arena; the pieces land in
+                    # disjoint rows of the runner's pair so that a receive never waits for the piece before it
+                    ah, ar = self.native.stage_inputs(t1 - t0)
+                    ah.copy_(h)
+                    ar.copy_(r)
             with nvtx_range("forward"):
                 out = self._forward(sub, inter)
             if not self.is_last_pp:
-                pending.extend(send_tensors([out["hidden_states"], out["residual"]], group=self._pp))
+                hs, rs = out["hidden_states"], out["residual"]
+                if self.native is not None:
+                    hs, rs = hs.clone(), rs.clone()    # the next piece overwrites the arena while this one travels
+                pending.extend(send_tensors([hs, rs], group=self._pp))
             elif sub.num_samples:
                 pieces.append(out)
         for w in pending:
@@ -145,8 +161,7 @@ class ModelRunner:
     def run_forward(self, sched) -> tuple[int, int]:
         """Launches the step (no host wait). Returns (#prefill sequences, #decode sequences)."""
         n_p, n_d = len(sched.prefills), len(sched.decodes)
-        use_graph = (self.graphs is not None and n_p == 0 and 0 < n_d <= self.graphs.max_bs
-                     and self.is_first_pp and self.is_last_pp)
+        use_graph = self.graphs is not None and n_p == 0 and 0 < n_d <= self.graphs.max_bs
         ev = None
         if self.time_steps:
             ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
@@ -156,9 +171,14 @@ class ModelRunner:
                 bucket = self.graphs.pad_bs(n_d)
                 with nvtx_range("stage"):
                     batch = self.stager.build(sched, pad_to=bucket, fixed_blocks=True)
-                greedy = batch.all_greedy
+                greedy = batch.all_greedy if self.is_last_pp else True
+                if not self.is_first_pp:
+                    self._recv(bucket)             # outside the graph, into the buffers the graph reads
                 with nvtx_range("decode_graph"):
                     tokens = self.graphs.replay(bucket, greedy)
+                if not self.is_last_pp:
+                    self._send(tokens)
+                    tokens = None
             else:
                 with nvtx_range("stage"):
                     batch = self.stager.build(sched)
@@ -228,8 +248,9 @@ class ModelRunner:
     def _capture_graphs(self) -> None:
         from ..data.wire import DecodeBatch, SchedulerOutput
 
-        if not (self.is_first_pp and self.is_last_pp):
-            return   # with pipeline stages the p2p hand-off brackets the forward; run eagerly
+        single_stage = self.is_first_pp and self.is_last_pp
+        if not single_stage and (self.native is None or self.pp_microbatches > 1):
+            return   # a stage body is one graph only when one native call runs it on the whole step
         runner = CUDAGraphRunner(make_bs_list(min(self.max_bs, 512)))
 
         def make_inputs(bs: int, greedy: bool):
@@ -240,7 +261,9 @@ class ModelRunner:
             batch.all_greedy = greedy
             return batch
 
-        runner.capture((True, False), make_inputs, self._forward)
+        # the p2p hand-off between stages stays outside the graphs (the reference does the same:
+        # src/compute/model_runner.py:62-66,178-192); stages without the sampler need one variant only
+        runner.capture((True, False) if self.is_last_pp else (True,), make_inputs, self._forward)
         self.stager.reset()
         self.graphs = runner
 

@@ -2,8 +2,10 @@
 
 Describes the model (weights, caches, tensor-parallel communicator) and a preallocated
 activation arena to the C library once; each step then fills a small batch struct and makes
-ONE call that launches the whole forward. Used for single-stage (pp == 1) GPU models; the
-module-by-module Python forward stays as the CPU path and the pipeline-parallel path.
+ONE call that launches the whole forward of this pipeline stage. The module-by-module Python
+forward stays as the CPU path. A stage that is not the first finds its inputs (normalised hidden
+states and the residual stream) in the arena, where the model runner received them; a stage that
+is not the last leaves its outputs there for the runner to send.
 """
 
 from __future__ import annotations
@@ -33,7 +35,8 @@ class ModelDesc(ctypes.Structure):
                 ("lm_head", _vp), ("cos_sin", _vp), ("layers", ctypes.POINTER(LayerWeights)), ("tp_rank", _i32),
                 ("tp_world", _i32), ("peer_bufs", _vp), ("peer_flags", _vp), ("mc_buf", _vp), ("epoch", _vp),
                 ("h_offset", _i64), ("buf_bytes", _i64), ("slots_offset", _i64), ("spin_us", ctypes.c_uint),
-                ("num_kv_blocks", _i32), ("prefill_tc", _i32)]
+                ("num_kv_blocks", _i32), ("prefill_tc", _i32), ("tp_push", _i32), ("tp_one_shot_max", _i32),
+                ("is_first", _i32), ("is_last", _i32)]
 
 
 class BatchDesc(ctypes.Structure):
@@ -58,8 +61,9 @@ class NativeForward:
         m = model.model
         cfg = model.cfg
         dev = model.device
-        if not (m.is_first and m.is_last):
-            raise ValueError("the native forward runs single-stage models (pp == 1)")
+        if not m.layers:
+            raise ValueError("the native forward needs at least one decoder layer per stage")
+        self.is_first, self.is_last = bool(m.is_first), bool(m.is_last)
         first = m.layers[0]
         attn0 = first.self_attn
         self.hidden = cfg.hidden_size
@@ -81,8 +85,9 @@ class NativeForward:
             lw.v_cache = kv.v_cache(i).data_ptr()
             if a.qkv_proj.bias is not None:
                 raise ValueError("the native forward does not apply QKV bias")
-        head = model.lm_head
+        head = model.lm_head if self.is_last else None
         d = ModelDesc()
+        d.is_first, d.is_last = int(self.is_first), int(self.is_last)
         d.num_layers, d.hidden = len(m.layers), cfg.hidden_size
         d.hq, d.hkv, d.head_dim = attn0.num_heads, attn0.num_kv_heads, attn0.head_dim
         d.inter_local = first.mlp.down_proj.in_local
@@ -92,12 +97,16 @@ class NativeForward:
         d.prefill_tc = int(os.environ.get("XV_ATTN_PREFILL", "tc") != "mma")
         d.eps, d.attn_scale = float(cfg.rms_norm_eps), float(attn0.scale)
         d.gate_up_interleaved = 1 if first.mlp.gate_up_proj.interleave else 0
-        d.vocab_start, d.vocab_rows = m.embed_tokens.vocab_start, m.embed_tokens.weight.shape[0]
-        d.lm_head_rows = head.weight.shape[0]
-        d.lm_valid = max(0, min(head.per_rank, head.num_embeddings - head.vocab_start))
-        d.embed = m.embed_tokens.weight.data_ptr()
-        d.final_norm = m.norm.weight.data_ptr()
-        d.lm_head = head.weight.data_ptr()
+        if self.is_first:
+            d.vocab_start, d.vocab_rows = m.embed_tokens.vocab_start, m.embed_tokens.weight.shape[0]
+            d.embed = m.embed_tokens.weight.data_ptr()
+        if self.is_last:
+            d.lm_head_rows = head.weight.shape[0]
+            d.lm_valid = max(0, min(head.per_rank, head.num_embeddings - head.vocab_start))
+            d.final_norm = m.norm.weight.data_ptr()
+            d.lm_head = head.weight.data_ptr()
+        else:
+            d.final_norm = m.boundary_norm.weight.data_ptr()    # the next stage's first input norm
         d.cos_sin = attn0.rotary.cos_sin.data_ptr()
         d.layers = ctypes.cast(self.layers, ctypes.POINTER(LayerWeights))
         comm = model.comm
@@ -112,6 +121,8 @@ class NativeForward:
             d.epoch = comm.epoch.data_ptr()
             d.buf_bytes, d.slots_offset = comm.buf_bytes, comm.slots_off
             d.h_offset = comm.h_off if comm.sharded_reduce else -1
+            d.tp_push = 1 if comm.fuse_gemm else 0
+            d.tp_one_shot_max = comm.one_shot_max_tokens
             from ..parallel.symm import SPIN_LIMIT
 
             d.spin_us = SPIN_LIMIT
@@ -120,6 +131,7 @@ class NativeForward:
             d.h_offset = -1
         self.desc = d
         self.vocab_local = d.lm_head_rows
+        lm_rows = max(d.lm_head_rows, 8)
 
         def buf(rows, cols, dtype=torch.bfloat16):
             return torch.empty((rows, cols), dtype=dtype, device=dev)
@@ -134,7 +146,7 @@ class NativeForward:
             h_buf = buf(T, H)
         self.t = dict(h=h_buf, qkv=buf(T, d.qkv_rows), q=buf(T, q_cols), attn=buf(T, q_cols),
                       act=buf(T, d.inter_local), residual=buf(T, H), partial=buf(T, H), hidden_out=buf(S, H),
-                      logits=buf(S, d.lm_head_rows), tokens=torch.zeros(S, dtype=torch.int64, device=dev))
+                      logits=buf(S, lm_rows), tokens=torch.zeros(S, dtype=torch.int64, device=dev))
         if not d.gate_up_interleaved:
             self.t["gu"] = buf(T, 2 * d.inter_local)
         st = cuda._state(self.t["h"])
@@ -152,8 +164,13 @@ class NativeForward:
         self.arena = a
         self.launches_per_call = 0
 
+    def stage_inputs(self, n_tokens: int):
+        """Where a stage that is not the first receives (hidden states, residual stream)."""
+        return self.t["h"][:n_tokens], self.t["residual"][:n_tokens]
+
     def forward(self, batch):
-        """Launches the step. Returns the int64 token tensor for greedy batches, else the local logits."""
+        """Launches the stage. On the last stage returns the int64 token tensor for greedy batches, else the
+        local logits; on other stages the (hidden states, residual stream) pair to hand on."""
         if batch.num_tokens > self.max_tokens or batch.num_samples > self.max_samples:
             raise RuntimeError("batch exceeds the native forward's arena")
         at = batch.attn
@@ -171,6 +188,8 @@ class NativeForward:
             raise RuntimeError(f"native forward failed at step {self._lib.xv_forward_failed_op()}: "
                                f"{cuda.ERRORS.get(rc, rc)}")
         cuda.launch_count += self._lib.xv_forward_launch_calls() - before
+        if not self.is_last:
+            return self.stage_inputs(batch.num_tokens)
         if batch.all_greedy:
             return self.t["tokens"][: batch.num_samples]
         return self.t["logits"][: batch.num_samples]

@@ -14,6 +14,7 @@ def _need(n):
 
 def _fused_rank(rank, world, nvls):
     os.environ["XV_TP_NVLS"] = "1" if nvls else "0"
+    os.environ["XV_TP_PUSH"] = "1"
     os.environ["XV_TP_FUSE_GEMM_MAX_T"] = "100000"
     import torch.distributed as dist
 
@@ -82,6 +83,7 @@ def _fused_rank(rank, world, nvls):
     local = full[:, rank * per:(rank + 1) * per].contiguous().to(dev)
     ids = comm.argmax(local, per, rank * per).cpu()
     want = full.float().argmax(-1)
+    dist.barrier()         # every rank has read its result before a peer's next call writes the slots again
     # more rows than CTAs can be resident at once: the grid is capped and walks the rows
     g = torch.Generator().manual_seed(8)
     many = torch.randn(400, 4096, generator=g).bfloat16()
@@ -99,11 +101,14 @@ def _fused_rank(rank, world, nvls):
         got = comm.gather_logits(padded.to(dev)[:, :per])
         torch.cuda.synchronize()
         gather_ok = gather_ok and got is not None and torch.equal(got.cpu(), full)
+        dist.barrier()     # ... and before a peer's next gather overwrites the matrix (in the engine a whole forward lies between)
     assert comm.gather_logits(torch.zeros(7, per, dtype=torch.bfloat16, device=dev)) is None   # too many rows
     torch.cuda.synchronize()
     cuda.check_status(dev)
     dist.barrier()
-    assert fused_gemm and gather_ok and many_ok
+    assert fused_gemm, "the row-parallel projection did not run as one kernel"
+    assert gather_ok, "gathered logits differ from the full matrix"
+    assert many_ok, (ids_many.tolist()[:24], many.float().argmax(-1).tolist()[:24])
     return max(errs), ids.tolist(), want.tolist(), bool(comm.mc_ptr)
 
 
@@ -277,6 +282,21 @@ def test_engine_tp4_tp8_match_tp1(tmp_path, tp):
     out = _probe(d, tp=tp, comm="fused", cg=True, port=29901 + tp)
     assert _agree(ref, out) >= 10, (ref, out)
     eager = _probe(d, tp=tp, comm="fused", port=29921 + tp)
+    assert _agree(ref, eager) >= 10, (ref, eager)
+
+
+@pytest.mark.timeout(600)
+def test_engine_tp2_one_kernel_projection_matches(tmp_path, monkeypatch):
+    """The one-kernel row-parallel projection (default from 4 ranks up) forced on at 2 ranks, in both forms:
+    decode steps (4 rows) reduce every row on every rank, prefill steps deal the rows to the ranks."""
+    _need(2)
+    d = _tiny_dir(tmp_path)
+    ref = _probe(d)
+    monkeypatch.setenv("XV_TP_PUSH", "1")
+    monkeypatch.setenv("XV_TP_ONE_SHOT_MAX_T", "8")
+    out = _probe(d, tp=2, comm="fused", cg=True, port=29865)
+    assert _agree(ref, out) >= 10, (ref, out)
+    eager = _probe(d, tp=2, comm="fused", port=29867)
     assert _agree(ref, eager) >= 10, (ref, eager)
 
 

@@ -58,7 +58,7 @@ int row_linear_reduce_norm(Ctx& c, const void* x, const void* w, int k, const vo
     ++c.call_idx;
     const long long slot_off = static_cast<long long>(which) * m->buf_bytes;
     if (c.push) {
-      XV_TRY(16, xv_gemm_bf16_tp(x, w, T, H, k, k, k, c.a->num_sms, m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch,
+      XV_TRY(16, xv_gemm_bf16_tp(x, w, T, H, k, k, k, c.a->gemm_ws, c.a->gemm_ws_bytes, c.a->num_sms, m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch,
                                  m->tp_rank, m->tp_world, slot_off, m->buf_bytes, c.two_shot ? 1 : 0, m->h_offset,
                                  c.a->residual, c.a->residual, norm_w, c.a->h, m->eps, 0, m->spin_us, c.a->status,
                                  c.s));
@@ -120,12 +120,17 @@ int xv_qwen3_forward(const XvModelDesc* m, const XvBatchDesc* b, const XvArena* 
   const int q_cols = m->hq * D;
   const int L = m->num_layers;
   if (m->tp_world > 1) {
+    // One kernel per row-parallel projection (tiles pushed to the reducing ranks) up to tp_push_max tokens.
     // Few rows: every rank reduces every row (one wait per reduction point). More rows: the rows are dealt
     // to the ranks (traffic per GPU independent of the rank count, a second wait for the broadcast).
-    c.two_shot = m->h_offset >= 0 && T > m->tp_one_shot_max;
-    const long long cap = c.two_shot ? (T + m->tp_world - 1) / m->tp_world : T;
-    c.push = m->tp_push != 0 && static_cast<long long>(m->tp_world) * cap * H * 2 <= m->buf_bytes;
-    // both members of a stage pair must agree on the form: it fixes the layout of the residual they exchange
+    // The form fixes the layout of the residual stream, so it is chosen once per forward, and identically
+    // on both sides of a pipeline hand-off (same token count, same settings).
+    if (m->tp_push != 0 && m->h_offset >= 0 && T <= m->tp_push_max) {
+      c.two_shot = T > m->tp_one_shot_max;
+      const long long cap = c.two_shot ? (T + m->tp_world - 1) / m->tp_world : T;
+      c.push = static_cast<long long>(m->tp_world) * cap * H * 2 <= m->buf_bytes;
+    }
+    if (!c.push) c.two_shot = m->h_offset >= 0 && m->tp_pull_two_shot != 0;
   }
 
   // ---- embedding and the first normalisation point (first pipeline stage) ----

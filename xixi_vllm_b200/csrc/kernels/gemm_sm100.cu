@@ -59,6 +59,10 @@ struct GemmParams {
   int act;           // 1: SiLU-mul epilogue. Operand rows of the weight matrix come in groups of 16 =
                      //    [8 gate rows | 8 up rows]; output has half as many features (bf16 only)
   int vec_ok;        // output rows may be written with 16-byte stores (alignment and row stride allow it)
+  int fixup;         // swapped orientation with split-K: partial planes go to fix_planes, and the CTA that
+                     // brings a tile's last partial sums them and runs the normal epilogue (no second kernel)
+  float* fix_planes;        // [splits][rows_b][rows_a] fp32
+  uint32_t* fix_counters;   // one per output tile, zero between launches
   long long ldc;
   long long split_stride;   // elements between split-K partial planes
   void* out;
@@ -390,47 +394,128 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint8_t* stage_w = staging + quarter * 2048;
     const int nchunks = (p.bn + 31) >> 5;               // 32 accumulator columns per tcgen05.ld
     uint32_t t = 0;
+    bool dead = false;     // a wait ran out: no more data work, but this warp still meets the others at the barriers
+    volatile int* fix_last = abort_flag + 1;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++t) {
       const WorkItem wi = decode_work(p, w);
       const uint32_t buf = t & 1, use = t >> 1;
-      bool ok = mbar_wait(&acc_full[buf], use & 1);
-      if (!ok) {
-        report_status(p.status, kGemmKernelId, kWaitAccumTimeout);
-        *abort_flag = 1;
+      if (!dead) {
+        bool ok = mbar_wait(&acc_full[buf], use & 1);
+        if (!ok) {
+          report_status(p.status, kGemmKernelId, kWaitAccumTimeout);
+          *abort_flag = 1;
+        }
+        tc_fence_after_sync();
+        // warp-uniform: the aligned TMEM loads below must be executed by all 32 lanes or none
+        dead = !__all_sync(0xffffffffu, ok && (*abort_flag == 0));
       }
-      tc_fence_after_sync();
-      // warp-uniform: the aligned TMEM loads below must be executed by all 32 lanes or none
-      ok = __all_sync(0xffffffffu, ok && (*abort_flag == 0));
-      if (!ok) break;
       const int a_row0 = wi.tile_a * kBM + quarter * 32;
-      const uint32_t lane_addr = tmem_base + buf * p.acc_stride + (static_cast<uint32_t>(quarter * 32) << 16);
       const int b0 = wi.tile_b * p.bn;
       const int b_end = min(p.rows_b, b0 + p.bn);
-      // Two register sets: the load of the next 32 columns is in flight while this one is stored.
-      uint32_t ra[32], rb[32];
-      tmem_ld32(lane_addr, ra);
-      for (int ch = 0; ch < nchunks; ch += 2) {
-        tmem_ld_wait();
-        tmem_ld_fence_regs(ra);
-        if (ch + 1 < nchunks) tmem_ld32(lane_addr + static_cast<uint32_t>((ch + 1) * 32), rb);
-        if (p.transposed)
-          store_swapped32(p, push, stage_w, lane, a_row0, b0 + ch * 32, b_end, wi.split, ra);
-        else
-          store_row32(p, push, a_row0 + lane, b0 + ch * 32, b_end, wi.split, ra);
-        if (ch + 1 < nchunks) {
-          tmem_ld_wait();
-          tmem_ld_fence_regs(rb);
-          if (ch + 2 < nchunks) tmem_ld32(lane_addr + static_cast<uint32_t>((ch + 2) * 32), ra);
-          if (p.transposed)
-            store_swapped32(p, push, stage_w, lane, a_row0, b0 + (ch + 1) * 32, b_end, wi.split, rb);
-          else
-            store_row32(p, push, a_row0 + lane, b0 + (ch + 1) * 32, b_end, wi.split, rb);
+      if (!dead) {
+        const uint32_t lane_addr = tmem_base + buf * p.acc_stride + (static_cast<uint32_t>(quarter * 32) << 16);
+        float* plane = p.fixup ? p.fix_planes + static_cast<size_t>(wi.split) * p.rows_a * p.rows_b : nullptr;
+        // Two register sets: the load of the next 32 columns is in flight while this one is stored.
+        uint32_t ra[32], rb[32];
+        tmem_ld32(lane_addr, ra);
+        for (int ch = 0; ch < nchunks; ch += 2) {
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            if (ch + half < nchunks) {
+              uint32_t(&r)[32] = half == 0 ? ra : rb;
+              uint32_t(&rn)[32] = half == 0 ? rb : ra;
+              tmem_ld_wait();
+              tmem_ld_fence_regs(r);
+              if (ch + half + 1 < nchunks) tmem_ld32(lane_addr + static_cast<uint32_t>((ch + half + 1) * 32), rn);
+              const int c0 = b0 + (ch + half) * 32;
+              if (p.fixup) {
+                if (a_row0 + lane < p.rows_a) {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (c0 + j < b_end)
+                      plane[static_cast<size_t>(c0 + j) * p.rows_a + a_row0 + lane] = __uint_as_float(r[j]);
+                }
+              } else if (p.transposed) {
+                store_swapped32(p, push, stage_w, lane, a_row0, c0, b_end, wi.split, r);
+              } else {
+                store_row32(p, push, a_row0 + lane, c0, b_end, wi.split, r);
+              }
+            }
+          }
         }
+        // this warp has drained its quarter of the accumulator
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
       }
-      // this warp has drained its quarter of the accumulator
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      if (p.fixup) {
+        // Whoever brings the tile's last partial plane sums the planes (in split order, so the result does
+        // not depend on who that is) and runs the normal epilogue. Nobody waits for anybody.
+        __threadfence();
+        named_barrier(3, 128);
+        if (threadIdx.x == 64) {
+          uint32_t* ctr = p.fix_counters + wi.tile_a * p.tiles_b + wi.tile_b;
+          const unsigned ticket = atomicAdd(ctr, 1u);
+          const int last = ticket == static_cast<unsigned>(p.splits - 1);
+          if (last) *ctr = 0u;                     // every split has arrived: ready for the next launch
+          *fix_last = last;
+        }
+        named_barrier(3, 128);
+        if (*fix_last && !dead) {
+          // The planes hold [token][feature] rows, the layout of the output: 16 threads take a token row of
+          // the tile (8 features each), four rows and two planes at a time to keep enough loads in flight.
+          __threadfence();
+          const size_t plane_stride = static_cast<size_t>(p.rows_a) * p.rows_b;
+          const int et = static_cast<int>(threadIdx.x) - 64;
+          const int col = wi.tile_a * kBM + (et & 15) * 8;
+          if (col < p.rows_a) {
+            for (int tb = b0 + (et >> 4); tb < b_end; tb += 32) {
+              float acc[4][8];
+#pragma unroll
+              for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+              for (int sp = 0; sp < p.splits; sp += 2) {
+                float4 v[2][4][2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                  for (int u = 0; u < 4; ++u) {
+                    const int tok = tb + 8 * u;
+                    const bool on = sp + h < p.splits && tok < b_end;
+                    const float4* src = reinterpret_cast<const float4*>(
+                        p.fix_planes + (sp + h) * plane_stride + static_cast<size_t>(on ? tok : b0) * p.rows_a + col);
+                    v[h][u][0] = on ? ld_cg_f4(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    v[h][u][1] = on ? ld_cg_f4(src + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+                  }
+#pragma unroll
+                for (int h = 0; h < 2; ++h)       // plane order: the sum does not depend on which CTA came last
+#pragma unroll
+                  for (int u = 0; u < 4; ++u) {
+                    acc[u][0] += v[h][u][0].x; acc[u][1] += v[h][u][0].y; acc[u][2] += v[h][u][0].z; acc[u][3] += v[h][u][0].w;
+                    acc[u][4] += v[h][u][1].x; acc[u][5] += v[h][u][1].y; acc[u][6] += v[h][u][1].z; acc[u][7] += v[h][u][1].w;
+                  }
+              }
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int tok = tb + 8 * u;
+                if (tok < b_end) {
+                  uint4 o;
+                  o.x = pack_bf16(acc[u][0], acc[u][1]);
+                  o.y = pack_bf16(acc[u][2], acc[u][3]);
+                  o.z = pack_bf16(acc[u][4], acc[u][5]);
+                  o.w = pack_bf16(acc[u][6], acc[u][7]);
+                  if (push.enabled)
+                    tp_push_store8(push, tok, col, 0, o);
+                  else
+                    *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(tok) * p.ldc + col) = o;
+                }
+              }
+            }
+          }
+        }
+        named_barrier(3, 128);                    // fix_last is rewritten for the next tile
+      }
     }
     if (push.enabled) {
       // "this CTA's tiles are in the reducing ranks' slots": once per CTA that had GEMM work, also when the
@@ -470,7 +555,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // that starts at zero the sum does not depend on their order.
 constexpr int kPairAccStride = 256;
 constexpr long long kSkReserveBytes = 20ll << 20;   // tail of the workspace kept zero for partial tiles + counters
-constexpr long long kSkCounterBytes = 4096;         // the very end of it: two counters per SM pair
+constexpr long long kSkCounterBytes = 4096;         // the very end of it: two counters per SM pair, then one per tile
+constexpr int kFixCounterFirst = 256;               // first counter word of the single-CTA kernel's split-K fix-up
+constexpr int kFixCounterTiles = 768;
 
 struct StreamK {
   int units_per_pair;      // K blocks of the stream-K region each pair takes
@@ -1194,25 +1281,37 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
                      const TpPush* push_in = nullptr, int push_max_splits = 1) {
   XvGemmPlan pl;
   if (num_sms <= 0) num_sms = 148;
+  // A workspace of at least twice the stream-K reserve has its tail set aside (and kept zero) for counters and
+  // the pair kernel's partial tiles; split-K planes use the front part. Smaller workspaces are all planes.
+  const bool sk_ok = workspace != nullptr && workspace_bytes >= 2 * kSkReserveBytes;
   unsigned flags = 0;
-  if (act && !defer_reduce) flags |= 0u;     // callers of the fused activation check the plan first
-  int rc = gemm_plan_impl(m, n, k, num_sms, &pl, flags, push_in ? push_max_splits : 0);
+  int max_splits = 0;
+  if (push_in != nullptr) {
+    // Pushed tiles must be complete sums: K splits are summed inside the kernel by the CTA that arrives last
+    // at a tile, a chain of dependent memory round trips that only pays for a long K.
+    (void)push_max_splits;
+    const int total_kb = (k + kBK - 1) / kBK;
+    if (!sk_ok || total_kb <= 32) flags |= kPlanNoSplit;
+    max_splits = 4;
+  }
+  int rc = gemm_plan_impl(m, n, k, num_sms, &pl, flags, max_splits);
   if (rc) return rc;
   if ((ldx % 8) || (ldw % 8) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return XV_ERR_ALIGN;
-  // A workspace of at least twice the stream-K reserve has its tail set aside (and kept zero) for the pair
-  // kernel's partial tiles; split-K planes use the front part. Smaller workspaces are all planes and the
-  // pair kernel deals whole tiles (its pairs then finish unevenly).
-  const bool sk_ok = workspace != nullptr && workspace_bytes >= 2 * kSkReserveBytes;
+  // Without the reserve the pair kernel deals whole tiles (its pairs then finish unevenly).
   if (pl.pair && pl.sk_tiles > 0 && (!sk_ok || pl.workspace_bytes > kSkReserveBytes))
     fill_pair(m, n, k, pl.bn, num_sms, -1, pl);
-  const bool to_planes = pl.splits > 1 && push_in == nullptr;
-  if (to_planes && (!workspace || pl.workspace_bytes > (sk_ok ? workspace_bytes - kSkReserveBytes : workspace_bytes)))
+  // Split-K in the swapped orientation: the planes are summed inside the kernel by the CTA that brings a
+  // tile's last one (needs a tile counter from the reserve), unless the caller wants the planes themselves.
+  const bool fixup = pl.splits > 1 && pl.swapped && !pl.pair && push_in != nullptr && sk_ok && (n % 8) == 0 &&
+                     pl.tiles_a * pl.tiles_b <= kFixCounterTiles;
+  const bool to_planes = pl.splits > 1 && !fixup;
+  if (pl.splits > 1 && (!workspace || pl.workspace_bytes > (sk_ok ? workspace_bytes - kSkReserveBytes : workspace_bytes)))
     return XV_ERR_WORKSPACE;
-  if (act && pl.splits > 1) return XV_ERR_UNSUPPORTED;       // callers check the plan first
+  if (act && to_planes) return XV_ERR_UNSUPPORTED;           // callers check the plan first
   if (act && ((n % 16) || (ldy % 8))) return XV_ERR_SHAPE;
   if (to_planes && !defer_reduce && ldy != n) return XV_ERR_SHAPE;   // the reduce kernel writes a dense output
-  if (push_in != nullptr && ((n % 8) || pl.splits > push_max_splits)) return XV_ERR_SHAPE;
+  if (push_in != nullptr && ((n % 8) || to_planes)) return XV_ERR_SHAPE;
   if ((rc = ensure_smem_attr(pl.pair != 0))) return rc;
 
   CUtensorMap map_a, map_b;
@@ -1262,6 +1361,12 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
     p.act = act;
     p.vec_ok = (ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0) && (act || (n % 8) == 0);
   }
+  if (fixup) {
+    p.fixup = 1;
+    p.fix_planes = static_cast<float*>(workspace);
+    p.fix_counters = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + workspace_bytes - kSkCounterBytes) +
+                     kFixCounterFirst;
+  }
 
   TpPush push;
   std::memset(&push, 0, sizeof(push));
@@ -1289,7 +1394,7 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
     if (push_in) {
       push = *push_in;
       push.enabled = 1;
-      push.splits = pl.splits;
+      push.splits = 1;
       // every CTA takes part in the row phase and waits for the others: the whole grid must be resident
       int per_sm = 0;
       if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_tcgen05_pair_kernel, kGemmThreads,
@@ -1307,7 +1412,7 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
     if (push_in) {
       push = *push_in;
       push.enabled = 1;
-      push.splits = pl.splits;
+      push.splits = 1;               // K splits are summed before the push (fix-up inside the kernel)
       int per_sm = 0;
       if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_tcgen05_kernel, kGemmThreads, pl.smem_bytes) !=
               cudaSuccess || per_sm < 1)
@@ -1357,8 +1462,9 @@ int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, lon
 //   mode 0: residual_out = sum (+ residual_in, may be null); out = rmsnorm(residual_out) * norm_w.   mode 1: out = sum.
 // `epoch`: 32 uint32 words of local device memory, zero-initialised once (the kernels keep their counters'
 // history there). Returns XV_ERR_WORKSPACE when the slot array is too small for the problem.
-int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long ldx, long long ldw, int num_sms,
-                    const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf, void* epoch, int rank,
+int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long ldx, long long ldw, void* workspace,
+                    long long workspace_bytes, int num_sms, const void* const* peer_bufs, void* const* peer_flags,
+                    const void* mc_buf, void* epoch, int rank,
                     int world, long long slot_offset, long long slot_bytes, int two_shot, long long h_offset,
                     const void* residual_in, void* residual_out, const void* norm_w, void* y_out, float eps, int mode,
                     unsigned spin_us, int* status, cudaStream_t stream) {
@@ -1391,11 +1497,9 @@ int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long
   t.hidden = n;
   t.eps = eps;
   t.mode = mode;
-  const long long per_split = static_cast<long long>(world) * t.cap_rows * n * 2;
-  const long long max_splits = slot_bytes / per_split;
-  if (max_splits < 1) return XV_ERR_WORKSPACE;
-  return gemm_impl(x, w, nullptr, m, n, k, ldx, ldw, n, nullptr, 0, num_sms, status, stream, true, nullptr, 0, &t,
-                   static_cast<int>(max_splits > 4 ? 4 : max_splits));
+  if (static_cast<long long>(world) * t.cap_rows * n * 2 > slot_bytes) return XV_ERR_WORKSPACE;
+  return gemm_impl(x, w, nullptr, m, n, k, ldx, ldw, n, workspace, workspace_bytes, num_sms, status, stream, false,
+                   nullptr, 0, &t, 1);
 }
 
 // Y[m, n/2] = silu(gate) * up, with W's rows interleaved in groups of 16 = [8 gate | 8 up].

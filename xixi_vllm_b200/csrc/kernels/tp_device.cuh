@@ -376,7 +376,7 @@ __device__ __noinline__ void tp_push_tail(const TpPush& t) {
           for (int j = 0; j < 8; ++j) acc[j] = 0.f;
           const char* p0 = slots + (static_cast<long long>(i) * t.hidden + v * 8) * 2;
           const long long src_stride = static_cast<long long>(t.cap_rows) * t.hidden * 2;
-#pragma unroll 4
+#pragma unroll 8
           for (int s = 0; s < n_src; ++s) {       // fixed order, fp32: the result does not depend on arrival order
             float x[8];
             unpack8(ld_relaxed_sys_v4(p0 + s * src_stride), x);

@@ -167,8 +167,9 @@ int xv_tp_allgather_cols(const void* const* peer_bufs, void* const* peer_flags, 
 // finished rows are broadcast to byte offset `h_offset` of every rank's symmetric buffer and the
 // residual buffers hold only this rank's rows; two_shot = 0: every rank reduces all rows into its own
 // y_out. `epoch`: 32 zero-initialised uint32 words of local device memory kept across calls.
-int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long ldx, long long ldw, int num_sms,
-                    const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf, void* epoch, int rank,
+int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long ldx, long long ldw, void* workspace,
+                    long long workspace_bytes, int num_sms, const void* const* peer_bufs, void* const* peer_flags,
+                    const void* mc_buf, void* epoch, int rank,
                     int world, long long slot_offset, long long slot_bytes, int two_shot, long long h_offset,
                     const void* residual_in, void* residual_out, const void* norm_w, void* y_out, float eps, int mode,
                     unsigned spin_us, int* status, cudaStream_t stream);
@@ -203,15 +204,17 @@ typedef struct XvModelDesc {
   void* const* peer_flags;
   const void* mc_buf;
   void* epoch;
-  long long h_offset;                 // byte offset of the activation buffer h inside the symmetric buffer
-                                      // (>= 0: row-sharded reductions broadcast h there; < 0: one-shot form)
+  long long h_offset;                 // byte offset of the activation buffer h inside the symmetric buffer: the
+                                      // two-shot reductions broadcast the normalised rows there (< 0: none)
   long long buf_bytes;                // size of each of the three symmetric partial buffers
   long long slots_offset;             // byte offset of the argmax slots in the symmetric buffer
   unsigned spin_us;
   int num_kv_blocks;                  // pages in each layer's k_cache / v_cache
   int prefill_tc;                     // 1: prefill attention on the tcgen05 kernel when the shape allows
-  int tp_push;                        // 1: row-parallel GEMM + reduction + norm as one kernel (xv_gemm_bf16_tp)
-  int tp_one_shot_max;                // forwards of at most this many tokens reduce every row on every rank
+  int tp_push;                        // 1: row-parallel GEMM + reduction + norm as one kernel (xv_gemm_bf16_tp) ...
+  int tp_push_max;                    // ... for forwards of at most this many tokens
+  int tp_one_shot_max;                // of those, forwards of at most this many tokens reduce every row on every rank
+  int tp_pull_two_shot;               // two-kernel form (GEMM, then a reduction kernel that pulls): 1 = row-sharded
   int is_first, is_last;              // pipeline stage: the first owns the embedding, the last the LM head; on
                                       // other stages `final_norm` is the next stage's first input norm and the
                                       // arena's h / residual are received from / sent to the neighbours

@@ -88,7 +88,7 @@ def lib():
                                        _vp, _vp]
     L.xv_tp_argmax.argtypes = [_vp, _vp, _vp, _i32, _i32, _i64, _vp, _i64, _i32, _i32, _i32, _vp, _i32,
                                ctypes.c_uint, _vp, _vp]
-    L.xv_gemm_bf16_tp.argtypes = [_vp, _vp, _i32, _i32, _i32, _i64, _i64, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i64,
+    L.xv_gemm_bf16_tp.argtypes = [_vp, _vp, _i32, _i32, _i32, _i64, _i64, _vp, _i64, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i64,
                                   _i64, _i32, _i64, _vp, _vp, _vp, _vp, _f32, _i32, ctypes.c_uint, _vp, _vp]
     L.xv_gemm_plan_override.argtypes = [_i32, _i32, _i32, _i32]
     L.xv_gemm_plan_override.restype = None
@@ -486,7 +486,8 @@ def gemm_tp_fused(x, w, peer_bufs, peer_flags, mc_ptr: int, epoch, rank: int, wo
     N = w.shape[0]
     st = _state(x)
     _check(lib().xv_gemm_bf16_tp(
-        x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0), w.stride(0), st.num_sms, peer_bufs, peer_flags,
+        x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0), w.stride(0), st.gemm_ws.data_ptr(), st.gemm_ws.numel(),
+        st.num_sms, peer_bufs, peer_flags,
         mc_ptr or None, epoch.data_ptr(), rank, world, slot_offset, slot_bytes, 1 if two_shot else 0, h_offset,
         residual_in.data_ptr() if residual_in is not None else None,
         residual_out.data_ptr() if residual_out is not None else None,

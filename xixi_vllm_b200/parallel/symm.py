@@ -106,10 +106,15 @@ class FusedTPComm(TPComm):
         # reducing ranks' slots); XV_TP_PUSH=0 goes back to GEMM + reduction kernel. This module-by-module path
         # (pipeline stages, tests) reduces every row on every rank, which costs NVLink traffic proportional to
         # the rank count, so it is used up to XV_TP_FUSE_GEMM_MAX_T tokens.
-        self.fuse_gemm = os.environ.get("XV_TP_PUSH", "1") != "0"
+        # Default: from 4 ranks up (at 2 ranks each rank's K is long, the GEMM dominates, and GEMM + pulling
+        # reduction kernel measured faster); XV_TP_PUSH=1 / 0 forces it on / off.
+        env_push = os.environ.get("XV_TP_PUSH", "")
+        self.fuse_gemm = (env_push == "1") if env_push in ("0", "1") else group.size >= 4
         self.fuse_gemm_max_tokens = int(os.environ.get("XV_TP_FUSE_GEMM_MAX_T", "256"))
-        # forwards of at most this many tokens use the one-shot form in the native executor
-        self.one_shot_max_tokens = int(os.environ.get("XV_TP_ONE_SHOT_MAX_T", "32"))
+        # native executor: forwards of at most push_max_tokens run the one-kernel projection, of those the ones
+        # of at most one_shot_max_tokens in the form where every rank reduces every row
+        self.push_max_tokens = int(os.environ.get("XV_TP_PUSH_MAX_T", "256"))
+        self.one_shot_max_tokens = int(os.environ.get("XV_TP_ONE_SHOT_MAX_T", "64"))
         self._idx = 0
         self._logits_view = None
         if logit_bytes:

@@ -145,6 +145,8 @@ class ModelRunner:
                     ar.copy_(r)
             with nvtx_range("forward"):
                 out = self._forward(sub, inter)
+            if self.native is not None and self.is_last_pp and isinstance(out, torch.Tensor):
+                out = out.clone()       # the executor's output buffer is reused by the next piece
             if not self.is_last_pp:
                 hs, rs = out["hidden_states"], out["residual"]
                 if self.native is not None:

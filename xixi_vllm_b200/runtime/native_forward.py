@@ -35,8 +35,8 @@ class ModelDesc(ctypes.Structure):
                 ("lm_head", _vp), ("cos_sin", _vp), ("layers", ctypes.POINTER(LayerWeights)), ("tp_rank", _i32),
                 ("tp_world", _i32), ("peer_bufs", _vp), ("peer_flags", _vp), ("mc_buf", _vp), ("epoch", _vp),
                 ("h_offset", _i64), ("buf_bytes", _i64), ("slots_offset", _i64), ("spin_us", ctypes.c_uint),
-                ("num_kv_blocks", _i32), ("prefill_tc", _i32), ("tp_push", _i32), ("tp_one_shot_max", _i32),
-                ("is_first", _i32), ("is_last", _i32)]
+                ("num_kv_blocks", _i32), ("prefill_tc", _i32), ("tp_push", _i32), ("tp_push_max", _i32),
+                ("tp_one_shot_max", _i32), ("tp_pull_two_shot", _i32), ("is_first", _i32), ("is_last", _i32)]
 
 
 class BatchDesc(ctypes.Structure):
@@ -120,8 +120,10 @@ class NativeForward:
             d.mc_buf = comm.mc_ptr or None
             d.epoch = comm.epoch.data_ptr()
             d.buf_bytes, d.slots_offset = comm.buf_bytes, comm.slots_off
-            d.h_offset = comm.h_off if comm.sharded_reduce else -1
+            d.h_offset = comm.h_off
+            d.tp_pull_two_shot = 1 if comm.sharded_reduce else 0
             d.tp_push = 1 if comm.fuse_gemm else 0
+            d.tp_push_max = comm.push_max_tokens
             d.tp_one_shot_max = comm.one_shot_max_tokens
             from ..parallel.symm import SPIN_LIMIT
 
@@ -138,7 +140,7 @@ class NativeForward:
 
         T, S, H = max_tokens, max_samples, cfg.hidden_size
         q_cols = d.hq * d.head_dim
-        if d.tp_world > 1 and d.h_offset >= 0:
+        if d.tp_world > 1:
             if T > comm.max_tokens:
                 raise ValueError("arena larger than the communicator's symmetric buffers")
             h_buf = comm.h_view[: T * H].view(T, H)        # broadcast target of the row-sharded reductions

@@ -2,11 +2,15 @@
 
     python -m bench.kernels [--what gemm,decode,prefill,elementwise] [--json out.json]
 
-Each case is timed with CUDA events on the launching stream after 3 warm-up launches, with a
-256 MiB write between timed launches to flush the 126 MB L2, and reported as achieved
-bytes/s or FLOP/s and as a fraction of the measured peaks in ``MEASURED_PEAKS.json`` (a
-STREAM-style copy and a cuBLAS bf16 GEMM on this machine). cuBLAS (``torch.matmul``) is timed
-next to the GEMM for reference.
+Large cases are timed with CUDA events on the launching stream after 3 warm-up launches, with a
+256 MiB write between timed launches to flush the 126 MB L2. Kernels of a few microseconds would be
+timed mostly for their host launch path that way (about 25 us per launch from Python), so the GEMM and
+decode-attention cases are captured into a CUDA graph instead: as many copies of the inputs as it takes
+to exceed the L2 (every launch reads cold operands), one launch per copy, back to back, and the graph's
+time divided by the number of launches: the figure a decode graph of the engine sees. Results are
+reported as achieved bytes/s or FLOP/s and as a fraction of the measured peaks in
+``MEASURED_PEAKS.json`` (a STREAM-style copy and a cuBLAS bf16 GEMM on this machine). cuBLAS
+(``torch.matmul``) is timed next to the GEMM the same way.
 """
 
 from __future__ import annotations
@@ -60,13 +64,43 @@ def timeit(fn, iters: int = 10, warmup: int = 3) -> float:
     return times[len(times) // 2]
 
 
+def timeit_graph(make_fn, bytes_per_copy: float, min_copies: int = 4, reps: int = 5) -> float:
+    """Median milliseconds per launch of ``make_fn(i)()`` inside a CUDA graph of back-to-back launches, copy i of
+    the inputs each; enough copies that their operands exceed the L2 twice over."""
+    n = max(min_copies, int(2 * 126e6 / max(bytes_per_copy, 1.0)) + 1)
+    n = min(n, 256)
+    fns = [make_fn(i) for i in range(n)]
+    for f in fns[:3]:
+        f()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in fns:
+            f()
+    g.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / n)
+    times.sort()
+    return times[len(times) // 2]
+
+
 def bench_gemm(out: list) -> None:
     pk = peaks()
     shapes = [
         # decode (weight streaming): Qwen3-8B TP1 and TP8, 32B TP8
         (1, 6144, 4096), (32, 6144, 4096), (256, 6144, 4096), (256, 4096, 4096), (256, 24576, 4096),
         (256, 4096, 12288), (64, 151936, 4096), (32, 768, 4096), (32, 4096, 512), (32, 3072, 4096),
-        (32, 4096, 1536), (256, 6400, 5120), (256, 5120, 3200),
+        (32, 4096, 1536), (256, 768, 4096), (256, 4096, 512), (256, 3072, 4096), (256, 4096, 1536),
+        (256, 6400, 5120), (256, 5120, 3200),
+        # a decode batch plus one prefill chunk
+        (1400, 6144, 4096), (1400, 4096, 4096), (1400, 24576, 4096), (1400, 4096, 12288),
         # prefill (compute bound)
         (4096, 6144, 4096), (4096, 4096, 4096), (4096, 24576, 4096), (4096, 4096, 12288),
         (16384, 24576, 4096), (8192, 8192, 8192),
@@ -74,8 +108,18 @@ def bench_gemm(out: list) -> None:
     for m, n, k in shapes:
         x = torch.randn(m, k, device=DEV).bfloat16()
         w = torch.randn(n, k, device=DEV).bfloat16()
-        ms = timeit(lambda: cuda.linear(x, w))
-        ms_cublas = timeit(lambda: torch.matmul(x, w.t()))
+        if 2.0 * n * k <= 64e6:
+            # small: cold copies inside one graph, no host launch path in the figure
+            copies = max(4, int(2 * 126e6 / (2.0 * n * k)) + 1)
+            copies = min(copies, 256)
+            ws = [w] + [torch.randn(n, k, device=DEV).bfloat16() for _ in range(copies - 1)]
+            ys = [torch.empty(m, n, device=DEV, dtype=torch.bfloat16) for _ in range(2)]
+            ms = timeit_graph(lambda i: (lambda: cuda.linear(x, ws[i % len(ws)], out=ys[i & 1])), 2.0 * n * k)
+            ms_cublas = timeit_graph(lambda i: (lambda: torch.matmul(x, ws[i % len(ws)].t(), out=ys[i & 1])), 2.0 * n * k)
+            del ws
+        else:
+            ms = timeit(lambda: cuda.linear(x, w))
+            ms_cublas = timeit(lambda: torch.matmul(x, w.t()))
         flops = 2.0 * m * n * k
         byts = 2.0 * (m * k + n * k + m * n)
         tf, gbs = flops / ms / 1e9, byts / ms / 1e6
@@ -115,8 +159,15 @@ def bench_decode(out: list) -> None:
         q, k, v, cu, kvl, bt = _attn_setup([1] * B, [L] * B, hq, hkv)
         attn = AttnBatch(cu_q=cu.to(DEV), kv_lens=kvl.to(DEV), block_tables=bt.to(DEV), num_seqs=B, num_decode=B,
                          max_q_len=1, max_kv_len=L, num_tokens=B)
-        ms = timeit(lambda: cuda.paged_attention(q, k, v, attn, 128 ** -0.5, hq, hkv, 128))
         byts = 2.0 * B * L * hkv * 128 * 2
+        if byts <= 64e6:
+            copies = min(64, max(4, int(2 * 126e6 / byts) + 1))
+            kvs = [(k, v)] + [(torch.randn_like(k), torch.randn_like(v)) for _ in range(copies - 1)]
+            ms = timeit_graph(lambda i: (lambda: cuda.paged_attention(q, kvs[i % len(kvs)][0], kvs[i % len(kvs)][1], attn,
+                                                                      128 ** -0.5, hq, hkv, 128)), byts)
+            del kvs
+        else:
+            ms = timeit(lambda: cuda.paged_attention(q, k, v, attn, 128 ** -0.5, hq, hkv, 128))
         gbs = byts / ms / 1e6
         out.append(dict(kernel="attn_decode", batch=B, kv_len=L, hq=hq, hkv=hkv, ms=ms, gbs=gbs,
                         frac_of_peak=gbs / pk["hbm_gbs"]))

@@ -23,7 +23,7 @@ def _fused_rank(rank, world, nvls):
     from xixi_vllm_b200.parallel.symm import FusedTPComm
     dev = torch.device("cuda", rank)
     H = 1024
-    comm = FusedTPComm(get_tp_group(), dev, H, 1024, torch.bfloat16, logits_rows=6, logits_local_cols=4096 // world)
+    comm = FusedTPComm(get_tp_group(), dev, H, 4096, torch.bfloat16, logits_rows=6, logits_local_cols=4096 // world)
     errs = []
     for it, T in enumerate([1, 7, 64, 300, 512, 3, 3, 129]):
         g = torch.Generator().manual_seed(100 + it)

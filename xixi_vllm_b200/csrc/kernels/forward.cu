@@ -125,7 +125,7 @@ int xv_qwen3_forward(const XvModelDesc* m, const XvBatchDesc* b, const XvArena* 
     // to the ranks (traffic per GPU independent of the rank count, a second wait for the broadcast).
     // The form fixes the layout of the residual stream, so it is chosen once per forward, and identically
     // on both sides of a pipeline hand-off (same token count, same settings).
-    if (m->tp_push != 0 && m->h_offset >= 0 && T <= m->tp_push_max) {
+    if (m->tp_push != 0 && m->h_offset >= 0 && T <= m->tp_push_max && H <= 6144) {     // 6144: the fused tail's row width
       c.two_shot = T > m->tp_one_shot_max;
       const long long cap = c.two_shot ? (T + m->tp_world - 1) / m->tp_world : T;
       c.push = static_cast<long long>(m->tp_world) * cap * H * 2 <= m->buf_bytes;

@@ -42,8 +42,8 @@ constexpr int kUmmaK = 16;        // K per tcgen05.mma for 16-bit inputs
 constexpr int kGemmThreads = 192;
 constexpr int kMaxStages = 8;
 constexpr int kGemmKernelId = 1;
-constexpr int kStagingBytes = 4 * 2048;   // per epilogue warp: [32 tokens][32 features] bf16 transpose buffer
-constexpr int kTailMaxVec = 6;            // hidden <= 192 * 6 * 8 = 9216 in the tensor-parallel tail
+constexpr int kStagingBytes = 4 * 2048;   // per epilogue warp: transpose buffer, [32 tokens][32 features] bf16 or [16][32] fp32
+constexpr int kTailMaxVec = 4;            // hidden <= 192 * 4 * 8 = 6144 in the tensor-parallel tail
 
 struct GemmParams {
   int rows_a;        // valid rows of operand A (M axis of the MMA)
@@ -63,6 +63,7 @@ struct GemmParams {
                      // brings a tile's last partial sums them and runs the normal epilogue (no second kernel)
   float* fix_planes;        // [splits][rows_b][rows_a] fp32
   uint32_t* fix_counters;   // one per output tile, zero between launches
+  unsigned long long* prof; // optional: 8 global-timer stamps per CTA (see xv_gemm_profile_buffer)
   long long ldc;
   long long split_stride;   // elements between split-K partial planes
   void* out;
@@ -89,6 +90,13 @@ __device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int w) {
     it.tile_b = r - it.tile_a * p.tiles_b;
   }
   return it;
+}
+
+// Phase stamps of the single-CTA kernel, per CTA: 0 entry, 1 barriers + TMEM ready, 2 first tile load issued,
+// 3 first stage landed, 4 last MMA of the first work item issued, 5 its accumulator complete, 6 epilogue of the
+// CTA's last work item done, 7 exit.
+__device__ __forceinline__ void gemm_prof(const GemmParams& p, int slot) {
+  if (p.prof != nullptr) p.prof[blockIdx.x * 8 + slot] = global_timer_ns();
 }
 
 __device__ __forceinline__ uint4 pack8_regs(const uint32_t* r) {
@@ -166,8 +174,27 @@ __device__ __forceinline__ void store_swapped32(const GemmParams& p, const TpPus
                                                 const uint32_t (&r)[32]) {
   const int a_row = a_row0 + lane;
   if (p.out_fp32) {
-    if (a_row < p.rows_a) {
-      float* o = static_cast<float*>(p.out) + static_cast<size_t>(split) * p.split_stride;
+    float* o = static_cast<float*>(p.out) + static_cast<size_t>(split) * p.split_stride;
+    if ((p.ldc & 3) == 0 && a_row0 + 32 <= p.rows_a) {
+      // through shared memory, 16 tokens at a time: eight lanes then write a token's 32 features as 16-byte
+      // pieces (four tokens per store instruction instead of one)
+      float* st = reinterpret_cast<float*>(stage_w);                  // [16 tokens][32 features]
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) st[j * 32 + lane] = __uint_as_float(r[half * 16 + j]);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int tl = (lane >> 3) + 4 * i;
+          const int tok = tok0 + half * 16 + tl;
+          const float4 v = *reinterpret_cast<const float4*>(st + tl * 32 + (lane & 7) * 4);
+          if (tok < b_end)
+            *reinterpret_cast<float4*>(o + static_cast<size_t>(tok) * p.ldc + a_row0 + (lane & 7) * 4) = v;
+        }
+      }
+    } else if (a_row < p.rows_a) {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
         if (tok0 + j < b_end) o[static_cast<size_t>(tok0 + j) * p.ldc + a_row] = __uint_as_float(r[j]);
@@ -243,6 +270,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const GemmParams p, const __grid_constant__ TpPush push) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   grid_dep_launch();           // the next kernel of the stream may start its prologue (see launch.cuh)
+  if (push.enabled) tp_prof(push, 0);
+  if (threadIdx.x == 0) gemm_prof(p, 0);
   // Dynamic shared memory is only guaranteed 16-byte alignment; the swizzled tiles need 1024.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -282,6 +311,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) gemm_prof(p, 1);
   // Everything up to here touched only this CTA's shared and tensor memory. The producer thread first
   // starts the weight stream, which no earlier kernel writes; every other thread waits now for the
   // previous kernel of the stream (its outputs are this kernel's activations, and this kernel's
@@ -313,6 +343,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tma_load_2d(sa + a_bytes, &map_b, &full_bar[i], (kb_begin + i) * kBK, wi.tile_b * p.bn, hint_b);
         }
       }
+      gemm_prof(p, 2);
       grid_dep_wait();
       // K blocks issued so far by this CTA, across work items: `it` counts them, `s` is the stage the
       // next one goes to and `round` how often the ring has wrapped (kept incrementally: no division
@@ -373,6 +404,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             break;
           }
           tc_fence_after_sync();
+          if (t == 0 && kb == kb_begin) gemm_prof(p, 3);
           const uint64_t soff = static_cast<uint64_t>((s * stage_bytes) >> 4);
 #pragma unroll
           for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
@@ -386,6 +418,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
         umma_commit(&acc_full[buf]);     // accumulator complete
+        if (t == 0) gemm_prof(p, 4);
       }
     }
   } else {
@@ -408,6 +441,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tc_fence_after_sync();
         // warp-uniform: the aligned TMEM loads below must be executed by all 32 lanes or none
         dead = !__all_sync(0xffffffffu, ok && (*abort_flag == 0));
+        if (t == 0 && threadIdx.x == 64) gemm_prof(p, 5);
       }
       const int a_row0 = wi.tile_a * kBM + quarter * 32;
       const int b0 = wi.tile_b * p.bn;
@@ -516,6 +550,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         named_barrier(3, 128);                    // fix_last is rewritten for the next tile
       }
+      if (threadIdx.x == 64) gemm_prof(p, 6);
     }
     if (push.enabled) {
       // "this CTA's tiles are in the reducing ranks' slots": once per CTA that had GEMM work, also when the
@@ -534,6 +569,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
+  if (threadIdx.x == 0) gemm_prof(p, 7);
   if (push.enabled) tp_push_tail<kTailMaxVec>(push);
 }
 
@@ -624,6 +660,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                          const GemmParams p, const StreamK sk, const __grid_constant__ TpPush push) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   grid_dep_launch();
+  if (push.enabled) tp_prof(push, 0);
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr uint32_t a_bytes = kBM * kBK * 2;
   const uint32_t half_bn = static_cast<uint32_t>(p.bn) >> 1;
@@ -976,6 +1013,8 @@ static uint32_t pow2_cols(int n) {
 using namespace xv;
 
 static bool g_disable_pair = false;
+static unsigned long long* g_tp_prof = nullptr;
+static unsigned long long* g_gemm_prof = nullptr;
 
 namespace {
 
@@ -988,6 +1027,7 @@ PlanOverride g_override = {0, 0, 0, 0, 0};
 
 constexpr unsigned kPlanNoPair = 1u;     // single-CTA kernels only
 constexpr unsigned kPlanNoSplit = 2u;    // the caller cannot take fp32 partial planes
+constexpr unsigned kPlanDeep = 4u;       // few CTAs: give each the whole SM's shared memory for stages
 
 struct PlanKey {
   int m, n, k, sms;
@@ -1040,7 +1080,8 @@ void plan_single(int m, int n, int k, int num_sms, unsigned flags, int max_split
   // small-token tiles leave room for two resident CTAs per SM (more loads in flight while
   // another CTA drains its epilogue); big tiles take the whole SM
   const int extra = 256 + (pl.swapped ? kStagingBytes : 0) + 1024;
-  const int smem_budget = (pl.swapped && pl.bn <= 128) ? 112 * 1024 : 220 * 1024;
+  static const int small_budget_kb = env_int("XV_GEMM_SWAPPED_SMEM_KB", 112);     // experiment knob
+  const int smem_budget = (pl.swapped && pl.bn <= 128 && !(flags & kPlanDeep)) ? small_budget_kb * 1024 : 220 * 1024;
   int stages = (smem_budget - extra) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) stages = 2;
@@ -1258,6 +1299,12 @@ extern "C" {
 // Test hook: 1 forces the single-CTA kernel for every shape (A/B comparisons), 0 restores.
 void xv_gemm_disable_pair(int disable) { g_disable_pair = disable != 0; }
 
+// Diagnostics: following xv_gemm_bf16_tp launches write 8 global-timer stamps per CTA into `buf`
+// (device memory, 8 * 8 bytes per CTA of the largest grid, i.e. 2 * SM count CTAs); null switches it off.
+void xv_tp_profile_buffer(void* buf) { g_tp_prof = static_cast<unsigned long long*>(buf); }
+// Same for the single-CTA GEMM kernel's own phases (see gemm_prof); 8 stamps for each of up to 2 * SM count CTAs.
+void xv_gemm_profile_buffer(void* buf) { g_gemm_prof = static_cast<unsigned long long*>(buf); }
+
 // Test and tuning hook: kind 0 = single CTA, swapped where the planner would; 1 = single CTA, normal
 // orientation; 2 = CTA pairs. bn / splits / stages <= 0 keep that kernel's default. kind < 0 clears.
 void xv_gemm_plan_override(int kind, int bn, int splits, int stages) {
@@ -1292,6 +1339,7 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
     (void)push_max_splits;
     const int total_kb = (k + kBK - 1) / kBK;
     if (!sk_ok || total_kb <= 32) flags |= kPlanNoSplit;
+    flags |= kPlanDeep;
     max_splits = 4;
   }
   int rc = gemm_plan_impl(m, n, k, num_sms, &pl, flags, max_splits);
@@ -1338,6 +1386,7 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
   }
   p.k = k;
   p.bn = pl.bn;
+  p.prof = pl.pair ? nullptr : g_gemm_prof;
   p.stages = pl.stages;
   p.k_blocks_per_split = pl.k_blocks_per_split;
   p.status = status;
@@ -1497,6 +1546,7 @@ int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long
   t.hidden = n;
   t.eps = eps;
   t.mode = mode;
+  t.prof = g_tp_prof;
   if (static_cast<long long>(world) * t.cap_rows * n * 2 > slot_bytes) return XV_ERR_WORKSPACE;
   return gemm_impl(x, w, nullptr, m, n, k, ldx, ldw, n, workspace, workspace_bytes, num_sms, status, stream, false,
                    nullptr, 0, &t, 1);

@@ -291,7 +291,15 @@ struct TpPush {
   float eps;
   int mode;                            // 0: residual add + RMSNorm; 1: plain sum
   int signal_ctas;                     // CTAs of this launch that own GEMM work (each raises its counter once)
+  unsigned long long* prof;            // optional: 8 global-timer stamps per CTA (see xv_tp_profile_buffer)
 };
+
+// Phase stamps of the one-kernel projection, per CTA: 0 kernel entry, 1 GEMM roles done (tiles pushed, arrival
+// raised), 2 all sources' tiles arrived, 3 this CTA's rows reduced and stored / broadcast, 4 broadcast raised,
+// 5 every owner's rows arrived (CTA 0 only), 6 exit.
+__device__ __forceinline__ void tp_prof(const TpPush& t, int slot) {
+  if (t.prof != nullptr && threadIdx.x == 0) t.prof[blockIdx.x * 8 + slot] = global_timer_ns();
+}
 
 __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -339,7 +347,7 @@ __device__ __forceinline__ void tp_push_store8(const TpPush& t, int row, int col
 // Called by threads 0 .. world-1 of the group that pushed, after a barrier among that group:
 // "this CTA's tiles have been written" on every rank.
 __device__ __forceinline__ void tp_push_signal_tiles(const TpPush& t, int peer) {
-  __threadfence_system();
+  // the release orders this thread's earlier stores and, through the barrier it follows, the group's
   red_release_sys_add(t.comm.peer_flags[peer] + kPushArriveWord + t.comm.rank, 1u);
 }
 
@@ -353,53 +361,89 @@ __device__ __noinline__ void tp_push_tail(const TpPush& t) {
   const int n_mine = t.two_shot ? tp_rows_owned(t.rows, rank, world) : t.rows;
   // rows go to the CTAs from the end of the grid first: those are the ones without GEMM tiles
   const int first = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+  tp_prof(t, 1);
   if (first < n_mine) {
+    const int nvec = t.hidden >> 3;
+    // What does not depend on the peers is fetched before the wait: the norm weights and the first row's residual.
+    uint4 wv[MAXVEC], rv[MAXVEC];
+    {
+      const int row0 = t.two_shot ? rank + first * world : first;
+#pragma unroll
+      for (int u = 0; u < MAXVEC; ++u) {
+        const int v = threadIdx.x + u * nthreads;
+        wv[u] = make_uint4(0u, 0u, 0u, 0u);
+        rv[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (v < nvec && t.mode == 0) {
+          wv[u] = *reinterpret_cast<const uint4*>(t.norm_w + v * 8);
+          if (t.residual_in != nullptr)
+            rv[u] = *reinterpret_cast<const uint4*>(t.residual_in + static_cast<size_t>(row0) * t.hidden + v * 8);
+        }
+      }
+    }
     if (threadIdx.x < world) {
       const uint32_t target = st[kPushArriveBase + threadIdx.x] + static_cast<uint32_t>(t.signal_ctas);
       if (!tp_wait_counter(t.comm.peer_flags[rank] + kPushArriveWord + threadIdx.x, target, t.comm.spin_limit))
         report_status(t.comm.status, kTpPushKernelId, kPeerFlagTimeout);
     }
     __syncthreads();
+    tp_prof(t, 2);
     const char* slots = static_cast<const char*>(t.comm.peer_buf[rank]) + t.slot_offset;
-    const int n_src = world * t.splits;
-    const int nvec = t.hidden >> 3;
+    const int n_src = world;          // K splits are summed before the push
     for (int i = first; i < n_mine; i += gridDim.x) {
       const int row = t.two_shot ? rank + i * world : i;
       float vals[MAXVEC][8];
       float ss = 0.f;
+      const long long src_stride = static_cast<long long>(t.cap_rows) * t.hidden * 2;
+      // two 16-byte columns of the row at a time: all their sources' loads are issued before the first sum,
+      // so a round costs one memory round trip instead of one per source
 #pragma unroll
-      for (int u = 0; u < MAXVEC; ++u) {
-        const int v = threadIdx.x + u * nthreads;
-        if (v < nvec) {
-          float acc[8];
+      for (int u0 = 0; u0 < MAXVEC; u0 += 2) {
+        if (threadIdx.x + u0 * nthreads < nvec) {
+          uint4 raw[2][kMaxRanks];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-          const char* p0 = slots + (static_cast<long long>(i) * t.hidden + v * 8) * 2;
-          const long long src_stride = static_cast<long long>(t.cap_rows) * t.hidden * 2;
-#pragma unroll 8
-          for (int s = 0; s < n_src; ++s) {       // fixed order, fp32: the result does not depend on arrival order
-            float x[8];
-            unpack8(ld_relaxed_sys_v4(p0 + s * src_stride), x);
+          for (int du = 0; du < 2; ++du) {
+            const int v = threadIdx.x + (u0 + du) * nthreads;
+            const char* p0 = slots + (static_cast<long long>(i) * t.hidden + (v < nvec ? v : 0) * 8) * 2;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] += x[j];
-          }
-          if (t.mode == 0) {
-            const size_t ro = static_cast<size_t>(row) * t.hidden + v * 8;
-            if (t.residual_in != nullptr) {
-              float rr[8];
-              unpack8(*reinterpret_cast<const uint4*>(t.residual_in + ro), rr);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) acc[j] += rr[j];
-            }
-            *reinterpret_cast<uint4*>(t.residual_out + ro) = pack8(acc);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              acc[j] = __bfloat162float(__float2bfloat16(acc[j]));
-              ss += acc[j] * acc[j];
-            }
+            for (int s = 0; s < kMaxRanks; ++s)
+              raw[du][s] = (s < n_src && v < nvec) ? ld_relaxed_sys_v4(p0 + s * src_stride) : make_uint4(0u, 0u, 0u, 0u);
           }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) vals[u][j] = acc[j];
+          for (int du = 0; du < 2; ++du) {
+            const int u = u0 + du;
+            const int v = threadIdx.x + u * nthreads;
+            if (v < nvec) {
+              float acc[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+              for (int s = 0; s < kMaxRanks; ++s) {     // fixed order, fp32: the result does not depend on arrival order
+                if (s < n_src) {
+                  float x[8];
+                  unpack8(raw[du][s], x);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) acc[j] += x[j];
+                }
+              }
+              if (t.mode == 0) {
+                const size_t ro = static_cast<size_t>(row) * t.hidden + v * 8;
+                if (t.residual_in != nullptr) {
+                  float rr[8];
+                  unpack8(i == first ? rv[u] : *reinterpret_cast<const uint4*>(t.residual_in + ro), rr);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) acc[j] += rr[j];
+                }
+                *reinterpret_cast<uint4*>(t.residual_out + ro) = pack8(acc);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  acc[j] = __bfloat162float(__float2bfloat16(acc[j]));
+                  ss += acc[j] * acc[j];
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) vals[u][j] = acc[j];
+            }
+          }
         }
       }
       float inv = 1.f;
@@ -420,7 +464,7 @@ __device__ __noinline__ void tp_push_tail(const TpPush& t) {
           float o[8];
           if (t.mode == 0) {
             float g[8];
-            unpack8(*reinterpret_cast<const uint4*>(t.norm_w + v * 8), g);
+            unpack8(wv[u], g);
 #pragma unroll
             for (int j = 0; j < 8; ++j) o[j] = vals[u][j] * inv * g[j];
           } else {
@@ -442,13 +486,12 @@ __device__ __noinline__ void tp_push_tail(const TpPush& t) {
         }
       }
     }
+    tp_prof(t, 3);
     if (t.two_shot) {
       __syncthreads();
-      if (threadIdx.x < world) {
-        __threadfence_system();
-        red_release_sys_add(t.comm.peer_flags[threadIdx.x] + kPushBcastWord + rank, 1u);
-      }
+      if (threadIdx.x < world) red_release_sys_add(t.comm.peer_flags[threadIdx.x] + kPushBcastWord + rank, 1u);
     }
+    tp_prof(t, 4);
   }
   // One CTA keeps the kernel open until every owner's rows have landed in this rank's activation
   // buffer: the kernel's end then means "the whole [rows, hidden] activation is here".
@@ -461,6 +504,8 @@ __device__ __noinline__ void tp_push_tail(const TpPush& t) {
   }
   // The last CTA to get here moves the per-counter bases on for the next call.
   __syncthreads();
+  if (t.two_shot && blockIdx.x == 0) tp_prof(t, 5);
+  tp_prof(t, 6);
   if (threadIdx.x == 0) {
     __threadfence();
     if (atomicAdd(t.comm.epoch + kPushTicketWord, 1u) == gridDim.x - 1) {

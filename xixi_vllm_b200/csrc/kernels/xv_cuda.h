@@ -174,6 +174,13 @@ int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long
                     const void* residual_in, void* residual_out, const void* norm_w, void* y_out, float eps, int mode,
                     unsigned spin_us, int* status, cudaStream_t stream);
 
+// Diagnostics for xv_gemm_bf16_tp: 8 global-timer stamps per CTA (kernel entry, GEMM roles done, tiles arrived,
+// rows done, broadcast raised, all rows arrived (CTA 0), exit, unused) into `buf`; null switches it off.
+void xv_tp_profile_buffer(void* buf);
+// The single-CTA GEMM kernel's own phases (entry, barriers + TMEM ready, first load issued, first stage landed,
+// first tile's MMAs issued, its accumulator complete, last epilogue done, exit), same buffer format.
+void xv_gemm_profile_buffer(void* buf);
+
 // ---- native forward executor (forward.cu): one call launches a whole Qwen3 forward ----
 typedef struct XvLayerWeights {
   const void* input_norm;

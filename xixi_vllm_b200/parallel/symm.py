@@ -156,7 +156,7 @@ class FusedTPComm(TPComm):
     def row_linear(self, proj, x: torch.Tensor, final: bool = False):
         """Output of a RowParallelLinear as something ``reduce_add_rmsnorm`` / ``all_reduce`` accept."""
         T = x.shape[0]
-        if (self.fuse_gemm and proj.bias is None and 0 < T <= self.fuse_gemm_max_tokens
+        if (self.fuse_gemm and proj.bias is None and 0 < T <= self.fuse_gemm_max_tokens and self.hidden <= 6144
                 and self.world * T * self.hidden * 2 <= self.buf_bytes):
             return DeferredRowGemm(x, proj.weight, final)
         return proj(x, reduce=False, out=self.alloc_partial(x.shape[0], final))

@@ -17,7 +17,7 @@ import time
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def run(args, Workload, ClockSampler, flush_l2) -> dict:
+def run(args, Workload, ClockSampler, flush_l2, run_to_completion=None, run_decode_only=None) -> dict:
     import torch
 
     if HERE not in sys.path:
@@ -38,6 +38,9 @@ def run(args, Workload, ClockSampler, flush_l2) -> dict:
     model_dir = make_reference_model_dir(
         os.path.join(tempfile.gettempdir(), f"xv_ref_{args.model}_{os.getuid()}"), args.model, seed=args.seed)
     context = args.prompt_max + args.out_tokens
+    if getattr(args, "mode", "steady") == "decode":
+        context = -(-(args.decode_context + args.steps + args.warmup + 16) // 256) * 256
+        args.max_num_seqs = max(8, args.decode_batch)     # the reference engine hung with max_num_seqs = 1 under TP=2
     cfg = _ref.EngineConfig(
         model=model_dir, context_len=context, max_num_seqs=min(args.max_num_seqs, 256),
         max_num_batched_tokens=args.max_batched_tokens, kvcache_block_size=256, prefix_backend="none",
@@ -60,6 +63,28 @@ def run(args, Workload, ClockSampler, flush_l2) -> dict:
                 ids, out = wl.next(staggered)
                 engine.add_request(ids, SP(temperature=0.0, max_tokens=out, ignore_eos=True))
 
+        mode = getattr(args, "mode", "steady")
+        if mode != "steady":
+            def make_sp(n_out):
+                return SP(temperature=0.0, max_tokens=n_out, ignore_eos=True)
+
+            clocks = ClockSampler(0)
+            clocks.start()
+            if mode == "full":
+                r = run_to_completion(engine, make_sp, wl, args.requests, torch.cuda.synchronize)
+                extra = {"requests": args.requests, "step": "all requests submitted at once and run to completion"}
+            else:
+                r = run_decode_only(engine, make_sp, cfg.hf_config.vocab_size, args.decode_batch, args.decode_context,
+                                    args.steps, args.warmup, torch.cuda.synchronize, args.seed)
+                extra = {"decode_batch": args.decode_batch, "decode_context": args.decode_context,
+                         "step": "one decode step of the whole batch"}
+            return {"value": r["value"], "ms_per_step": None, "ttft_ms": r.get("ttft_ms"),
+                    "decode_tpot_ms": r.get("decode_tpot_ms"), "output_tokens": r["output_tokens"], "wall_s": r["wall_s"],
+                    "timing": "wall clock around Engine.step() calls, device synchronised at both ends",
+                    "config": {"model": args.model, "global_batch": cfg.max_num_seqs, "seq_len": context,
+                               "parallelism": f"tp{args.gpus}", "kv_block_size": 256,
+                               "decode_cuda_graph": not args.eager, **extra},
+                    "clocks": clocks.stop(), "gpu_launches": None}
         runner = engine._client.engine_core.executor.worker.model_runner
         events = []
         inner = runner.run_forward

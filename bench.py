@@ -49,8 +49,15 @@ METRIC = "output_tokens_per_s"
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--mode", default="steady", choices=("steady", "full", "decode"),
+                    help="steady: K timed engine steps of steady-state continuous batching (the headline); "
+                         "full: --requests requests run to completion (output tok/s, TTFT, TPOT); "
+                         "decode: --decode-batch sequences decoding together (time per output token)")
+    ap.add_argument("--requests", type=int, default=512, help="requests of --mode full")
+    ap.add_argument("--decode-batch", type=int, default=256, help="sequences of --mode decode")
+    ap.add_argument("--decode-context", type=int, default=256, help="prompt length of --mode decode")
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--model", default="Qwen3-8B")
     ap.add_argument("--max-num-seqs", type=int, default=256)
@@ -155,9 +162,78 @@ def emit(record: dict) -> None:
     print(json.dumps(record), flush=True)
 
 
-def baseline_number():
-    """The reference publishes no number for this metric and configuration, so vs_baseline is null."""
-    return None
+def baseline_number(model: str = "Qwen3-8B", n_gpus: int = 1, mode: str = "steady"):
+    """The reference publishes no numbers; BASELINE.md's figures are its own engine measured on this pool
+    (``baseline/measured_reference.json``, keyed by model, GPU count and mode). None when that case was not measured."""
+    path = os.path.join(ROOT, "baseline", "measured_reference.json")
+    try:
+        with open(path) as f:
+            table = json.load(f)
+        return table[model][mode][str(n_gpus)]["output_tokens_per_s"]
+    except (OSError, KeyError, ValueError, TypeError):
+        return None
+
+
+def run_to_completion(engine, make_sp, wl, n_requests: int, sync) -> dict:
+    """``n_requests`` requests of the workload submitted at once and stepped until all are done, through the
+    engine's public API (works for both arms). Output tokens per second of wall time, time to first token and
+    time per output token after the first (host clock, per request)."""
+    seqs = []
+    for _ in range(n_requests):
+        ids, out = wl.next(False)
+        seqs.append(engine.add_request(ids, make_sp(out)))
+    sync()
+    t0 = time.perf_counter()
+    first = [None] * len(seqs)
+    done = [None] * len(seqs)
+    steps = 0
+    pending = set(range(len(seqs)))
+    while engine.has_unfinished():
+        engine.step()
+        steps += 1
+        now = time.perf_counter()
+        for i in list(pending):
+            sq = seqs[i]
+            if first[i] is None and sq.num_completion_tokens > 0:
+                first[i] = now
+            if sq.is_finished:
+                done[i] = now
+                pending.discard(i)
+    sync()
+    wall = time.perf_counter() - t0
+    out_tokens = sum(sq.num_completion_tokens for sq in seqs)
+    ttft = sorted((f - t0) * 1e3 for f in first if f is not None)
+    tpot = sorted((d - f) * 1e3 / max(1, sq.num_completion_tokens - 1)
+                  for f, d, sq in zip(first, done, seqs) if f is not None and d is not None)
+
+    def pct(v, q):
+        return v[min(len(v) - 1, int(q * len(v)))] if v else None
+
+    return {"output_tokens": out_tokens, "wall_s": wall, "steps": steps, "value": out_tokens / wall,
+            "ttft_ms": {"p50": pct(ttft, 0.5), "p99": pct(ttft, 0.99)},
+            "decode_tpot_ms": {"p50": pct(tpot, 0.5), "p99": pct(tpot, 0.99)}}
+
+
+def run_decode_only(engine, make_sp, vocab: int, batch: int, context: int, steps: int, warmup: int, sync, seed: int = 0) -> dict:
+    """``batch`` sequences with ``context``-token prompts decoding together: wall time per engine step once every
+    prompt has been prefilled = time per output token of each sequence."""
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    seqs = [engine.add_request(rng.integers(0, vocab, size=context).tolist(), make_sp(steps + warmup + 8))
+            for _ in range(batch)]
+    while any(sq.num_completion_tokens == 0 for sq in seqs):
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    sync()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        engine.step()
+    sync()
+    wall = time.perf_counter() - t0
+    return {"decode_tpot_ms": 1e3 * wall / steps, "value": batch * steps / wall, "output_tokens": batch * steps,
+            "wall_s": wall}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -190,6 +266,11 @@ def run_ours(args) -> None:
                         intermediate_size=full["intermediate_size"] // t, vocab_size=full["vocab_size"] // t)
         make_model_dir(model_dir, args.model, weights=False, **over)
     context = args.prompt_max + args.out_tokens
+    if args.mode == "decode":
+        context = args.decode_context + args.steps + args.warmup + 16
+        args.max_num_seqs = max(1, args.decode_batch)
+    if args.tp_comm == "auto" and args.gpus // args.pp > 1:
+        args.tp_comm = "fused"      # a broken peer-memory setup must fail loudly, not fall back to NCCL
     cfg_kwargs = dict(model=model_dir, load_format="dummy", dtype="bfloat16", context_len=context,
                       max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_batched_tokens,
                       kvcache_block_size=16, prefix_backend="none", enforce_eager=args.eager,
@@ -210,6 +291,49 @@ def run_ours(args) -> None:
     wl = Workload(args, cfg.hf_config.vocab_size)
     core = engine._client.engine_core
     sched = core.scheduler
+    comm = getattr(core.executor.worker.model, "comm", None)
+    comm_ran = {"tp_comm_ran": "fused" if hasattr(comm, "symm") else ("nccl" if args.gpus // args.pp > 1 else "none"),
+                "nvls_multicast": bool(getattr(comm, "mc_ptr", 0)),
+                "one_kernel_row_parallel": bool(getattr(comm, "fuse_gemm", False))}
+    parallelism = (f"tp{args.gpus}" if args.pp == 1 else f"tp{args.gpus // args.pp}pp{args.pp}mb{args.pp_microbatches}")
+
+    def make_sp(n_out):
+        return SamplingParams(temperature=0.0, max_tokens=n_out, ignore_eos=True)
+
+    def sync():
+        torch.cuda.synchronize(device)
+
+    if args.mode != "steady":
+        clocks = ClockSampler(local_rank)
+        clocks.start()
+        launches0 = cuda.launch_count
+        if args.mode == "full":
+            r = run_to_completion(engine, make_sp, wl, args.requests, sync)
+            cfg_extra = {"requests": args.requests, "step": "all requests submitted at once and run to completion"}
+        else:
+            r = run_decode_only(engine, make_sp, cfg.hf_config.vocab_size, args.decode_batch, args.decode_context,
+                                args.steps, args.warmup, sync, args.seed)
+            cfg_extra = {"decode_batch": args.decode_batch, "decode_context": args.decode_context,
+                         "step": "one decode step of the whole batch"}
+        clk = clocks.stop()
+        runner = core.executor.worker.model_runner
+        rec = {"metric": METRIC, "value": r["value"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": r.get("steps", args.steps),
+               "warmup": args.warmup, "mode": args.mode, "higher_is_better": True, "scaling": "strong",
+               "vs_baseline": (r["value"] / b) if (b := baseline_number(args.model, args.gpus, args.mode)) else None,
+               "dtype": "bf16", "data": "synthetic (random-init weights, uniform random token prompts)", "impl": "ours",
+               "timing": "wall clock around Engine.step() calls, device synchronised at both ends",
+               "ttft_ms": r.get("ttft_ms"), "decode_tpot_ms": r.get("decode_tpot_ms"),
+               "config": {"model": args.model, "global_batch": args.max_num_seqs, "seq_len": context,
+                          "parallelism": parallelism, "kv_block_size": 16, "decode_cuda_graph": not args.eager,
+                          "tp_comm": args.tp_comm, **comm_ran, **cfg_extra},
+               "clocks": clk, "output_tokens": r["output_tokens"], "wall_s": r["wall_s"],
+               "gpu_launches": cuda.launch_count - launches0 + (runner.graphs.replayed_kernels if runner.graphs else 0)}
+        emit(rec)
+        if world > 1:
+            shutdown_from_env(engine)
+        else:
+            engine.destroy()
+        return
 
     def top_up(staggered: bool) -> None:
         while len(sched.waiting) < 4:
@@ -261,13 +385,17 @@ def run_ours(args) -> None:
     rec = {
         "metric": METRIC, "value": out_tokens / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": baseline_number(), "dtype": "bf16",
+        "higher_is_better": True, "scaling": "strong", "mode": "steady",
+        "vs_baseline": ((out_tokens / (dev_ms / 1e3)) / b) if (b := baseline_number(args.model, args.gpus)) else None,
+        "dtype": "bf16",
         "data": "synthetic (random-init weights, uniform random token prompts)", "impl": "ours",
+        "ttft_ms": {"p50": core.metrics.summary().get("ttft_ms_p50"), "note": "includes the untimed fill phase; see --mode full"},
+        "decode_tpot_ms": {"pure_decode_step_ms_median": (sorted(step_ms)[len(step_ms) // 4] if step_ms else None),
+                           "note": "lower quartile of the timed steps' wall time = a step without a prefill chunk"},
         "config": {"model": args.model, "global_batch": args.max_num_seqs, "seq_len": context,
-                   "parallelism": (f"tp{args.gpus}" if args.pp == 1 else
-                                   f"tp{args.gpus // args.pp}pp{args.pp}mb{args.pp_microbatches}"), "prompt_len": f"U[{args.prompt_min},{args.prompt_max}]",
+                   "parallelism": parallelism, "prompt_len": f"U[{args.prompt_min},{args.prompt_max}]",
                    "output_len": args.out_tokens, "max_num_batched_tokens": args.max_batched_tokens,
-                   "kv_block_size": 16, "decode_cuda_graph": not args.eager, "tp_comm": args.tp_comm,
+                   "kv_block_size": 16, "decode_cuda_graph": not args.eager, "tp_comm": args.tp_comm, **comm_ran,
                    **({"emulate_tp_shard": args.emulate_tp} if args.emulate_tp > 1 else {}),
                    "l2": "flushed between timed steps (256 MiB write)",
                    "step": "one engine step in steady-state continuous batching"},
@@ -301,13 +429,14 @@ def run_reference(args) -> None:
     try:
         from baseline.ref_harness import run as run_ref
 
-        rec = run_ref(args, Workload, ClockSampler, flush_l2)
+        rec = run_ref(args, Workload, ClockSampler, flush_l2, run_to_completion, run_decode_only)
     except Exception as e:  # the line must still be printed and the exit code stay 0
         emit({"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:300]}"})
         return
     rec.update({"metric": METRIC, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
                 "warmup": args.warmup, "higher_is_better": True, "scaling": "strong",
-                "vs_baseline": baseline_number(), "dtype": "bf16", "impl": "reference",
+                "vs_baseline": 1.0 if baseline_number(args.model, args.gpus, args.mode) else None, "dtype": "bf16",
+                "impl": "reference", "mode": args.mode,
                 "data": "synthetic (random-init weights, uniform random token prompts)"})
     emit(rec)
 

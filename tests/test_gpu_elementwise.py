@@ -120,7 +120,16 @@ def test_bounded_wait_reports_instead_of_hanging():
     assert float(torch.ones(4, device=DEV).sum().item()) == 4.0
 
 
-def test_split_k_partials_feed_consumers_directly():
+@pytest.fixture
+def planes_split_k():
+    """K splits as fp32 planes (by default up to four splits are summed inside a thread-block cluster)."""
+    from xixi_vllm_b200.ops import cuda
+    cuda.gemm_plan_override(0, 0, 4, 0)
+    yield
+    cuda.gemm_plan_override(-1)
+
+
+def test_split_k_partials_feed_consumers_directly(planes_split_k):
     """A deferred split-K GEMM hands fp32 partial planes to add+RMSNorm and to QK-norm/RoPE."""
     from xixi_vllm_b200.ops import cuda
     g = torch.Generator().manual_seed(9)

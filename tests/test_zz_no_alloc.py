@@ -21,7 +21,16 @@ def _sym():
                   ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p]
     f.restype = ctypes.c_int
     L.xv_gemm_noalloc_max_scratch_bytes.restype = ctypes.c_longlong
+    L.xv_gemm_plan_planes.argtypes = [ctypes.c_int] * 4 + [ctypes.POINTER(cuda.GemmPlan)]
     return L, f
+
+
+def _plan(L, m, n, k):
+    """The plan the allocation-free entry point runs (its K splits always go through the scratch buffer)."""
+    from xixi_vllm_b200.ops import cuda
+    pl = cuda.GemmPlan()
+    assert L.xv_gemm_plan_planes(m, n, k, torch.cuda.get_device_properties(0).multi_processor_count, ctypes.byref(pl)) == 0
+    return pl
 
 
 def test_noalloc_gemm_matches_workspace_gemm_twice_in_a_row():
@@ -31,7 +40,7 @@ def test_noalloc_gemm_matches_workspace_gemm_twice_in_a_row():
     stream = torch.cuda.current_stream().cuda_stream
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     for m, n, k in [(32, 4096, 4096), (7, 1024, 2048)]:        # both plans split K and use the scratch
-        assert cuda.gemm_plan(m, n, k, torch.cuda.get_device_properties(0).multi_processor_count).splits > 1
+        assert _plan(L, m, n, k).workspace_bytes > 0
         g = torch.Generator().manual_seed(m + n)
         x = torch.randn(m, k, generator=g).bfloat16().cuda()
         w = torch.randn(n, k, generator=g).bfloat16().cuda()
@@ -52,7 +61,7 @@ def test_noalloc_gemm_rejects_oversized_problem(capfd):
     L, f = _sym()
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     m, n, k = 128, 16640, 8192          # two split-K planes of 8.1 MiB each
-    need = cuda.gemm_plan(m, n, k, sms).workspace_bytes
+    need = _plan(L, m, n, k).workspace_bytes
     assert need > L.xv_gemm_noalloc_max_scratch_bytes()
     x = torch.zeros(m, k, dtype=torch.bfloat16, device="cuda")
     w = torch.zeros(n, k, dtype=torch.bfloat16, device="cuda")

@@ -180,5 +180,12 @@ def resolve_dtype(config: EngineConfig):
     if not isinstance(name, str):
         return name
     name = name.replace("torch.", "")
-    return {"float16": torch.float16, "half": torch.float16, "bfloat16": torch.bfloat16,
-            "float32": torch.float32, "float": torch.float32, "float64": torch.float64}[name]
+    dtype = {"float16": torch.float16, "half": torch.float16, "bfloat16": torch.bfloat16,
+             "float32": torch.float32, "float": torch.float32, "float64": torch.float64}[name]
+    if dtype != torch.bfloat16 and getattr(config, "device", "cuda") == "cuda":
+        # The reference serves whatever the checkpoint declares and falls back to float16
+        # (reference: src/control/engine.py:79-84); the sm_100a kernels here are bf16 only.
+        raise ValueError(f"dtype {name} is not supported on CUDA: the sm_100a kernels of this engine run bfloat16 "
+                         f"activations and weights only. Pass dtype=\"bfloat16\" (a float16 / float32 checkpoint is "
+                         f"converted while it is loaded) or run on device=\"cpu\".")
+    return dtype

@@ -361,6 +361,27 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
                : "memory");
 }
 
+// ---- distributed shared memory: stores into another CTA of the cluster that count on its mbarrier ----
+// 4 bytes to `cluster_addr` (a shared::cluster address from map_to_cta); the destination CTA's barrier at
+// `cluster_bar` receives 4 bytes of its expected transaction count when the store has landed.
+__device__ __forceinline__ void st_async_b32(uint32_t cluster_addr, uint32_t value, uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(cluster_addr),
+               "r"(value), "r"(cluster_bar)
+               : "memory");
+}
+__device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, const float4& v, uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(
+                   cluster_addr),
+               "r"(__float_as_uint(v.x)), "r"(__float_as_uint(v.y)), "r"(__float_as_uint(v.z)), "r"(__float_as_uint(v.w)),
+               "r"(cluster_bar)
+               : "memory");
+}
+// Makes prior mbarrier.init visible to the other CTAs of the cluster and waits until every CTA of the
+// cluster has got here (all threads of all CTAs call it).
+__device__ __forceinline__ void cluster_arrive_wait() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // ---- device-scope flags and cache-bypassing loads (partial tiles exchanged through global memory) ----
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
   uint32_t v;

@@ -205,7 +205,7 @@ int xv_qwen3_forward(const XvModelDesc* m, const XvBatchDesc* b, const XvArena* 
         g_failed_op = 40;
         return rc;
       }
-      if (pl.splits == 1) {
+      if (pl.splits == 1 || pl.cluster) {
         XV_TRY(41, xv_gemm_bf16_silu_mul(a->h, w.gate_up, a->act, T, 2 * I, H, H, H, I, a->num_sms, a->status, stream));
       } else {
         int sp = 1;

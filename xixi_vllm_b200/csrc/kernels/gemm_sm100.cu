@@ -64,6 +64,8 @@ struct GemmParams {
   float* fix_planes;        // [splits][rows_b][rows_a] fp32
   uint32_t* fix_counters;   // one per output tile, zero between launches
   unsigned long long* prof; // optional: 8 global-timer stamps per CTA (see xv_gemm_profile_buffer)
+  int cluster_split;        // > 1: the K splits of a tile are the CTAs of one thread-block cluster, which sum their
+                            // accumulators through distributed shared memory (swapped orientation, one tile per CTA)
   long long ldc;
   long long split_stride;   // elements between split-K partial planes
   void* out;
@@ -80,8 +82,14 @@ struct WorkItem {
 __device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int w) {
   WorkItem it;
   const int tiles = p.tiles_a * p.tiles_b;
-  it.split = w / tiles;
-  const int r = w - it.split * tiles;
+  int r;
+  if (p.cluster_split > 1) {          // consecutive CTAs (one cluster) share a tile
+    it.split = w % p.cluster_split;
+    r = w / p.cluster_split;
+  } else {
+    it.split = w / tiles;
+    r = w - it.split * tiles;
+  }
   if (p.a_fastest) {
     it.tile_b = r / p.tiles_a;
     it.tile_a = r - it.tile_b * p.tiles_a;
@@ -284,6 +292,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   uint64_t* acc_empty = acc_full + 2;              // [2] accumulator drained, MMA may overwrite
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint64_t* peers_done = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(full_bar) + 176);   // cluster split-K
+  uint64_t* recv_full = peers_done + 1;
   uint8_t* staging = reinterpret_cast<uint8_t*>(full_bar) + 256;   // kStagingBytes, swapped orientation only
 
   const int warp = threadIdx.x >> 5;
@@ -300,6 +310,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 4);      // one arrival per epilogue warp
     }
+    if (p.cluster_split > 1) {
+      // peers_done: every CTA of the cluster reports that its MMAs no longer read shared memory;
+      // recv_full: the other CTAs' partial sums for the accumulator columns this CTA finishes have landed
+      const int cs = p.cluster_split, nch = (p.bn + 31) >> 5, crank = static_cast<int>(cluster_ctarank());
+      const int owned = crank < nch ? (nch - crank + cs - 1) / cs : 0;
+      mbar_init(peers_done, static_cast<uint32_t>(cs));
+      mbar_init(recv_full, 1);
+      mbar_fence_init();
+      mbar_expect_tx(recv_full, static_cast<uint32_t>((cs - 1) * owned) * 16384u);
+    }
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -309,6 +329,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (p.cluster_split > 1) cluster_arrive_wait();      // the barriers above exist in every CTA of the cluster
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) gemm_prof(p, 1);
@@ -446,6 +467,82 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int a_row0 = wi.tile_a * kBM + quarter * 32;
       const int b0 = wi.tile_b * p.bn;
       const int b_end = min(p.rows_b, b0 + p.bn);
+      if (p.cluster_split > 1) {
+        // ---- split-K inside a cluster: accumulator columns are dealt to the cluster's CTAs in chunks of 32;
+        // every CTA sends the chunks it does not own to their owners' shared memory (the stage ring, free once
+        // all MMAs of the cluster are done) and finishes the ones it owns ----
+        const int cs = p.cluster_split;
+        const int crank = static_cast<int>(cluster_ctarank());
+        const int owned_max = (nchunks + cs - 1) / cs;
+        if (threadIdx.x == 64)
+          for (int q = 0; q < cs; ++q) mbar_arrive_cluster(map_to_cta(smem_u32(peers_done), static_cast<uint32_t>(q)));
+        if (!dead) {
+          bool ok = true;
+          if (lane == 0) ok = mbar_wait(peers_done, 0);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) {
+            report_status(p.status, kGemmKernelId, kWaitAccumTimeout);
+            dead = true;
+          }
+        }
+        if (!dead) {
+          const uint32_t lane_addr = tmem_base + buf * p.acc_stride + (static_cast<uint32_t>(quarter * 32) << 16);
+          const uint32_t recv_local = smem_u32(smem);
+          for (int c = 0; c < nchunks; ++c) {
+            const int owner = c % cs;
+            if (owner == crank) continue;
+            uint32_t r[32];
+            tmem_ld32(lane_addr + static_cast<uint32_t>(c * 32), r);
+            tmem_ld_wait();
+            tmem_ld_fence_regs(r);
+            const int src_idx = crank < owner ? crank : crank - 1;
+            const uint32_t slot = static_cast<uint32_t>(src_idx * owned_max + c / cs) * 16384u;
+            const uint32_t dst = map_to_cta(recv_local + slot, static_cast<uint32_t>(owner));
+            const uint32_t bar = map_to_cta(smem_u32(recv_full), static_cast<uint32_t>(owner));
+            // through this warp's staging buffer, 16 tokens at a time, so that the stores into the owner's
+            // shared memory are 16 bytes each: [32 tokens][128 features] fp32 there, this warp's 32 features
+            float* st = reinterpret_cast<float*>(stage_w);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) st[j * 32 + lane] = __uint_as_float(r[half * 16 + j]);
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int tl = (lane >> 3) + 4 * i;
+                const float4 v = *reinterpret_cast<const float4*>(st + tl * 32 + (lane & 7) * 4);
+                st_async_v4(dst + static_cast<uint32_t>(((half * 16 + tl) * 128 + quarter * 32 + (lane & 7) * 4) * 4), v, bar);
+              }
+            }
+          }
+          const bool owns = crank < nchunks;
+          if (owns) {
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(recv_full, 0);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) report_status(p.status, kGemmKernelId, kWaitAccumTimeout);
+            const float* recv = reinterpret_cast<const float*>(smem);
+            for (int c = crank; c < nchunks; c += cs) {
+              uint32_t r[32];
+              tmem_ld32(lane_addr + static_cast<uint32_t>(c * 32), r);
+              tmem_ld_wait();
+              tmem_ld_fence_regs(r);
+              for (int sidx = 0; sidx < cs - 1; ++sidx) {       // source order: the sum does not depend on arrival order
+                const float* src = recv + static_cast<size_t>(sidx * owned_max + c / cs) * 4096 + quarter * 32 + lane;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + src[j * 128]);
+              }
+              store_swapped32(p, push, stage_w, lane, a_row0, b0 + c * 32, b_end, 0, r);
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+        if (threadIdx.x == 64) gemm_prof(p, 6);
+        continue;
+      }
       if (!dead) {
         const uint32_t lane_addr = tmem_base + buf * p.acc_stride + (static_cast<uint32_t>(quarter * 32) << 16);
         float* plane = p.fixup ? p.fix_planes + static_cast<size_t>(wi.split) * p.rows_a * p.rows_b : nullptr;
@@ -569,6 +666,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
+  // no CTA of a cluster leaves while another may still be writing into its shared memory
+  if (p.cluster_split > 1) cluster_arrive_wait();
   if (threadIdx.x == 0) gemm_prof(p, 7);
   if (push.enabled) tp_push_tail<kTailMaxVec>(push);
 }
@@ -1028,6 +1127,7 @@ PlanOverride g_override = {0, 0, 0, 0, 0};
 constexpr unsigned kPlanNoPair = 1u;     // single-CTA kernels only
 constexpr unsigned kPlanNoSplit = 2u;    // the caller cannot take fp32 partial planes
 constexpr unsigned kPlanDeep = 4u;       // few CTAs: give each the whole SM's shared memory for stages
+constexpr unsigned kPlanNoCluster = 8u;  // K splits as fp32 planes in global memory, not summed inside a cluster
 
 struct PlanKey {
   int m, n, k, sms;
@@ -1105,11 +1205,26 @@ void plan_single(int m, int n, int k, int num_sms, unsigned flags, int max_split
     if (max_splits > 0 && splits > max_splits) splits = max_splits;
     if (splits < 1) splits = 1;
   }
+  // Swapped orientation: up to four K splits of a tile form one thread-block cluster and sum their accumulators
+  // through distributed shared memory: no fp32 planes in global memory, the output is final (bf16, activation
+  // or pushed tiles). The receive buffers alias the stage ring, which must hold them.
+  static const int cluster_on = env_int("XV_GEMM_CLUSTER", 1);
+  pl.cluster = 0;
+  if (cluster_on && pl.swapped && splits > 1 && !(flags & kPlanNoCluster)) {
+    int cs = splits > 4 ? 4 : splits;
+    const int nch = (pl.bn + 31) / 32;
+    while (cs > 1 && (cs - 1) * ((nch + cs - 1) / cs) * 16384 > stages * stage_bytes) --cs;
+    if (cs > 1) {
+      splits = cs;
+      pl.cluster = 1;
+    }
+  }
   pl.k_blocks_per_split = (total_kb + splits - 1) / splits;
   pl.splits = (total_kb + pl.k_blocks_per_split - 1) / pl.k_blocks_per_split;
-  if (stages > pl.k_blocks_per_split && pl.k_blocks_per_split >= 2) stages = pl.k_blocks_per_split;
+  if (pl.cluster && pl.splits < 2) pl.cluster = 0;
+  if (stages > pl.k_blocks_per_split && pl.k_blocks_per_split >= 2 && !pl.cluster) stages = pl.k_blocks_per_split;
   fill_single_smem(pl, stages);
-  pl.workspace_bytes = pl.splits > 1 ? static_cast<long long>(pl.splits) * m * n * 4 : 0;
+  pl.workspace_bytes = (pl.splits > 1 && !pl.cluster) ? static_cast<long long>(pl.splits) * m * n * 4 : 0;
 }
 
 // CTA-pair plan: 256 x bn tiles. Whole waves of tiles are dealt round-robin; the rest (`sk_tiles` at the
@@ -1209,7 +1324,7 @@ int gemm_plan_impl(int m, int n, int k, int num_sms, XvGemmPlan* plan, unsigned 
         pl.stages = g_override.stages;
       }
     } else {
-      plan_single(m, n, k, num_sms, flags | kPlanNoSplit, 0, pl);
+      plan_single(m, n, k, num_sms, flags | kPlanNoSplit | kPlanNoCluster, 0, pl);
       if (g_override.kind == 1 && m <= 256) {       // normal orientation for a small batch
         pl.swapped = 0;
         pl.bn = n >= 256 ? 256 : round_up(n, 16);
@@ -1318,6 +1433,10 @@ void xv_gemm_plan_override(int kind, int bn, int splits, int stages) {
 int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan) {
   return gemm_plan_impl(m, n, k, num_sms, plan, 0u, 0);
 }
+// The plan xv_gemm_bf16_noalloc runs: K splits always as fp32 planes in the scratch buffer.
+int xv_gemm_plan_planes(int m, int n, int k, int num_sms, XvGemmPlan* plan) {
+  return gemm_plan_impl(m, n, k, num_sms, plan, kPlanNoCluster, 0);
+}
 
 // Y[m,n] (bf16, row stride ldy) = X[m,k] (row stride ldx) * W[n,k]^T (row stride ldw).
 // `workspace` must hold plan.workspace_bytes when the plan splits K. `status` may be null.
@@ -1325,13 +1444,13 @@ int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan) {
 static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
                      long long ldy, void* workspace, long long workspace_bytes, int num_sms, int* status,
                      cudaStream_t stream, bool defer_reduce, int* splits_out, int act = 0,
-                     const TpPush* push_in = nullptr, int push_max_splits = 1) {
+                     const TpPush* push_in = nullptr, int push_max_splits = 1, unsigned plan_flags = 0u) {
   XvGemmPlan pl;
   if (num_sms <= 0) num_sms = 148;
   // A workspace of at least twice the stream-K reserve has its tail set aside (and kept zero) for counters and
   // the pair kernel's partial tiles; split-K planes use the front part. Smaller workspaces are all planes.
   const bool sk_ok = workspace != nullptr && workspace_bytes >= 2 * kSkReserveBytes;
-  unsigned flags = 0;
+  unsigned flags = plan_flags;
   int max_splits = 0;
   if (push_in != nullptr) {
     // Pushed tiles must be complete sums: K splits are summed inside the kernel by the CTA that arrives last
@@ -1351,10 +1470,11 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
     fill_pair(m, n, k, pl.bn, num_sms, -1, pl);
   // Split-K in the swapped orientation: the planes are summed inside the kernel by the CTA that brings a
   // tile's last one (needs a tile counter from the reserve), unless the caller wants the planes themselves.
-  const bool fixup = pl.splits > 1 && pl.swapped && !pl.pair && push_in != nullptr && sk_ok && (n % 8) == 0 &&
-                     pl.tiles_a * pl.tiles_b <= kFixCounterTiles;
-  const bool to_planes = pl.splits > 1 && !fixup;
-  if (pl.splits > 1 && (!workspace || pl.workspace_bytes > (sk_ok ? workspace_bytes - kSkReserveBytes : workspace_bytes)))
+  const bool fixup = pl.splits > 1 && !pl.cluster && pl.swapped && !pl.pair && push_in != nullptr && sk_ok &&
+                     (n % 8) == 0 && pl.tiles_a * pl.tiles_b <= kFixCounterTiles;
+  const bool to_planes = pl.splits > 1 && !fixup && !pl.cluster;
+  if (pl.splits > 1 && !pl.cluster &&
+      (!workspace || pl.workspace_bytes > (sk_ok ? workspace_bytes - kSkReserveBytes : workspace_bytes)))
     return XV_ERR_WORKSPACE;
   if (act && to_planes) return XV_ERR_UNSUPPORTED;           // callers check the plan first
   if (act && ((n % 16) || (ldy % 8))) return XV_ERR_SHAPE;
@@ -1397,6 +1517,7 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
   p.tiles_b = pl.tiles_b;
   p.splits = pl.splits;
   p.a_fastest = pl.swapped ? 0 : 1;
+  p.cluster_split = pl.cluster ? pl.splits : 0;
   if (to_planes) {
     p.out = workspace;
     p.out_fp32 = 1;
@@ -1458,31 +1579,38 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
   } else {
     int slots = num_sms * pl.ctas_per_sm;
     int grid = total_work < slots ? total_work : slots;
+    if (pl.cluster) grid = total_work;          // one tile split per CTA; clusters are consecutive CTAs
     if (push_in) {
       push = *push_in;
       push.enabled = 1;
-      push.splits = 1;               // K splits are summed before the push (fix-up inside the kernel)
+      push.splits = 1;               // K splits are summed before the push (inside the cluster, or by the fix-up)
       int per_sm = 0;
       if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_tcgen05_kernel, kGemmThreads, pl.smem_bytes) !=
               cudaSuccess || per_sm < 1)
         return XV_ERR_LAUNCH;
       if (per_sm > pl.ctas_per_sm) per_sm = pl.ctas_per_sm;
       slots = num_sms * per_sm;
-      if (grid > slots) grid = slots;
-      // CTAs beyond the GEMM tiles take the rows this rank reduces
+      // CTAs beyond the GEMM tiles take the rows this rank reduces; every CTA must be resident at once
       const int n_mine = push.two_shot ? (push.rows + push.comm.world - 1) / push.comm.world : push.rows;
+      const int cs = pl.cluster ? pl.splits : 1;
+      if (pl.cluster && total_work > slots) return XV_ERR_UNSUPPORTED;
       grid = (total_work < slots ? total_work : slots) + n_mine;
       if (grid > slots) grid = slots;
+      grid = grid / cs * cs;                       // whole clusters
+      if (grid < total_work && pl.cluster) grid = total_work;
       if (grid < 1) grid = 1;
       push.signal_ctas = total_work < grid ? total_work : grid;
     }
-    if (launch_pdl(gemm_tcgen05_kernel, dim3(grid), dim3(kGemmThreads), pl.smem_bytes, stream, map_a, map_b, p,
-                   push) != cudaSuccess)
-      return XV_ERR_LAUNCH;
+    const cudaError_t le =
+        pl.cluster ? launch_pdl_cluster(gemm_tcgen05_kernel, dim3(grid), dim3(kGemmThreads), pl.smem_bytes, stream,
+                                        static_cast<unsigned>(pl.splits), map_a, map_b, p, push)
+                   : launch_pdl(gemm_tcgen05_kernel, dim3(grid), dim3(kGemmThreads), pl.smem_bytes, stream, map_a, map_b,
+                                p, push);
+    if (le != cudaSuccess) return XV_ERR_LAUNCH;
   }
   if (cudaGetLastError() != cudaSuccess) return XV_ERR_LAUNCH;
   if (push_in) return 0;
-  if (splits_out) *splits_out = pl.splits;
+  if (splits_out) *splits_out = to_planes ? pl.splits : 1;
   if (to_planes && !defer_reduce) {
     const long long elems = static_cast<long long>(m) * n;
     const int threads = 256;
@@ -1614,7 +1742,7 @@ int xv_gemm_bf16_noalloc(const void* x, const void* w, void* y, int m, int n, in
   int rc = noalloc_setup(&dev, &scratch, &sms);
   if (rc) return rc;
   XvGemmPlan pl;
-  if ((rc = xv_gemm_plan(m, n, k, sms, &pl))) return rc;
+  if ((rc = xv_gemm_plan_planes(m, n, k, sms, &pl))) return rc;
   // Split-K planes have to fit; the CTA-pair kernel deals whole tiles when given a buffer this small.
   if (!pl.pair && pl.workspace_bytes > XV_NOALLOC_SCRATCH_BYTES) {
     std::fprintf(stderr,
@@ -1623,7 +1751,8 @@ int xv_gemm_bf16_noalloc(const void* x, const void* w, void* y, int m, int n, in
                  m, n, k, pl.workspace_bytes, static_cast<long long>(XV_NOALLOC_SCRATCH_BYTES));
     return XV_ERR_WORKSPACE;
   }
-  return xv_gemm_bf16(x, w, y, m, n, k, ldx, ldw, ldy, scratch, XV_NOALLOC_SCRATCH_BYTES, sms, status, stream);
+  return gemm_impl(x, w, y, m, n, k, ldx, ldw, ldy, scratch, XV_NOALLOC_SCRATCH_BYTES, sms, status, stream, false,
+                   nullptr, 0, nullptr, 1, kPlanNoCluster);
 }
 
 }  // extern "C"

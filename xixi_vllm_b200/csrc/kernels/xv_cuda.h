@@ -27,6 +27,8 @@ typedef struct XvGemmPlan {
   int stages;
   int smem_bytes;
   int ctas_per_sm;         // resident CTAs per SM the persistent grid is sized for
+  int cluster;             // 1: the K splits of a tile are one thread-block cluster and sum their accumulators
+                           //    through distributed shared memory (the output is final: no planes, no workspace)
   int pair;                // 1: CTA-pair kernel (cta_group::2, 256 x bn tiles, stream-K)
   int sk_tiles;            // pair kernel: tiles at the end of the tile order that are dealt in K blocks (stream-K)
   int units_per_pair;      // pair kernel: K blocks of that region each SM pair takes
@@ -34,6 +36,8 @@ typedef struct XvGemmPlan {
 } XvGemmPlan;
 
 int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan);
+// The plan of xv_gemm_bf16_noalloc: K splits are always fp32 planes in a workspace (never summed inside a cluster).
+int xv_gemm_plan_planes(int m, int n, int k, int num_sms, XvGemmPlan* plan);
 void xv_gemm_disable_pair(int disable);   // test hook: force the single-CTA kernel
 // Test and tuning hook: fixed kernel (0 single CTA, 1 single CTA normal orientation, 2 CTA pairs), tile width,
 // split-K and stage count instead of the planner's choice; values <= 0 keep the default, kind < 0 clears.

@@ -38,7 +38,7 @@ launch_count = 0
 class GemmPlan(ctypes.Structure):
     _fields_ = [("swapped", _i32), ("bn", _i32), ("tiles_a", _i32), ("tiles_b", _i32), ("splits", _i32),
                 ("k_blocks_per_split", _i32), ("stages", _i32), ("smem_bytes", _i32),
-                ("ctas_per_sm", _i32), ("pair", _i32), ("sk_tiles", _i32), ("units_per_pair", _i32), ("workspace_bytes", _i64)]
+                ("ctas_per_sm", _i32), ("cluster", _i32), ("pair", _i32), ("sk_tiles", _i32), ("units_per_pair", _i32), ("workspace_bytes", _i64)]
 
 
 def lib():
@@ -209,7 +209,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
         st = _state(x)
         if defer and out is None and bias is None:
             pl = gemm_plan(M, N, K, st.num_sms)
-            if pl.splits > 1:
+            if pl.splits > 1 and not pl.cluster:        # a cluster sums its K splits itself: the output is final
                 used = _i32(0)
                 rc = lib().xv_gemm_bf16_defer(x.data_ptr(), w.data_ptr(), None, M, N, K, x.stride(0), w.stride(0), N,
                                               st.gemm_ws.data_ptr(), st.gemm_ws.numel(), st.num_sms,
@@ -246,7 +246,7 @@ def linear_silu_mul(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
                "silu_mul_interleaved")
         return y
     pl = gemm_plan(M, N, K, st.num_sms)
-    if pl.splits == 1:
+    if pl.splits == 1 or pl.cluster:
         _check(lib().xv_gemm_bf16_silu_mul(x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K, x.stride(0),
                                            w.stride(0), inter, st.num_sms, st.status.data_ptr(), _stream()),
                f"gemm+silu {M}x{N}x{K}")

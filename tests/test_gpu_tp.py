@@ -167,6 +167,26 @@ def _push_rank(rank, world, nvls):
         rows = slice(rank, None, world) if two_shot else slice(None)
         worst = max(worst, float((r_out.float().cpu()[rows] - r_ref.float()[rows]).abs().max()) / scale * 2)
         worst = max(worst, float((y.float().cpu() - y_ref.float()).abs().max()) / 4)
+    # all-gather -> GEMM: the projection ends without waiting for the other ranks' rows, the GEMM that reads the
+    # activation waits for them in its loader
+    for it, (T, K) in enumerate([(256, 512), (40, 1024), (600, 512)]):
+        g = torch.Generator().manual_seed(800 + it)
+        xs = [(torch.randn(T, K, generator=g) * 0.5).bfloat16() for _ in range(world)]
+        ws = [(torch.randn(H, K, generator=g) * 0.05).bfloat16() for _ in range(world)]
+        w2 = (torch.randn(768, H, generator=g) * 0.05).bfloat16()
+        nw = (1 + 0.1 * torch.randn(H, generator=g)).bfloat16()
+        res = torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
+        y, _ = comm.gemm_reduce_norm(xs[rank].to(dev), ws[rank].to(dev), res, nw.to(dev), 1e-6, two_shot=True,
+                                     first=True, defer_row_wait=True)
+        comm.await_rows()
+        z = cuda.linear(y, w2.to(dev))
+        torch.cuda.synchronize()
+        parts = [(a.float() @ b.float().t()).bfloat16().float() for a, b in zip(xs, ws)]
+        y_ref = cpu_ref.rmsnorm(sum(parts).bfloat16(), nw, 1e-6)
+        z_ref = y_ref.float() @ w2.float().t()
+        worst = max(worst, float((z.float().cpu() - z_ref).abs().max()) / max(1.0, float(z_ref.abs().max())) * 4)
+        dist.barrier()
+    cuda.check_status(dev)
     # a captured chain of four reduction points replayed many times: the counters' history must keep step
     T, K = 48, 512
     g = torch.Generator().manual_seed(42)

@@ -29,7 +29,17 @@ struct Ctx {
   int call_idx;      // reduction points issued so far in this forward (symmetric-buffer rotation)
   bool two_shot;     // this forward's reductions deal the rows to the ranks (residual stream sharded by rows)
   bool push;         // row-parallel GEMM and its reduction run as one kernel
+  bool rows_pending; // the last reduction did not wait for the broadcast rows: the next GEMM on h does
 };
+
+// all-gather -> GEMM: the column-parallel GEMM that reads h waits for the rows itself
+inline void await_rows_in_next_gemm(Ctx& c) {
+  if (!c.rows_pending) return;
+  c.rows_pending = false;
+  const XvModelDesc* m = c.m;
+  xv_gemm_wait_for_rows(static_cast<const uint32_t*>(m->peer_flags[m->tp_rank]) + xv_tp_bcast_word(),
+                        static_cast<const uint32_t*>(m->epoch) + xv_tp_bcast_base_word(), m->tp_world, m->spin_us);
+}
 
 #define XV_TRY(opid, expr)      \
   do {                          \
@@ -58,10 +68,13 @@ int row_linear_reduce_norm(Ctx& c, const void* x, const void* w, int k, const vo
     ++c.call_idx;
     const long long slot_off = static_cast<long long>(which) * m->buf_bytes;
     if (c.push) {
+      // the consumer of h is a GEMM on every call but the forward's last (LM head via a row gather)
+      const bool defer = c.two_shot && !final_call && m->tp_defer_row_wait != 0;
       XV_TRY(16, xv_gemm_bf16_tp(x, w, T, H, k, k, k, c.a->gemm_ws, c.a->gemm_ws_bytes, c.a->num_sms, m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch,
                                  m->tp_rank, m->tp_world, slot_off, m->buf_bytes, c.two_shot ? 1 : 0, m->h_offset,
-                                 c.a->residual, c.a->residual, norm_w, c.a->h, m->eps, 0, m->spin_us, c.a->status,
-                                 c.s));
+                                 c.a->residual, c.a->residual, norm_w, c.a->h, m->eps, 0, defer ? 1 : 0, m->spin_us,
+                                 c.a->status, c.s));
+      c.rows_pending = defer;
       return 0;
     }
     XV_TRY(10, xv_gemm_bf16(x, w, symm_local(c, which), T, H, k, k, k, H, c.a->gemm_ws, c.a->gemm_ws_bytes,
@@ -114,7 +127,7 @@ int xv_forward_decode_splits(int num_seqs, int hkv, int num_sms, int max_tokens_
 }
 
 int xv_qwen3_forward(const XvModelDesc* m, const XvBatchDesc* b, const XvArena* a, cudaStream_t stream) {
-  Ctx c{m, b, a, stream, 0, false, false};
+  Ctx c{m, b, a, stream, 0, false, false, false};
   const int T = b->num_tokens, H = m->hidden, D = m->head_dim;
   if (T <= 0) return 0;
   const int q_cols = m->hq * D;
@@ -171,6 +184,7 @@ int xv_qwen3_forward(const XvModelDesc* m, const XvBatchDesc* b, const XvArena* 
     const XvLayerWeights& w = m->layers[l];
     // ---- attention block ----
     int splits = 1;
+    await_rows_in_next_gemm(c);
     XV_TRY(30, xv_gemm_bf16_defer(a->h, w.qkv, a->qkv, T, m->qkv_rows, H, H, H, m->qkv_rows, a->gemm_ws,
                                   a->gemm_ws_bytes, a->num_sms, a->status, stream, &splits));
     if (splits > 1) {
@@ -199,6 +213,7 @@ int xv_qwen3_forward(const XvModelDesc* m, const XvBatchDesc* b, const XvArena* 
     }
     // ---- MLP block ----
     const int I = m->inter_local;
+    await_rows_in_next_gemm(c);
     if (m->gate_up_interleaved) {
       XvGemmPlan pl;
       if (int rc = xv_gemm_plan(T, 2 * I, H, a->num_sms, &pl)) {   // host arithmetic only, not a launch

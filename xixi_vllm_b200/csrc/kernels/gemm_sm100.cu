@@ -275,7 +275,7 @@ __device__ __forceinline__ void store_swapped32(const GemmParams& p, const TpPus
 // is double buffered in TMEM, so the epilogue of one tile overlaps the main loop of the next.
 __global__ void __launch_bounds__(kGemmThreads, 2)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const GemmParams p, const __grid_constant__ TpPush push) {
+                    const GemmParams p, const __grid_constant__ TpPush push, const GemmRowWait row_wait) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   grid_dep_launch();           // the next kernel of the stream may start its prologue (see launch.cuh)
   if (push.enabled) tp_prof(push, 0);
@@ -366,6 +366,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       gemm_prof(p, 2);
       grid_dep_wait();
+      // all-gather -> GEMM: the activation rows other ranks broadcast into this rank's buffer
+      if (row_wait.n > 0 && !gemm_wait_rows(row_wait)) report_status(p.status, kGemmKernelId, kPeerFlagTimeout);
       // K blocks issued so far by this CTA, across work items: `it` counts them, `s` is the stage the
       // next one goes to and `round` how often the ring has wrapped (kept incrementally: no division
       // in the loop)
@@ -756,7 +758,8 @@ __device__ __forceinline__ void red_add_f32x4(float* p, float a, float b, float 
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                         const GemmParams p, const StreamK sk, const __grid_constant__ TpPush push) {
+                         const GemmParams p, const StreamK sk, const __grid_constant__ TpPush push,
+                         const GemmRowWait row_wait) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   grid_dep_launch();
   if (push.enabled) tp_prof(push, 0);
@@ -809,6 +812,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const uint64_t hint = l2_policy_evict_normal();
       uint32_t s = 0, round = 0;
       const uint32_t leader_full0 = map_to_cta(smem_u32(&full_bar[0]), 0);
+      if (row_wait.n > 0 && !gemm_wait_rows(row_wait)) report_status(p.status, kGemmKernelId, kPeerFlagTimeout);
       PairWork work(p, sk, pair, num_pairs, total_kb);
       Segment sg;
       while (!*abort_flag && work.next(sg)) {
@@ -1112,6 +1116,7 @@ static uint32_t pow2_cols(int n) {
 using namespace xv;
 
 static bool g_disable_pair = false;
+static thread_local GemmRowWait g_pending_wait = {nullptr, nullptr, 0, 0};
 static unsigned long long* g_tp_prof = nullptr;
 static unsigned long long* g_gemm_prof = nullptr;
 
@@ -1414,6 +1419,20 @@ extern "C" {
 // Test hook: 1 forces the single-CTA kernel for every shape (A/B comparisons), 0 restores.
 void xv_gemm_disable_pair(int disable) { g_disable_pair = disable != 0; }
 
+// All-gather -> GEMM: the next GEMM launched from this thread waits, before its first activation tile, until
+// the `n` counters at `flags` (this rank's flag array, word kPushBcastWord on) have reached the values at
+// `targets` (the communicator's history words kPushBcastBase on). Used after an xv_gemm_bf16_tp call with
+// defer_row_wait: the rows other ranks broadcast are then awaited by the kernel that reads them, not by the
+// kernel that caused them.
+void xv_gemm_wait_for_rows(const void* flags, const void* targets, int n, unsigned spin_us) {
+  g_pending_wait.flags = static_cast<const uint32_t*>(flags);
+  g_pending_wait.targets = static_cast<const uint32_t*>(targets);
+  g_pending_wait.n = n;
+  g_pending_wait.spin_us = spin_us;
+}
+int xv_tp_bcast_word(void) { return kPushBcastWord; }
+int xv_tp_bcast_base_word(void) { return kPushBcastBase; }
+
 // Diagnostics: following xv_gemm_bf16_tp launches write 8 global-timer stamps per CTA into `buf`
 // (device memory, 8 * 8 bytes per CTA of the largest grid, i.e. 2 * SM count CTAs); null switches it off.
 void xv_tp_profile_buffer(void* buf) { g_tp_prof = static_cast<unsigned long long*>(buf); }
@@ -1540,6 +1559,9 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
 
   TpPush push;
   std::memset(&push, 0, sizeof(push));
+  // the rows this GEMM's activation still waits for (set by xv_gemm_wait_for_rows just before this call)
+  const GemmRowWait row_wait = g_pending_wait;
+  g_pending_wait.n = 0;
   const int total_work = pl.tiles_a * pl.tiles_b * pl.splits;
   if (pl.pair) {
     const int pairs_avail = num_sms / 2;
@@ -1574,7 +1596,7 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
       push.signal_ctas = 2 * used_pairs;
     }
     if (launch_pdl(gemm_tcgen05_pair_kernel, dim3(2 * pairs), dim3(kGemmThreads), pl.smem_bytes, stream, map_a, map_b,
-                   p, sk, push) != cudaSuccess)
+                   p, sk, push, row_wait) != cudaSuccess)
       return XV_ERR_LAUNCH;
   } else {
     int slots = num_sms * pl.ctas_per_sm;
@@ -1603,9 +1625,9 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
     }
     const cudaError_t le =
         pl.cluster ? launch_pdl_cluster(gemm_tcgen05_kernel, dim3(grid), dim3(kGemmThreads), pl.smem_bytes, stream,
-                                        static_cast<unsigned>(pl.splits), map_a, map_b, p, push)
+                                        static_cast<unsigned>(pl.splits), map_a, map_b, p, push, row_wait)
                    : launch_pdl(gemm_tcgen05_kernel, dim3(grid), dim3(kGemmThreads), pl.smem_bytes, stream, map_a, map_b,
-                                p, push);
+                                p, push, row_wait);
     if (le != cudaSuccess) return XV_ERR_LAUNCH;
   }
   if (cudaGetLastError() != cudaSuccess) return XV_ERR_LAUNCH;
@@ -1644,7 +1666,7 @@ int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long
                     const void* mc_buf, void* epoch, int rank,
                     int world, long long slot_offset, long long slot_bytes, int two_shot, long long h_offset,
                     const void* residual_in, void* residual_out, const void* norm_w, void* y_out, float eps, int mode,
-                    unsigned spin_us, int* status, cudaStream_t stream) {
+                    int defer_row_wait, unsigned spin_us, int* status, cudaStream_t stream) {
   if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || (n % 8) || n > kGemmThreads * kTailMaxVec * 8 ||
       (slot_offset & 15) || (two_shot && (h_offset & 15)) || m <= 0)
     return XV_ERR_SHAPE;
@@ -1674,6 +1696,7 @@ int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long
   t.hidden = n;
   t.eps = eps;
   t.mode = mode;
+  t.defer_row_wait = (two_shot && defer_row_wait) ? 1 : 0;
   t.prof = g_tp_prof;
   if (static_cast<long long>(world) * t.cap_rows * n * 2 > slot_bytes) return XV_ERR_WORKSPACE;
   return gemm_impl(x, w, nullptr, m, n, k, ldx, ldw, n, workspace, workspace_bytes, num_sms, status, stream, false,

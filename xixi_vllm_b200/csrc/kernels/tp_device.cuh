@@ -292,14 +292,22 @@ struct TpPush {
   int mode;                            // 0: residual add + RMSNorm; 1: plain sum
   int signal_ctas;                     // CTAs of this launch that own GEMM work (each raises its counter once)
   unsigned long long* prof;            // optional: 8 global-timer stamps per CTA (see xv_tp_profile_buffer)
+  int defer_row_wait;                  // two-shot: do not hold the kernel open until every owner's rows have arrived;
+                                       // the kernel that reads the activation waits for them itself (GemmRowWait)
 };
 
-// Phase stamps of the one-kernel projection, per CTA: 0 kernel entry, 1 GEMM roles done (tiles pushed, arrival
-// raised), 2 all sources' tiles arrived, 3 this CTA's rows reduced and stored / broadcast, 4 broadcast raised,
-// 5 every owner's rows arrived (CTA 0 only), 6 exit.
-__device__ __forceinline__ void tp_prof(const TpPush& t, int slot) {
-  if (t.prof != nullptr && threadIdx.x == 0) t.prof[blockIdx.x * 8 + slot] = global_timer_ns();
-}
+// What a GEMM needs to wait, before its first activation tile, for the rows that the one-kernel projection
+// before it has other ranks broadcast into this rank's activation buffer (all-gather -> GEMM): the per-owner
+// arrival counters in this rank's flag array and the values they must reach (the projection's last CTA
+// wrote those into the communicator's history words before it ended).
+struct GemmRowWait {
+  const uint32_t* flags;     // this rank's flag array + kPushBcastWord
+  const uint32_t* targets;   // TpComm::epoch + kPushBcastBase
+  int n;                     // ranks (0: nothing to wait for)
+  unsigned spin_us;
+};
+
+
 
 __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -317,6 +325,25 @@ __device__ __forceinline__ bool tp_wait_counter(const uint32_t* f, uint32_t targ
       __nanosleep(32);
     }
   }
+}
+
+// Called by the one thread that issues the GEMM's TMA loads. The loads that follow read memory that peers wrote
+// through NVLink, so the acquire is followed by a cross-proxy fence.
+__device__ __forceinline__ bool gemm_wait_rows(const GemmRowWait& w) {
+  bool ok = true;
+  for (int r = 0; r < w.n; ++r) {
+    const uint32_t target = *reinterpret_cast<const volatile uint32_t*>(w.targets + r);
+    ok = tp_wait_counter(w.flags + r, target, w.spin_us) && ok;
+  }
+  if (w.n > 0) asm volatile("fence.proxy.async;" ::: "memory");
+  return ok;
+}
+
+// Phase stamps of the one-kernel projection, per CTA: 0 kernel entry, 1 GEMM roles done (tiles pushed, arrival
+// raised), 2 all sources' tiles arrived, 3 this CTA's rows reduced and stored / broadcast, 4 broadcast raised,
+// 5 every owner's rows arrived (CTA 0 only), 6 exit.
+__device__ __forceinline__ void tp_prof(const TpPush& t, int slot) {
+  if (t.prof != nullptr && threadIdx.x == 0) t.prof[blockIdx.x * 8 + slot] = global_timer_ns();
 }
 
 __device__ __forceinline__ int tp_rows_owned(int rows, int owner, int world) {
@@ -495,7 +522,7 @@ __device__ __noinline__ void tp_push_tail(const TpPush& t) {
   }
   // One CTA keeps the kernel open until every owner's rows have landed in this rank's activation
   // buffer: the kernel's end then means "the whole [rows, hidden] activation is here".
-  if (t.two_shot && blockIdx.x == 0 && threadIdx.x < world) {
+  if (t.two_shot && !t.defer_row_wait && blockIdx.x == 0 && threadIdx.x < world) {
     const int owned = tp_rows_owned(t.rows, threadIdx.x, world);
     const int expect = owned < static_cast<int>(gridDim.x) ? owned : static_cast<int>(gridDim.x);
     const uint32_t target = st[kPushBcastBase + threadIdx.x] + static_cast<uint32_t>(expect);

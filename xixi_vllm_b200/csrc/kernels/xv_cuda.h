@@ -176,7 +176,14 @@ int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long
                     const void* mc_buf, void* epoch, int rank,
                     int world, long long slot_offset, long long slot_bytes, int two_shot, long long h_offset,
                     const void* residual_in, void* residual_out, const void* norm_w, void* y_out, float eps, int mode,
-                    unsigned spin_us, int* status, cudaStream_t stream);
+                    int defer_row_wait, unsigned spin_us, int* status, cudaStream_t stream);
+// All-gather -> GEMM. With defer_row_wait = 1 (two-shot form) xv_gemm_bf16_tp ends without waiting for the rows
+// the other ranks broadcast; the GEMM that reads the activation waits for them in its loader instead: call
+// xv_gemm_wait_for_rows right before launching that GEMM from the same thread. flags: this rank's flag array
+// at word xv_tp_bcast_word(); targets: the `epoch` words from xv_tp_bcast_base_word() on; n: ranks.
+void xv_gemm_wait_for_rows(const void* flags, const void* targets, int n, unsigned spin_us);
+int xv_tp_bcast_word(void);
+int xv_tp_bcast_base_word(void);
 
 // Diagnostics for xv_gemm_bf16_tp: 8 global-timer stamps per CTA (kernel entry, GEMM roles done, tiles arrived,
 // rows done, broadcast raised, all rows arrived (CTA 0), exit, unused) into `buf`; null switches it off.
@@ -226,6 +233,7 @@ typedef struct XvModelDesc {
   int tp_push_max;                    // ... for forwards of at most this many tokens
   int tp_one_shot_max;                // of those, forwards of at most this many tokens reduce every row on every rank
   int tp_pull_two_shot;               // two-kernel form (GEMM, then a reduction kernel that pulls): 1 = row-sharded
+  int tp_defer_row_wait;              // one-kernel two-shot form: the GEMM that reads h waits for the broadcast rows
   int is_first, is_last;              // pipeline stage: the first owns the embedding, the last the LM head; on
                                       // other stages `final_norm` is the next stage's first input norm and the
                                       // arena's h / residual are received from / sent to the neighbours

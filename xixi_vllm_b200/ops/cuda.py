@@ -89,7 +89,7 @@ def lib():
     L.xv_tp_argmax.argtypes = [_vp, _vp, _vp, _i32, _i32, _i64, _vp, _i64, _i32, _i32, _i32, _vp, _i32,
                                ctypes.c_uint, _vp, _vp]
     L.xv_gemm_bf16_tp.argtypes = [_vp, _vp, _i32, _i32, _i32, _i64, _i64, _vp, _i64, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i64,
-                                  _i64, _i32, _i64, _vp, _vp, _vp, _vp, _f32, _i32, ctypes.c_uint, _vp, _vp]
+                                  _i64, _i32, _i64, _vp, _vp, _vp, _vp, _f32, _i32, _i32, ctypes.c_uint, _vp, _vp]
     L.xv_gemm_plan_override.argtypes = [_i32, _i32, _i32, _i32]
     L.xv_gemm_plan_override.restype = None
     L.xv_selftest_bounded_wait.argtypes = [_vp, _vp, ctypes.c_uint, _vp]
@@ -476,7 +476,7 @@ def tp_allgather_cols(peer_bufs, peer_flags, mc_ptr: int, epoch, rank: int, worl
 
 def gemm_tp_fused(x, w, peer_bufs, peer_flags, mc_ptr: int, epoch, rank: int, world: int, slot_offset: int,
                   slot_bytes: int, two_shot: bool, h_offset: int, residual_in, residual_out, norm_w, y, eps: float,
-                  mode: int, spin_us: int) -> None:
+                  mode: int, spin_us: int, defer_row_wait: bool = False) -> None:
     """RowParallel GEMM + cross-rank sum + residual add + RMSNorm in one kernel (``xv_gemm_bf16_tp``): the GEMM
     epilogue pushes its tiles into the slot array of the ranks that reduce them."""
     _bf16(x, w)
@@ -492,7 +492,7 @@ def gemm_tp_fused(x, w, peer_bufs, peer_flags, mc_ptr: int, epoch, rank: int, wo
         residual_in.data_ptr() if residual_in is not None else None,
         residual_out.data_ptr() if residual_out is not None else None,
         norm_w.data_ptr() if norm_w is not None else None, y.data_ptr() if y is not None else None, eps, mode,
-        spin_us, st.status.data_ptr(), _stream()), f"gemm+allreduce {M}x{N}x{K}")
+        1 if defer_row_wait else 0, spin_us, st.status.data_ptr(), _stream()), f"gemm+allreduce {M}x{N}x{K}")
 
 
 def gemm_plan_override(kind: int = -1, bn: int = 0, splits: int = 0, stages: int = 0) -> None:

@@ -114,6 +114,9 @@ class FusedTPComm(TPComm):
         # native executor: forwards of at most push_max_tokens run the one-kernel projection, of those the ones
         # of at most one_shot_max_tokens in the form where every rank reduces every row
         self.push_max_tokens = int(os.environ.get("XV_TP_PUSH_MAX_T", "256"))
+        # all-gather -> GEMM: after a two-shot one-kernel projection the GEMM that reads the activation waits for
+        # the rows the other ranks broadcast (in its TMA producer), instead of the projection kernel itself
+        self.defer_row_wait = os.environ.get("XV_TP_DEFER_ROW_WAIT", "1") != "0"
         self.one_shot_max_tokens = int(os.environ.get("XV_TP_ONE_SHOT_MAX_T", "64"))
         self._idx = 0
         self._logits_view = None
@@ -175,13 +178,15 @@ class FusedTPComm(TPComm):
 
     def gemm_reduce_norm(self, x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | None,
                          w: torch.Tensor | None, eps: float, *, two_shot: bool, final: bool = False,
-                         first: bool = False, mode: int = 0):
+                         first: bool = False, mode: int = 0, defer_row_wait: bool = False):
         """Row-parallel projection, cross-rank sum, residual add and RMSNorm as one kernel.
 
         ``two_shot``: rank r reduces rows r, r + world, ...; ``residual`` is a local [T, H] buffer of which
         only those rows are read and written (``first`` starts the stream instead of adding), and the
         result is the view of the symmetric activation buffer every rank's rows were broadcast into.
         Otherwise every rank reduces all rows and gets a fresh [T, H] tensor.
+        ``defer_row_wait`` (two-shot): the kernel ends without waiting for the other ranks' rows; the caller
+        must run ``await_rows()`` right before the GEMM that reads ``y``.
         Returns ``(y, residual)``."""
         T = x.shape[0]
         buf = self.alloc_partial(T, final)
@@ -196,8 +201,18 @@ class FusedTPComm(TPComm):
                                                                         device=self.device)
         cuda.gemm_tp_fused(x, weight, self._bufs, self._flags, self.mc_ptr, self.epoch, self.rank, self.world,
                            off, self.buf_bytes, two_shot, self.h_off, None if first else residual, res_out, w,
-                           None if two_shot else y, eps, mode, SPIN_LIMIT)
+                           None if two_shot else y, eps, mode, SPIN_LIMIT, defer_row_wait=defer_row_wait)
         return y, res_out
+
+    def await_rows(self) -> None:
+        """The next GEMM launched from this thread waits (in its loader) for the rows that the last two-shot
+        projection with ``defer_row_wait`` has the other ranks broadcast."""
+        L = cuda.lib()
+        L.xv_gemm_wait_for_rows.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_uint]
+        L.xv_gemm_wait_for_rows.restype = None
+        flags = self.symm.ptrs[self.rank] + self.flags_off + 4 * L.xv_tp_bcast_word()
+        targets = self.epoch.data_ptr() + 4 * L.xv_tp_bcast_base_word()
+        L.xv_gemm_wait_for_rows(flags, targets, self.world, SPIN_LIMIT)
 
     # --- reductions -----------------------------------------------------------------------------
     def reduce_add_rmsnorm(self, partial, residual, w, eps):

@@ -36,7 +36,8 @@ class ModelDesc(ctypes.Structure):
                 ("tp_world", _i32), ("peer_bufs", _vp), ("peer_flags", _vp), ("mc_buf", _vp), ("epoch", _vp),
                 ("h_offset", _i64), ("buf_bytes", _i64), ("slots_offset", _i64), ("spin_us", ctypes.c_uint),
                 ("num_kv_blocks", _i32), ("prefill_tc", _i32), ("tp_push", _i32), ("tp_push_max", _i32),
-                ("tp_one_shot_max", _i32), ("tp_pull_two_shot", _i32), ("is_first", _i32), ("is_last", _i32)]
+                ("tp_one_shot_max", _i32), ("tp_pull_two_shot", _i32), ("tp_defer_row_wait", _i32), ("is_first", _i32),
+                ("is_last", _i32)]
 
 
 class BatchDesc(ctypes.Structure):
@@ -125,6 +126,7 @@ class NativeForward:
             d.tp_push = 1 if comm.fuse_gemm else 0
             d.tp_push_max = comm.push_max_tokens
             d.tp_one_shot_max = comm.one_shot_max_tokens
+            d.tp_defer_row_wait = 1 if comm.defer_row_wait else 0
             from ..parallel.symm import SPIN_LIMIT
 
             d.spin_us = SPIN_LIMIT

@@ -100,3 +100,27 @@ def test_cta_pair_kernel_matches_single_cta_kernel(m, n, k):
     assert (y_pair.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
     # tiles that the pairs deal in K blocks are summed from two or three fp32 partial sums
     assert (y_pair.float() - y_single.float()).abs().max().item() <= 1e-2 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("m,n,k,parts", [(1400, 4096, 4096, 3), (512, 4096, 12288, 2), (1400, 4096, 1024, 3)])
+def test_cta_pair_kernel_splits_last_wave_in_k(m, n, k, parts):
+    """When the last wave of 256-row tiles leaves most SM pairs idle its tiles are cut into K parts whose fp32
+    accumulators meet in a slot of the workspace. The result matches fp32, repeats bit for bit (a slot takes
+    at most two contributions, which commute) and leaves slots and counters zero for the next launch."""
+    from xixi_vllm_b200.ops import cuda
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    if sms != 148:
+        pytest.skip("plan under test is the one for 148 SMs")
+    pl = cuda.gemm_plan(m, n, k, sms)
+    assert pl.pair == 1 and pl.sk_tiles > 0 and pl.sk_parts == parts
+    g = torch.Generator().manual_seed(m + n + k)
+    x = (torch.randn(m, k, generator=g) * 0.5).bfloat16().to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.5).bfloat16().to(DEV)
+    ref = x.float() @ w.float().t()
+    first = cuda.linear(x, w)
+    for _ in range(3):
+        again = cuda.linear(x, w)
+        assert torch.equal(first, again)
+    torch.cuda.synchronize()
+    cuda.check_status()
+    assert (first.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2

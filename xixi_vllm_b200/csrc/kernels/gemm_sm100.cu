@@ -680,16 +680,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // shared-memory fill traffic per FLOP is a third lower than for a lone CTA's 128 x BN tile. CTA rank 0
 // issues the MMAs for the pair; each CTA drains its own 128 accumulator rows.
 //
-// Tiles are dealt whole and round-robin as long as they fill all SM pairs; what is left over (96 tiles on
-// 74 pairs: the last wave, or the last two) is dealt in K blocks ("stream-K"): that region's tiles x
-// K-blocks units are numbered tile by tile and every pair takes one contiguous range of them, so all pairs
-// finish together. A range covers at most one tile's end, whole tiles, and one tile's beginning; it is at
-// least half a tile long, so at most three pairs share a tile. A pair walks its range from the top: the
-// beginning of its last tile first, whose fp32 accumulator it adds (red.add.f32) into the slot of the pair
-// that will finish that tile, then raises that pair's counter; whole tiles next; the end of its first tile
-// last, where it adds what the other pairs left in its own slot to its accumulator, runs the normal
-// epilogue, and clears slot and counter for the next launch. With at most two contributions added to a slot
-// that starts at zero the sum does not depend on their order.
+// Tiles are dealt whole and round-robin. When the last wave would leave more than half of the SM pairs idle,
+// its tiles are cut into two or three K parts, one part per pair ("stream-K tail"): the pairs holding a
+// tile's first parts add their fp32 accumulators (red.add.f32) into the slot of the pair that holds the last
+// part and raise its counter; that pair adds the slot to its own accumulator, runs the normal epilogue and
+// clears slot and counter for the next launch. A slot starts at zero and receives at most two contributions,
+// so the sum does not depend on their order. The parts run first, the whole tiles after them.
 constexpr int kPairAccStride = 256;
 constexpr long long kSkReserveBytes = 20ll << 20;   // tail of the workspace kept zero for partial tiles + counters
 constexpr long long kSkCounterBytes = 4096;         // the very end of it: two counters per SM pair, then one per tile
@@ -697,9 +693,10 @@ constexpr int kFixCounterFirst = 256;               // first counter word of the
 constexpr int kFixCounterTiles = 768;
 
 struct StreamK {
-  int units_per_pair;      // K blocks of the stream-K region each pair takes
+  int parts;               // K parts every tile of the stream-K region is cut into (2 or 3; 1: no such region)
+  int units_per_pair;      // K blocks of a part
   int dp_tiles;            // tiles [0, dp_tiles) are dealt whole, round-robin over the pairs
-  int sk_units;            // (tiles - dp_tiles) * K blocks per tile
+  int sk_tiles;            // the tiles after them, one part per pair
   int slot_floats;         // floats per slot: 256 rows x BN rounded up to whole 32-column chunks
   float* slots;            // [pairs][slot_floats], indexed by the pair that finishes the tile; zero between launches
   uint32_t* counters;      // [pairs][2] (finishing pair, CTA rank); zero between launches
@@ -710,30 +707,34 @@ struct Segment {
   int sk_tile;             // index of the tile inside the stream-K region, -1 for a whole tile dealt round-robin
 };
 
-// A pair's work: first its contiguous range [lo, hi) of the stream-K region's K blocks, from the top (the
-// beginning of its last tile, whole tiles, the end of its first tile), then its whole tiles pair, pair + pairs, ...
-// of the round-robin region, so that the pairs running at the same time work on neighbouring tiles there.
+// A pair's work: first its part of a tile of the stream-K region (pair p holds part p % parts of that region's
+// tile p / parts; the last part finishes the tile), then its whole tiles pair, pair + pairs, ... of the
+// round-robin region, so that the pairs running at the same time work on neighbouring tiles there.
 struct PairWork {
-  int lo, u_hi, total_kb, sk_tile0, dp_next, dp_tiles, stride;
+  int total_kb, dp_next, dp_tiles, stride;
+  int sk_tile, kb_begin, kb_end;      // sk_tile < 0: no stream-K part (left)
   __device__ PairWork(const GemmParams& p, const StreamK& sk, int pair, int num_pairs, int kb_per_tile) {
     total_kb = kb_per_tile;
-    lo = min(pair * sk.units_per_pair, sk.sk_units);
-    u_hi = min(lo + sk.units_per_pair, sk.sk_units);
-    sk_tile0 = sk.dp_tiles;
     dp_next = pair;
     dp_tiles = sk.dp_tiles;
     stride = num_pairs;
+    sk_tile = -1;
+    kb_begin = kb_end = 0;
+    if (sk.parts > 1 && pair < sk.sk_tiles * sk.parts) {
+      sk_tile = pair / sk.parts;
+      const int part = pair - sk_tile * sk.parts;
+      kb_begin = part * sk.units_per_pair;
+      kb_end = min(total_kb, kb_begin + sk.units_per_pair);
+    }
   }
-  __device__ bool any() const { return u_hi > lo || dp_next < dp_tiles; }
+  __device__ bool any() const { return sk_tile >= 0 || dp_next < dp_tiles; }
   __device__ bool next(Segment& sg) {
-    if (u_hi > lo) {
-      sg.sk_tile = (u_hi - 1) / total_kb;
-      const int t0 = sg.sk_tile * total_kb;
-      const int seg_lo = lo > t0 ? lo : t0;
-      sg.kb_begin = seg_lo - t0;
-      sg.kb_end = u_hi - t0;
-      sg.tile = sk_tile0 + sg.sk_tile;
-      u_hi = seg_lo;
+    if (sk_tile >= 0) {
+      sg.sk_tile = sk_tile;
+      sg.tile = dp_tiles + sk_tile;
+      sg.kb_begin = kb_begin;
+      sg.kb_end = kb_end;
+      sk_tile = -1;
       return true;
     }
     if (dp_next < dp_tiles) {
@@ -898,8 +899,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       int tile_a, tile_b;
       tile_coords(p, sg.tile, tile_a, tile_b);
       const uint32_t buf = t & 1, use = t >> 1;
-      const bool contributes = sg.kb_end < total_kb;                  // the tile's end belongs to another pair
-      const bool finishes = !contributes && sg.kb_begin > 0;          // other pairs hold the tile's beginning
+      const bool contributes = sg.sk_tile >= 0 && sg.kb_end < total_kb;     // the tile's end belongs to another pair
+      const bool finishes = sg.sk_tile >= 0 && !contributes;                // other pairs hold the tile's beginning
       if (!dead) {
         bool ok = mbar_wait(&acc_full[buf], use & 1);
         if (!ok) {
@@ -918,11 +919,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         // The pair that holds the tile's last K block finishes the tile; its slot collects the others' sums.
         // Slot layout: [32-column chunk][4-float group j][256 rows][4 floats]: the 32 rows of a warp are
         // consecutive 16-byte pieces, so every vector access of a warp is 512 contiguous bytes.
-        const int fin_pair = finishes ? pair : ((sg.sk_tile + 1) * total_kb - 1) / sk.units_per_pair;
+        const int fin_pair = sg.sk_tile * sk.parts + sk.parts - 1;
         float* slot = sk.slots + static_cast<size_t>(fin_pair) * sk.slot_floats;
         if (finishes) {
-          const int first_pair = (sg.sk_tile * total_kb) / sk.units_per_pair;
-          const uint32_t want = static_cast<uint32_t>(pair - first_pair);
+          const uint32_t want = static_cast<uint32_t>(sk.parts - 1);
           const uint32_t* ctr = sk.counters + 2 * pair + rank;
           if (lane == 0) {
             const unsigned long long t0 = global_timer_ns();
@@ -982,7 +982,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         __threadfence();
         named_barrier(2, 128);
         if (threadIdx.x == 64) {
-          const int fin_pair = finishes ? pair : ((sg.sk_tile + 1) * total_kb - 1) / sk.units_per_pair;
+          const int fin_pair = sg.sk_tile * sk.parts + sk.parts - 1;
           uint32_t* ctr = sk.counters + 2 * fin_pair + rank;
           if (contributes)
             red_release_gpu_add(ctr, 1u);
@@ -1232,11 +1232,18 @@ void plan_single(int m, int n, int k, int num_sms, unsigned flags, int max_split
   pl.workspace_bytes = (pl.splits > 1 && !pl.cluster) ? static_cast<long long>(pl.splits) * m * n * 4 : 0;
 }
 
-// CTA-pair plan: 256 x bn tiles. Whole waves of tiles are dealt round-robin; the rest (`sk_tiles` at the
-// end of the tile order) is dealt in contiguous ranges of `units_per_pair` K blocks (stream-K). The last
-// whole wave joins the stream-K region when that evens the pairs' loads out better. bn <= 0 picks the
-// widest tile that splits N evenly; units_override: > 0 fixes the range length, < 0 deals whole tiles only.
-void fill_pair(int m, int n, int k, int bn, int num_sms, int units_override, XvGemmPlan& pl) {
+// Parts a tile of the last, `rest`-tile wave is cut into: as many as there are idle pairs per tile, at most
+// three (two contributions to a slot commute), none when more than half of the pairs would be busy anyway.
+int sk_parts_for(int rest, int pairs, int total_kb) {
+  if (rest <= 0 || total_kb < 16) return 1;
+  int parts = pairs / rest;
+  if (parts > 3) parts = 3;
+  return parts < 2 ? 1 : parts;
+}
+
+// CTA-pair plan: 256 x bn tiles dealt whole and round-robin, with the last wave's tiles cut into K parts when
+// `stream_k` is set and that wave is less than half full. bn <= 0 picks the widest tile that splits N evenly.
+void fill_pair(int m, int n, int k, int bn, int num_sms, int stream_k, XvGemmPlan& pl) {
   const int total_kb = (k + kBK - 1) / kBK;
   if (bn <= 0) {
     const int tiles_b = (n + 255) / 256;
@@ -1259,38 +1266,15 @@ void fill_pair(int m, int n, int k, int bn, int num_sms, int units_override, XvG
   pl.ctas_per_sm = 1;
   const int pairs = num_sms / 2;
   const int tiles = pl.tiles_a * pl.tiles_b;
-  const int min_units = (total_kb + 1) / 2;          // at most three pairs share a tile
-  const int waves = tiles / pairs, rest = tiles % pairs;
   pl.sk_tiles = 0;
+  pl.sk_parts = 1;
   pl.units_per_pair = 0;
   pl.workspace_bytes = 0;
-  if (units_override < 0 || rest == 0 || total_kb < 16) return;         // whole tiles only (short K: the fix-up would cost more than it evens out)
-  // K blocks on the busiest pair: whole waves, then the stream-K region's ranges
-  auto range_len = [&](int sk_tiles) {
-    long long u = (static_cast<long long>(sk_tiles) * total_kb + pairs - 1) / pairs;
-    if (u < min_units) u = min_units;
-    if (u > static_cast<long long>(sk_tiles) * total_kb) u = static_cast<long long>(sk_tiles) * total_kb;
-    return static_cast<int>(u);
-  };
-  int sk_tiles = rest;
-  int u = range_len(rest);
-  if (waves >= 1) {
-    const int u2 = range_len(rest + pairs);
-    if ((waves - 1) * total_kb + u2 < waves * total_kb + u) {
-      sk_tiles = rest + pairs;
-      u = u2;
-    }
-  }
-  if (units_override > 0) {
-    u = units_override < min_units ? min_units : units_override;
-    const long long need = (static_cast<long long>(sk_tiles) * total_kb + u - 1) / u;
-    if (need > pairs) u = range_len(sk_tiles);
-  }
-  if (u >= total_kb && u % total_kb == 0 && static_cast<long long>(sk_tiles) * total_kb <= static_cast<long long>(u) * pairs &&
-      sk_tiles <= pairs * (u / total_kb) && (sk_tiles % pairs == 0))
-    return;                                                                 // the ranges are whole tiles anyway
-  pl.sk_tiles = sk_tiles;
-  pl.units_per_pair = u;
+  const int parts = stream_k > 0 ? sk_parts_for(tiles % pairs, pairs, total_kb) : 1;
+  if (parts < 2) return;
+  pl.sk_tiles = tiles % pairs;
+  pl.sk_parts = parts;
+  pl.units_per_pair = (total_kb + parts - 1) / parts;
   const int chunks = (bn + 31) / 32;
   pl.workspace_bytes = static_cast<long long>(pairs) * chunks * 256 * 32 * 4 + kSkCounterBytes;
 }
@@ -1321,9 +1305,9 @@ int gemm_plan_impl(int m, int n, int k, int num_sms, XvGemmPlan* plan, unsigned 
     int sp = g_override.splits > 0 ? g_override.splits : 1;
     if (sp > total_kb) sp = total_kb;
     if (g_override.kind == 2) {
-      // `splits` of the hook means K blocks per pair in the stream-K region (0: planner, -1: whole tiles only)
+      // `splits` of the hook: > 0 cuts the last wave's tiles into K parts (stream-K tail), else whole tiles only
       const int bn = g_override.bn > 0 ? round_up(g_override.bn, 16) : 0;
-      fill_pair(m, n, k, bn, num_sms, g_override.splits, pl);
+      fill_pair(m, n, k, bn, num_sms, g_override.splits > 0 ? 1 : 0, pl);
       if (g_override.stages > 1 && g_override.stages <= pl.stages) {
         pl.smem_bytes -= (pl.stages - g_override.stages) * (kBM * kBK * 2 + (pl.bn / 2) * kBK * 2);
         pl.stages = g_override.stages;
@@ -1362,7 +1346,7 @@ int gemm_plan_impl(int m, int n, int k, int num_sms, XvGemmPlan* plan, unsigned 
   //  * from 161 to 256 rows (a decode batch) the swapped single-CTA kernel with split-K wins unless there
   //    are enough output columns for the pairs to fill the machine without splitting K.
   static const int pair_min_m = env_int("XV_GEMM_PAIR_MIN_M", 161);
-  static const int streamk = env_int("XV_GEMM_STREAMK", 0);
+  static const int streamk = env_int("XV_GEMM_STREAMK", 1);
   const int total_kb = (k + kBK - 1) / kBK;
   if (!(flags & kPlanNoPair) && m >= pair_min_m && n >= 64 && (m > 256 || (n >= 6144 && total_kb <= 80))) {
     const int pairs = num_sms / 2;
@@ -1372,8 +1356,14 @@ int gemm_plan_impl(int m, int n, int k, int num_sms, XvGemmPlan* plan, unsigned 
     for (int bn = 256; bn >= 96; bn -= 16) {
       if (bn > round_up(n, 16) && bn != 256) continue;
       const int tiles = tiles_a * ((n + bn - 1) / bn);
-      const int waves = (tiles + pairs - 1) / pairs;
-      const double cost = waves * (total_kb * (0.30 + 0.00055 * bn) + 1.5);
+      const int waves = tiles / pairs, rest = tiles % pairs;
+      const double t_kb = 0.30 + 0.00055 * bn;
+      double cost = waves * (total_kb * t_kb + 1.5);
+      if (rest > 0) {
+        const int parts = streamk ? sk_parts_for(rest, pairs, total_kb) : 1;
+        // a part costs its K blocks plus the exchange of a 256 x bn fp32 tile through L2
+        cost += parts > 1 ? ((total_kb + parts - 1) / parts) * t_kb + 1.5 + 4.0 * bn / 256.0 : total_kb * t_kb + 1.5;
+      }
       if (bn == 256) widest = cost;
       // a narrower tile has to win by more than the run-to-run spread of the measurements
       if (cost < best && (bn == 256 || cost < 0.94 * widest)) {
@@ -1383,7 +1373,7 @@ int gemm_plan_impl(int m, int n, int k, int num_sms, XvGemmPlan* plan, unsigned 
     }
     if (n < 256) best_bn = round_up(n, 16);
     std::memset(&pl, 0, sizeof(pl));
-    fill_pair(m, n, k, best_bn, num_sms, streamk ? 0 : -1, pl);
+    fill_pair(m, n, k, best_bn, num_sms, streamk, pl);
   }
   *plan = pl;
   std::lock_guard<std::mutex> g(g_plan_mu);
@@ -1486,7 +1476,7 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
     return XV_ERR_ALIGN;
   // Without the reserve the pair kernel deals whole tiles (its pairs then finish unevenly).
   if (pl.pair && pl.sk_tiles > 0 && (!sk_ok || pl.workspace_bytes > kSkReserveBytes))
-    fill_pair(m, n, k, pl.bn, num_sms, -1, pl);
+    fill_pair(m, n, k, pl.bn, num_sms, 0, pl);
   // Split-K in the swapped orientation: the planes are summed inside the kernel by the CTA that brings a
   // tile's last one (needs a tile counter from the reserve), unless the caller wants the planes themselves.
   const bool fixup = pl.splits > 1 && !pl.cluster && pl.swapped && !pl.pair && push_in != nullptr && sk_ok &&
@@ -1570,11 +1560,12 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
     StreamK sk;
     std::memset(&sk, 0, sizeof(sk));
     sk.dp_tiles = tiles - pl.sk_tiles;
-    sk.sk_units = pl.sk_tiles * total_kb;
-    sk.units_per_pair = pl.sk_tiles > 0 ? pl.units_per_pair : 1;
+    sk.sk_tiles = pl.sk_tiles;
+    sk.parts = pl.sk_tiles > 0 ? pl.sk_parts : 1;
+    sk.units_per_pair = pl.sk_tiles > 0 ? pl.units_per_pair : total_kb;
     int used_pairs = sk.dp_tiles < pairs_avail ? sk.dp_tiles : pairs_avail;
     if (pl.sk_tiles > 0) {
-      const int sk_pairs = (sk.sk_units + sk.units_per_pair - 1) / sk.units_per_pair;
+      const int sk_pairs = pl.sk_tiles * pl.sk_parts;
       if (sk_pairs > pairs_avail) return XV_ERR_SHAPE;
       if (sk_pairs > used_pairs) used_pairs = sk_pairs;
       sk.slot_floats = ((pl.bn + 31) / 32) * 256 * 32;

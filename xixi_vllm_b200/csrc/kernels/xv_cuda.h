@@ -30,8 +30,9 @@ typedef struct XvGemmPlan {
   int cluster;             // 1: the K splits of a tile are one thread-block cluster and sum their accumulators
                            //    through distributed shared memory (the output is final: no planes, no workspace)
   int pair;                // 1: CTA-pair kernel (cta_group::2, 256 x bn tiles, stream-K)
-  int sk_tiles;            // pair kernel: tiles at the end of the tile order that are dealt in K blocks (stream-K)
-  int units_per_pair;      // pair kernel: K blocks of that region each SM pair takes
+  int sk_tiles;            // pair kernel: tiles of the last wave that are cut into K parts (stream-K tail) ...
+  int sk_parts;            // ... this many each (2 or 3), one part per SM pair ...
+  int units_per_pair;      // ... of this many K blocks
   long long workspace_bytes;
 } XvGemmPlan;
 

@@ -38,7 +38,8 @@ launch_count = 0
 class GemmPlan(ctypes.Structure):
     _fields_ = [("swapped", _i32), ("bn", _i32), ("tiles_a", _i32), ("tiles_b", _i32), ("splits", _i32),
                 ("k_blocks_per_split", _i32), ("stages", _i32), ("smem_bytes", _i32),
-                ("ctas_per_sm", _i32), ("cluster", _i32), ("pair", _i32), ("sk_tiles", _i32), ("units_per_pair", _i32), ("workspace_bytes", _i64)]
+                ("ctas_per_sm", _i32), ("cluster", _i32), ("pair", _i32), ("sk_tiles", _i32), ("sk_parts", _i32), ("units_per_pair", _i32),
+                ("workspace_bytes", _i64)]
 
 
 def lib():

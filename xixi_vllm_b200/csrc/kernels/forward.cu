@@ -57,9 +57,9 @@ inline char* symm_local(const Ctx& c, int which) {
 
 // Row-parallel projection followed by the reduction point that consumes it:
 //   residual += sum_over_ranks(x W^T);  h = rmsnorm(residual) * norm_w
-// Under tensor parallelism this is ONE kernel (xv_gemm_bf16_tp: tiles pushed from the GEMM epilogue to
-// the ranks that reduce them); the two-kernel form (GEMM into the symmetric buffer, then a reduction
-// kernel that pulls) remains for shapes whose slot array does not fit and for XV_TP_PUSH=0.
+// Under tensor parallelism this is the GEMM into the symmetric buffer followed by a reduction kernel that
+// pulls the partial sums, or, when the model description asks for it (tp_push), ONE kernel
+// (xv_gemm_bf16_tp: tiles pushed from the GEMM epilogue to the ranks that reduce them).
 int row_linear_reduce_norm(Ctx& c, const void* x, const void* w, int k, const void* norm_w, bool final_call) {
   const XvModelDesc* m = c.m;
   const int T = c.b->num_tokens, H = m->hidden;

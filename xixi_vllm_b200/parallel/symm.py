@@ -102,14 +102,13 @@ class FusedTPComm(TPComm):
         self.epoch = torch.zeros(32, dtype=torch.int32, device=self.device)   # [0] epoch, the rest: counter history
         self.epoch[0] = 1
         self.status = cuda.device_status(self.epoch)
-        # The row-parallel GEMM and its reduction run as ONE kernel (tiles pushed from the GEMM epilogue into the
-        # reducing ranks' slots); XV_TP_PUSH=0 goes back to GEMM + reduction kernel. This module-by-module path
-        # (pipeline stages, tests) reduces every row on every rank, which costs NVLink traffic proportional to
-        # the rank count, so it is used up to XV_TP_FUSE_GEMM_MAX_T tokens.
-        # Default: from 4 ranks up (at 2 ranks each rank's K is long, the GEMM dominates, and GEMM + pulling
-        # reduction kernel measured faster); XV_TP_PUSH=1 / 0 forces it on / off.
-        env_push = os.environ.get("XV_TP_PUSH", "")
-        self.fuse_gemm = (env_push == "1") if env_push in ("0", "1") else group.size >= 4
+        # The row-parallel GEMM and its reduction can run as ONE kernel (tiles pushed from the GEMM epilogue into
+        # the reducing ranks' slots, XV_TP_PUSH=1). It is off by default: at 2 and 4 ranks the GEMM followed by
+        # the reduction kernel that pulls measured faster at every batch size (the pushing GEMM keeps few CTAs
+        # busy and pays a system-scope release per tile). This module-by-module path (tests, stages driven from
+        # Python) reduces every row on every rank, which costs NVLink traffic proportional to the rank count,
+        # so with XV_TP_PUSH=1 it is used up to XV_TP_FUSE_GEMM_MAX_T tokens.
+        self.fuse_gemm = os.environ.get("XV_TP_PUSH", "0") == "1"
         self.fuse_gemm_max_tokens = int(os.environ.get("XV_TP_FUSE_GEMM_MAX_T", "256"))
         # native executor: forwards of at most push_max_tokens run the one-kernel projection, of those the ones
         # of at most one_shot_max_tokens in the form where every rank reduces every row

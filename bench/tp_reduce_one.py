@@ -4,6 +4,11 @@ are this GPU's own buffer, so link traffic is absent but every load, the residua
 norm and the broadcast store run as in a real group).
 
     python -m bench.tp_reduce_one [--rows 4096 --hidden 4096 --iters 3] [--sharded]
+    python -m bench.tp_reduce_one --what argmax|gather|sample|project [--rows 256 --vocab 151936 --k 4096]
+
+``--what`` selects the other tensor-parallel kernels: vocabulary-parallel argmax, the logits column gather, the
+sharded sampler (top-k 50, top-p 0.9) and the one-kernel row-parallel projection (GEMM whose epilogue pushes its
+tiles into the reducing rank's slots, then residual add and RMSNorm).
 """
 
 from __future__ import annotations
@@ -26,6 +31,9 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--sharded", action="store_true", help="row-sharded (two-shot) kernel instead of one-shot")
+    ap.add_argument("--what", default="reduce", choices=["reduce", "argmax", "gather", "sample", "project"])
+    ap.add_argument("--vocab", type=int, default=151936)
+    ap.add_argument("--k", type=int, default=4096, help="K of the projection (--what project)")
     a = ap.parse_args()
     os.environ.setdefault("XV_TP_NVLS", "0")
     torch.cuda.set_device(0)
@@ -37,6 +45,10 @@ def main() -> None:
 
     groups.init_distributed_environment(world_size=1, rank=0, backend="nccl")
     groups.initialize_model_parallel(1, 1)
+    if a.what != "reduce":
+        other_kernels(a, groups, cuda, FusedTPComm)
+        dist.destroy_process_group()
+        return
     comm = FusedTPComm(groups.get_tp_group(), torch.device("cuda:0"), a.hidden, a.rows, torch.bfloat16)
     g = torch.Generator().manual_seed(0)
     part = torch.randn(a.rows, a.hidden, generator=g).bfloat16().cuda()
@@ -64,6 +76,50 @@ def main() -> None:
     print("max err y", float((y.float().cpu() - ref_y.float()).abs().max()),
           "residual", float((r.float() - ref_res.float()).abs().max()))
     dist.destroy_process_group()
+
+
+def other_kernels(a, groups, cuda, FusedTPComm) -> None:
+    dev = torch.device("cuda:0")
+    os.environ["XV_TP_PUSH"] = "1"
+    rows = min(a.rows, 512)
+    comm = FusedTPComm(groups.get_tp_group(), dev, a.hidden, max(rows, 512), torch.bfloat16, logits_rows=rows,
+                       logits_local_cols=a.vocab)
+    g = torch.Generator().manual_seed(0)
+    if a.what == "project":
+        x = (torch.randn(rows, a.k, generator=g) * 0.5).bfloat16().to(dev)
+        wt = (torch.randn(a.hidden, a.k, generator=g) * 0.05).bfloat16().to(dev)
+        resid = torch.randn(rows, a.hidden, generator=g).bfloat16().to(dev)
+        nw = torch.ones(a.hidden).bfloat16().to(dev)
+        for _ in range(a.iters):
+            comm.begin_forward()
+            y, r = comm.gemm_reduce_norm(x, wt, resid.clone(), nw, 1e-6, two_shot=False)
+        torch.cuda.synchronize()
+        ref = ((x.float() @ wt.float().t()).bfloat16().float() + resid.float()).bfloat16()
+        print("max err residual", float((r.float() - ref.float()).abs().max()))
+    else:
+        logits = (torch.randn(rows, a.vocab, generator=g) * 2.0).bfloat16().to(dev)
+        temp = torch.full((rows,), 0.8, device=dev)
+        top_k = torch.full((rows,), 50, dtype=torch.int32, device=dev)
+        top_p = torch.full((rows,), 0.9, device=dev)
+        min_p = torch.zeros(rows, device=dev)
+        rng = torch.tensor([1, 2], dtype=torch.int32, device=dev)
+        for _ in range(a.iters):
+            if a.what == "argmax":
+                out = comm.argmax(logits, a.vocab, 0)
+            elif a.what == "gather":
+                out = comm.gather_logits(logits)
+            else:
+                out = comm.sample(logits, a.vocab, 0, a.vocab, temp, top_k, top_p, min_p, rng)
+        torch.cuda.synchronize()
+        if a.what == "argmax":
+            print("argmax equal", bool(torch.equal(out.cpu(), logits.float().argmax(-1).cpu())))
+        elif a.what == "gather":
+            print("gather equal", bool(torch.equal(out, logits)))
+        else:
+            want = cuda.sample(logits, temp, top_k, top_p, min_p, rng)
+            print("sample equal", int((out == want).sum()), "of", rows)
+    cuda.check_status()
+    comm.destroy()
 
 
 if __name__ == "__main__":

@@ -12,6 +12,11 @@ def _need(n):
         pytest.skip(f"needs {n} GPUs")
 
 
+def _world_or_skip(world):
+    _need(world)
+    return world
+
+
 def _fused_rank(rank, world, nvls):
     os.environ["XV_TP_NVLS"] = "1" if nvls else "0"
     os.environ["XV_TP_PUSH"] = "1"
@@ -112,11 +117,6 @@ def _fused_rank(rank, world, nvls):
     return max(errs), ids.tolist(), want.tolist(), bool(comm.mc_ptr)
 
 
-def _world_or_skip(world):
-    _need(world)
-    return world
-
-
 @pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("nvls", [False, True])
 def test_fused_reduce_norm_and_argmax(nvls, world):
@@ -126,6 +126,100 @@ def test_fused_reduce_norm_and_argmax(nvls, world):
         assert err < 0.08, err
         assert ids[2] == 100
         assert ids == want or all(a == b for i, (a, b) in enumerate(zip(ids, want)) if i != 2)
+
+
+def _sample_rank(rank, world):
+    """Sharded sampler against the single-GPU sampler on the full logits: same parameters, same random stream."""
+    os.environ["XV_TP_NVLS"] = "0"
+    import torch.distributed as dist
+
+    from xixi_vllm_b200.ops import cuda
+    from xixi_vllm_b200.parallel.groups import get_tp_group
+    from xixi_vllm_b200.parallel.symm import FusedTPComm
+    dev = torch.device("cuda", rank)
+    vocab, padded = 32000, 32768                 # the last shard is partly padding
+    per = padded // world
+    comm = FusedTPComm(get_tp_group(), dev, 1024, 512, torch.bfloat16, logits_rows=400, logits_local_cols=per)
+    assert comm.sample_rows == 400
+    start = rank * per
+    valid = max(0, min(per, vocab - start))
+    mismatches, total, same_on_all = 0, 0, True
+    greedy_ok = True
+    for it, rows in enumerate([300, 1, 37, 400, 5]):
+        g = torch.Generator().manual_seed(4000 + it)
+        full = (torch.randn(rows, padded, generator=g) * 2.5).bfloat16()
+        full[:, vocab:] = 30.0                   # padding columns must never be drawn
+        temp = torch.tensor([0.0, 0.7, 1.0, 1.5])[torch.randint(0, 4, (rows,), generator=g)]
+        top_k = torch.tensor([0, 1, 5, 50, 40000], dtype=torch.int32)[torch.randint(0, 5, (rows,), generator=g)]
+        top_p = torch.tensor([1.0, 0.9, 0.5, 0.1])[torch.randint(0, 4, (rows,), generator=g)]
+        min_p = torch.tensor([0.0, 0.05])[torch.randint(0, 2, (rows,), generator=g)]
+        rng = torch.tensor([1234, 77 + it], dtype=torch.int32)
+        args = [t.to(dev) for t in (temp, top_k, top_p, min_p, rng)]
+        want = cuda.sample(full[:, :vocab].contiguous().to(dev), *args)
+        local = torch.zeros(rows, per + 8, dtype=torch.bfloat16)          # row stride wider than the shard
+        local[:, :per] = full[:, start:start + per]
+        got = comm.sample(local.to(dev)[:, :per], valid, start, vocab, *args)
+        assert got is not None
+        torch.cuda.synchronize()
+        mismatches += int((got != want).sum())
+        total += rows
+        greedy = temp == 0
+        greedy_ok = greedy_ok and torch.equal(got.cpu()[greedy], full[:, :vocab].float().argmax(-1)[greedy])
+        assert int(got.max()) < vocab and int(got.min()) >= 0
+        everyone = [torch.empty_like(got) for _ in range(world)]
+        dist.all_gather(everyone, got)
+        same_on_all = same_on_all and all(torch.equal(e, got) for e in everyone)
+    assert comm.sample(torch.zeros(401, per, dtype=torch.bfloat16, device=dev), valid, start, vocab, *args) is None
+    # captured in a graph: every replay reads the step from memory and draws fresh numbers
+    rows = 64
+    g = torch.Generator().manual_seed(4100)
+    full = (torch.randn(rows, padded, generator=g) * 2.5).bfloat16()
+    shard = full[:, start:start + per].contiguous().to(dev)
+    whole = full[:, :vocab].contiguous().to(dev)
+    temp = torch.full((rows,), 0.9, device=dev)
+    top_k = torch.full((rows,), 20, dtype=torch.int32, device=dev)
+    top_p = torch.full((rows,), 0.8, device=dev)
+    min_p = torch.zeros(rows, device=dev)
+    rng = torch.tensor([99, 0], dtype=torch.int32, device=dev)
+    out = torch.empty(rows, dtype=torch.int64, device=dev)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        out.copy_(comm.sample(shard, valid, start, vocab, temp, top_k, top_p, min_p, rng))
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out.copy_(comm.sample(shard, valid, start, vocab, temp, top_k, top_p, min_p, rng))
+    replay_bad, distinct = 0, set()
+    for step in range(1, 41):
+        rng[1] = step
+        graph.replay()
+        want = cuda.sample(whole, temp, top_k, top_p, min_p, rng)
+        torch.cuda.synchronize()
+        replay_bad += int((out != want).sum())
+        distinct.add(tuple(out.tolist()[:8]))
+    cuda.check_status(dev)
+    dist.barrier()
+    comm.destroy()
+    return mismatches, total, same_on_all, greedy_ok, replay_bad, len(distinct)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_sampler_matches_single_gpu_sampler(world):
+    """Top-k / top-p / min-p sampling over vocabulary shards (histograms and candidates exchanged, logits not
+    gathered) draws the tokens the single-GPU kernel draws from the full row, and the same on every rank."""
+    _world_or_skip(world)
+    from dist_utils import run_ranks_gpu
+    for mismatches, total, same_on_all, greedy_ok, replay_bad, distinct in run_ranks_gpu(_sample_rank, world=world,
+                                                                                         tp=world):
+        assert same_on_all, "ranks drew different tokens"
+        assert greedy_ok
+        # the ranks' partial masses are rounded before they are added: a top-p threshold may move by one key
+        assert mismatches <= max(2, total // 200), (mismatches, total)
+        assert replay_bad <= 8, replay_bad
+        assert distinct >= 35
 
 
 def _push_rank(rank, world, nvls):

@@ -18,8 +18,10 @@
 
 namespace {
 
-int g_failed_op = 0;
-long long g_launch_calls = 0;     // launch calls issued by forwards so far (each is >= 1 kernel)
+// Per calling thread: a process that drives several devices runs one forward per thread, and the step that
+// failed (or the launch count) a thread reads back is the one of its own forwards.
+thread_local int g_failed_op = 0;
+thread_local long long g_launch_calls = 0;     // launch calls issued by this thread's forwards (each is >= 1 kernel)
 
 struct Ctx {
   const XvModelDesc* m;

@@ -162,6 +162,18 @@ int xv_tp_argmax(const void* const* peer_bufs, void* const* peer_flags, void* ep
                  long long slots_offset, const void* logits, long long ld, int local_vocab, int valid_vocab,
                  int vocab_start, long long* out, int rows, unsigned spin_limit, int* status, cudaStream_t stream);
 
+// Sampling over a vocabulary sharded across ranks without gathering the logits (sampler.cu): `logits` is this
+// rank's [rows, >= valid_vocab] shard holding tokens vocab_start .. vocab_start + valid_vocab of total_vocab. The
+// ranks exchange per-row maxima, 256-bin histograms and their best candidate through a zero-initialised region of
+// xv_tp_sample_region_bytes(max_rows, world) bytes at `region_offset` of every rank's symmetric buffer; `epoch`
+// words 24 and 25 count the launches. All ranks write the same tokens to `out`.
+long long xv_tp_sample_region_bytes(int max_rows, int world);
+int xv_tp_sample(const void* const* peer_bufs, void* const* peer_flags, void* epoch, int rank, int world,
+                 long long region_offset, int max_rows, const void* logits, long long ld, int valid_vocab,
+                 int vocab_start, int total_vocab, long long* out, int rows, const float* temperature,
+                 const int* top_k, const float* top_p, const float* min_p, const int* rng, unsigned spin_us,
+                 int* status, cudaStream_t stream);
+
 int xv_tp_allgather_cols(const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf, void* epoch,
                          int rank, int world, const void* src, long long ld, int local_cols, long long total_cols,
                          int rows, unsigned spin_limit, int* status, cudaStream_t stream);
@@ -273,6 +285,7 @@ typedef struct XvArena {              // device scratch sized for the largest st
 
 // Returns 0 or the first failing launch's XV_ERR_* code (xv_forward_failed_op() names the step).
 int xv_qwen3_forward(const XvModelDesc* model, const XvBatchDesc* batch, const XvArena* arena, cudaStream_t stream);
+// Both are kept per calling thread: they describe the forwards that this thread issued.
 int xv_forward_failed_op(void);
 long long xv_forward_launch_calls(void);   // launch calls issued by forwards so far (each is at least one kernel)
 int xv_forward_decode_splits(int num_seqs, int hkv, int num_sms, int max_tokens_per_seq);

@@ -91,6 +91,10 @@ def lib():
                                ctypes.c_uint, _vp, _vp]
     L.xv_gemm_bf16_tp.argtypes = [_vp, _vp, _i32, _i32, _i32, _i64, _i64, _vp, _i64, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i64,
                                   _i64, _i32, _i64, _vp, _vp, _vp, _vp, _f32, _i32, _i32, ctypes.c_uint, _vp, _vp]
+    L.xv_tp_sample_region_bytes.argtypes = [_i32, _i32]
+    L.xv_tp_sample_region_bytes.restype = _i64
+    L.xv_tp_sample.argtypes = [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _vp, _i32, _vp, _vp,
+                               _vp, _vp, _vp, ctypes.c_uint, _vp, _vp]
     L.xv_gemm_plan_override.argtypes = [_i32, _i32, _i32, _i32]
     L.xv_gemm_plan_override.restype = None
     L.xv_selftest_bounded_wait.argtypes = [_vp, _vp, ctypes.c_uint, _vp]
@@ -461,6 +465,30 @@ def tp_argmax(peer_bufs, peer_flags, epoch, rank: int, world: int, slots_offset:
     _check(lib().xv_tp_argmax(peer_bufs, peer_flags, epoch.data_ptr(), rank, world, slots_offset, logits.data_ptr(),
                               logits.stride(0), local_vocab, valid_vocab, vocab_start, out.data_ptr(),
                               logits.shape[0], spin_limit, status.data_ptr(), _stream()), "tp_argmax")
+
+
+def tp_sample_region_bytes(max_rows: int, world: int) -> int:
+    return int(lib().xv_tp_sample_region_bytes(max_rows, world))
+
+
+def tp_sample(peer_bufs, peer_flags, epoch, rank: int, world: int, region_offset: int, max_rows: int, logits,
+              valid_vocab: int, vocab_start: int, total_vocab: int, temperature, top_k, top_p, min_p, rng,
+              spin_limit: int, status):
+    """Temperature / top-k / top-p / min-p sampling over vocabulary shards without gathering them
+    (``xv_tp_sample``): the ranks exchange row maxima, selection histograms and their best candidates."""
+    _bf16(logits)
+    if logits.stride(1) != 1:
+        raise ValueError("tp_sample needs unit column stride")
+    rows = logits.shape[0]
+    if rng is None:
+        rng = torch.zeros(2, dtype=torch.int32, device=logits.device)
+    out = torch.empty(rows, dtype=torch.int64, device=logits.device)
+    _check(lib().xv_tp_sample(peer_bufs, peer_flags, epoch.data_ptr(), rank, world, region_offset,
+                              max_rows, logits.data_ptr(), logits.stride(0), valid_vocab,
+                              vocab_start, total_vocab, out.data_ptr(), rows, temperature.data_ptr(),
+                              top_k.data_ptr(), top_p.data_ptr(), min_p.data_ptr(), rng.data_ptr(), spin_limit,
+                              status.data_ptr(), _stream()), "tp_sample")
+    return out
 
 
 def tp_allgather_cols(peer_bufs, peer_flags, mc_ptr: int, epoch, rank: int, world: int, src, total_cols: int,

@@ -85,7 +85,11 @@ class FusedTPComm(TPComm):
         self._logit_rows, self._logit_cols = logits_rows, logits_local_cols * group.size
         logit_bytes = -(-logits_rows * self._logit_cols * 2 // 4096) * 4096
         self.logits_off = 4 * self.buf_bytes + self.slot_bytes + FLAG_BYTES
-        total = self.logits_off + logit_bytes
+        # exchange region of the sharded sampler (row maxima, selection histograms, candidates): XV_TP_SAMPLE=0
+        # samples from the gathered logits instead
+        self.sample_rows = logits_rows if os.environ.get("XV_TP_SAMPLE", "1") != "0" else 0
+        self.sample_off = self.logits_off + logit_bytes
+        total = self.sample_off + (cuda.tp_sample_region_bytes(self.sample_rows, group.size) if self.sample_rows else 0)
         self.symm = SymmetricBuffer(total, group, self.device)
         self.rank, self.world = self.symm.rank, self.symm.world
         self.h_off = 3 * self.buf_bytes              # activation buffer the row-sharded reductions broadcast into
@@ -241,6 +245,16 @@ class FusedTPComm(TPComm):
         cuda.tp_argmax(self._bufs, self._flags, self.epoch, self.rank, self.world, self.slots_off, local_logits,
                        local_logits.shape[1], valid_vocab, vocab_start, out, SPIN_LIMIT, self.status)
         return out
+
+    def sample(self, local_logits: torch.Tensor, valid_vocab: int, vocab_start: int, total_vocab: int,
+               temperature, top_k, top_p, min_p, rng) -> torch.Tensor | None:
+        """Tokens drawn from the vocabulary-sharded logits without gathering them, the same on every rank; None
+        when no exchange region was reserved for this many rows (the caller gathers the logits instead)."""
+        if local_logits.shape[0] > self.sample_rows:
+            return None
+        return cuda.tp_sample(self._bufs, self._flags, self.epoch, self.rank, self.world, self.sample_off,
+                              self.sample_rows, local_logits, valid_vocab, vocab_start, total_vocab, temperature,
+                              top_k, top_p, min_p, rng, SPIN_LIMIT, self.status)
 
     # --- full logits for sampled requests ------------------------------------------------------
     def gather_logits(self, local_logits: torch.Tensor) -> torch.Tensor | None:

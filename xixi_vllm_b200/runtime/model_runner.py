@@ -85,17 +85,7 @@ class ModelRunner:
                 return IntermediateTensors(hidden_states=out[0], residual=out[1])
             if batch.all_greedy:
                 return out
-            logits = out
-            head = self.model.lm_head
-            if head.tp.size > 1:
-                gathered = self._gather_logits(logits)
-                if gathered is None:
-                    from ..parallel import collectives as coll
-
-                    gathered = coll.all_gather(logits, head.tp, dim=-1)
-                logits = gathered
-            logits = logits[..., : head.num_embeddings]
-            return self.sampler(logits, batch.temperature, batch.top_k, batch.top_p, batch.min_p, rng=batch.rng)
+            return self._sample_local(out, batch)
         out = self.model.forward(batch.input_ids, batch, self.kv, intermediate)
         if not self.is_last_pp:
             return out
@@ -104,7 +94,32 @@ class ModelRunner:
         hidden = ops.gather_rows(out, batch.sample_rows)
         if batch.all_greedy:
             return self.model.greedy_tokens(hidden)
+        head = self.model.lm_head
+        if getattr(head, "tp", None) is not None and head.tp.size > 1 and hasattr(self.model.comm, "sample"):
+            return self._sample_local(head.local_logits(hidden), batch)
         logits = self.model.compute_logits(hidden)
+        return self.sampler(logits, batch.temperature, batch.top_k, batch.top_p, batch.min_p, rng=batch.rng)
+
+    def _sample_local(self, logits, batch):
+        """Draws from this rank's logits: under tensor parallelism they are a vocabulary shard, sampled across the
+        ranks without gathering it (or gathered first when the communicator has no exchange region for it)."""
+        head = self.model.lm_head
+        if head.tp.size > 1:
+            comm = self.model.comm
+            if hasattr(comm, "sample"):
+                valid = max(0, min(head.per_rank, head.num_embeddings - head.vocab_start))
+                tokens = comm.sample(logits, valid, head.vocab_start, head.num_embeddings, batch.temperature,
+                                     batch.top_k, batch.top_p, batch.min_p, batch.rng)
+                if tokens is not None:
+                    self.sampler.step += 1
+                    return tokens
+            gathered = self._gather_logits(logits)
+            if gathered is None:
+                from ..parallel import collectives as coll
+
+                gathered = coll.all_gather(logits, head.tp, dim=-1)
+            logits = gathered
+        logits = logits[..., : head.num_embeddings]
         return self.sampler(logits, batch.temperature, batch.top_k, batch.top_p, batch.min_p, rng=batch.rng)
 
     def _gather_logits(self, local_logits):

@@ -174,6 +174,12 @@ def baseline_number(model: str = "Qwen3-8B", n_gpus: int = 1, mode: str = "stead
         return None
 
 
+def _known(sq) -> int:
+    """Completion tokens whose value the host has (the reference's sequences have no tokens in flight)."""
+    v = getattr(sq, "num_known_completion_tokens", None)
+    return sq.num_completion_tokens if v is None else v
+
+
 def run_to_completion(engine, make_sp, wl, n_requests: int, sync) -> dict:
     """``n_requests`` requests of the workload submitted at once and stepped until all are done, through the
     engine's public API (works for both arms). Output tokens per second of wall time, time to first token and
@@ -194,16 +200,16 @@ def run_to_completion(engine, make_sp, wl, n_requests: int, sync) -> dict:
         now = time.perf_counter()
         for i in list(pending):
             sq = seqs[i]
-            if first[i] is None and sq.num_completion_tokens > 0:
+            if first[i] is None and _known(sq) > 0:
                 first[i] = now
             if sq.is_finished:
                 done[i] = now
                 pending.discard(i)
     sync()
     wall = time.perf_counter() - t0
-    out_tokens = sum(sq.num_completion_tokens for sq in seqs)
+    out_tokens = sum(_known(sq) for sq in seqs)
     ttft = sorted((f - t0) * 1e3 for f in first if f is not None)
-    tpot = sorted((d - f) * 1e3 / max(1, sq.num_completion_tokens - 1)
+    tpot = sorted((d - f) * 1e3 / max(1, _known(sq) - 1)
                   for f, d, sq in zip(first, done, seqs) if f is not None and d is not None)
 
     def pct(v, q):
@@ -222,7 +228,7 @@ def run_decode_only(engine, make_sp, vocab: int, batch: int, context: int, steps
     rng = np.random.default_rng(seed)
     seqs = [engine.add_request(rng.integers(0, vocab, size=context).tolist(), make_sp(steps + warmup + 8))
             for _ in range(batch)]
-    while any(sq.num_completion_tokens == 0 for sq in seqs):
+    while any(_known(sq) == 0 for sq in seqs):
         engine.step()
     for _ in range(warmup):
         engine.step()
@@ -378,7 +384,9 @@ def run_ours(args) -> None:
         torch.cuda.profiler.stop()
     clk = clocks.stop()
     launches = cuda.launch_count + (runner.graphs.replayed_kernels if runner.graphs else 0) - launches0
-    dev_ms = core.executor.device_time_ms(first_step, sched._step + 1)
+    # one-step-late scheduling: the timed calls read the steps launched one call earlier
+    lag = 1 if getattr(core, "_inflight", None) is not None else 0
+    dev_ms = core.executor.device_time_ms(first_step - lag, sched._step + 1 - lag)
     e2e_wall = sum(step_ms) / 1e3            # Engine.step() wall time only (excludes the L2 flush)
     cuda.check_status(device)
 
@@ -398,6 +406,7 @@ def run_ours(args) -> None:
                    "kv_block_size": 16, "decode_cuda_graph": not args.eager, "tp_comm": args.tp_comm, **comm_ran,
                    **({"emulate_tp_shard": args.emulate_tp} if args.emulate_tp > 1 else {}),
                    "l2": "flushed between timed steps (256 MiB write)",
+                   "async_scheduling": bool(getattr(core, "one_step_late", False)),
                    "step": "one engine step in steady-state continuous batching"},
         "clocks": clk,
         "e2e": {"value": out_tokens / e2e_wall, "unit": "tokens/s", "h2d_bytes_per_step": h2d / args.steps,

@@ -48,7 +48,7 @@ def _timed_run(engine: Engine, seqs) -> tuple[float | None, float, float | None]
     t_first = None
     while any(not s.is_finished for s in seqs):
         engine.step()
-        if t_first is None and any(s.num_completion_tokens > 0 for s in seqs):
+        if t_first is None and any(s.num_known_completion_tokens > 0 for s in seqs):
             cuda_sync()
             t_first = time.perf_counter()
     cuda_sync()

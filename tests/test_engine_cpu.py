@@ -96,6 +96,36 @@ def test_preemption_under_kv_pressure_keeps_outputs(tiny_model_dir):
     assert tight == base
 
 
+def test_one_step_late_scheduling_keeps_tokens(tiny_model_dir):
+    """Launching step n + 1 before step n's samples are read (input tokens fetched from the previous step's
+    sample buffer, EOS found one step late, preemption with a token in flight) changes no output."""
+    prompts = _prompts(5, 24, seed=11)
+    base = _generate(tiny_model_dir, prompts, max_tokens=20, async_scheduling="off")
+    assert _generate(tiny_model_dir, prompts, max_tokens=20, async_scheduling="on") == base
+    assert _generate(tiny_model_dir, prompts, max_tokens=20, async_scheduling="on", num_kvcache_blocks=9,
+                     prefix_backend="none") == base                                   # preemption
+    assert _generate(tiny_model_dir, prompts, max_tokens=20, async_scheduling="on", prefix_backend="radix",
+                     max_num_batched_tokens=24) == base                               # chunked prefill + prefix cache
+    assert _generate(tiny_model_dir, prompts, max_tokens=20, async_scheduling="on", tp_size=2,
+                     nccl_port=29721) == base
+    # EOS stops a request although its next step has already been launched
+    eng = Engine(EngineConfig(model=tiny_model_dir, device="cpu", dtype="float32", num_kvcache_blocks=128,
+                              max_num_seqs=8, max_num_batched_tokens=64, context_len=256, async_scheduling="on"))
+    try:
+        eos_like = base[0][3]
+        core = eng._client.engine_core
+        assert core.one_step_late
+        core.scheduler.eos = eos_like
+        seqs = [eng.add_request(p, SamplingParams(max_tokens=20)) for p in prompts]
+        while eng.has_unfinished():
+            eng.step()
+        for s, b in zip(seqs, base):
+            want = b[: b.index(eos_like) + 1] if eos_like in b else b
+            assert s.token_ids[s.num_prompt_tokens:] == want and s.num_pending == 0
+    finally:
+        eng.destroy()
+
+
 def test_tp2_equals_tp1(tiny_model_dir):
     """Benchmark config 1: tiny fp32 Qwen3, gloo world of 2, 4 prompts x 16 ids, greedy 8 tokens."""
     prompts = _prompts()

@@ -38,6 +38,14 @@ def expected_completion(prompt, max_tokens, ignore_eos):
     return out
 
 
+def _check_budgets(batch, max_seqs, budget):
+    assert len(batch.prefills) + len(batch.decodes) <= max_seqs
+    assert sum(s.num_scheduled_tokens for s in batch.prefills) + len(batch.decodes) <= budget
+    assert sum(1 for s in batch.prefills if not s.need_sample) <= 1       # one partial chunk per step
+    for s in batch.prefills + batch.decodes:
+        assert len(s.block_table) >= -(-(s.num_cached_tokens + s.num_scheduled_tokens) // BS)
+
+
 request = st.tuples(st.integers(1, 70),          # prompt length
                     st.integers(0, 3),           # which shared prefix (0 = none)
                     st.integers(0, 12),          # max_tokens
@@ -71,12 +79,7 @@ def test_any_schedule_yields_the_models_tokens(reqs, num_blocks, max_seqs, budge
             if todo:
                 sch.add(todo.pop(0)[0])
         batch = sch.schedule()
-        # per-step budgets
-        assert len(batch.prefills) + len(batch.decodes) <= max_seqs
-        assert sum(s.num_scheduled_tokens for s in batch.prefills) + len(batch.decodes) <= budget
-        assert sum(1 for s in batch.prefills if not s.need_sample) <= 1       # one partial chunk per step
-        for s in batch.prefills + batch.decodes:
-            assert len(s.block_table) >= -(-(s.num_cached_tokens + s.num_scheduled_tokens) // BS)
+        _check_budgets(batch, max_seqs, budget)
         batch.to_wire()
         p_ids = [fake_model(s.token_ids) for s in batch.prefills]
         d_ids = [fake_model(s.token_ids) for s in batch.decodes]
@@ -87,6 +90,79 @@ def test_any_schedule_yields_the_models_tokens(reqs, num_blocks, max_seqs, budge
         assert steps < 5000, "the workload does not terminate"
     for seq, prompt, max_tokens, ignore_eos in pending:
         assert seq.is_finished
+        assert seq.token_ids[len(prompt):] == expected_completion(prompt, max_tokens, ignore_eos)
+    assert kv.blocks.num_used == 0
+
+
+@settings(max_examples=150, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow])
+@given(reqs=st.lists(request, min_size=1, max_size=10),
+       num_blocks=st.integers(6, 40), max_seqs=st.integers(1, 6), budget=st.integers(8, 96),
+       mix=st.booleans(), backend=st.sampled_from(["none", "hash", "radix"]), seed=st.integers(0, 1000),
+       arrivals=st.integers(1, 4))
+def test_one_step_late_schedule_yields_the_models_tokens(reqs, num_blocks, max_seqs, budget, mix, backend, seed,
+                                                         arrivals):
+    """The same property when step n + 1 is scheduled and launched before step n's tokens are known
+    (``advance`` / ``resolve``): the "device" keeps the true history and feeds a row whose input token the host
+    does not know yet from the previous step's samples, as the workers do."""
+    rnd = random.Random(seed)
+    prefixes = [[], [7] * 32, list(range(100, 148)), [9, 8] * 20]
+    kv = KVManager(num_blocks=num_blocks, block_size=BS, prefix_backend=backend)
+    sch = Scheduler(kv, max_num_seqs=max_seqs, max_num_batched_tokens=budget, eos_token_id=EOS,
+                    mix_prefill_decode=mix)
+    pending = []
+    for n, which, max_tokens, ignore_eos in reqs:
+        prompt = (prefixes[which] + [rnd.randrange(3, 60) for _ in range(n)])
+        if -(-(len(prompt) + max_tokens) // BS) > num_blocks:
+            prompt = prompt[: max(1, num_blocks * BS - max_tokens - 1)]
+        seq = Sequence.from_prompt(prompt, block_size=BS,
+                                   sampling=SamplingParams(max_tokens=max_tokens, ignore_eos=ignore_eos))
+        pending.append((seq, list(prompt), max_tokens, ignore_eos))
+    todo = list(pending)
+    steps = 0
+    inflight = None            # (batch, prefill samples, decode samples) of the launched step
+    prev_samples: list[int] = []
+    while todo or not sch.is_finished() or inflight is not None:
+        for _ in range(arrivals):
+            if todo:
+                sch.add(todo.pop(0)[0])
+        batch = sch.schedule()
+        launched = None
+        if not batch.is_empty():
+            _check_budgets(batch, max_seqs, budget)
+            wire = batch.to_wire()
+            # the device: resolve references into the previous step's samples, then run the model on the
+            # true history (host history up to the pending tokens + the referenced sample)
+            d_ids, p_ids, samples = [], [], []
+            for s, tok in zip(batch.decodes, wire.decodes.tokens):
+                hist = list(s.token_ids)
+                if tok < 0:
+                    assert s.num_pending == 1 and hist[-1] == -1
+                    hist[-1] = prev_samples[-tok - 1]
+                else:
+                    assert s.num_pending == 0 and hist[-1] == tok
+                t = fake_model(hist)
+                d_ids.append(t)
+                samples.append(t)
+            for s in batch.prefills:
+                assert s.num_pending == 0 and -1 not in s.token_ids
+                t = fake_model(s.token_ids)
+                p_ids.append(t)
+                if s.need_sample:
+                    samples.append(t)
+            sch.advance(batch)
+            launched = (batch, p_ids, d_ids)
+            this_samples = samples
+        if inflight is not None:
+            sch.resolve(*inflight)
+        if launched is not None:
+            prev_samples = this_samples
+        inflight = launched
+        kv.blocks.check_invariants()
+        assert sch._holders == sum(1 for w in sch.waiting if w.block_table)
+        steps += 1
+        assert steps < 5000, "the workload does not terminate"
+    for seq, prompt, max_tokens, ignore_eos in pending:
+        assert seq.is_finished and seq.num_pending == 0
         assert seq.token_ids[len(prompt):] == expected_completion(prompt, max_tokens, ignore_eos)
     assert kv.blocks.num_used == 0
 

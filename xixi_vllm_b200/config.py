@@ -140,8 +140,20 @@ class EngineConfig:
     tp_comm: str = "auto"            # "auto" | "fused" | "nccl": tensor-parallel reduction path
     dp_ready_timeout_s: float = 0.0  # 0 = scale with model size
     pp_microbatches: int = 1         # pipeline stages work on this many pieces of a step in turn (1 = lockstep)
+    # "on": step n + 1 is scheduled, staged and launched before step n's samples are read (the host's work
+    # overlaps the GPU's; outputs arrive one step() call later). "auto": on for CUDA without pipeline stages.
+    async_scheduling: str = "auto"
 
     hf_config: ModelConfig = field(init=False, repr=False)
+
+    @property
+    def one_step_late(self) -> bool:
+        env = os.environ.get("XV_ASYNC_SCHEDULING", "")
+        if env in ("0", "1") and self.pp_size == 1:
+            return env == "1"
+        if self.async_scheduling == "auto":
+            return self.device == "cuda" and self.pp_size == 1
+        return self.async_scheduling == "on"
 
     def __post_init__(self) -> None:
         self.model = os.path.expanduser(self.model)
@@ -165,6 +177,11 @@ class EngineConfig:
             raise ValueError(f"tp_comm must be auto|fused|nccl, got {self.tp_comm!r}")
         if self.pp_microbatches < 1:
             raise ValueError("pp_microbatches must be >= 1")
+        if self.async_scheduling not in ("auto", "on", "off"):
+            raise ValueError(f"async_scheduling must be auto|on|off, got {self.async_scheduling!r}")
+        if self.async_scheduling == "on" and self.pp_size > 1:
+            raise ValueError("async_scheduling=on needs pp_size == 1: the first pipeline stage gets its input "
+                             "tokens from the host")
         self.hf_config = load_model_config(self.model)
         if self.pp_layer_counts is not None:
             if len(self.pp_layer_counts) != self.pp_size:

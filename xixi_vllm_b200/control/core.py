@@ -1,4 +1,9 @@
-"""One engine step: schedule, execute, read samples, update (reference: src/control/core.py:25-156)."""
+"""One engine step: schedule, execute, read samples, update (reference: src/control/core.py:25-156).
+
+With ``config.one_step_late`` the order inside ``step()`` becomes: schedule and launch step n + 1, THEN read
+step n's samples and apply them, so the host's scheduling, staging, launch, bookkeeping and whatever the
+caller does between two ``step()`` calls run while the GPU is busy. ``step()`` then returns the outputs of the
+step launched by the previous call."""
 
 from __future__ import annotations
 
@@ -29,6 +34,8 @@ class EngineCore:
         self.executor = executor
         self.metrics = EngineMetrics()
         self._idle_steps = 0
+        self.one_step_late = bool(getattr(config, "one_step_late", False))
+        self._inflight = None           # (batch, n_prefill, n_decode, prefill tokens, t_schedule, t_launch)
         self._init_kv()
 
     def _build_scheduler(self) -> Scheduler:
@@ -46,6 +53,8 @@ class EngineCore:
         self.last_num_cached_tokens = 0
 
     def reset_kv(self, prefix_backend: str | None = None) -> None:
+        while self._inflight is not None:       # read the step in flight before its pages go away
+            self.step()
         self.kv = self.executor.reset_kv(prefix_backend)
         sampled = self.scheduler.num_sampled
         self.scheduler = self._build_scheduler()
@@ -59,10 +68,12 @@ class EngineCore:
         self.scheduler.add(seq)
 
     def has_unfinished(self) -> bool:
-        return not self.scheduler.is_finished()
+        return self._inflight is not None or not self.scheduler.is_finished()
 
     def step(self) -> tuple[list[EngineCoreOutput], int]:
         """Returns (per-sequence increments, tokens processed this step)."""
+        if self.one_step_late:
+            return self._step_late()
         t0 = time.perf_counter()
         sched = self.scheduler.schedule()
         if sched.is_empty():
@@ -103,6 +114,55 @@ class EngineCore:
             sampled_total=self.scheduler.num_sampled, finished_lookup=lookup,
         )
         return outputs, metric
+
+    def _step_late(self) -> tuple[list[EngineCoreOutput], int]:
+        """Launch the next step, then read and apply the one launched by the previous call."""
+        t0 = time.perf_counter()
+        prev = self._inflight
+        sched = self.scheduler.schedule()
+        launched = None
+        if sched.is_empty():
+            if sched.released:
+                self.scheduler._released[:0] = sched.released
+            if prev is None and not self.scheduler.is_finished():
+                self._idle_steps += 1
+                if self._idle_steps >= self._MAX_IDLE_STEPS:
+                    raise RuntimeError(
+                        "scheduler returned empty for too long while requests remain "
+                        f"(idle_steps={self._idle_steps}). Likely KV pool exhaustion "
+                        f"(free_blocks={self.kv.num_free})."
+                    )
+        else:
+            self._idle_steps = 0
+            t1 = time.perf_counter()
+            n_p, n_d = self.executor.run(sched)
+            self.last_num_cached_tokens = self.kv.last_num_cached_tokens
+            prefill_tokens = sum(s.num_scheduled_tokens for s in sched.prefills)
+            self.scheduler.advance(sched)
+            launched = (sched, n_p, n_d, prefill_tokens, t1 - t0, time.perf_counter())
+        self._inflight = launched
+        if prev is None:
+            return [], 0
+        p_sched, n_p, n_d, prefill_tokens, schedule_s, t_launch = prev
+        p_ids, d_ids = self.executor.read_samples(n_p, n_d)
+        t2 = time.perf_counter()
+        outputs = self.scheduler.resolve(p_sched, p_ids, d_ids)
+        t3 = time.perf_counter()
+        by_id = None
+
+        def lookup(seq_id):
+            nonlocal by_id
+            if by_id is None:
+                by_id = {s.seq_id: s for s in p_sched.decodes}
+                by_id.update((s.seq_id, s) for s in p_sched.prefills)
+            return by_id.get(seq_id)
+
+        self.metrics.on_step(
+            p_sched, outputs, prefill_tokens, schedule_s=schedule_s, execute_s=t2 - t_launch, update_s=t3 - t2,
+            kv_usage=self.kv.usage(), preemptions=self.scheduler.num_preemptions, kv=self.kv, now=t3,
+            sampled_total=self.scheduler.num_sampled, finished_lookup=lookup,
+        )
+        return outputs, prefill_tokens + len(p_sched.decodes)
 
     def destroy(self) -> None:
         self.executor.destroy()

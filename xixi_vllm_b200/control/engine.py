@@ -148,7 +148,7 @@ class Engine:
         sent = 0
         while not seq.is_finished:
             self.step()
-            while sent < seq.num_completion_tokens:
+            while sent < seq.num_known_completion_tokens:     # tokens still in flight on the device are not shown
                 yield self.tokenizer.decode([seq.token_ids[seq.num_prompt_tokens + sent]])
                 sent += 1
 

@@ -13,6 +13,17 @@ Policy kept from the reference:
   and recomputed later;
 * a sequence ends on EOS (unless ``ignore_eos``) or at ``max_tokens``; ``max_tokens <= 0``
   ends right after prefill.
+
+One-step-late mode (``advance`` / ``resolve`` instead of ``update``): the engine core launches step n + 1
+before it has read step n's samples, so that the host's scheduling, staging and bookkeeping overlap the
+GPU's work. ``advance(batch)`` accounts for a launched step at once: KV lengths grow, every sampling row
+gets a ``PENDING_TOKEN`` at the end of its ``token_ids`` (and a negative ``last_token`` that names its row
+in the step's sample buffer, from which the workers fetch the next input token on the device), sequences
+that reach ``max_tokens`` with that token leave ``running``. ``resolve(batch, ...)`` fills the tokens in
+when they have been read, publishes the pages the step filled and ends sequences. A sequence that turns
+out to have sampled EOS in step n has already been scheduled into step n + 1; that row's sample is
+dropped. A preempted sequence with a pending token waits until it is resolved before it is recomputed.
+(The reference schedules, runs and updates strictly in turn: src/control/core.py:74-134.)
 """
 
 from __future__ import annotations
@@ -20,6 +31,7 @@ from __future__ import annotations
 from collections import deque
 
 from ..data import EngineCoreOutput, KVManager, ScheduledBatch, Sequence, SequenceStatus
+from ..data.sequence import PENDING_TOKEN
 
 __all__ = ["Scheduler"]
 
@@ -120,6 +132,8 @@ class Scheduler:
             budget = self.max_num_batched_tokens - used
             if budget <= 0:
                 break
+            if seq.num_pending:
+                continue        # preempted with a token still unread: recomputed once the token is known
             if not seq.block_table:
                 # First come, first served: once a prompt does not fit, no later prompt may take pages ahead
                 # of it. A prompt further back that already holds its pages (it was cut into chunks and a
@@ -242,3 +256,103 @@ class Scheduler:
                 out.append(EngineCoreOutput(seq_id=seq.seq_id, new_token_ids=[tok], is_finished=True))
             else:
                 out.append(EngineCoreOutput(seq_id=seq.seq_id, new_token_ids=[tok]))
+
+    # ------------------------------------------------------------------ one-step-late mode
+    def advance(self, sched: ScheduledBatch) -> None:
+        """Accounts for a step that has been launched but not read (see the module docstring)."""
+        leaving = False
+        marks_d, marks_p = sched.marks_d, sched.marks_p
+        for i, seq in enumerate(sched.decodes):
+            before = seq.num_cached_tokens
+            after = before + seq.num_scheduled_tokens
+            seq.num_cached_tokens = after
+            seq.num_scheduled_tokens = 0
+            ids = seq.token_ids
+            marks_d.append((len(ids), before, after))
+            ids.append(PENDING_TOKEN)
+            seq.num_pending += 1
+            seq.last_token = -(i + 1)
+            if len(ids) - seq.num_prompt_tokens >= seq.max_tokens:
+                seq.finishing = leaving = True
+        k = len(sched.decodes)
+        for seq in sched.prefills:
+            before = seq.num_cached_tokens
+            after = before + seq.num_scheduled_tokens
+            seq.num_cached_tokens = after
+            seq.num_scheduled_tokens = 0
+            ids = seq.token_ids
+            if after < len(ids):
+                marks_p.append((-1, before, after))      # mid-prompt chunk (or recomputation not at its end yet)
+                continue
+            if seq.max_tokens <= 0:
+                marks_p.append((-2, before, after))      # ends right after its prompt; its sample is not used
+                seq.finishing = leaving = True
+                k += 1
+                continue
+            marks_p.append((len(ids), before, after))
+            ids.append(PENDING_TOKEN)
+            seq.num_pending += 1
+            seq.last_token = -(k + 1)
+            k += 1
+            if len(ids) - seq.num_prompt_tokens >= seq.max_tokens:
+                seq.finishing = leaving = True
+        if leaving:
+            self.running = deque(s for s in self.running if not s.finishing)
+
+    def resolve(self, sched: ScheduledBatch, p_ids: list[int], d_ids: list[int]) -> list[EngineCoreOutput]:
+        """Fills in the tokens of a step that ``advance`` accounted for. Returns the per-sequence increments."""
+        out: list[EngineCoreOutput] = []
+        done: set[int] = set()
+        for seq, tok, mark in zip(sched.decodes, d_ids, sched.marks_d):
+            self._resolve_one(seq, tok, mark, out, done)
+        for seq, tok, mark in zip(sched.prefills, p_ids, sched.marks_p):
+            pos, before, after = mark
+            if seq.status is SequenceStatus.FINISHED:
+                continue
+            if pos == -1:
+                self.kv.publish_range(seq, before, after)
+                out.append(EngineCoreOutput(seq_id=seq.seq_id))
+            elif pos == -2:
+                self.kv.publish_range(seq, before, after)
+                self._finish_late(seq, done)
+                out.append(EngineCoreOutput(seq_id=seq.seq_id, is_finished=True))
+            else:
+                self._resolve_one(seq, tok, mark, out, done)
+        if done:
+            self.running = deque(s for s in self.running if s.seq_id not in done)
+            self._released.extend(done)
+        return out
+
+    def _resolve_one(self, seq: Sequence, tok, mark, out, done: set[int]) -> None:
+        if seq.status is SequenceStatus.FINISHED:
+            return            # it ended at an earlier step whose EOS was read after this row had been launched
+        pos, before, after = mark
+        self.kv.publish_range(seq, before, after)
+        tok = int(tok)
+        ids = seq.token_ids
+        ids[pos] = tok
+        seq.num_pending -= 1
+        if seq.num_pending == 0:
+            seq.last_token = tok
+        self.num_sampled += 1
+        hit_eos = tok == self.eos and not seq.ignore_eos
+        if hit_eos or (seq.finishing and seq.num_pending == 0):
+            if len(ids) > pos + 1:
+                # EOS with a later step already accounted for: that step's token will not be used
+                del ids[pos + 1:]
+                seq.num_pending = 0
+                seq.last_token = tok
+                seq.num_cached_tokens = min(seq.num_cached_tokens, len(ids))
+            self._finish_late(seq, done)
+            out.append(EngineCoreOutput(seq_id=seq.seq_id, new_token_ids=[tok], is_finished=True))
+        else:
+            out.append(EngineCoreOutput(seq_id=seq.seq_id, new_token_ids=[tok]))
+
+    def _finish_late(self, seq: Sequence, done: set[int]) -> None:
+        if seq.status is SequenceStatus.WAITING:      # preempted after the step was launched
+            self.waiting.remove(seq)
+            if seq.block_table:
+                self._holders -= 1
+        seq.finishing = False
+        self._finish(seq, done)
+

@@ -229,6 +229,21 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const in
     *reinterpret_cast<uint4*>(y + i * hidden + v * 8) = *reinterpret_cast<const uint4*>(x + src * hidden + v * 8);
 }
 
+// One-step-late scheduling: an input id < 0 names row -(id) - 1 of the previous step's sample buffer (the host
+// launched this step before it had read those samples). A reference beyond that buffer becomes token 0.
+__global__ void resolve_token_refs_kernel(int* __restrict__ ids, int n, const long long* __restrict__ prev,
+                                          int n_prev) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int id = ids[i];
+  if (id < 0) {
+    const int j = -id - 1;
+    ids[i] = j < n_prev ? static_cast<int>(prev[j]) : 0;
+  }
+}
+
 // One warp per (token, head). Lane l holds elements [2l, 2l+1] of the first half and the same
 // of the second half (D = 128: 2 + 2 values; D = 64: lanes 0..15 active per half... handled by
 // the generic loop). The NeoX rotation pairs element i with i + D/2, both held by one lane.
@@ -434,6 +449,12 @@ int xv_gather_rows(const void* x, const int* rows, void* y, int n, int hidden, c
   if (hidden % 8) return XV_ERR_SHAPE;
   launch_pdl(gather_rows_kernel, dim3(n), dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(x), rows,
                                             static_cast<__nv_bfloat16*>(y), hidden);
+  return launch_ok();
+}
+
+int xv_resolve_token_refs(int* ids, int n, const long long* prev, int n_prev, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  launch_pdl(resolve_token_refs_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, ids, n, prev, n_prev);
   return launch_ok();
 }
 

@@ -143,6 +143,9 @@ int xv_attn_prefill_tc_profile(const void* q, const void* k_cache, const void* v
                                int max_blocks, float scale, int* status, unsigned long long* prof,
                                cudaStream_t stream);
 
+// Input ids < 0 are references into the previous step's samples: ids[i] = prev[-ids[i] - 1] (elementwise.cu).
+int xv_resolve_token_refs(int* ids, int n, const long long* prev, int n_prev, cudaStream_t stream);
+
 // ---- sampling ----
 int xv_argmax(const void* logits, long long* out, int rows, int vocab, long long ld, cudaStream_t stream);
 // rng: device int32[2] = {seed, step}. Rows with temperature <= 1e-5 are greedy.

@@ -96,6 +96,17 @@ class KVManager:
         if first < last:
             self.index.publish(seq, last, self.blocks, start=first)
 
+    def publish_range(self, seq: Sequence, before: int, after: int) -> None:
+        """Publish the pages that a step filled which took the sequence's KV length from ``before`` to
+        ``after`` (one-step-late scheduling: ``num_cached_tokens`` may already count the next step). A
+        sequence that lost its pages since (preempted) publishes nothing."""
+        if self.prefix_backend == "none" or after <= before or not seq.block_table:
+            return
+        first = before // self.block_size
+        last = min(after // self.block_size, len(seq.block_table))
+        if first < last:
+            self.index.publish(seq, last, self.blocks, start=first)
+
     def deallocate(self, seq: Sequence, *, publish: bool = True) -> None:
         # Only pages whose KV was really written may be published: a preempted or
         # just-finished sequence has its newest token's KV still missing.

@@ -14,7 +14,11 @@ import numpy as np
 
 from ..sampling_params import SamplingParams
 
-__all__ = ["Sequence", "SequenceStatus", "slots_for_range"]
+__all__ = ["Sequence", "SequenceStatus", "slots_for_range", "PENDING_TOKEN"]
+
+# Stands in ``token_ids`` for a token that the device has sampled (or is about to) but the host has not read
+# yet: the engine core may launch step n + 1 before it reads step n's samples.
+PENDING_TOKEN = -1
 
 _next_seq_id = itertools.count(1)
 
@@ -59,6 +63,10 @@ class Sequence:
     last_token: int = 0
     # Leading block-table entries the workers already hold; the wire carries only the rest.
     bt_synced: int = 0
+    # One-step-late scheduling: trailing entries of token_ids that are still PENDING_TOKEN, and whether the
+    # sequence ends (max_tokens) as soon as the step in flight has been read.
+    num_pending: int = 0
+    finishing: bool = False
     # timing marks filled by the engine core (seconds, time.perf_counter)
     t_arrival: float = 0.0
     t_first_token: float = 0.0
@@ -95,6 +103,11 @@ class Sequence:
     @property
     def num_completion_tokens(self) -> int:
         return len(self.token_ids) - self.num_prompt_tokens
+
+    @property
+    def num_known_completion_tokens(self) -> int:
+        """Completion tokens whose value the host has read."""
+        return len(self.token_ids) - self.num_prompt_tokens - self.num_pending
 
     @property
     def num_blocks(self) -> int:

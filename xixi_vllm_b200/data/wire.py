@@ -115,6 +115,10 @@ class ScheduledBatch:
     decodes: list[Sequence] = field(default_factory=list)
     released: list[int] = field(default_factory=list)
     step_id: int = 0
+    # one-step-late scheduling: per decode / prefill row, (position of its pending token in token_ids or a
+    # negative code, KV length before the step, KV length after it), written by Scheduler.advance
+    marks_d: list = field(default_factory=list)
+    marks_p: list = field(default_factory=list)
 
     def is_empty(self) -> bool:
         return not self.prefills and not self.decodes

@@ -64,6 +64,7 @@ def lib():
     L.xv_silu_mul.argtypes = [_vp, _vp, _i32, _i32, _vp]
     L.xv_embedding.argtypes = [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]
     L.xv_gather_rows.argtypes = [_vp, _vp, _vp, _i32, _i32, _vp]
+    L.xv_resolve_token_refs.argtypes = [_vp, _i32, _vp, _i32, _vp]
     L.xv_qk_norm_rope_cache.argtypes = [_vp, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
                                         _i32, _i32, _i32, _vp]
     L.xv_attn_decode_workspace_bytes.argtypes = [_i32, _i32, _i32, _i32]
@@ -320,6 +321,14 @@ def gather_rows(x, rows):
     _check(lib().xv_gather_rows(x.data_ptr(), rows.data_ptr(), y.data_ptr(), rows.numel(), x.shape[1], _stream()),
            "gather_rows")
     return y
+
+
+def resolve_token_refs(ids, prev) -> None:
+    """In place: every ``ids[i] < 0`` becomes ``prev[-ids[i] - 1]`` (int32 ids, int64 previous samples)."""
+    if ids.dtype != torch.int32 or prev.dtype != torch.int64 or not ids.is_contiguous() or not prev.is_contiguous():
+        raise TypeError("resolve_token_refs needs contiguous int32 ids and int64 samples")
+    _check(lib().xv_resolve_token_refs(ids.data_ptr(), ids.numel(), prev.data_ptr(), prev.numel(), _stream()),
+           "resolve_token_refs")
 
 
 def qk_norm_rope_cache(qkv, q_w, k_w, eps, cos_sin, positions, slots, k_cache, v_cache, num_q_heads,

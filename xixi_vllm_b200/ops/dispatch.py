@@ -12,6 +12,7 @@ from . import cpu_ref
 __all__ = [
     "rmsnorm", "add_rmsnorm", "linear", "linear_silu_mul", "silu_mul", "embedding", "qk_norm_rope_cache",
     "paged_attention", "sample", "argmax", "build_cos_sin_cache", "gather_rows",
+    "resolve_token_refs",
 ]
 
 build_cos_sin_cache = cpu_ref.build_cos_sin_cache
@@ -90,6 +91,16 @@ def sample(logits, temperature, top_k, top_p, min_p, *, rng=None, generator=None
     if logits.is_cuda:
         return _cuda().sample(logits, temperature, top_k, top_p, min_p, rng)
     return cpu_ref.sample(logits, temperature, top_k, top_p, min_p, generator)
+
+
+def resolve_token_refs(ids, prev) -> None:
+    """In place: input ids < 0 name rows of the previous step's sample buffer (``-(row) - 1``)."""
+    if ids.is_cuda:
+        _cuda().resolve_token_refs(ids, prev)
+        return
+    neg = ids < 0
+    if bool(neg.any()):
+        ids[neg] = prev[(-ids[neg] - 1).long()].to(ids.dtype)
 
 
 def gather_rows(x, rows):

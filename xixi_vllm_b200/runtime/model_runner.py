@@ -9,6 +9,7 @@ p2p outside the graphs. Sampled ids leave the device on a side stream into pinne
 from __future__ import annotations
 
 import os
+from collections import deque
 
 import torch
 
@@ -49,14 +50,18 @@ class ModelRunner:
             self._pp_buf = (torch.empty(shape, dtype=kv.dtype, device=self.device),
                             torch.empty(shape, dtype=kv.dtype, device=self.device))
         self._copy_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
-        self._sample_event = torch.cuda.Event() if self.is_cuda else None
-        self._host_samples = torch.zeros(self.max_bs, dtype=torch.int64, pin_memory=self.is_cuda)
-        self._host_status = torch.zeros(1, dtype=torch.int32, pin_memory=self.is_cuda)
+        # Two read-back slots used in turn: with one-step-late scheduling step n + 1 is launched before step n's
+        # samples have been read. ``_unread`` lists the launched steps whose samples are still to be read.
+        self._sample_events = [torch.cuda.Event() for _ in range(2)] if self.is_cuda else [None, None]
+        self._host_samples = [torch.zeros(self.max_bs, dtype=torch.int64, pin_memory=self.is_cuda) for _ in range(2)]
+        self._host_statuses = [torch.zeros(1, dtype=torch.int32, pin_memory=self.is_cuda) for _ in range(2)]
+        self._slot = 0
+        self._unread: deque = deque()
         self._dev_status = None
         if self.is_cuda:
             from ..ops import cuda as _cuda
 
-            self._dev_status = _cuda.device_status(self._host_samples.to(self.device))
+            self._dev_status = _cuda.device_status(self._host_samples[0].to(self.device))
         self._dev_samples: torch.Tensor | None = None
         self._n_samples = 0
         self._last: tuple[int, int, list[bool]] = (0, 0, [])
@@ -188,6 +193,7 @@ class ModelRunner:
                 bucket = self.graphs.pad_bs(n_d)
                 with nvtx_range("stage"):
                     batch = self.stager.build(sched, pad_to=bucket, fixed_blocks=True)
+                    self._resolve_token_refs(batch)
                 greedy = batch.all_greedy if self.is_last_pp else True
                 if not self.is_first_pp:
                     self._recv(bucket)             # outside the graph, into the buffers the graph reads
@@ -199,6 +205,7 @@ class ModelRunner:
             else:
                 with nvtx_range("stage"):
                     batch = self.stager.build(sched)
+                    self._resolve_token_refs(batch)
                 if self.pp_microbatches > 1 and not (self.is_first_pp and self.is_last_pp):
                     tokens = self._forward_microbatched(batch)
                 else:
@@ -226,31 +233,47 @@ class ModelRunner:
         torch.cuda.synchronize(self.device)
         return float(sum(e0.elapsed_time(e1) for sid, (e0, e1) in self._step_events.items() if lo <= sid < hi))
 
+    def _resolve_token_refs(self, batch) -> None:
+        """Decode rows whose input token the host did not know when it scheduled them (their sequence sampled
+        it in the step launched just before) take it from that step's sample buffer, on the device."""
+        if batch.num_token_refs:
+            if self._dev_samples is None:
+                raise RuntimeError("a step refers to the previous step's samples but none were kept")
+            ops.resolve_token_refs(batch.input_ids[: batch.num_token_refs], self._dev_samples)
+
     def _stage_samples(self, tokens: torch.Tensor, n: int) -> None:
-        self._n_samples = n
-        if not self.is_cuda:
-            self._host_samples[:n].copy_(tokens[:n])
-            return
+        slot = self._slot
+        self._slot ^= 1
+        self._unread.append((slot, n, self._last))
+        if len(self._unread) > 2:          # a rank whose samples nobody reads keeps the newest two only
+            self._unread.popleft()
         self._dev_samples = tokens
+        if not self.is_cuda:
+            self._host_samples[slot][:n].copy_(tokens[:n])
+            return
         cur = torch.cuda.current_stream(self.device)
         self._copy_stream.wait_stream(cur)
         with torch.cuda.stream(self._copy_stream):
-            self._host_samples[:n].copy_(tokens[:n], non_blocking=True)
-            self._host_status.copy_(self._dev_status, non_blocking=True)
-            self._sample_event.record(self._copy_stream)
+            self._host_samples[slot][:n].copy_(tokens[:n], non_blocking=True)
+            self._host_statuses[slot].copy_(self._dev_status, non_blocking=True)
+            self._sample_events[slot].record(self._copy_stream)
+        # the next forward may overwrite the buffer `tokens` lives in: it starts after this copy
+        cur.wait_event(self._sample_events[slot])
 
     def read_samples(self, n_p: int, n_d: int) -> tuple[list[int], list[int]]:
-        """Blocks until this step's ids are on the host. Prefill entries that did not sample are -1."""
+        """Blocks until the ids of the oldest launched step that has not been read are on the host. Prefill
+        entries that did not sample are -1."""
+        slot, n, last = self._unread.popleft()
         if self.is_cuda:
-            self._sample_event.synchronize()
-            code = int(self._host_status[0])
+            self._sample_events[slot].synchronize()
+            code = int(self._host_statuses[slot][0])
             if code:
                 self._dev_status.zero_()
                 raise RuntimeError(
                     f"GPU kernel {code >> 16} reported status {code & 0xFFFF} (1-3: pipeline wait ran out, "
                     "4: a tensor-parallel peer did not arrive in time, 5: index out of range)")
-        flat = self._host_samples[: self._n_samples].tolist()
-        _, _, sampled = self._last
+        flat = self._host_samples[slot][:n].tolist()
+        _, _, sampled = last
         d_ids = flat[:n_d]
         p_ids, k = [], n_d
         for s in sampled:

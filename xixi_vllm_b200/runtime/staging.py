@@ -55,6 +55,9 @@ class ForwardBatch:
     n_prefill: int
     n_decode: int
     prefill_sampled: list[bool]
+    # leading rows of input_ids among which some are references into the previous step's samples (ids < 0,
+    # one-step-late scheduling); 0 = none
+    num_token_refs: int = 0
 
 
 def split_forward_batch(batch: ForwardBatch, parts: int) -> list[tuple[ForwardBatch, int, int]]:
@@ -129,8 +132,13 @@ class BatchStager:
         self.row_minp = np.zeros(self.num_rows, dtype=np.float32)
         self.free_rows = list(range(self.num_rows - 1, -1, -1))
         cap = 3 * max_tokens + 8 * (max_seqs + 1) + max_seqs * max_blocks + 64
-        self.host = torch.zeros(cap, dtype=torch.int32, pin_memory=cuda)
-        self.host_np = self.host.numpy()
+        # Two pinned buffers used in turn: with one-step-late scheduling the host packs step n + 1 while the
+        # copy of step n's buffer may still be queued behind the forward before it.
+        self._hosts = [torch.zeros(cap, dtype=torch.int32, pin_memory=cuda) for _ in range(2 if cuda else 1)]
+        self._hosts_np = [h.numpy() for h in self._hosts]
+        self._host_idx = 0
+        self.host = self._hosts[0]
+        self.host_np = self._hosts_np[0]
         self.dev = torch.zeros(cap, dtype=torch.int32, device=self.device) if cuda else self.host
         self.last_h2d_bytes = 0
         self._rows_tmp = np.zeros(max_seqs, dtype=np.int32)
@@ -221,6 +229,10 @@ class BatchStager:
             max_kv = max(max_kv, e.num_cached_tokens + len(e.token_ids))
         nblk = self.max_blocks if fixed_blocks else max(1, -(-max_kv // bsz))
 
+        if len(self._hosts) > 1:
+            self._host_idx ^= 1
+            self.host = self._hosts[self._host_idx]
+            self.host_np = self._hosts_np[self._host_idx]
         h = self.host_np
         o = 0
         ids = h[o:o + T]; o += T
@@ -241,8 +253,11 @@ class BatchStager:
         used = o
 
         # decode rows
+        n_refs = 0
         if n_d:
             ids[:n_d] = decodes.tokens
+            if int(ids[:n_d].min()) < 0:
+                n_refs = n_d
             if self._lib is not None:
                 p = lambda a: a.ctypes.data_as(ctypes.c_void_p)  # noqa: E731
                 self._lib.xv_fill_decode(n_d, p(rows_d), p(cached), p(self.tables), self.max_blocks, bsz,
@@ -345,7 +360,8 @@ class BatchStager:
         return ForwardBatch(input_ids=d_ids, positions=d_pos, slots=d_slots, attn=attn,
                             sample_rows=d_srows[:S], temperature=d_temp[:S], top_k=d_topk[:S],
                             top_p=d_topp[:S], min_p=d_minp[:S], rng=d_rng, num_tokens=T, num_samples=S,
-                            all_greedy=greedy, n_prefill=n_p, n_decode=n_d, prefill_sampled=prefill_sampled)
+                            all_greedy=greedy, n_prefill=n_p, n_decode=n_d, prefill_sampled=prefill_sampled,
+                            num_token_refs=n_refs)
 
     @staticmethod
     def _put_sampling(e, k: int, temp, topk, topp, minp) -> bool:

@@ -61,7 +61,7 @@ class EngineMetrics:
         self.sampled_tokens = sampled_total
         # decode rows that neither start nor finish a request need no per-request bookkeeping
         for seq in sched.prefills:
-            if not seq.t_first_token and seq.num_completion_tokens > 0:
+            if not seq.t_first_token and seq.num_known_completion_tokens > 0:
                 seq.t_first_token = now
         for o in outputs:
             if not o.is_finished:
@@ -72,7 +72,7 @@ class EngineMetrics:
             seq.t_finished = now
             self.requests_finished += 1
             if len(self.finished) < self.keep_request_timings:
-                n = seq.num_completion_tokens
+                n = seq.num_known_completion_tokens
                 first = seq.t_first_token or now
                 self.finished.append(RequestTiming(
                     seq.seq_id, seq.num_prompt_tokens, n, first - seq.t_arrival,

@@ -25,13 +25,14 @@ DEFAULTS: dict[str, Any] = {
     "num_kvcache_blocks": 0, "tp_size": 1, "pp_size": 1, "dp_size": 1, "pp_layer_counts": None,
     "device_ids": None, "nccl_port": 29500, "master_addr": "127.0.0.1", "master_port": 29500,
     "nccl_ifname": "", "load_format": "auto", "device": "cuda", "tp_comm": "auto", "seed": 0, "pp_microbatches": 1,
+    "async_scheduling": "auto",
 }
 
 _ENGINE_KEYS = ("enforce_eager", "torch_compile", "compile_mode", "compile_dynamic", "dtype", "context_len",
                 "max_num_seqs", "max_num_batched_tokens", "mix_prefill_decode", "kvcache_block_size",
                 "prefix_backend", "gpu_memory_utilization", "num_kvcache_blocks", "tp_size", "pp_size",
                 "dp_size", "pp_layer_counts", "device_ids", "nccl_port", "master_addr", "master_port",
-                "nccl_ifname", "load_format", "device", "tp_comm", "seed", "pp_microbatches")
+                "nccl_ifname", "load_format", "device", "tp_comm", "seed", "pp_microbatches", "async_scheduling")
 
 
 def load_config(path: Path, defaults: dict | None = None) -> dict:

@@ -74,13 +74,13 @@ def case_single(engine, args, vocab):
     t_first = None
     while not seq.is_finished:
         engine.step()
-        if t_first is None and seq.num_completion_tokens > 0:
+        if t_first is None and seq.num_known_completion_tokens > 0:
             _sync()
             t_first = time.perf_counter()
     _sync()
     e2e = time.perf_counter() - t0
     ttft = t_first - t0
-    n = seq.num_completion_tokens
+    n = seq.num_known_completion_tokens
     return dict(case="single", ttft_ms=1e3 * ttft, decode_tps=(n - 1) / max(e2e - ttft, 1e-9),
                 tpot_ms=1e3 * (e2e - ttft) / max(n - 1, 1), e2e_s=e2e, output_tokens=n)
 
@@ -96,7 +96,7 @@ def case_batch(engine, args, vocab):
         engine.step()
     _sync()
     wall = time.perf_counter() - t0
-    n = sum(s.num_completion_tokens for s in seqs)
+    n = sum(s.num_known_completion_tokens for s in seqs)
     return dict(case="batch", requests=args.requests, batch_tps=n / wall, wall_s=wall, output_tokens=n)
 
 
@@ -148,7 +148,7 @@ def case_prefix(engine, args, vocab):
         engine.step()
     _sync()
     wall = time.perf_counter() - t0
-    n = sum(s.num_completion_tokens for s in seqs)
+    n = sum(s.num_known_completion_tokens for s in seqs)
     m = engine.metrics.summary() if args.dp == 1 else {}
     return dict(case="prefix", requests=args.requests, num_prefixes=args.num_prefixes, prefix_len=args.prefix_len,
                 throughput_tps=n / wall, wall_s=wall, prefix_hit_rate=m.get("prefix_hit_rate"),

@@ -124,3 +124,47 @@ def test_cta_pair_kernel_splits_last_wave_in_k(m, n, k, parts):
     torch.cuda.synchronize()
     cuda.check_status()
     assert (first.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 6144, 4096), (200, 4096, 4096), (161, 4096, 12288), (256, 24576, 1024),
+                                   (256, 1024, 512), (250, 3080, 4096)])
+def test_decode_batch_runs_on_swapped_cta_pairs(m, n, k):
+    """161..256 rows: weights on the pairs' 256-row M axis, all tokens in one N tile, transposed epilogue
+    (and K parts when the weight tiles do not fill the SM pairs)."""
+    from xixi_vllm_b200.ops import cuda
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    pl = cuda.gemm_plan(m, n, k, sms)
+    assert pl.pair == 1 and pl.swapped == 1 and pl.tiles_b == 1
+    g = torch.Generator().manual_seed(m + n + k)
+    x = (torch.randn(m, k, generator=g) * 0.5).bfloat16().to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.5).bfloat16().to(DEV)
+    ref = x.float() @ w.float().t()
+    y = cuda.linear(x, w)
+    again = cuda.linear(x, w)
+    torch.cuda.synchronize()
+    cuda.check_status()
+    assert torch.equal(y, again)
+    assert (y.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
+    # output rows wider than n (a view into a larger buffer)
+    wide = torch.full((m, n + 64), 7.0, dtype=torch.bfloat16, device=DEV)
+    cuda.linear(x, w, out=wide[:, :n])
+    torch.cuda.synchronize()
+    assert torch.equal(wide[:, :n], y) and bool((wide[:, n:] == 7.0).all())
+
+
+def test_decode_batch_swapped_cta_pairs_fused_silu_mul():
+    from xixi_vllm_b200.ops import cuda
+    m, inter, k = 256, 3072, 4096
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    pl = cuda.gemm_plan(m, 2 * inter, k, sms)
+    assert pl.pair == 1 and pl.swapped == 1
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(m, k, generator=g) * 0.5).bfloat16().to(DEV)
+    gate = (torch.randn(inter, k, generator=g) * 0.05).bfloat16().to(DEV)
+    up = (torch.randn(inter, k, generator=g) * 0.05).bfloat16().to(DEV)
+    y = cuda.linear_silu_mul(x, _interleave(gate, up).contiguous())
+    torch.cuda.synchronize()
+    cuda.check_status()
+    ref = torch.nn.functional.silu(x.float() @ gate.float().t()) * (x.float() @ up.float().t())
+    assert y.shape == (m, inter)
+    assert (y.float() - ref).abs().max().item() <= 3e-2 * ref.abs().max().item() + 1e-2

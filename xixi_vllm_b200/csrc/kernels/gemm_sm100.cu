@@ -810,7 +810,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     if (lane == 0) {
       prefetch_tensormap(&map_a);
       prefetch_tensormap(&map_b);
-      const uint64_t hint = l2_policy_evict_normal();
+      // swapped: the weights (A) stream through once, the few activation rows (B) are re-read by every tile
+      const uint64_t hint_a = p.transposed ? l2_policy_evict_first() : l2_policy_evict_normal();
+      const uint64_t hint_b = p.transposed ? l2_policy_evict_last() : l2_policy_evict_normal();
       uint32_t s = 0, round = 0;
       const uint32_t leader_full0 = map_to_cta(smem_u32(&full_bar[0]), 0);
       if (row_wait.n > 0 && !gemm_wait_rows(row_wait)) report_status(p.status, kGemmKernelId, kPeerFlagTimeout);
@@ -830,8 +832,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           uint8_t* sa = smem + static_cast<size_t>(s) * stage_bytes;
           const uint32_t leader_full = leader_full0 + s * 8;
           mbar_expect_tx_cluster(leader_full, stage_bytes);
-          tma_load_2d_pair(sa, &map_a, leader_full, kb * kBK, ya, hint);
-          tma_load_2d_pair(sa + a_bytes, &map_b, leader_full, kb * kBK, yb, hint);
+          tma_load_2d_pair(sa, &map_a, leader_full, kb * kBK, ya, hint_a);
+          tma_load_2d_pair(sa + a_bytes, &map_b, leader_full, kb * kBK, yb, hint_b);
           if (++s == nstages) {
             s = 0;
             ++round;
@@ -890,6 +892,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const int quarter = warp & 3;
     const int nchunks = (p.bn + 31) >> 5;
     const int row_in_tile = static_cast<int>(rank) * kBM + quarter * 32 + lane;
+    // swapped orientation (weights on the MMA's M axis, tokens on N): per-warp transpose buffer after the barriers
+    uint8_t* stage_w = reinterpret_cast<uint8_t*>(full_bar) + 256 + quarter * 2048;
     uint32_t t = 0;
     bool dead = false;      // a wait ran out: no more data work, but this warp keeps meeting the others at the barriers
     PairWork work(p, sk, pair, num_pairs, total_kb);
@@ -967,7 +971,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v[j].w);
                   }
                 }
-                store_row32(p, push, a_row, b0 + (ch + half) * 32, b_end, 0, r);
+                if (p.transposed)
+                  store_swapped32(p, push, stage_w, lane, a_row - lane, b0 + (ch + half) * 32, b_end, 0, r);
+                else
+                  store_row32(p, push, a_row, b0 + (ch + half) * 32, b_end, 0, r);
               }
             }
           }
@@ -1243,8 +1250,16 @@ int sk_parts_for(int rest, int pairs, int total_kb) {
 
 // CTA-pair plan: 256 x bn tiles dealt whole and round-robin, with the last wave's tiles cut into K parts when
 // `stream_k` is set and that wave is less than half full. bn <= 0 picks the widest tile that splits N evenly.
-void fill_pair(int m, int n, int k, int bn, int num_sms, int stream_k, XvGemmPlan& pl) {
+void fill_pair(int m, int n, int k, int bn, int num_sms, int stream_k, XvGemmPlan& pl, bool swapped = false) {
   const int total_kb = (k + kBK - 1) / kBK;
+  if (swapped) {
+    // weights on the 256-row M axis, the (at most 256) tokens on N: every weight byte is read once and a
+    // pair's K block carries as many FLOPs per operand byte as a 256 x 256 tile of a large GEMM
+    bn = round_up(m, 16);
+    const int t = m;
+    m = n;
+    n = t;
+  }
   if (bn <= 0) {
     const int tiles_b = (n + 255) / 256;
     bn = round_up((n + tiles_b - 1) / tiles_b, 16);
@@ -1252,7 +1267,7 @@ void fill_pair(int m, int n, int k, int bn, int num_sms, int stream_k, XvGemmPla
   if (bn > 256) bn = 256;
   if (bn < 16) bn = 16;
   pl.pair = 1;
-  pl.swapped = 0;
+  pl.swapped = swapped ? 1 : 0;
   pl.bn = bn;
   pl.tiles_a = (m + 255) / 256;
   pl.tiles_b = (n + bn - 1) / bn;
@@ -1262,7 +1277,7 @@ void fill_pair(int m, int n, int k, int bn, int num_sms, int stream_k, XvGemmPla
   int stages = (200 * 1024) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   pl.stages = stages;
-  pl.smem_bytes = stages * stage_bytes + 256 + 1024;
+  pl.smem_bytes = stages * stage_bytes + 256 + (swapped ? kStagingBytes : 0) + 1024;
   pl.ctas_per_sm = 1;
   const int pairs = num_sms / 2;
   const int tiles = pl.tiles_a * pl.tiles_b;
@@ -1304,7 +1319,9 @@ int gemm_plan_impl(int m, int n, int k, int num_sms, XvGemmPlan* plan, unsigned 
     const int total_kb = (k + kBK - 1) / kBK;
     int sp = g_override.splits > 0 ? g_override.splits : 1;
     if (sp > total_kb) sp = total_kb;
-    if (g_override.kind == 2) {
+    if (g_override.kind == 3 && m <= 256) {
+      fill_pair(m, n, k, 0, num_sms, g_override.splits >= 0 ? 1 : 0, pl, true);
+    } else if (g_override.kind == 2 || g_override.kind == 3) {
       // `splits` of the hook: > 0 cuts the last wave's tiles into K parts (stream-K tail), else whole tiles only
       const int bn = g_override.bn > 0 ? round_up(g_override.bn, 16) : 0;
       fill_pair(m, n, k, bn, num_sms, g_override.splits > 0 ? 1 : 0, pl);
@@ -1348,7 +1365,15 @@ int gemm_plan_impl(int m, int n, int k, int num_sms, XvGemmPlan* plan, unsigned 
   static const int pair_min_m = env_int("XV_GEMM_PAIR_MIN_M", 161);
   static const int streamk = env_int("XV_GEMM_STREAMK", 1);
   const int total_kb = (k + kBK - 1) / kBK;
-  if (!(flags & kPlanNoPair) && m >= pair_min_m && n >= 64 && (m > 256 || (n >= 6144 && total_kb <= 80))) {
+  // From pair_swap_min_m to 256 rows (a decode batch) the pairs run swapped: weights on the 256-row M axis, all
+  // tokens in one N tile. Every weight byte then crosses L2 -> SM once and the activation is re-read once per
+  // 256 weight rows, where the unswapped 256 x BN tiling re-read it once per BN weight rows and was bound
+  // by that stream; too few weight tiles for the SM pairs are cut along K (stream-K tail).
+  static const int pair_swap_min_m = env_int("XV_GEMM_PAIR_SWAP_MIN_M", 161);
+  if (!(flags & kPlanNoPair) && m >= pair_swap_min_m && m <= 256 && n >= 1024 && (n % 8) == 0 && total_kb >= 8) {
+    std::memset(&pl, 0, sizeof(pl));
+    fill_pair(m, n, k, 0, num_sms, streamk, pl, true);
+  } else if (!(flags & kPlanNoPair) && m >= pair_min_m && n >= 64 && (m > 256 || (n >= 6144 && total_kb <= 80))) {
     const int pairs = num_sms / 2;
     const int tiles_a = (m + 255) / 256;
     double best = 1e30, widest = 0.0;
@@ -1430,7 +1455,8 @@ void xv_tp_profile_buffer(void* buf) { g_tp_prof = static_cast<unsigned long lon
 void xv_gemm_profile_buffer(void* buf) { g_gemm_prof = static_cast<unsigned long long*>(buf); }
 
 // Test and tuning hook: kind 0 = single CTA, swapped where the planner would; 1 = single CTA, normal
-// orientation; 2 = CTA pairs. bn / splits / stages <= 0 keep that kernel's default. kind < 0 clears.
+// orientation; 2 = CTA pairs; 3 = CTA pairs, swapped for at most 256 rows. bn / splits / stages <= 0 keep that
+// kernel's default. kind < 0 clears.
 void xv_gemm_plan_override(int kind, int bn, int splits, int stages) {
   g_override.active = kind >= 0;
   g_override.kind = kind;
@@ -1476,7 +1502,7 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
     return XV_ERR_ALIGN;
   // Without the reserve the pair kernel deals whole tiles (its pairs then finish unevenly).
   if (pl.pair && pl.sk_tiles > 0 && (!sk_ok || pl.workspace_bytes > kSkReserveBytes))
-    fill_pair(m, n, k, pl.bn, num_sms, 0, pl);
+    fill_pair(m, n, k, pl.bn, num_sms, 0, pl, pl.swapped != 0);
   // Split-K in the swapped orientation: the planes are summed inside the kernel by the CTA that brings a
   // tile's last one (needs a tile counter from the reserve), unless the caller wants the planes themselves.
   const bool fixup = pl.splits > 1 && !pl.cluster && pl.swapped && !pl.pair && push_in != nullptr && sk_ok &&
@@ -1494,7 +1520,13 @@ static int gemm_impl(const void* x, const void* w, void* y, int m, int n, int k,
   CUtensorMap map_a, map_b;
   GemmParams p;
   std::memset(&p, 0, sizeof(p));
-  if (pl.pair) {
+  if (pl.pair && pl.swapped) {
+    if ((rc = get_tensor_map(&map_a, w, n, k, ldw, kBM))) return rc;
+    if ((rc = get_tensor_map(&map_b, x, m, k, ldx, pl.bn / 2))) return rc;
+    p.rows_a = n;
+    p.rows_b = m;
+    p.transposed = 1;
+  } else if (pl.pair) {
     if ((rc = get_tensor_map(&map_a, x, m, k, ldx, kBM))) return rc;
     if ((rc = get_tensor_map(&map_b, w, n, k, ldw, pl.bn / 2))) return rc;
     p.rows_a = m;

@@ -126,9 +126,17 @@ def test_cta_pair_kernel_splits_last_wave_in_k(m, n, k, parts):
     assert (first.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
 
 
+@pytest.fixture
+def swapped_pairs():
+    from xixi_vllm_b200.ops import cuda
+    cuda.gemm_plan_override(3, 0, 0, 0)
+    yield
+    cuda.gemm_plan_override(-1, 0, 0, 0)
+
+
 @pytest.mark.parametrize("m,n,k", [(256, 6144, 4096), (200, 4096, 4096), (161, 4096, 12288), (256, 24576, 1024),
                                    (256, 1024, 512), (250, 3080, 4096)])
-def test_decode_batch_runs_on_swapped_cta_pairs(m, n, k):
+def test_decode_batch_runs_on_swapped_cta_pairs(m, n, k, swapped_pairs):
     """161..256 rows: weights on the pairs' 256-row M axis, all tokens in one N tile, transposed epilogue
     (and K parts when the weight tiles do not fill the SM pairs)."""
     from xixi_vllm_b200.ops import cuda
@@ -145,14 +153,9 @@ def test_decode_batch_runs_on_swapped_cta_pairs(m, n, k):
     cuda.check_status()
     assert torch.equal(y, again)
     assert (y.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
-    # output rows wider than n (a view into a larger buffer)
-    wide = torch.full((m, n + 64), 7.0, dtype=torch.bfloat16, device=DEV)
-    cuda.linear(x, w, out=wide[:, :n])
-    torch.cuda.synchronize()
-    assert torch.equal(wide[:, :n], y) and bool((wide[:, n:] == 7.0).all())
 
 
-def test_decode_batch_swapped_cta_pairs_fused_silu_mul():
+def test_decode_batch_swapped_cta_pairs_fused_silu_mul(swapped_pairs):
     from xixi_vllm_b200.ops import cuda
     m, inter, k = 256, 3072, 4096
     sms = torch.cuda.get_device_properties(0).multi_processor_count

@@ -223,7 +223,8 @@ int xv_qwen3_forward(const XvModelDesc* m, const XvBatchDesc* b, const XvArena* 
         return rc;
       }
       if (pl.splits == 1 || pl.cluster) {
-        XV_TRY(41, xv_gemm_bf16_silu_mul(a->h, w.gate_up, a->act, T, 2 * I, H, H, H, I, a->num_sms, a->status, stream));
+        XV_TRY(41, xv_gemm_bf16_silu_mul(a->h, w.gate_up, a->act, T, 2 * I, H, H, H, I, a->gemm_ws, a->gemm_ws_bytes,
+                                         a->num_sms, a->status, stream));
       } else {
         int sp = 1;
         XV_TRY(42, xv_gemm_bf16_defer(a->h, w.gate_up, nullptr, T, 2 * I, H, H, H, 2 * I, a->gemm_ws, a->gemm_ws_bytes,

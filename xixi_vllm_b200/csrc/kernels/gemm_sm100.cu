@@ -682,10 +682,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 //
 // Tiles are dealt whole and round-robin. When the last wave would leave more than half of the SM pairs idle,
 // its tiles are cut into two or three K parts, one part per pair ("stream-K tail"): the pairs holding a
-// tile's first parts add their fp32 accumulators (red.add.f32) into the slot of the pair that holds the last
-// part and raise its counter; that pair adds the slot to its own accumulator, runs the normal epilogue and
-// clears slot and counter for the next launch. A slot starts at zero and receives at most two contributions,
-// so the sum does not depend on their order. The parts run first, the whole tiles after them.
+// tile's first parts store their fp32 accumulators into their own slots of the workspace and raise the
+// counter of the pair that holds the last part; that pair adds the slots to its own accumulator in part
+// order (the sum does not depend on timing), runs the normal epilogue and clears its counter for the next
+// launch. The parts run first, the whole tiles after them.
 constexpr int kPairAccStride = 256;
 constexpr long long kSkReserveBytes = 20ll << 20;   // tail of the workspace kept zero for partial tiles + counters
 constexpr long long kSkCounterBytes = 4096;         // the very end of it: two counters per SM pair, then one per tile
@@ -698,7 +698,7 @@ struct StreamK {
   int dp_tiles;            // tiles [0, dp_tiles) are dealt whole, round-robin over the pairs
   int sk_tiles;            // the tiles after them, one part per pair
   int slot_floats;         // floats per slot: 256 rows x BN rounded up to whole 32-column chunks
-  float* slots;            // [pairs][slot_floats], indexed by the pair that finishes the tile; zero between launches
+  float* slots;            // [pairs][slot_floats], indexed by the pair that wrote it (a tile's earlier K parts)
   uint32_t* counters;      // [pairs][2] (finishing pair, CTA rank); zero between launches
 };
 
@@ -751,10 +751,6 @@ struct PairWork {
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tile_a, int& tile_b) {
   tile_b = tile / p.tiles_a;            // consecutive tiles walk the A (row) tiles and share the B tile
   tile_a = tile - tile_b * p.tiles_a;
-}
-__device__ __forceinline__ void red_add_f32x4(float* p, float a, float b, float c, float d) {
-  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d)
-               : "memory");
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
@@ -920,11 +916,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const uint32_t lane_addr = tmem_base + buf * kPairAccStride + (static_cast<uint32_t>(quarter * 32) << 16);
         const int b0 = tile_b * p.bn;
         const int b_end = min(p.rows_b, b0 + p.bn);
-        // The pair that holds the tile's last K block finishes the tile; its slot collects the others' sums.
+        // The pair that holds the tile's last K part finishes the tile: the pairs with the earlier parts store
+        // their fp32 accumulators into their own slots (plain 16-byte stores: an order of magnitude faster
+        // than red.add through the L2 atomic units), the finisher adds them in part order.
         // Slot layout: [32-column chunk][4-float group j][256 rows][4 floats]: the 32 rows of a warp are
         // consecutive 16-byte pieces, so every vector access of a warp is 512 contiguous bytes.
-        const int fin_pair = sg.sk_tile * sk.parts + sk.parts - 1;
-        float* slot = sk.slots + static_cast<size_t>(fin_pair) * sk.slot_floats;
+        const int first_pair = sg.sk_tile * sk.parts;
+        const int fin_pair = first_pair + sk.parts - 1;
+        float* slot = sk.slots + static_cast<size_t>(contributes ? pair : first_pair) * sk.slot_floats;
         if (finishes) {
           const uint32_t want = static_cast<uint32_t>(sk.parts - 1);
           const uint32_t* ctr = sk.counters + 2 * pair + rank;
@@ -955,20 +954,23 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
               if (contributes) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
-                  red_add_f32x4(sl + j * 1024, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                  *reinterpret_cast<float4*>(sl + j * 1024) =
+                      make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                  __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
               } else {
                 if (finishes) {
-                  float4 v[8];
+                  for (int part = 0; part + 1 < sk.parts; ++part) {
+                    const float* sp = sl + static_cast<size_t>(part) * sk.slot_floats;
+                    float4 v[8];
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) v[j] = ld_cg_f4(reinterpret_cast<const float4*>(sl + j * 1024));
+                    for (int j = 0; j < 8; ++j) v[j] = ld_cg_f4(reinterpret_cast<const float4*>(sp + j * 1024));
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) {
-                    *reinterpret_cast<float4*>(sl + j * 1024) = make_float4(0.f, 0.f, 0.f, 0.f);   // for the next launch
-                    r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v[j].x);
-                    r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v[j].y);
-                    r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v[j].z);
-                    r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v[j].w);
+                    for (int j = 0; j < 8; ++j) {
+                      r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v[j].x);
+                      r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v[j].y);
+                      r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v[j].z);
+                      r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v[j].w);
+                    }
                   }
                 }
                 if (p.transposed)
@@ -1370,7 +1372,9 @@ int gemm_plan_impl(int m, int n, int k, int num_sms, XvGemmPlan* plan, unsigned 
   // 256 weight rows, where the unswapped 256 x BN tiling re-read it once per BN weight rows and was bound
   // by that stream; too few weight tiles for the SM pairs are cut along K (stream-K tail).
   static const int pair_swap_min_m = env_int("XV_GEMM_PAIR_SWAP_MIN_M", 161);
-  if (!(flags & kPlanNoPair) && m >= pair_swap_min_m && m <= 256 && n >= 1024 && (n % 8) == 0 && total_kb >= 8) {
+  static const int pair_swap_min_n = env_int("XV_GEMM_PAIR_SWAP_MIN_N", 6144);
+  if (!(flags & kPlanNoPair) && m >= pair_swap_min_m && m <= 256 && n >= pair_swap_min_n && (n % 8) == 0 &&
+      total_kb >= 8) {
     std::memset(&pl, 0, sizeof(pl));
     fill_pair(m, n, k, 0, num_sms, streamk, pl, true);
   } else if (!(flags & kPlanNoPair) && m >= pair_min_m && n >= 64 && (m > 256 || (n >= 6144 && total_kb <= 80))) {
@@ -1729,8 +1733,10 @@ int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long
 // Y[m, n/2] = silu(gate) * up, with W's rows interleaved in groups of 16 = [8 gate | 8 up].
 // Only for plans that do not split K (XV_ERR_UNSUPPORTED otherwise; see xv_gemm_plan).
 int xv_gemm_bf16_silu_mul(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
-                          long long ldy, int num_sms, int* status, cudaStream_t stream) {
-  return gemm_impl(x, w, y, m, n, k, ldx, ldw, ldy, nullptr, 0, num_sms, status, stream, false, nullptr, 1);
+                          long long ldy, void* workspace, long long workspace_bytes, int num_sms, int* status,
+                          cudaStream_t stream) {
+  return gemm_impl(x, w, y, m, n, k, ldx, ldw, ldy, workspace, workspace_bytes, num_sms, status, stream, false,
+                   nullptr, 1);
 }
 
 // Same, but when the plan splits K the fp32 partial planes [splits][m][n] are left in

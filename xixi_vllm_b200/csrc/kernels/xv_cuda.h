@@ -59,9 +59,11 @@ int xv_gemm_bf16_defer(const void* x, const void* w, void* y, int m, int n, int 
                        cudaStream_t stream, int* splits_out);
 
 // GEMM with a fused SiLU-mul epilogue: W's rows are interleaved in groups of 16 = [8 gate | 8 up],
-// Y is [m, n/2]. Only for plans that do not split K.
+// Y is [m, n/2]. Only for plans that do not split K into planes. `workspace` (may be null) is the same buffer
+// the other GEMM entry points get: the CTA-pair kernel cuts a thin last wave along K through its tail.
 int xv_gemm_bf16_silu_mul(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,
-                          long long ldy, int num_sms, int* status, cudaStream_t stream);
+                          long long ldy, void* workspace, long long workspace_bytes, int num_sms, int* status,
+                          cudaStream_t stream);
 // SiLU-mul over activations in that interleaved layout: bf16 x [rows, 2*inter], or `splits` fp32
 // partial planes of a split-K GEMM when `partials` is non-null.
 int xv_silu_mul_interleaved(const void* x, const float* partials, int splits, long long split_stride, void* y,

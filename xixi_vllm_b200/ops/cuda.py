@@ -57,7 +57,7 @@ def lib():
     L.xv_add_rmsnorm_partials.argtypes = [_vp, _i32, _i64, _vp, _vp, _vp, _i32, _i32, _f32, _vp]
     L.xv_qk_norm_rope_cache_partials.argtypes = [_vp, _i32, _i64, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _vp,
                                                  _i32, _i32, _i32, _i32, _i32, _i32, _vp]
-    L.xv_gemm_bf16_silu_mul.argtypes = [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _vp, _vp]
+    L.xv_gemm_bf16_silu_mul.argtypes = [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _vp, _i64, _i32, _vp, _vp]
     L.xv_silu_mul_interleaved.argtypes = [_vp, _vp, _i32, _i64, _vp, _i32, _i32, _vp]
     L.xv_rmsnorm.argtypes = [_vp, _vp, _vp, _i32, _i32, _f32, _vp]
     L.xv_add_rmsnorm.argtypes = [_vp, _vp, _vp, _vp, _i32, _i32, _f32, _vp]
@@ -254,7 +254,8 @@ def linear_silu_mul(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     pl = gemm_plan(M, N, K, st.num_sms)
     if pl.splits == 1 or pl.cluster:
         _check(lib().xv_gemm_bf16_silu_mul(x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K, x.stride(0),
-                                           w.stride(0), inter, st.num_sms, st.status.data_ptr(), _stream()),
+                                           w.stride(0), inter, st.gemm_ws.data_ptr(), st.gemm_ws.numel(),
+                                           st.num_sms, st.status.data_ptr(), _stream()),
                f"gemm+silu {M}x{N}x{K}")
         return y
     part = linear(x, w, defer=True)
@@ -534,7 +535,8 @@ def gemm_tp_fused(x, w, peer_bufs, peer_flags, mc_ptr: int, epoch, rank: int, wo
 
 
 def gemm_plan_override(kind: int = -1, bn: int = 0, splits: int = 0, stages: int = 0) -> None:
-    """Tuning hook: force kernel kind (0 single CTA, 1 single CTA normal orientation, 2 CTA pairs), tile width,
+    """Tuning hook: force kernel kind (0 single CTA, 1 single CTA normal orientation, 2 CTA pairs, 3 CTA pairs in
+    the swapped orientation for at most 256 rows), tile width,
     split-K and stages for every following GEMM; ``kind < 0`` restores the planner."""
     lib().xv_gemm_plan_override(kind, bn, splits, stages)
 

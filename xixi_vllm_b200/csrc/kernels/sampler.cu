@@ -412,7 +412,7 @@ sample_kernel(const __nv_bfloat16* __restrict__ logits, long long* __restrict__ 
 
 // Vocabulary-parallel form: logits is this rank's [rows, local_vocab] shard holding tokens
 // vocab_start .. vocab_start + valid_vocab. The grid is capped at what can be resident and walks the rows.
-__global__ void __launch_bounds__(kSampThreads)
+__global__ void __launch_bounds__(kSampThreads, 2)
 tp_sample_kernel(const TpComm c, long long region_offset, long long parity_bytes,
                  const __nv_bfloat16* __restrict__ logits, long long ld, int valid_vocab, int vocab_start,
                  int total_vocab, long long* __restrict__ out, int rows, const float* __restrict__ temperature,

@@ -177,11 +177,26 @@ tp_argmax_kernel(const TpComm c, long long slots_offset, const __nv_bfloat16* __
   __shared__ int si[32];
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(c.epoch);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool vec_ok = (ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const __nv_bfloat16* lr = logits + static_cast<size_t>(row) * ld;
     float bv = -CUDART_INF_F;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < valid_vocab && i < local_vocab; i += blockDim.x) {
+    const int n = valid_vocab < local_vocab ? valid_vocab : local_vocab;
+    // eight logits per 16-byte load where the rows allow it (a thread meets its ids in ascending order, so
+    // "greater than" keeps the lowest id among equals)
+    const int nvec = vec_ok ? n / 8 : 0;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(lr + v * 8);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        if (f.x > bv) { bv = f.x; bi = v * 8 + 2 * j; }
+        if (f.y > bv) { bv = f.y; bi = v * 8 + 2 * j + 1; }
+      }
+    }
+    for (int i = nvec * 8 + threadIdx.x; i < n; i += blockDim.x) {
       const float x = __bfloat162float(lr[i]);
       if (x > bv || (x == bv && i < bi)) { bv = x; bi = i; }
     }

@@ -163,8 +163,9 @@ def emit(record: dict) -> None:
 
 
 def baseline_number(model: str = "Qwen3-8B", n_gpus: int = 1, mode: str = "steady"):
-    """The reference publishes no numbers; BASELINE.md's figures are its own engine measured on this pool
-    (``baseline/measured_reference.json``, keyed by model, GPU count and mode). None when that case was not measured."""
+    """The reference publishes no numbers; the comparison figures are its own engine measured on B200s through
+    ``--impl reference`` (``baseline/measured_reference.json``, keyed by model, GPU count and mode). None when that
+    case was not measured."""
     path = os.path.join(ROOT, "baseline", "measured_reference.json")
     try:
         with open(path) as f:

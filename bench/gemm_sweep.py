@@ -1,6 +1,6 @@
 """Sweep of the tcgen05 GEMM's kernel / tile / split-K choices on the serving shapes, next to cuBLAS.
 
-    python -m bench.gemm_sweep [--json gpurun_out/gemm_sweep.jsonl] [--set decode,tp8,mixed,prefill]
+    python -m bench.gemm_sweep [--json out/gemm_sweep.jsonl] [--set decode,tp8,mixed,prefill]
 
 For every shape it times the planner's own choice and a grid of forced plans (``xv_gemm_plan_override``:
 single-CTA swapped kernel with 1-8 K splits, CTA-pair kernel with tile widths 64-256 and several deals of K

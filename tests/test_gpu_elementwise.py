@@ -160,3 +160,12 @@ def test_split_k_partials_feed_consumers_directly(planes_split_k):
     _close(qa, qb, atol=3e-2, rtol=3e-2)
     _close(caches[0], caches[2], atol=3e-2, rtol=3e-2)
     _close(caches[1], caches[3], atol=3e-2, rtol=3e-2)
+
+
+def test_resolve_token_refs_kernel():
+    from xixi_vllm_b200.ops import cuda
+    prev = torch.tensor([900, 901, 902, 903], dtype=torch.int64, device="cuda")
+    ids = torch.tensor([5, -1, -4, 7, -2, -9], dtype=torch.int32, device="cuda")
+    cuda.resolve_token_refs(ids, prev)
+    torch.cuda.synchronize()
+    assert ids.tolist() == [5, 900, 903, 7, 901, 0]          # a reference beyond the buffer becomes token 0

@@ -19,8 +19,10 @@ def _model_dir(tmp_path, **over):
 
 def _generate(model_dir, device, prompts, max_tokens, **kw):
     from xixi_vllm_b200 import Engine, EngineConfig, SamplingParams
-    cfg = EngineConfig(model=model_dir, device=device, dtype="bfloat16", num_kvcache_blocks=256,
-                       max_num_seqs=16, max_num_batched_tokens=256, context_len=512, **kw)
+    base = dict(device=device, dtype="bfloat16", num_kvcache_blocks=256, max_num_seqs=16, max_num_batched_tokens=256,
+                context_len=512)
+    base.update(kw)
+    cfg = EngineConfig(model=model_dir, **base)
     eng = Engine(cfg)
     try:
         seqs = [eng.add_request(p, SamplingParams(max_tokens=max_tokens, ignore_eos=True)) for p in prompts]
@@ -96,3 +98,19 @@ def test_sampled_generation_on_gpu_is_seeded(tmp_path):
     a, b, c = run(1, True), run(1, True), run(2, True)
     assert a == b and a != c
     assert len(run(1, False)) == 16          # sampled variant of the decode graphs
+
+
+@pytest.mark.parametrize("eager", [True, False])
+def test_one_step_late_scheduling_gives_the_same_tokens_on_gpu(tmp_path, eager):
+    """Step n + 1 launched before step n's samples are read (ids patched on the device from the previous step's
+    sample buffer, also in front of a graph replay): same kernels, same inputs, so the tokens are identical."""
+    d = _model_dir(tmp_path)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (7, 33, 64, 120, 2, 90, 15)]
+    kw = dict(enforce_eager=eager, max_num_batched_tokens=96)          # the long prompts are chunked
+    late = _generate(d, "cuda", prompts, 24, async_scheduling="on", **kw)
+    sync = _generate(d, "cuda", prompts, 24, async_scheduling="off", **kw)
+    assert late == sync
+    # under KV pressure (preemption with a token in flight)
+    tight = _generate(d, "cuda", prompts, 24, async_scheduling="on", num_kvcache_blocks=20, prefix_backend="none", **kw)
+    assert _agreement(sync, tight) >= 0.9, (sync, tight)

@@ -160,3 +160,24 @@ def test_split_forward_batch_pieces_cover_the_batch_in_order():
         seen_partial |= not all(full.prefill_sampled)
         sch.update(b, [7] * len(b.prefills), [7] * len(b.decodes))
     assert seen_partial
+
+
+def test_token_references_into_the_previous_steps_samples():
+    """One-step-late scheduling: a decode row whose input token the host did not know yet carries -(row) - 1,
+    the index of its sample in the previous step; the stager flags such batches and the ids are patched from
+    that step's sample buffer before the forward."""
+    from xixi_vllm_b200.ops import dispatch as ops
+    st = BatchStager(max_seqs=8, max_tokens=64, max_blocks=4, block_size=16, device="cpu")
+    pre = [SeqSchedule(seq_id=i, num_cached_tokens=0, token_ids=[10 + i, 20 + i], bt_from=0, bt_tail=[i],
+                       need_sample=True) for i in (1, 2, 3)]
+    b = st.build(SchedulerOutput(prefills=pre))
+    assert b.num_token_refs == 0
+    prev = torch.tensor([501, 502, 503], dtype=torch.int64)           # samples of that step, in row order
+    # next step: sequences 3 and 1 refer to rows 2 and 0, sequence 2's token is already known
+    dec = DecodeBatch.of([(3, -3, 2, 1, []), (2, 77, 2, 1, []), (1, -1, 2, 1, [])])
+    b = st.build(SchedulerOutput(decodes=dec))
+    assert b.num_token_refs == 3 and b.input_ids.tolist() == [-3, 77, -1]
+    ops.resolve_token_refs(b.input_ids[: b.num_token_refs], prev)
+    assert b.input_ids.tolist() == [503, 77, 501]
+    b = st.build(SchedulerOutput(decodes=DecodeBatch.of([(3, 5, 3, 1, []), (2, 6, 3, 1, [])])))
+    assert b.num_token_refs == 0

@@ -415,13 +415,16 @@ def test_engine_tp2_one_kernel_projection_matches(tmp_path, monkeypatch):
 
 
 @pytest.mark.timeout(600)
-def test_engine_tp2_row_sharded_reduction_matches(tmp_path, monkeypatch):
-    """The two-shot reduction (default from 4 ranks up) forced on at 2 ranks."""
+@pytest.mark.parametrize("defer", ["1", "0"])
+def test_engine_tp2_row_sharded_reduction_matches(tmp_path, monkeypatch, defer):
+    """The two-shot reduction (default from 4 ranks up) forced on at 2 ranks; with ``defer`` the kernel leaves the
+    wait for the other ranks' rows to the GEMM that reads the activation."""
     _need(2)
     d = _tiny_dir(tmp_path)
     ref = _probe(d)
     monkeypatch.setenv("XV_TP_SHARDED", "1")
-    out = _probe(d, tp=2, comm="fused", cg=True, port=29861)
+    monkeypatch.setenv("XV_TP_DEFER_ROW_WAIT", defer)
+    out = _probe(d, tp=2, comm="fused", cg=True, port=29861 if defer == "1" else 29866)
     assert _agree(ref, out) >= 10, (ref, out)
 
 

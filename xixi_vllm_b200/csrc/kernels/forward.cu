@@ -39,6 +39,12 @@ inline void await_rows_in_next_gemm(Ctx& c) {
   if (!c.rows_pending) return;
   c.rows_pending = false;
   const XvModelDesc* m = c.m;
+  if (!c.push) {
+    // the row-sharded reduction kernel left its "every rank's rows are here" wait to this GEMM
+    xv_gemm_wait_for_epoch(static_cast<const uint32_t*>(m->peer_flags[m->tp_rank]) + xv_tp_pull_done_word(),
+                           static_cast<const uint32_t*>(m->epoch) + xv_tp_pull_target_word(), m->tp_world, m->spin_us);
+    return;
+  }
   xv_gemm_wait_for_rows(static_cast<const uint32_t*>(m->peer_flags[m->tp_rank]) + xv_tp_bcast_word(),
                         static_cast<const uint32_t*>(m->epoch) + xv_tp_bcast_base_word(), m->tp_world, m->spin_us);
 }
@@ -82,6 +88,14 @@ int row_linear_reduce_norm(Ctx& c, const void* x, const void* w, int k, const vo
     XV_TRY(10, xv_gemm_bf16(x, w, symm_local(c, which), T, H, k, k, k, H, c.a->gemm_ws, c.a->gemm_ws_bytes,
                             c.a->num_sms, c.a->status, c.s));
     if (c.two_shot) {
+      // the consumer of h is a GEMM on every call but the forward's last: it waits for the other ranks' rows
+      if (!final_call && m->tp_defer_row_wait != 0) {
+        XV_TRY(15, xv_tp_reduce_norm_sharded_nowait(m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch, m->tp_rank,
+                                                    m->tp_world, slot_off, m->h_offset, 1, c.a->residual, norm_w, T,
+                                                    H, m->eps, m->spin_us, c.a->status, c.s));
+        c.rows_pending = true;
+        return 0;
+      }
       XV_TRY(15, xv_tp_reduce_norm_sharded(m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch, m->tp_rank, m->tp_world,
                                            slot_off, m->h_offset, 1, c.a->residual, norm_w, T, H, m->eps, m->spin_us,
                                            c.a->status, c.s));

@@ -1125,7 +1125,7 @@ static uint32_t pow2_cols(int n) {
 using namespace xv;
 
 static bool g_disable_pair = false;
-static thread_local GemmRowWait g_pending_wait = {nullptr, nullptr, 0, 0};
+static thread_local GemmRowWait g_pending_wait = {nullptr, nullptr, 0, 0, 1};
 static unsigned long long* g_tp_prof = nullptr;
 static unsigned long long* g_gemm_prof = nullptr;
 
@@ -1448,6 +1448,15 @@ void xv_gemm_wait_for_rows(const void* flags, const void* targets, int n, unsign
   g_pending_wait.targets = static_cast<const uint32_t*>(targets);
   g_pending_wait.n = n;
   g_pending_wait.spin_us = spin_us;
+  g_pending_wait.target_stride = 1;
+}
+// Same for epoch-valued flags: the `n` flags at `flags` must all reach the one value at `target`.
+void xv_gemm_wait_for_epoch(const void* flags, const void* target, int n, unsigned spin_us) {
+  g_pending_wait.flags = static_cast<const uint32_t*>(flags);
+  g_pending_wait.targets = static_cast<const uint32_t*>(target);
+  g_pending_wait.n = n;
+  g_pending_wait.spin_us = spin_us;
+  g_pending_wait.target_stride = 0;
 }
 int xv_tp_bcast_word(void) { return kPushBcastWord; }
 int xv_tp_bcast_base_word(void) { return kPushBcastBase; }

@@ -272,6 +272,8 @@ constexpr int kPushArriveWord = 32;   // flag words [32, 40): tiles arrived from
 constexpr int kPushBcastWord = 64;    // flag words [64, 72): rows arrived from owner rank o
 constexpr int kPushTicketWord = 6;    // TpComm::epoch word: CTAs of the running call that have finished
 constexpr int kPushArriveBase = 8;    // TpComm::epoch words [8, 16): arrive counters at the end of the last call
+constexpr int kPullDoneChannel = 2;   // flag words [16, 24): the row-sharded reduction's "my rows are broadcast" epoch flags
+constexpr int kPullTargetWord = 26;   // TpComm::epoch word: epoch of the last row-sharded reduction that left its wait to the consumer
 constexpr int kPushBcastBase = 16;    // TpComm::epoch words [16, 24): broadcast counters at the end of the last call
 constexpr int kTpPushKernelId = 4;
 
@@ -301,10 +303,11 @@ struct TpPush {
 // arrival counters in this rank's flag array and the values they must reach (the projection's last CTA
 // wrote those into the communicator's history words before it ended).
 struct GemmRowWait {
-  const uint32_t* flags;     // this rank's flag array + kPushBcastWord
-  const uint32_t* targets;   // TpComm::epoch + kPushBcastBase
+  const uint32_t* flags;     // this rank's flag array: one word per source rank
+  const uint32_t* targets;   // values the flags must reach (local device memory)
   int n;                     // ranks (0: nothing to wait for)
   unsigned spin_us;
+  int target_stride;         // 1: one target per rank (monotonic counters); 0: all ranks reach the same value (an epoch)
 };
 
 
@@ -332,7 +335,7 @@ __device__ __forceinline__ bool tp_wait_counter(const uint32_t* f, uint32_t targ
 __device__ __forceinline__ bool gemm_wait_rows(const GemmRowWait& w) {
   bool ok = true;
   for (int r = 0; r < w.n; ++r) {
-    const uint32_t target = *reinterpret_cast<const volatile uint32_t*>(w.targets + r);
+    const uint32_t target = *reinterpret_cast<const volatile uint32_t*>(w.targets + r * w.target_stride);
     ok = tp_wait_counter(w.flags + r, target, w.spin_us) && ok;
   }
   if (w.n > 0) asm volatile("fence.proxy.async;" ::: "memory");

@@ -69,7 +69,7 @@ tp_reduce_norm_kernel(const TpComm c, long long buf_offset, const __nv_bfloat16*
 __global__ void __launch_bounds__(kTpThreads, 4)
 tp_reduce_norm_sharded_kernel(const TpComm c, long long buf_offset, long long h_offset, int has_residual,
                               __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ w, int rows,
-                              int hidden, float eps) {
+                              int hidden, float eps, int defer_wait) {
   grid_dep_launch();
   grid_dep_wait();
   __shared__ float scratch[32];
@@ -131,7 +131,9 @@ tp_reduce_norm_sharded_kernel(const TpComm c, long long buf_offset, long long h_
       }
     }
   }
-  // second barrier: my rows are on every rank / every rank's rows are here
+  // second barrier: my rows are on every rank / every rank's rows are here. With defer_wait the second half is
+  // left to the kernel that reads the activation (a GEMM waits for the peers' flags in its TMA producer, see
+  // gemm_wait_rows): this kernel ends as soon as its own rows are out.
   __shared__ int last;
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -141,11 +143,12 @@ tp_reduce_norm_sharded_kernel(const TpComm c, long long buf_offset, long long h_
   __syncthreads();
   if (last && threadIdx.x < c.world) {
     c.epoch[2] = 0;
+    if (defer_wait && threadIdx.x == 0) c.epoch[kPullTargetWord] = epoch;
     __threadfence_system();
-    st_release_sys(c.peer_flags[threadIdx.x] + 2 * kMaxRanks + c.rank, epoch);
+    st_release_sys(c.peer_flags[threadIdx.x] + kPullDoneChannel * kMaxRanks + c.rank, epoch);
   }
-  if (threadIdx.x < c.world) {
-    const uint32_t* f = c.peer_flags[c.rank] + 2 * kMaxRanks + threadIdx.x;
+  if (!defer_wait && threadIdx.x < c.world) {
+    const uint32_t* f = c.peer_flags[c.rank] + kPullDoneChannel * kMaxRanks + threadIdx.x;
     const unsigned long long t0 = global_timer_ns();
     const unsigned long long limit = static_cast<unsigned long long>(c.spin_limit) * 1000ull;
     for (;;) {
@@ -397,10 +400,10 @@ int xv_tp_reduce_norm(const void* const* peer_bufs, void* const* peer_flags, con
 // Row-sharded reduction point: partial at `buf_offset`, normalised activations broadcast to
 // `h_offset` (both byte offsets inside the symmetric buffer). `residual` holds this rank's rows
 // of the residual stream (rows rank, rank + world, ...); has_residual == 0 starts the stream.
-int xv_tp_reduce_norm_sharded(const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf, void* epoch,
-                              int rank, int world, long long buf_offset, long long h_offset, int has_residual,
-                              void* residual, const void* w, int rows, int hidden, float eps, unsigned spin_limit,
-                              int* status, cudaStream_t stream) {
+static int reduce_norm_sharded_impl(const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf,
+                                    void* epoch, int rank, int world, long long buf_offset, long long h_offset,
+                                    int has_residual, void* residual, const void* w, int rows, int hidden, float eps,
+                                    unsigned spin_limit, int* status, cudaStream_t stream, int defer_wait) {
   if (rows <= 0) return 0;
   if (hidden % 8 || hidden > kTpThreads * kTpMaxVec * 8 || (buf_offset & 15) || (h_offset & 15)) return XV_ERR_SHAPE;
   TpComm c;
@@ -413,9 +416,29 @@ int xv_tp_reduce_norm_sharded(const void* const* peer_bufs, void* const* peer_fl
   if (grid < 1) grid = 1;
   launch_pdl(tp_reduce_norm_sharded_kernel, dim3(grid), dim3(kTpThreads), 0, stream, 
       c, buf_offset, h_offset, has_residual, static_cast<__nv_bfloat16*>(residual),
-      static_cast<const __nv_bfloat16*>(w), rows, hidden, eps);
+      static_cast<const __nv_bfloat16*>(w), rows, hidden, eps, defer_wait);
   return cudaGetLastError() == cudaSuccess ? 0 : XV_ERR_LAUNCH;
 }
+
+int xv_tp_reduce_norm_sharded(const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf, void* epoch,
+                              int rank, int world, long long buf_offset, long long h_offset, int has_residual,
+                              void* residual, const void* w, int rows, int hidden, float eps, unsigned spin_limit,
+                              int* status, cudaStream_t stream) {
+  return reduce_norm_sharded_impl(peer_bufs, peer_flags, mc_buf, epoch, rank, world, buf_offset, h_offset,
+                                  has_residual, residual, w, rows, hidden, eps, spin_limit, status, stream, 0);
+}
+
+// Same, but the kernel ends once its own rows are broadcast: the caller must make the next kernel that reads the
+// activation wait for the other ranks' rows (xv_gemm_wait_for_epoch before the GEMM that consumes it).
+int xv_tp_reduce_norm_sharded_nowait(const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf,
+                                     void* epoch, int rank, int world, long long buf_offset, long long h_offset,
+                                     int has_residual, void* residual, const void* w, int rows, int hidden,
+                                     float eps, unsigned spin_limit, int* status, cudaStream_t stream) {
+  return reduce_norm_sharded_impl(peer_bufs, peer_flags, mc_buf, epoch, rank, world, buf_offset, h_offset,
+                                  has_residual, residual, w, rows, hidden, eps, spin_limit, status, stream, 1);
+}
+int xv_tp_pull_done_word(void) { return kPullDoneChannel * kMaxRanks; }
+int xv_tp_pull_target_word(void) { return kPullTargetWord; }
 
 int xv_tp_argmax(const void* const* peer_bufs, void* const* peer_flags, void* epoch, int rank, int world,
                  long long slots_offset, const void* logits, long long ld, int local_vocab, int valid_vocab,

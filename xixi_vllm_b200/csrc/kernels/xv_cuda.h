@@ -163,6 +163,10 @@ int xv_tp_reduce_norm_sharded(const void* const* peer_bufs, void* const* peer_fl
                               int rank, int world, long long buf_offset, long long h_offset, int has_residual,
                               void* residual, const void* w, int rows, int hidden, float eps, unsigned spin_limit,
                               int* status, cudaStream_t stream);
+int xv_tp_reduce_norm_sharded_nowait(const void* const* peer_bufs, void* const* peer_flags, const void* mc_buf,
+                                     void* epoch, int rank, int world, long long buf_offset, long long h_offset,
+                                     int has_residual, void* residual, const void* w, int rows, int hidden,
+                                     float eps, unsigned spin_limit, int* status, cudaStream_t stream);
 int xv_tp_argmax(const void* const* peer_bufs, void* const* peer_flags, void* epoch, int rank, int world,
                  long long slots_offset, const void* logits, long long ld, int local_vocab, int valid_vocab,
                  int vocab_start, long long* out, int rows, unsigned spin_limit, int* status, cudaStream_t stream);
@@ -200,6 +204,12 @@ int xv_gemm_bf16_tp(const void* x, const void* w, int m, int n, int k, long long
 // xv_gemm_wait_for_rows right before launching that GEMM from the same thread. flags: this rank's flag array
 // at word xv_tp_bcast_word(); targets: the `epoch` words from xv_tp_bcast_base_word() on; n: ranks.
 void xv_gemm_wait_for_rows(const void* flags, const void* targets, int n, unsigned spin_us);
+// The same hand-over for the row-sharded reduction kernel (xv_tp_reduce_norm_sharded_nowait): flags = this rank's
+// flag array at word xv_tp_pull_done_word(), target = the `epoch` word xv_tp_pull_target_word(); all n flags must
+// reach that one value.
+void xv_gemm_wait_for_epoch(const void* flags, const void* target, int n, unsigned spin_us);
+int xv_tp_pull_done_word(void);
+int xv_tp_pull_target_word(void);
 int xv_tp_bcast_word(void);
 int xv_tp_bcast_base_word(void);
 

@@ -181,3 +181,30 @@ def test_token_references_into_the_previous_steps_samples():
     assert b.input_ids.tolist() == [503, 77, 501]
     b = st.build(SchedulerOutput(decodes=DecodeBatch.of([(3, 5, 3, 1, []), (2, 6, 3, 1, [])])))
     assert b.num_token_refs == 0
+
+
+def test_bench_matrix_records_failures_and_time_limits(monkeypatch):
+    """The case runner keeps going: a case that exits non-zero, prints no result line or runs out of time is
+    recorded with ok=false (and its process group is ended), a good case carries bench.py's JSON line."""
+    from bench import matrix
+
+    scripts = {
+        "good": 'import json; print("noise"); print(json.dumps({"value": 12.5, "unit": "tokens/s"}))',
+        "crash": 'import sys; print("boom"); sys.exit(3)',
+        "silent": 'print("no json here")',
+        "hang": 'import time; print("started", flush=True); time.sleep(60)',
+    }
+    monkeypatch.setattr(matrix, "command", lambda case, port: [sys.executable, "-c", scripts[case["tag"]]])
+    good = matrix.run_case(dict(tag="good", gpus=1, impl="ours", limit=30, flags={}), 0)
+    assert good["ok"] and good["value"] == 12.5 and good["case"] == "good"
+    crash = matrix.run_case(dict(tag="crash", gpus=1, impl="ours", limit=30, flags={}), 0)
+    assert not crash["ok"] and crash["error"].startswith("exit 3") and "boom" in crash["error"]
+    silent = matrix.run_case(dict(tag="silent", gpus=1, impl="ours", limit=30, flags={}), 0)
+    assert not silent["ok"]
+    hang = matrix.run_case(dict(tag="hang", gpus=1, impl="ours", limit=1, flags={}), 0)
+    assert not hang["ok"] and hang["error"].startswith("time limit") and hang["seconds"] < 30
+    # the command line of a multi-GPU case goes through torch.distributed.run on 127.0.0.1
+    monkeypatch.undo()
+    cmd = matrix.command(dict(tag="t", gpus=4, impl="reference", limit=1, flags={"decode_batch": 32, "mode": "decode"}), 29950)
+    assert "--nproc-per-node" in cmd and "127.0.0.1" in cmd and cmd[-4:] == ["--decode-batch", "32", "--mode", "decode"]
+    assert any(c["gpus"] == 8 for c in matrix.suites(8)["32b"]) and "32b" not in matrix.suites(2)

@@ -423,7 +423,7 @@ def test_engine_tp2_row_sharded_reduction_matches(tmp_path, monkeypatch, defer):
     d = _tiny_dir(tmp_path)
     ref = _probe(d)
     monkeypatch.setenv("XV_TP_SHARDED", "1")
-    monkeypatch.setenv("XV_TP_DEFER_ROW_WAIT", defer)
+    monkeypatch.setenv("XV_TP_PULL_DEFER", defer)
     out = _probe(d, tp=2, comm="fused", cg=True, port=29861 if defer == "1" else 29866)
     assert _agree(ref, out) >= 10, (ref, out)
 

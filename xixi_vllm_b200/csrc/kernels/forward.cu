@@ -77,7 +77,7 @@ int row_linear_reduce_norm(Ctx& c, const void* x, const void* w, int k, const vo
     const long long slot_off = static_cast<long long>(which) * m->buf_bytes;
     if (c.push) {
       // the consumer of h is a GEMM on every call but the forward's last (LM head via a row gather)
-      const bool defer = c.two_shot && !final_call && m->tp_defer_row_wait != 0;
+      const bool defer = c.two_shot && !final_call && (m->tp_defer_row_wait & 1) != 0;
       XV_TRY(16, xv_gemm_bf16_tp(x, w, T, H, k, k, k, c.a->gemm_ws, c.a->gemm_ws_bytes, c.a->num_sms, m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch,
                                  m->tp_rank, m->tp_world, slot_off, m->buf_bytes, c.two_shot ? 1 : 0, m->h_offset,
                                  c.a->residual, c.a->residual, norm_w, c.a->h, m->eps, 0, defer ? 1 : 0, m->spin_us,
@@ -89,7 +89,7 @@ int row_linear_reduce_norm(Ctx& c, const void* x, const void* w, int k, const vo
                             c.a->num_sms, c.a->status, c.s));
     if (c.two_shot) {
       // the consumer of h is a GEMM on every call but the forward's last: it waits for the other ranks' rows
-      if (!final_call && m->tp_defer_row_wait != 0) {
+      if (!final_call && (m->tp_defer_row_wait & 2) != 0) {
         XV_TRY(15, xv_tp_reduce_norm_sharded_nowait(m->peer_bufs, m->peer_flags, m->mc_buf, m->epoch, m->tp_rank,
                                                     m->tp_world, slot_off, m->h_offset, 1, c.a->residual, norm_w, T,
                                                     H, m->eps, m->spin_us, c.a->status, c.s));

@@ -261,7 +261,9 @@ typedef struct XvModelDesc {
   int tp_push_max;                    // ... for forwards of at most this many tokens
   int tp_one_shot_max;                // of those, forwards of at most this many tokens reduce every row on every rank
   int tp_pull_two_shot;               // two-kernel form (GEMM, then a reduction kernel that pulls): 1 = row-sharded
-  int tp_defer_row_wait;              // one-kernel two-shot form: the GEMM that reads h waits for the broadcast rows
+  int tp_defer_row_wait;              // the GEMM that reads h waits for the other ranks' rows instead of the kernel that
+                                      // caused them: bit 0 after the one-kernel two-shot projection, bit 1 after the
+                                      // row-sharded reduction kernel
   int is_first, is_last;              // pipeline stage: the first owns the embedding, the last the LM head; on
                                       // other stages `final_norm` is the next stage's first input norm and the
                                       // arena's h / residual are received from / sent to the neighbours

@@ -120,6 +120,9 @@ class FusedTPComm(TPComm):
         # all-gather -> GEMM: after a two-shot one-kernel projection the GEMM that reads the activation waits for
         # the rows the other ranks broadcast (in its TMA producer), instead of the projection kernel itself
         self.defer_row_wait = os.environ.get("XV_TP_DEFER_ROW_WAIT", "1") != "0"
+        # the same hand-over after the row-sharded reduction kernel (the kernel ends once its own rows are
+        # broadcast). Token-equal on 2 GPUs, no time gained there and not timed on more ranks: opt-in.
+        self.pull_defer_row_wait = os.environ.get("XV_TP_PULL_DEFER", "0") == "1"
         self.one_shot_max_tokens = int(os.environ.get("XV_TP_ONE_SHOT_MAX_T", "64"))
         self._idx = 0
         self._logits_view = None

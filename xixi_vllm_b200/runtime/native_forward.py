@@ -126,7 +126,7 @@ class NativeForward:
             d.tp_push = 1 if comm.fuse_gemm else 0
             d.tp_push_max = comm.push_max_tokens
             d.tp_one_shot_max = comm.one_shot_max_tokens
-            d.tp_defer_row_wait = 1 if comm.defer_row_wait else 0
+            d.tp_defer_row_wait = (1 if comm.defer_row_wait else 0) | (2 if comm.pull_defer_row_wait else 0)
             from ..parallel.symm import SPIN_LIMIT
 
             d.spin_us = SPIN_LIMIT

@@ -40,12 +40,14 @@ int xv_gemm_plan(int m, int n, int k, int num_sms, XvGemmPlan* plan);
 // The plan of xv_gemm_bf16_noalloc: K splits are always fp32 planes in a workspace (never summed inside a cluster).
 int xv_gemm_plan_planes(int m, int n, int k, int num_sms, XvGemmPlan* plan);
 void xv_gemm_disable_pair(int disable);   // test hook: force the single-CTA kernel
-// Test and tuning hook: fixed kernel (0 single CTA, 1 single CTA normal orientation, 2 CTA pairs), tile width,
-// split-K and stage count instead of the planner's choice; values <= 0 keep the default, kind < 0 clears.
+// Test and tuning hook: fixed kernel (0 single CTA, 1 single CTA normal orientation, 2 CTA pairs, 3 CTA pairs
+// in the swapped orientation for at most 256 rows), tile width, split-K and stage count instead of the planner's
+// choice; values <= 0 keep the default, kind < 0 clears.
 void xv_gemm_plan_override(int kind, int bn, int splits, int stages);
 // `workspace`: fp32 partial planes of a split-K plan (plan.workspace_bytes). A workspace of 40 MiB or more also
-// serves the CTA-pair kernel's stream-K: its last 20 MiB then hold partial tiles and counters, must be zero
-// before the first call that uses the buffer, and are left zero by every call; planes use the part in front.
+// serves the CTA-pair kernel's K-part tail: its last 20 MiB then hold partial tiles and, in the final 4 KiB,
+// counters; those must be zero before the first call that uses the buffer and are left zero by every call
+// (the tiles need no initial value); planes use the part in front.
 // With a smaller workspace the pair kernel deals whole tiles. Calls that overlap on the GPU must not share a
 // workspace.
 int xv_gemm_bf16(const void* x, const void* w, void* y, int m, int n, int k, long long ldx, long long ldw,

@@ -388,7 +388,14 @@ def run_ours(args) -> None:
     # one-step-late scheduling: the timed calls read the steps launched one call earlier
     lag = 1 if getattr(core, "_inflight", None) is not None else 0
     dev_ms = core.executor.device_time_ms(first_step - lag, sched._step + 1 - lag)
-    e2e_wall = sum(step_ms) / 1e3            # Engine.step() wall time only (excludes the L2 flush)
+    if lag:
+        # One-step-late scheduling: a call launches step n + 1 and returns step n, and the GPU keeps working between
+        # two calls, so only the whole loop is a fair clock: from the synchronised start to the synchronisation
+        # after the last call it holds exactly `steps` forwards and `steps` steps' tokens (plus the L2 flushes
+        # and the host's refill of the queue, which run while the GPU is busy).
+        e2e_wall = wall
+    else:
+        e2e_wall = sum(step_ms) / 1e3        # Engine.step() wall time only (excludes the L2 flush)
     cuda.check_status(device)
 
     rec = {
@@ -412,7 +419,9 @@ def run_ours(args) -> None:
         "clocks": clk,
         "e2e": {"value": out_tokens / e2e_wall, "unit": "tokens/s", "h2d_bytes_per_step": h2d / args.steps,
                 "d2h_bytes_per_step": d2h / args.steps, "ms_per_step": 1e3 * e2e_wall / args.steps,
-                "wall_s_incl_flush": wall},
+                "wall_s_incl_flush": wall,
+                "timed": ("whole timed loop incl. L2 flushes, synchronised at both ends (step n + 1 is launched "
+                          "before step n is read)") if lag else "sum of Engine.step() wall times"},
         "gpu_launches": launches,
         "output_tokens": out_tokens,
         "engine": core.metrics.summary(),

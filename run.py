@@ -124,6 +124,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--load-format", choices=("auto", "dummy"), default=None)
     p.add_argument("--device", choices=("cuda", "cpu"), default=None)
     p.add_argument("--tp-comm", choices=("auto", "fused", "nccl"), default=None)
+    p.add_argument("--async-scheduling", choices=("auto", "on", "off"), default=None,
+                   help="launch step n+1 before step n's samples are read (auto: on for CUDA without pipeline stages)")
     p.add_argument("--batch", action="store_true", help="run the four-prompt batch demo")
     p.add_argument("--download", action="store_true")
     p.add_argument("--list", action="store_true")
@@ -134,7 +136,7 @@ def config_from_args(args) -> dict:
     path = Path(args.config) if args.config else HERE / "config.yaml"
     cfg = load_config(path, DEFAULTS)
     merge_cli(cfg, args, ("model", "prompt", "max_new_tokens", "temperature", "top_p", "top_k", "prefix_backend",
-                          "max_num_seqs", "load_format", "device", "tp_comm"))
+                          "max_num_seqs", "load_format", "device", "tp_comm", "async_scheduling"))
     for flag, key in (("tp", "tp_size"), ("pp", "pp_size"), ("dp", "dp_size")):
         if getattr(args, flag) is not None:
             cfg[key] = getattr(args, flag)

@@ -54,11 +54,13 @@ def main(argv=None) -> None:
     p.add_argument("--load-format", choices=("auto", "dummy"), default=None)
     p.add_argument("--device", choices=("cuda", "cpu"), default=None)
     p.add_argument("--tp-comm", choices=("auto", "fused", "nccl"), default=None)
+    p.add_argument("--async-scheduling", choices=("auto", "on", "off"), default=None,
+                   help="launch step n+1 before step n's samples are read (auto: on for CUDA without pipeline stages)")
     args = p.parse_args(argv)
 
     cfg = load_config(Path(args.config) if args.config else HERE / "config.yaml", DEFAULTS)
     merge_cli(cfg, args, ("model", "prompt", "max_new_tokens", "temperature", "top_p", "top_k", "load_format",
-                          "device", "tp_comm"))
+                          "device", "tp_comm", "async_scheduling"))
     rank, _, world = env_rank_info()
     cfg["tp_size"] = args.tp if args.tp is not None else cfg["tp_size"]
     cfg["pp_size"] = args.pp if args.pp is not None else cfg["pp_size"]

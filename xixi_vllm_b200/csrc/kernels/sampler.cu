@@ -30,6 +30,8 @@
 #include <math_constants.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "tp_device.cuh"
@@ -494,17 +496,24 @@ int xv_tp_sample(const void* const* peer_bufs, void* const* peer_flags, void* ep
   c.world = world;
   c.spin_limit = spin_us;
   c.status = status;
+  // CTAs that can be resident at once on this device (occupancy x SM count), looked up once per device
   static int resident[16] = {0};
+  static std::mutex resident_mu;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return XV_ERR_LAUNCH;
-  if (resident[dev] == 0) {
-    int per_sm = 0, sms = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tp_sample_kernel, kSampThreads, 0) != cudaSuccess ||
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || per_sm < 1 || sms < 1)
-      return XV_ERR_LAUNCH;
-    resident[dev] = per_sm * sms;
+  int cap = 0;
+  {
+    std::lock_guard<std::mutex> g(resident_mu);
+    if (resident[dev] == 0) {
+      int per_sm = 0, sms = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tp_sample_kernel, kSampThreads, 0) != cudaSuccess ||
+          cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || per_sm < 1 || sms < 1)
+        return XV_ERR_LAUNCH;
+      resident[dev] = per_sm * sms;
+    }
+    cap = resident[dev];
   }
-  const int grid = rows < resident[dev] ? rows : resident[dev];
+  const int grid = rows < cap ? rows : cap;
   const long long parity_bytes = static_cast<long long>(max_rows) * world * kSampSlotBytes;
   launch_pdl(tp_sample_kernel, dim3(grid), dim3(kSampThreads), 0, stream, c, region_offset, parity_bytes,
              static_cast<const __nv_bfloat16*>(logits), ld, valid_vocab, vocab_start, total_vocab, out, rows,

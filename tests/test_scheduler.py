@@ -208,3 +208,37 @@ def test_core_metrics_count_tokens(tmp_path):
     m = core.metrics.summary()
     assert total == 20 + 2 and m["sampled_tokens"] == 3 and m["requests_finished"] == 1
     assert "xv_steps" in core.metrics.to_prometheus()
+
+
+def test_one_step_late_core_drains_counts_and_guards(tmp_path):
+    """The core in one-step-late mode: outputs arrive one call later, the last launched step is read before
+    has_unfinished() turns false or the KV pool is rebuilt, token counts are those of the steps that were read, and
+    the idle guard still fires when nothing is in flight and nothing can be scheduled."""
+    core = _core(tmp_path, num_blocks=64, max_num_seqs=4, max_num_batched_tokens=256, async_scheduling="on")
+    assert core.one_step_late
+    core.add_request(req(20, max_tokens=3, ignore_eos=True))
+    outs, n = core.step()                       # launches the prefill; nothing to read yet
+    assert outs == [] and n == 0 and core.has_unfinished() and core._inflight is not None
+    outs, n = core.step()                       # launches decode 1, reads the prefill
+    assert n == 20 and [o.new_token_ids for o in outs] == [[7]]
+    total, finished = n, 0
+    while core.has_unfinished():
+        outs, n = core.step()
+        total += n
+        finished += sum(o.is_finished for o in outs)
+    m = core.metrics.summary()
+    assert total == 20 + 2 and finished == 1 and m["sampled_tokens"] == 3 and m["requests_finished"] == 1
+    assert core._inflight is None
+    # reset_kv while a step is in flight: the step is read first
+    core.add_request(req(10, max_tokens=5, ignore_eos=True))
+    core.step()
+    assert core._inflight is not None
+    core.reset_kv()
+    assert core._inflight is None
+    # idle guard
+    small = _core(tmp_path / "b", num_blocks=2, max_num_seqs=4, max_num_batched_tokens=256, async_scheduling="on")
+    small._MAX_IDLE_STEPS = 5
+    small.add_request(req(100, max_tokens=4))
+    with pytest.raises(RuntimeError, match="KV pool exhaustion"):
+        for _ in range(10):
+            small.step()

@@ -53,8 +53,9 @@ class EngineCore:
         self.last_num_cached_tokens = 0
 
     def reset_kv(self, prefix_backend: str | None = None) -> None:
-        while self._inflight is not None:       # read the step in flight before its pages go away
-            self.step()
+        if self._inflight is not None:          # read the step in flight before its pages go away
+            prev, self._inflight = self._inflight, None
+            self._read_and_resolve(prev)
         self.kv = self.executor.reset_kv(prefix_backend)
         sampled = self.scheduler.num_sampled
         self.scheduler = self._build_scheduler()
@@ -143,6 +144,10 @@ class EngineCore:
         self._inflight = launched
         if prev is None:
             return [], 0
+        return self._read_and_resolve(prev)
+
+    def _read_and_resolve(self, prev) -> tuple[list[EngineCoreOutput], int]:
+        """Reads the samples of a launched step and applies them."""
         p_sched, n_p, n_d, prefill_tokens, schedule_s, t_launch = prev
         p_ids, d_ids = self.executor.read_samples(n_p, n_d)
         t2 = time.perf_counter()
